@@ -1,0 +1,140 @@
+/*
+ * kuiper_b200 - C ABI of the sm_100a decode kernels.
+ *
+ * Every entry point is what the reference's per-device kernel getter would bind for
+ * DeviceCUDA: the reference's pattern is one function pointer per op returned by
+ * kernel::get_<op>_kernel(base::DeviceType) (kuiper/source/op/kernel/kernel_interface.h:10-11,
+ * kernel_interface.cpp:6-14) and the CUDA function behind it
+ * (kuiper/source/op/kernel/cuda/add_kernel.cu:14-52).  The hot-path ops other than add
+ * have only empty placeholder headers in the reference (kuiper/include/op/matmul.h:1-11,
+ * mha.h:1-11, rmsnorm.h:1-10, rope.h:1-10, swiglu.h:1-10, embedding.h:1-10); the entry
+ * points below are what their getters bind.
+ *
+ * Conventions
+ *  - plain device pointers and sizes; no allocation, no synchronisation, no host
+ *    read-back inside any call: all work is enqueued on `stream` (NULL = default
+ *    stream, as add_kernel.cu:31-48) and is CUDA-graph capturable;
+ *  - return value: 0 success, 7 invalid argument, 5 internal (launch) error - the
+ *    numbering of base::StatusCode (kuiper/include/base/base.h:76-84);
+ *  - activations are fp32, row-major [M, width]; fp16 / bf16 tensors travel as
+ *    uint16_t bit patterns; M is the number of token rows in the pass;
+ *  - INT4-AWQ weight of a K-in x N-out linear layer: qweight int32 [K, N/8], nibble i
+ *    (bits 4i..4i+3) of word (k, j) = logical column 8j + {0,2,4,6,1,3,5,7}[i];
+ *    qzeros int32 [K/group, N/8] packed the same way; scales fp16 [K/group, N];
+ *    w[k,n] = (q[k,n] - z[k/group,n]) * s[k/group,n].
+ */
+#ifndef KUIPER_B200_H
+#define KUIPER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* kuiper_stream_t; /* == cudaStream_t */
+
+enum {
+    KUIPER_OK = 0,
+    KUIPER_INTERNAL_ERROR = 5,
+    KUIPER_INVALID_ARGUMENT = 7,
+};
+
+/* how the INT4 matmul rounds its activation operand */
+enum {
+    KUIPER_ACT_FP16 = 1, /* x rounded to fp16, exact products, fp32 accumulation */
+    KUIPER_ACT_FP32 = 0, /* x kept in fp32 */
+};
+
+const char* kuiper_version(void);
+/* text of the last error raised on the calling thread ("" if none) */
+const char* kuiper_last_error(void);
+/* benchmark sweeps only: override a launch heuristic ("gemv_rows", "gemv_math", "flash_splits"; 0 or -1 restores it) */
+int kuiper_set_tuning(const char* key, int value);
+
+/* ---- residual add: replaces add_kernel_cu (kernel/cuda/add_kernel.cu:14-52) ---- */
+int kuiper_add_f32(const float* a, const float* b, float* out, int64_t n, kuiper_stream_t stream);
+
+/* ---- INT4-AWQ: placeholder kuiper/include/op/matmul.h:1-11, quant fields op/layer.h:151-155 ---- */
+/* nibble unpack to uint8 [K, N] (logical column order) */
+int kuiper_awq_unpack_u8(const int32_t* qweight, uint8_t* out, int K, int N, kuiper_stream_t stream);
+/* fp32 dequantisation W[K,N] = (q - z) * s, exact */
+int kuiper_awq_dequant_f32(const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
+                           float* W, int K, int N, int group, kuiper_stream_t stream);
+/* bf16 dequantisation (round to nearest even) used by the M>=16 tensor-core path */
+int kuiper_awq_dequant_bf16(const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
+                            uint16_t* W, int K, int N, int group, kuiper_stream_t stream);
+
+/*
+ * Scratch for the split-K GEMV: partial sums plus per-tile arrival counters.  The
+ * counters must be zero before the first use (kuiper_workspace_init) and are left
+ * zero by every call.  Two calls that overlap on the GPU must not share a workspace.
+ */
+size_t kuiper_awq_gemv_workspace_bytes(int M, int K, int N);
+int kuiper_workspace_init(void* workspace, size_t bytes, kuiper_stream_t stream);
+
+/*
+ * y[M,N] = x[M,K] . dequant(qweight) (+ residual[M,N] if residual != NULL; y may alias
+ * residual).  group must be 128, K % 128 == 0, N % 8 == 0.  M <= 8 runs the SIMT
+ * dequant-fused GEMV; larger M is processed in row blocks.
+ * act_mode: KUIPER_ACT_FP16 or KUIPER_ACT_FP32.
+ */
+int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
+                        const uint16_t* scales, float* y, const float* residual,
+                        int M, int K, int N, int group, int act_mode,
+                        void* workspace, size_t workspace_bytes, kuiper_stream_t stream);
+
+/* ---- BF16 GEMV (lm_head): W bf16 [N, K], y[M,N] = x[M,K] . W^T ---- */
+int kuiper_bf16_gemv_f32(const float* x, const uint16_t* W, float* y, int M, int K, int N,
+                         kuiper_stream_t stream);
+
+/* ---- RMSNorm: placeholder kuiper/include/op/rmsnorm.h:1-10 ---- */
+/* y = (x * rstd) * w, rstd = 1/sqrt(mean(x^2) + eps); w bf16 [H]; y may alias x */
+int kuiper_rmsnorm_f32(const float* x, const uint16_t* w, float* y, int M, int H, float eps,
+                       kuiper_stream_t stream);
+
+/* ---- per-head q/k RMSNorm + rotary + KV-cache write: placeholder kuiper/include/op/rope.h:1-10 ---- */
+/*
+ * qkv [M, (Nq+2Nkv)*D] fp32 (q heads | k heads | v heads); cos/sin fp32 [max_pos, D/2]
+ * (half-split pairing (i, i+D/2)); pos[M], slot[M] int32 on the device.
+ * q_out [M, Nq, D] fp32; k, v rounded to bf16 into cache[(slot*Nkv + h)*max_seq + pos][D];
+ * the caches hold n_slots sequences; pos and slot are clamped into range on the device.
+ * D must be 128.
+ */
+int kuiper_qknorm_rope_kvwrite(const float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
+                               const float* cos_t, const float* sin_t, const int32_t* pos,
+                               const int32_t* slot, int M, int Nq, int Nkv, int D, float eps,
+                               int max_seq, int n_slots, float* q_out, uint16_t* kcache,
+                               uint16_t* vcache, kuiper_stream_t stream);
+
+/* ---- GQA flash-decoding: placeholder kuiper/include/op/mha.h:1-11 ---- */
+/*
+ * out[m,h,:] = softmax(q[m,h,:].K^T / sqrt(D)) . V over cache positions [0, seq_len[m]) of
+ * sequence slot[m]; q head h reads kv head h / (Nq/Nkv).  The KV range is split across
+ * CTAs and the partial (max, sum, out) triples are merged with a log-sum-exp combine.
+ * workspace: kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq) bytes, counters zeroed once
+ * with kuiper_workspace_init.  D must be 128, Nq/Nkv in {1,2,4,8}.
+ */
+size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq);
+int kuiper_flash_decode(const float* q, const uint16_t* kcache, const uint16_t* vcache,
+                        const int32_t* seq_len, const int32_t* slot, float* out,
+                        int M, int Nq, int Nkv, int D, int max_seq, int n_slots,
+                        void* workspace, size_t workspace_bytes, kuiper_stream_t stream);
+
+/* ---- SwiGLU: placeholder kuiper/include/op/swiglu.h:1-10 ---- */
+/* out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]; gate_up is [M, 2I] */
+int kuiper_swiglu_f32(const float* gate_up, float* out, int M, int I, kuiper_stream_t stream);
+
+/* ---- embedding gather: placeholder kuiper/include/op/embedding.h:1-10 ---- */
+int kuiper_embedding_bf16(const int32_t* tokens, const uint16_t* table, float* out, int M, int H,
+                          int vocab, kuiper_stream_t stream);
+
+/* ---- greedy sampler (the reference's sampler directory is absent, CMakeLists.txt:87) ---- */
+/* out[m] = lowest index of the maximum of logits[m, 0..V) */
+int kuiper_argmax_f32(const float* logits, int32_t* out, int M, int V, kuiper_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KUIPER_B200_H */

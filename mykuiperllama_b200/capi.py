@@ -1,0 +1,146 @@
+"""Torch-tensor front end of the kernel C ABI (``include/kuiper_b200.h``).
+
+PyTorch only supplies device memory and streams here; every function hands raw device
+pointers to the C ABI, which enqueues the hand-written sm_100a kernel on the current
+torch stream.  Shapes and dtypes follow the header: activations fp32, bf16 / fp16
+tensors as ``torch.bfloat16`` / ``torch.float16`` (or int16 bit patterns), packed INT4
+as int32.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import check, kernels
+
+ACT_FP32, ACT_FP16 = 0, 1
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(*ts):
+    for t in ts:
+        if t is not None:
+            assert t.is_cuda and t.is_contiguous(), "kuiper kernels take contiguous CUDA tensors"
+
+
+def set_tuning(key: str, value: int) -> None:
+    check(kernels().kuiper_set_tuning(key.encode(), value))
+
+
+def add(a, b, out=None):
+    _dev(a, b, out)
+    out = torch.empty_like(a) if out is None else out
+    check(kernels().kuiper_add_f32(_ptr(a), _ptr(b), _ptr(out), a.numel(), _stream()))
+    return out
+
+
+def awq_unpack(qweight):
+    _dev(qweight)
+    K, NW = qweight.shape
+    out = torch.empty((K, NW * 8), dtype=torch.uint8, device=qweight.device)
+    check(kernels().kuiper_awq_unpack_u8(_ptr(qweight), _ptr(out), K, NW * 8, _stream()))
+    return out
+
+
+def awq_dequant(qweight, qzeros, scales, group=128, dtype=torch.float32):
+    _dev(qweight, qzeros, scales)
+    K, NW = qweight.shape
+    out = torch.empty((K, NW * 8), dtype=dtype, device=qweight.device)
+    fn = kernels().kuiper_awq_dequant_f32 if dtype == torch.float32 else kernels().kuiper_awq_dequant_bf16
+    check(fn(_ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(out), K, NW * 8, group, _stream()))
+    return out
+
+
+def awq_gemv_workspace(M, K, N, device="cuda"):
+    n = kernels().kuiper_awq_gemv_workspace_bytes(M, K, N)
+    ws = torch.zeros(max(n, 16), dtype=torch.uint8, device=device)  # zeroed: counters start at 0
+    return ws
+
+
+def awq_gemv(x, qweight, qzeros, scales, workspace=None, residual=None, out=None, group=128, act_mode=ACT_FP16):
+    _dev(x, qweight, qzeros, scales, workspace, residual, out)
+    M, K = x.shape
+    N = qweight.shape[1] * 8
+    if workspace is None:
+        workspace = awq_gemv_workspace(M, K, N, x.device)
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device) if out is None else out
+    check(kernels().kuiper_awq_gemv_f32(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(out), _ptr(residual),
+                                        M, K, N, group, act_mode, _ptr(workspace), workspace.numel(), _stream()))
+    return out
+
+
+def bf16_gemv(x, W, out=None):
+    _dev(x, W, out)
+    M, K = x.shape
+    N = W.shape[0]
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device) if out is None else out
+    check(kernels().kuiper_bf16_gemv_f32(_ptr(x), _ptr(W), _ptr(out), M, K, N, _stream()))
+    return out
+
+
+def rmsnorm(x, w, eps=1e-6, out=None):
+    _dev(x, w, out)
+    M, H = x.shape
+    out = torch.empty_like(x) if out is None else out
+    check(kernels().kuiper_rmsnorm_f32(_ptr(x), _ptr(w), _ptr(out), M, H, eps, _stream()))
+    return out
+
+
+def qknorm_rope_kvwrite(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, Nq, Nkv, D, eps, kcache, vcache):
+    """kcache / vcache: [n_slots, Nkv, max_seq, D] bf16, updated in place; returns q [M, Nq, D]."""
+    _dev(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, kcache, vcache)
+    M = qkv.shape[0]
+    n_slots, _, max_seq, _ = kcache.shape
+    q = torch.empty((M, Nq, D), dtype=torch.float32, device=qkv.device)
+    check(kernels().kuiper_qknorm_rope_kvwrite(_ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_t), _ptr(sin_t),
+                                               _ptr(pos), _ptr(slot), M, Nq, Nkv, D, eps, max_seq, n_slots,
+                                               _ptr(q), _ptr(kcache), _ptr(vcache), _stream()))
+    return q
+
+
+def flash_decode_workspace(M, Nq, D, max_seq, device="cuda"):
+    n = kernels().kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq)
+    return torch.zeros(max(n, 16), dtype=torch.uint8, device=device)
+
+
+def flash_decode(q, kcache, vcache, seq_len, slot, workspace=None, out=None):
+    _dev(q, kcache, vcache, seq_len, slot, workspace, out)
+    M, Nq, D = q.shape
+    n_slots, Nkv, max_seq, _ = kcache.shape
+    if workspace is None:
+        workspace = flash_decode_workspace(M, Nq, D, max_seq, q.device)
+    out = torch.empty_like(q) if out is None else out
+    check(kernels().kuiper_flash_decode(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(seq_len), _ptr(slot), _ptr(out),
+                                        M, Nq, Nkv, D, max_seq, n_slots, _ptr(workspace), workspace.numel(), _stream()))
+    return out
+
+
+def swiglu(gate_up, out=None):
+    _dev(gate_up, out)
+    M, I2 = gate_up.shape
+    out = torch.empty((M, I2 // 2), dtype=torch.float32, device=gate_up.device) if out is None else out
+    check(kernels().kuiper_swiglu_f32(_ptr(gate_up), _ptr(out), M, I2 // 2, _stream()))
+    return out
+
+
+def embedding(tokens, table, out=None):
+    _dev(tokens, table, out)
+    V, H = table.shape
+    M = tokens.numel()
+    out = torch.empty((M, H), dtype=torch.float32, device=table.device) if out is None else out
+    check(kernels().kuiper_embedding_bf16(_ptr(tokens), _ptr(table), _ptr(out), M, H, V, _stream()))
+    return out
+
+
+def argmax(logits, out=None):
+    _dev(logits, out)
+    M, V = logits.shape
+    out = torch.empty(M, dtype=torch.int32, device=logits.device) if out is None else out
+    check(kernels().kuiper_argmax_f32(_ptr(logits), _ptr(out), M, V, _stream()))
+    return out

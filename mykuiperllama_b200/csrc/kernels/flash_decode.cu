@@ -1,0 +1,331 @@
+// GQA flash-decoding for sm_100a: split-KV attention over a bf16 KV cache with a
+// log-sum-exp combine.  Fills the reference's empty attention placeholder
+// (kuiper/include/op/mha.h:1-11); the reference's buffer list has a ScoreStorage entry
+// (kuiper/include/base/base.h:19), i.e. it intended to materialise the score row - here
+// scores never leave registers.
+//
+// Layout: cache[(slot*Nkv + kv_head)*max_seq + pos][128] bf16, so one KV head of one
+// sequence is a contiguous run of 256-byte rows.
+//
+// grid = (splits, Nkv, M).  A CTA (4 warps) takes one contiguous slice of the KV range of
+// one (token row, kv head) and serves all R = Nq/Nkv query heads that share it, so K and V
+// are read once.  16 lanes cover one 256-byte row (16 bytes per lane); a warp step loads
+// 16 rows (8 per half warp) of K and of V before the first use.  Each warp keeps running
+// (max, sum, out) per head; warps merge through shared memory, CTAs through the workspace,
+// where the last CTA to arrive at a (row, kv head) does the final combine in slice order.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace kuiper {
+namespace {
+
+constexpr int kD = 128;
+constexpr int kWarps = 4;
+constexpr int kRowsPerStep = 8;  // row slots per half warp per step
+
+int g_force_splits = 0;
+
+struct FlashParams {
+    const float* q;       // [M, Nq, 128]
+    const uint16_t* kc;
+    const uint16_t* vc;
+    const int32_t* seq_len;
+    const int32_t* slot;
+    float* out;           // [M, Nq, 128]
+    float* part_o;        // [M, Nkv, S, R, 128]
+    float* part_ml;       // [M, Nkv, S, R, 2]
+    int* counters;        // [M * Nkv]
+    int M, Nq, Nkv, max_seq, n_slots, S;
+};
+
+template <int R>
+__global__ void __launch_bounds__(kWarps * 32)
+flash_decode_kernel(const FlashParams p) {
+    __shared__ float s_o[kWarps][R][kD];
+    __shared__ float s_ml[kWarps][R][2];
+    __shared__ int s_last;
+
+    const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int half = lane >> 4, li = lane & 15;  // half warp and lane within it
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    int L = p.seq_len[m];
+    L = L < 0 ? 0 : (L > p.max_seq ? p.max_seq : L);
+    int sl = p.slot[m];
+    sl = sl < 0 ? 0 : (sl >= p.n_slots ? p.n_slots - 1 : sl);
+    // slice of the KV range owned by this CTA, in units of 64 rows
+    const int blocks = (L + 63) / 64;
+    const int per = (blocks + p.S - 1) / p.S;
+    const int begin = split * per * 64;
+    const int end = min(L, begin + per * 64);
+
+    const size_t head_off = (size_t(sl) * p.Nkv + kvh) * p.max_seq * kD;
+    const uint16_t* kb = p.kc + head_off;
+    const uint16_t* vb = p.vc + head_off;
+
+    // q slice of this lane: elements li*8 .. li*8+7 of each of the R heads, pre-scaled
+    const float scale = 0.08838834764831845f;  // 1/sqrt(128)
+    float qr[R][8];
+#pragma unroll
+    for (int h = 0; h < R; h++) {
+        const float* qp = p.q + (size_t(m) * p.Nq + kvh * R + h) * kD + li * 8;
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(qp));
+        const float4 b = __ldcg(reinterpret_cast<const float4*>(qp + 4));
+        qr[h][0] = a.x * scale; qr[h][1] = a.y * scale; qr[h][2] = a.z * scale; qr[h][3] = a.w * scale;
+        qr[h][4] = b.x * scale; qr[h][5] = b.y * scale; qr[h][6] = b.z * scale; qr[h][7] = b.w * scale;
+    }
+
+    float o[R][8];
+    float mx[R], sum[R];
+#pragma unroll
+    for (int h = 0; h < R; h++) {
+        mx[h] = -INFINITY;
+        sum[h] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) o[h][e] = 0.f;
+    }
+
+    // warp w takes rows begin + w*16 + step*64 + half + 2*r, r = 0..7
+    for (int base = begin + warp * 16; base < end; base += kWarps * 16) {
+        uint4 kraw[kRowsPerStep], vraw[kRowsPerStep];
+#pragma unroll
+        for (int r = 0; r < kRowsPerStep; r++) {
+            const int row = base + half + 2 * r;
+            const bool ok = row < end;
+            kraw[r] = ok ? ld_stream_u4(kb + size_t(row) * kD + li * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int r = 0; r < kRowsPerStep; r++) {
+            const int row = base + half + 2 * r;
+            const bool ok = row < end;
+            vraw[r] = ok ? ld_stream_u4(vb + size_t(row) * kD + li * 8) : make_uint4(0, 0, 0, 0);
+        }
+        float s[kRowsPerStep][R];
+#pragma unroll
+        for (int r = 0; r < kRowsPerStep; r++) {
+            const float kf[8] = {bf16_lo(kraw[r].x), bf16_hi(kraw[r].x), bf16_lo(kraw[r].y), bf16_hi(kraw[r].y),
+                                 bf16_lo(kraw[r].z), bf16_hi(kraw[r].z), bf16_lo(kraw[r].w), bf16_hi(kraw[r].w)};
+#pragma unroll
+            for (int h = 0; h < R; h++) {
+                float d = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; e++) d = fmaf(qr[h][e], kf[e], d);
+                s[r][h] = d;
+            }
+        }
+        // sum over the 16 lanes of a half warp
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1)
+#pragma unroll
+            for (int r = 0; r < kRowsPerStep; r++)
+#pragma unroll
+                for (int h = 0; h < R; h++) s[r][h] += __shfl_xor_sync(0xffffffffu, s[r][h], off);
+
+#pragma unroll
+        for (int h = 0; h < R; h++) {
+            float bm = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < kRowsPerStep; r++) {
+                const bool ok = (base + half + 2 * r) < end;
+                s[r][h] = ok ? s[r][h] : -INFINITY;
+                bm = fmaxf(bm, s[r][h]);
+            }
+            const float nm = fmaxf(mx[h], bm);
+            // nm is -inf only while this half warp has not seen a valid row yet
+            const float corr = (nm == -INFINITY) ? 1.f : __expf(mx[h] - nm);
+            mx[h] = nm;
+            sum[h] *= corr;
+#pragma unroll
+            for (int e = 0; e < 8; e++) o[h][e] *= corr;
+#pragma unroll
+            for (int r = 0; r < kRowsPerStep; r++) {
+                const float pexp = (s[r][h] == -INFINITY) ? 0.f : __expf(s[r][h] - nm);
+                s[r][h] = pexp;
+                sum[h] += pexp;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kRowsPerStep; r++) {
+            const float vf[8] = {bf16_lo(vraw[r].x), bf16_hi(vraw[r].x), bf16_lo(vraw[r].y), bf16_hi(vraw[r].y),
+                                 bf16_lo(vraw[r].z), bf16_hi(vraw[r].z), bf16_lo(vraw[r].w), bf16_hi(vraw[r].w)};
+#pragma unroll
+            for (int h = 0; h < R; h++)
+#pragma unroll
+                for (int e = 0; e < 8; e++) o[h][e] = fmaf(s[r][h], vf[e], o[h][e]);
+        }
+    }
+
+    // merge the two half warps (they saw different rows)
+#pragma unroll
+    for (int h = 0; h < R; h++) {
+        const float om = __shfl_xor_sync(0xffffffffu, mx[h], 16);
+        const float os = __shfl_xor_sync(0xffffffffu, sum[h], 16);
+        const float nm = fmaxf(mx[h], om);
+        const float c_self = (mx[h] == -INFINITY) ? 0.f : __expf(mx[h] - nm);
+        const float c_other = (om == -INFINITY) ? 0.f : __expf(om - nm);
+        sum[h] = sum[h] * c_self + os * c_other;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const float oo = __shfl_xor_sync(0xffffffffu, o[h][e], 16);
+            o[h][e] = o[h][e] * c_self + oo * c_other;
+        }
+        mx[h] = nm;
+    }
+    if (half == 0) {
+#pragma unroll
+        for (int h = 0; h < R; h++) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) s_o[warp][h][li * 8 + e] = o[h][e];
+            if (li == 0) { s_ml[warp][h][0] = mx[h]; s_ml[warp][h][1] = sum[h]; }
+        }
+    }
+    __syncthreads();
+
+    // merge the warps: thread t owns element t of every head
+    const int t = threadIdx.x;
+    float fo[R], fm[R], fs[R];
+#pragma unroll
+    for (int h = 0; h < R; h++) {
+        float nm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) nm = fmaxf(nm, s_ml[w][h][0]);
+        float acc = 0.f, ssum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) {
+            const float wm = s_ml[w][h][0];
+            const float c = (wm == -INFINITY) ? 0.f : __expf(wm - nm);
+            acc += s_o[w][h][t] * c;
+            ssum += s_ml[w][h][1] * c;
+        }
+        fo[h] = acc; fm[h] = nm; fs[h] = ssum;
+    }
+
+    if (p.S == 1) {
+#pragma unroll
+        for (int h = 0; h < R; h++)
+            p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + t] = fs[h] > 0.f ? fo[h] / fs[h] : 0.f;
+        return;
+    }
+
+    const size_t pbase = (size_t(m) * p.Nkv + kvh) * p.S;
+#pragma unroll
+    for (int h = 0; h < R; h++) {
+        p.part_o[((pbase + split) * R + h) * kD + t] = fo[h];
+        if (t == 0) {
+            p.part_ml[((pbase + split) * R + h) * 2] = fm[h];
+            p.part_ml[((pbase + split) * R + h) * 2 + 1] = fs[h];
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (t == 0) {
+        const int prev = atomicAdd(p.counters + m * p.Nkv + kvh, 1);
+        s_last = (prev == p.S - 1);
+        if (s_last) p.counters[m * p.Nkv + kvh] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+#pragma unroll
+    for (int h = 0; h < R; h++) {
+        float nm = -INFINITY;
+        for (int sp = 0; sp < p.S; sp++) nm = fmaxf(nm, __ldcg(p.part_ml + ((pbase + sp) * R + h) * 2));
+        float acc = 0.f, ssum = 0.f;
+        for (int sp = 0; sp < p.S; sp++) {
+            const float wm = __ldcg(p.part_ml + ((pbase + sp) * R + h) * 2);
+            const float c = (wm == -INFINITY) ? 0.f : __expf(wm - nm);
+            acc += __ldcg(p.part_o + ((pbase + sp) * R + h) * kD + t) * c;
+            ssum += __ldcg(p.part_ml + ((pbase + sp) * R + h) * 2 + 1) * c;
+        }
+        p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + t] = ssum > 0.f ? acc / ssum : 0.f;
+    }
+}
+
+int pick_splits(int M, int Nkv, int max_seq) {
+    if (g_force_splits > 0) return g_force_splits;
+    const int by_len = (max_seq + 255) / 256;  // at least 256 rows per slice
+    int want = (148 * 4 + M * Nkv - 1) / (M * Nkv);
+    int s = want < by_len ? want : by_len;
+    if (s < 1) s = 1;
+    if (s > 64) s = 64;
+    return s;
+}
+
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace
+
+void flash_decode_set_tuning(const char* key, int value) {
+    if (!strcmp(key, "flash_splits")) g_force_splits = value;
+}
+
+}  // namespace kuiper
+
+using namespace kuiper;
+
+extern "C" size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq) {
+    if (M <= 0 || Nq <= 0 || D <= 0 || max_seq <= 0) return 0;
+    const size_t S = 64;  // upper bound of pick_splits
+    return align256(size_t(M) * Nq * sizeof(int)) + align256(size_t(M) * Nq * S * D * sizeof(float)) +
+           align256(size_t(M) * Nq * S * 2 * sizeof(float));
+}
+
+extern "C" int kuiper_flash_decode(const float* q, const uint16_t* kcache, const uint16_t* vcache,
+                                   const int32_t* seq_len, const int32_t* slot, float* out,
+                                   int M, int Nq, int Nkv, int D, int max_seq, int n_slots,
+                                   void* workspace, size_t workspace_bytes, kuiper_stream_t stream) {
+    KUIPER_REQUIRE(q && kcache && vcache && seq_len && slot && out, "flash_decode: null tensor pointer");
+    KUIPER_REQUIRE(D == kD, "flash_decode: head_dim %d is not supported (128 only)", D);
+    KUIPER_REQUIRE(M > 0 && Nq > 0 && Nkv > 0 && max_seq > 0 && n_slots > 0, "flash_decode: empty shape");
+    KUIPER_REQUIRE(Nq % Nkv == 0, "flash_decode: Nq=%d is not a multiple of Nkv=%d", Nq, Nkv);
+    KUIPER_REQUIRE(M <= 65535 && Nkv <= 65535, "flash_decode: grid too large");
+    const int R = Nq / Nkv;
+    KUIPER_REQUIRE(R == 1 || R == 2 || R == 4 || R == 8, "flash_decode: group size %d is not supported", R);
+    KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(kcache) & 15) == 0 && (reinterpret_cast<uintptr_t>(vcache) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(q) & 15) == 0,
+                   "flash_decode: q and caches must be 16-byte aligned");
+
+    FlashParams p;
+    p.q = q; p.kc = kcache; p.vc = vcache; p.seq_len = seq_len; p.slot = slot; p.out = out;
+    p.M = M; p.Nq = Nq; p.Nkv = Nkv; p.max_seq = max_seq; p.n_slots = n_slots;
+    p.S = pick_splits(M, Nkv, max_seq);
+    if (p.S > 1) {
+        KUIPER_REQUIRE(workspace != nullptr, "flash_decode: split KV needs a workspace");
+        KUIPER_REQUIRE(workspace_bytes >= kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq),
+                       "flash_decode: workspace of %zu bytes is too small", workspace_bytes);
+        char* w = reinterpret_cast<char*>(workspace);
+        p.counters = reinterpret_cast<int*>(w);
+        w += align256(size_t(M) * Nq * sizeof(int));
+        p.part_o = reinterpret_cast<float*>(w);
+        w += align256(size_t(M) * Nq * 64 * D * sizeof(float));
+        p.part_ml = reinterpret_cast<float*>(w);
+    } else {
+        p.counters = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
+    }
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.S, Nkv, M);
+    cfg.blockDim = dim3(kWarps * 32, 1, 1);
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t err;
+    switch (R) {
+        case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<1>, p); break;
+        case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<2>, p); break;
+        case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<4>, p); break;
+        default: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<8>, p); break;
+    }
+    if (err != cudaSuccess) {
+        set_error("flash_decode launch failed: %s", cudaGetErrorString(err));
+        return KUIPER_INTERNAL_ERROR;
+    }
+    return KUIPER_OK;
+}
