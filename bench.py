@@ -1,0 +1,439 @@
+#!/usr/bin/env python
+"""Decode-throughput benchmark of the B200 engine.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c4|c2] [--impl reference]
+
+Default workload: config "Qwen3-8B-shaped INT4-AWQ decode, batch 1, 2048-token prompt" of the
+workload list (the one the tokens/s target is quoted on); a step is one greedy decode token.
+Weights are random-init N(0, 0.02) quantised to INT4-AWQ g128 (synthetic data).
+
+  value      decode tokens/s with everything resident in HBM (CUDA-graph loop, device timed)
+  e2e        the same through Model::decode_predict with host token ids in / out every step
+  roofline   the INT4-AWQ GEMV launches of one token, timed alone with CUDA events
+  cpu_baseline  the CPU oracle's decoder timed on the host cores on a bounded sample
+
+With --gpus N (under torch.distributed.run) the model is tensor-parallel over N ranks.
+--impl reference times the CPU oracle (the reference has no implementation of this path to run).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (config kwargs, prompt length, decode tokens of the workload, batch)
+    "c2": (dict(n_layers=28, hidden=1024, n_q_heads=16, n_kv_heads=8, head_dim=128, inter=3072, vocab=151936), 64, 256, 1,
+           "qwen3-0.6b-shape int4-awq g128, batch 1, 64-token prompt"),
+    "c4": (dict(n_layers=36, hidden=2560, n_q_heads=32, n_kv_heads=8, head_dim=128, inter=9728, vocab=151936), 512, 512, 1,
+           "qwen3-4b-shape int4-awq g128, batch 1, 512-token prompt"),
+    "c5": (dict(n_layers=36, hidden=4096, n_q_heads=32, n_kv_heads=8, head_dim=128, inter=12288, vocab=151936), 2048, 1024, 1,
+           "qwen3-8b-shape int4-awq g128, batch 1, 2048-token prompt"),
+}
+AWQ_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def int4_bytes(K, N, g=128):
+    return K * N // 2 + (K // g) * N * 2 + (K // g) * N // 2
+
+
+def layer_shapes(cfg, tp=1):
+    H, D = cfg["hidden"], cfg["head_dim"]
+    Hq, Hkv, I = cfg["n_q_heads"] // tp, cfg["n_kv_heads"] // tp, cfg["inter"] // tp
+    return {"qkv": (H, (Hq + 2 * Hkv) * D), "o": (Hq * D, H), "gu": (H, 2 * I), "down": (I, H)}
+
+
+def token_bytes(cfg, ctx, batch=1):
+    """Algorithmic HBM bytes of one decode step: every weight once + the KV rows read."""
+    w = cfg["n_layers"] * sum(int4_bytes(K, N) for K, N in layer_shapes(cfg).values())
+    w += cfg["vocab"] * cfg["hidden"] * 2 + (2 * cfg["n_layers"] + 1) * cfg["hidden"] * 2
+    kv = cfg["n_layers"] * 2 * cfg["n_kv_heads"] * cfg["head_dim"] * 2 * ctx * batch
+    return w + kv
+
+
+# --------------------------------------------------------------------------- synthetic weights
+def quantize_awq_torch(W, g=128):
+    """Harness quantiser (per group/column min-max, 4 bit), same rule as the oracle's orc_awq_quantize."""
+    import torch
+    K, N = W.shape
+    Wg = W.view(K // g, g, N)
+    mn, mx = Wg.amin(1), Wg.amax(1)
+    s16 = ((mx - mn) / 15.0).clamp_min(1e-8).half()
+    s = s16.float()
+    z = torch.round(-mn / s).clamp_(0, 15)
+    q = (torch.round(Wg / s[:, None, :]) + z[:, None, :]).clamp_(0, 15).to(torch.int64).view(K, N)
+
+    def pack(v):
+        rows = v.shape[0]
+        v = v.view(rows, N // 8, 8)
+        w = torch.zeros((rows, N // 8), dtype=torch.int64, device=v.device)
+        for i, o in enumerate(AWQ_ORDER):
+            w |= v[:, :, o] << (4 * i)
+        return ((w + 2 ** 31) % 2 ** 32 - 2 ** 31).to(torch.int32).contiguous()
+
+    return pack(q), pack(z.to(torch.int64)), s16.contiguous()
+
+
+def make_layer_torch(cfg, gen, device):
+    import torch
+    H, D = cfg["hidden"], cfg["head_dim"]
+    lw = {}
+    for name, n in (("input_norm", H), ("post_norm", H), ("q_norm", D), ("k_norm", D)):
+        lw[name] = (1.0 + 0.02 * torch.randn(n, generator=gen, device=device)).bfloat16()
+    for name, (K, N) in layer_shapes(cfg).items():
+        W = torch.randn((K, N), generator=gen, device=device) * 0.02
+        lw[f"{name}_qw"], lw[f"{name}_qz"], lw[f"{name}_s"] = quantize_awq_torch(W)
+        del W
+    return lw
+
+
+def make_globals_torch(cfg, gen, device):
+    import torch
+    V, H = cfg["vocab"], cfg["hidden"]
+    embed = (torch.randn((V, H), generator=gen, device=device) * 0.02).bfloat16()
+    lm_head = (torch.randn((V, H), generator=gen, device=device) * 0.02).bfloat16()
+    final_norm = (1.0 + 0.02 * torch.randn(H, generator=gen, device=device)).bfloat16()
+    return embed, final_norm, lm_head
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """nvidia-smi samples (SM clock, throttle reasons) taken while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index, self.samples, self._stop, self._t = gpu_index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.gpu_index)], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        mhz = sorted(float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit())
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------- CPU oracle timing
+def make_cpu_weights(orc, ocfg, seed=0):
+    """Cheap synthetic weights for CPU timing: uniform nibbles / zeros, fp16 scales in [0.002, 0.02]
+    (the single-GEMV workload's distribution); bf16 tables tiled from a small random block."""
+    rng = np.random.default_rng(seed)
+    H, D, I, V = ocfg.hidden, ocfg.head_dim, ocfg.inter, ocfg.vocab
+    QKV = (ocfg.n_q_heads + 2 * ocfg.n_kv_heads) * D
+
+    def quant(K, N):
+        qw = rng.integers(-2 ** 31, 2 ** 31, (K, N // 8), dtype=np.int64).astype(np.int32)
+        qz = rng.integers(-2 ** 31, 2 ** 31, (K // 128, N // 8), dtype=np.int64).astype(np.int32)
+        s = rng.uniform(0.002, 0.02, (K // 128, N)).astype(np.float16).view(np.uint16)
+        return qw, qz, s
+
+    def norm(n):
+        return orc.f32_to_bf16(np.ones(n, np.float32))
+
+    block = orc.f32_to_bf16((rng.standard_normal((1024, H)) * 0.02).astype(np.float32))
+    table = np.ascontiguousarray(np.tile(block, ((V + 1023) // 1024, 1))[:V])
+    weights = {"embed": table, "final_norm": norm(H), "lm_head": table, "layers": []}
+    for _ in range(ocfg.n_layers):
+        lw = {"input_norm": norm(H), "post_norm": norm(H), "q_norm": norm(D), "k_norm": norm(D)}
+        for name, (K, N) in {"qkv": (H, QKV), "o": (ocfg.n_q_heads * D, H), "gu": (H, 2 * I), "down": (I, H)}.items():
+            lw[f"{name}_qw"], lw[f"{name}_qz"], lw[f"{name}_s"] = quant(K, N)
+        weights["layers"].append(lw)
+    return weights
+
+
+def cpu_decode_sample(cfg, n_layers_sample, steps, warmup, seed=0):
+    """Times the CPU oracle's decoder (fp32 accumulation, OpenMP over all host cores) on a model
+    truncated to n_layers_sample layers and extrapolates to the full depth.  Returns tokens/s."""
+    from oracle import cpu_oracle as orc
+    orc.build()
+    ocfg = orc.ModelConfig(**{**cfg, "n_layers": n_layers_sample}, max_seq=max(64, steps + warmup + 8), max_batch=1,
+                           act_round=orc.ROUND_FP16)
+    weights = make_cpu_weights(orc, ocfg, seed=seed)
+    model = orc.OracleModel(ocfg, weights)
+    tok, times = 1, []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        _, nx = model.forward([tok], [i], acc_double=False, want_logits=False)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+        tok = int(nx[0])
+    t_step = float(np.mean(times))
+    # head (final norm + lm_head + argmax) is paid once per token, layers scale with depth
+    t0 = time.perf_counter()
+    orc.bf16_gemv(np.ones((1, cfg["hidden"]), np.float32), weights["lm_head"], acc_double=False)
+    t_head = time.perf_counter() - t0
+    t_layers = max(t_step - t_head, 1e-9) / n_layers_sample
+    t_token = t_layers * cfg["n_layers"] + t_head
+    return 1.0 / t_token, t_step
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference(args, cfg, desc, rank, world):
+    """Reference arm: the reference ships no code for this path, so its CPU side is the oracle port."""
+    if rank != 0:
+        return
+    n_sample = 2 if cfg["hidden"] >= 2560 else 4
+    steps, warmup = max(1, min(args.steps, 12)), max(1, min(args.warmup, 2))
+    t0 = time.perf_counter()
+    tps, t_step = cpu_decode_sample(cfg, n_sample, steps, warmup)
+    sample = (f"{steps} greedy decode tokens (after {warmup} warm-up) of a {n_sample}-layer slice of the model at "
+              f"context < 32, fp32 accumulation, OpenMP; per-layer time scaled to {cfg['n_layers']} layers + full lm_head")
+    line = {
+        "impl": "reference", "metric": "Qwen3 INT4 decode tokens/s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / tps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights, fp32 accumulate",
+        "data": "synthetic", "config": {"workload": desc, "timed_steps_used": steps},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": host_cores(), "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+def gemv_roofline(cfg, tp, layers_kept, iters=3):
+    """INT4-AWQ GEMV launches of one token (4 shapes x n_layers), over distinct weights, timed alone."""
+    import torch
+    from mykuiperllama_b200 import capi
+    shapes = layer_shapes(cfg, tp)
+    x = {n: torch.randn((1, K), device="cuda") for n, (K, N) in shapes.items()}
+    y = {n: torch.empty((1, N), device="cuda") for n, (K, N) in shapes.items()}
+    ws = capi.awq_gemv_workspace(1, max(K for K, _ in shapes.values()), max(N for _, N in shapes.values()))
+    L = cfg["n_layers"]
+
+    def one_token():
+        for l in range(L):
+            lw = layers_kept[l % len(layers_kept)]
+            for n in ("qkv", "o", "gu", "down"):
+                capi.awq_gemv(x[n], lw[f"{n}_qw"], lw[f"{n}_qz"], lw[f"{n}_s"], workspace=ws, out=y[n])
+
+    one_token()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        one_token()
+    best = None
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        best = ms if best is None else min(best, ms)
+    launches = 4 * L
+    total_bytes = L * sum(int4_bytes(K, N) + 4 * K + 4 * N for K, N in shapes.values())
+    return total_bytes / launches, best * 1e-3 / launches, launches
+
+
+def run_engine(args, cfg, prompt_len, desc, rank, world):
+    import torch
+    import torch.distributed as dist
+    from mykuiperllama_b200 import engine as eng_mod
+
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    B = 1
+    steps_total = args.warmup + args.steps
+    max_seq = prompt_len + 2 * steps_total + 16
+    ecfg = eng_mod.EngineConfig(**cfg, max_seq=max_seq, max_batch=B, max_rows=8, tp_rank=rank, tp_size=world)
+    eng = eng_mod.Qwen3Engine(ecfg)
+
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1234)  # same weights on every rank
+    keep = []
+    for l in range(cfg["n_layers"]):
+        lw = make_layer_torch(cfg, gen, device)
+        eng.load_layer(l, lw)
+        if l < 4 and world == 1:
+            keep.append(lw)
+    embed, final_norm, lm_head = make_globals_torch(cfg, gen, device)
+    eng.load_globals(embed, final_norm, lm_head)
+    del embed, lm_head, lw
+    torch.cuda.empty_cache()
+
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8, device=device)
+        if rank == 0:
+            uid.copy_(torch.frombuffer(bytearray(eng_mod.Qwen3Engine.tp_unique_id()), dtype=torch.uint8))
+        dist.broadcast(uid, 0)
+        eng.init_tp(bytes(uid.cpu().numpy().tobytes()))
+
+    rng = np.random.default_rng(7)
+    prompt = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
+    t0 = time.perf_counter()
+    first = eng.prefill(prompt, slot=0)
+    prefill_s = time.perf_counter() - t0
+
+    stream = torch.cuda.ExternalStream(eng.stream, device=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident loop: value
+    eng.decode_begin([first], [prompt_len], [0])
+    eng.decode_step(args.warmup)
+    eng.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        e0.record(stream)
+        eng.decode_step(args.steps)
+        e1.record(stream)
+        eng.synchronize()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    value = args.steps * B / (ms * 1e-3)
+    tok_after = int(eng.decode_read(1)[0])
+
+    # ---- end to end: host token in, host token out, every step
+    pos_now = prompt_len + steps_total
+    eng.decode_begin([tok_after], [pos_now], [0])
+    tok = np.array([tok_after], np.int32)
+    for _ in range(args.warmup):
+        tok = eng.decode_predict(tok)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok = eng.decode_predict(tok)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = args.steps * B / float(t.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    ctx_mid = prompt_len + args.warmup + args.steps // 2
+    peak, peak_kind = measured_peak_gbs()
+    step_bytes = token_bytes(cfg, ctx_mid, B) / world  # per GPU under tensor parallelism (lm_head is replicated)
+    if world > 1:
+        step_bytes += (world - 1) / world * cfg["vocab"] * cfg["hidden"] * 2
+    roof_tps = peak * 1e9 / step_bytes
+    line = {
+        "metric": "Qwen3 INT4 decode tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights (AWQ g128), fp16 x operand, fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": desc, "batch": B, "prompt_tokens": prompt_len, "context_during_timing": ctx_mid,
+                   "parallelism": f"tp{world}", "l2_policy": "inputs larger than L2 (weights streamed once per token)",
+                   "prefill_s": round(prefill_s, 3)},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": eng.kernels_per_step * args.steps,
+        "clocks": clocks.summary(),
+        "decode_roofline": {"bytes_per_token_per_gpu": int(step_bytes), "tokens_per_s_at_peak": roof_tps,
+                            "frac_of_" + peak_kind: value / roof_tps,
+                            "frac_of_nominal_8TBs": value / (NOMINAL_HBM_GBS * 1e9 / step_bytes)},
+    }
+    if world == 1:
+        per_launch_bytes, per_launch_s, launches = gemv_roofline(cfg, 1, keep)
+        achieved = per_launch_bytes / per_launch_s / 1e9
+        line["roofline"] = {"bound": "hbm", "kernel": "awq_gemv_kernel", "achieved": achieved, "peak": peak,
+                            "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                            "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": None,
+                            "launches_per_token": launches, "avg_bytes_per_launch": int(per_launch_bytes),
+                            "avg_us_per_launch": per_launch_s * 1e6}
+        del keep
+        torch.cuda.empty_cache()
+        n_sample = 2 if cfg["hidden"] >= 2560 else 4
+        tps_cpu, _ = cpu_decode_sample(cfg, n_sample, steps=3, warmup=1)
+        line["cpu_baseline"] = {
+            "value": tps_cpu, "unit": "tokens/s", "cores": host_cores(), "kind": "port",
+            "sample": f"3 decode tokens of a {n_sample}-layer slice at context < 8 on the CPU oracle (fp32 accumulate, "
+                      f"OpenMP), per-layer time scaled to {cfg['n_layers']} layers + full lm_head"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "engine":
+        args.warmup = 3
+    cfg, prompt_len, _, _, desc = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, cfg, desc, rank, world)
+        return
+    if world != args.gpus:
+        if args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torch.distributed.run with {args.gpus} ranks (WORLD_SIZE={world})")
+    run_engine(args, cfg, prompt_len, desc, rank, world)
+
+
+if __name__ == "__main__":
+    main()

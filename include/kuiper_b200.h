@@ -35,6 +35,8 @@ extern "C" {
 
 typedef struct CUstream_st* kuiper_stream_t; /* == cudaStream_t */
 
+#define KUIPER_API __attribute__((visibility("default")))
+
 enum {
     KUIPER_OK = 0,
     KUIPER_INTERNAL_ERROR = 5,
@@ -47,23 +49,23 @@ enum {
     KUIPER_ACT_FP32 = 0, /* x kept in fp32 */
 };
 
-const char* kuiper_version(void);
+KUIPER_API const char* kuiper_version(void);
 /* text of the last error raised on the calling thread ("" if none) */
-const char* kuiper_last_error(void);
+KUIPER_API const char* kuiper_last_error(void);
 /* benchmark sweeps only: override a launch heuristic ("gemv_rows", "gemv_math", "flash_splits"; 0 or -1 restores it) */
-int kuiper_set_tuning(const char* key, int value);
+KUIPER_API int kuiper_set_tuning(const char* key, int value);
 
 /* ---- residual add: replaces add_kernel_cu (kernel/cuda/add_kernel.cu:14-52) ---- */
-int kuiper_add_f32(const float* a, const float* b, float* out, int64_t n, kuiper_stream_t stream);
+KUIPER_API int kuiper_add_f32(const float* a, const float* b, float* out, int64_t n, kuiper_stream_t stream);
 
 /* ---- INT4-AWQ: placeholder kuiper/include/op/matmul.h:1-11, quant fields op/layer.h:151-155 ---- */
 /* nibble unpack to uint8 [K, N] (logical column order) */
-int kuiper_awq_unpack_u8(const int32_t* qweight, uint8_t* out, int K, int N, kuiper_stream_t stream);
+KUIPER_API int kuiper_awq_unpack_u8(const int32_t* qweight, uint8_t* out, int K, int N, kuiper_stream_t stream);
 /* fp32 dequantisation W[K,N] = (q - z) * s, exact */
-int kuiper_awq_dequant_f32(const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
+KUIPER_API int kuiper_awq_dequant_f32(const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
                            float* W, int K, int N, int group, kuiper_stream_t stream);
 /* bf16 dequantisation (round to nearest even) used by the M>=16 tensor-core path */
-int kuiper_awq_dequant_bf16(const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
+KUIPER_API int kuiper_awq_dequant_bf16(const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
                             uint16_t* W, int K, int N, int group, kuiper_stream_t stream);
 
 /*
@@ -71,8 +73,8 @@ int kuiper_awq_dequant_bf16(const int32_t* qweight, const int32_t* qzeros, const
  * counters must be zero before the first use (kuiper_workspace_init) and are left
  * zero by every call.  Two calls that overlap on the GPU must not share a workspace.
  */
-size_t kuiper_awq_gemv_workspace_bytes(int M, int K, int N);
-int kuiper_workspace_init(void* workspace, size_t bytes, kuiper_stream_t stream);
+KUIPER_API size_t kuiper_awq_gemv_workspace_bytes(int M, int K, int N);
+KUIPER_API int kuiper_workspace_init(void* workspace, size_t bytes, kuiper_stream_t stream);
 
 /*
  * y[M,N] = x[M,K] . dequant(qweight) (+ residual[M,N] if residual != NULL; y may alias
@@ -80,18 +82,18 @@ int kuiper_workspace_init(void* workspace, size_t bytes, kuiper_stream_t stream)
  * dequant-fused GEMV; larger M is processed in row blocks.
  * act_mode: KUIPER_ACT_FP16 or KUIPER_ACT_FP32.
  */
-int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
+KUIPER_API int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
                         const uint16_t* scales, float* y, const float* residual,
                         int M, int K, int N, int group, int act_mode,
                         void* workspace, size_t workspace_bytes, kuiper_stream_t stream);
 
 /* ---- BF16 GEMV (lm_head): W bf16 [N, K], y[M,N] = x[M,K] . W^T ---- */
-int kuiper_bf16_gemv_f32(const float* x, const uint16_t* W, float* y, int M, int K, int N,
+KUIPER_API int kuiper_bf16_gemv_f32(const float* x, const uint16_t* W, float* y, int M, int K, int N,
                          kuiper_stream_t stream);
 
 /* ---- RMSNorm: placeholder kuiper/include/op/rmsnorm.h:1-10 ---- */
 /* y = (x * rstd) * w, rstd = 1/sqrt(mean(x^2) + eps); w bf16 [H]; y may alias x */
-int kuiper_rmsnorm_f32(const float* x, const uint16_t* w, float* y, int M, int H, float eps,
+KUIPER_API int kuiper_rmsnorm_f32(const float* x, const uint16_t* w, float* y, int M, int H, float eps,
                        kuiper_stream_t stream);
 
 /* ---- per-head q/k RMSNorm + rotary + KV-cache write: placeholder kuiper/include/op/rope.h:1-10 ---- */
@@ -102,7 +104,7 @@ int kuiper_rmsnorm_f32(const float* x, const uint16_t* w, float* y, int M, int H
  * the caches hold n_slots sequences; pos and slot are clamped into range on the device.
  * D must be 128.
  */
-int kuiper_qknorm_rope_kvwrite(const float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
+KUIPER_API int kuiper_qknorm_rope_kvwrite(const float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
                                const float* cos_t, const float* sin_t, const int32_t* pos,
                                const int32_t* slot, int M, int Nq, int Nkv, int D, float eps,
                                int max_seq, int n_slots, float* q_out, uint16_t* kcache,
@@ -116,23 +118,31 @@ int kuiper_qknorm_rope_kvwrite(const float* qkv, const uint16_t* q_norm_w, const
  * workspace: kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq) bytes, counters zeroed once
  * with kuiper_workspace_init.  D must be 128, Nq/Nkv in {1,2,4,8}.
  */
-size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq);
-int kuiper_flash_decode(const float* q, const uint16_t* kcache, const uint16_t* vcache,
+KUIPER_API size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq);
+KUIPER_API int kuiper_flash_decode(const float* q, const uint16_t* kcache, const uint16_t* vcache,
                         const int32_t* seq_len, const int32_t* slot, float* out,
                         int M, int Nq, int Nkv, int D, int max_seq, int n_slots,
                         void* workspace, size_t workspace_bytes, kuiper_stream_t stream);
 
 /* ---- SwiGLU: placeholder kuiper/include/op/swiglu.h:1-10 ---- */
 /* out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]; gate_up is [M, 2I] */
-int kuiper_swiglu_f32(const float* gate_up, float* out, int M, int I, kuiper_stream_t stream);
+KUIPER_API int kuiper_swiglu_f32(const float* gate_up, float* out, int M, int I, kuiper_stream_t stream);
 
 /* ---- embedding gather: placeholder kuiper/include/op/embedding.h:1-10 ---- */
-int kuiper_embedding_bf16(const int32_t* tokens, const uint16_t* table, float* out, int M, int H,
+KUIPER_API int kuiper_embedding_bf16(const int32_t* tokens, const uint16_t* table, float* out, int M, int H,
                           int vocab, kuiper_stream_t stream);
 
 /* ---- greedy sampler (the reference's sampler directory is absent, CMakeLists.txt:87) ---- */
 /* out[m] = lowest index of the maximum of logits[m, 0..V) */
-int kuiper_argmax_f32(const float* logits, int32_t* out, int M, int V, kuiper_stream_t stream);
+KUIPER_API int kuiper_argmax_f32(const float* logits, int32_t* out, int M, int V, kuiper_stream_t stream);
+
+/*
+ * End of a decode step, on the device: feed the chosen ids back as the next input and
+ * advance every sequence by one position (clamped to max_seq - 1).
+ * tokens[b] = next[b]; pos[b] += 1; seq_len[b] = pos[b] + 1.
+ */
+KUIPER_API int kuiper_decode_advance(int32_t* tokens, const int32_t* next, int32_t* pos, int32_t* seq_len,
+                                     int B, int max_seq, kuiper_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -47,6 +47,7 @@ KERNEL_API = {
     "kuiper_swiglu_f32": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "kuiper_embedding_bf16": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_argmax_f32": (_i32, [_vp, _vp, _i32, _i32, _vp]),
+    "kuiper_decode_advance": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),
 }
 
 
@@ -73,3 +74,58 @@ def kernels() -> C.CDLL:
 def check(code: int) -> None:
     if code != 0:
         raise KuiperError(code, kernels().kuiper_last_error().decode())
+
+
+class ModelConfigC(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layers", "hidden", "n_q_heads", "n_kv_heads", "head_dim", "inter", "vocab",
+                                         "group", "max_seq", "max_batch", "max_rows")] + \
+               [("eps", C.c_float), ("rope_theta", C.c_double), ("act_mode", C.c_int32), ("tp_rank", C.c_int32),
+                ("tp_size", C.c_int32)]
+
+
+LAYER_FIELDS = ("input_norm", "post_norm", "q_norm", "k_norm", "qkv_qw", "qkv_qz", "qkv_s", "o_qw", "o_qz", "o_s",
+                "gu_qw", "gu_qz", "gu_s", "down_qw", "down_qz", "down_s")
+
+
+class LayerWeightsC(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in LAYER_FIELDS]
+
+
+HOST_API = {
+    "kuiper_llama_last_error": (C.c_char_p, []),
+    "kuiper_model_create": (_vp, [C.POINTER(ModelConfigC)]),
+    "kuiper_model_destroy": (None, [_vp]),
+    "kuiper_model_load_layer": (_i32, [_vp, _i32, C.POINTER(LayerWeightsC), _i32]),
+    "kuiper_model_load_globals": (_i32, [_vp, _vp, _vp, _vp, _i32]),
+    "kuiper_tp_unique_id": (_i32, [_vp]),
+    "kuiper_model_init_tp": (_i32, [_vp, _vp]),
+    "kuiper_model_predict": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp]),
+    "kuiper_model_prefill": (_i32, [_vp, _vp, _i32, _i32, _vp]),
+    "kuiper_model_decode_begin": (_i32, [_vp, _vp, _vp, _vp, _i32]),
+    "kuiper_model_decode_step": (_i32, [_vp, _i32]),
+    "kuiper_model_decode_read": (_i32, [_vp, _vp, _i32]),
+    "kuiper_model_decode_predict": (_i32, [_vp, _vp, _i32, _vp]),
+    "kuiper_model_kernels_per_step": (_i32, [_vp]),
+    "kuiper_model_stream": (_vp, [_vp]),
+    "kuiper_model_synchronize": (_i32, [_vp]),
+    "kuiper_selftest": (_i32, [_i32, C.c_char_p, _sz]),
+}
+
+
+def host() -> C.CDLL:
+    """The C++ engine library (loads the kernel library first)."""
+    global _host
+    if _host is None:
+        kernels()
+        path = _build.HOST_LIB
+        if not os.path.exists(path):
+            _build.build_host()
+        lib = C.CDLL(path, mode=C.RTLD_GLOBAL)
+        _bind(lib, HOST_API)
+        _host = lib
+    return _host
+
+
+def check_host(code: int) -> None:
+    if code != 0:
+        raise KuiperError(code, host().kuiper_llama_last_error().decode())

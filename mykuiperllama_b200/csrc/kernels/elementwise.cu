@@ -171,6 +171,19 @@ __global__ void awq_dequant_kernel(const int32_t* __restrict__ qw, const int32_t
     }
 }
 
+// ---------------------------------------------------------------- decode bookkeeping
+__global__ void decode_advance_kernel(int32_t* tokens, const int32_t* next, int32_t* pos, int32_t* seq_len, int B,
+                                      int max_seq) {
+    pdl_wait();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    tokens[b] = next[b];
+    int p = pos[b] + 1;
+    p = p >= max_seq ? max_seq - 1 : p;
+    pos[b] = p;
+    seq_len[b] = p + 1;
+}
+
 int grid_for(int64_t work_items, int threads) {
     int64_t blocks = (work_items + threads - 1) / threads;
     const int64_t cap = 148 * 16;
@@ -275,4 +288,12 @@ extern "C" int kuiper_awq_dequant_f32(const int32_t* qweight, const int32_t* qze
 extern "C" int kuiper_awq_dequant_bf16(const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
                                        uint16_t* W, int K, int N, int group, kuiper_stream_t stream) {
     return dequant_common(qweight, qzeros, scales, W, K, N, group, true, stream);
+}
+
+extern "C" int kuiper_decode_advance(int32_t* tokens, const int32_t* next, int32_t* pos, int32_t* seq_len,
+                                     int B, int max_seq, kuiper_stream_t stream) {
+    KUIPER_REQUIRE(tokens && next && pos && seq_len, "decode_advance: null tensor pointer");
+    KUIPER_REQUIRE(B > 0 && max_seq > 0, "decode_advance: empty shape");
+    decode_advance_kernel<<<(B + 127) / 128, 128, 0, as_stream(stream)>>>(tokens, next, pos, seq_len, B, max_seq);
+    return launch_status("decode_advance");
 }

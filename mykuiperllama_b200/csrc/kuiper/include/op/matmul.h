@@ -1,0 +1,48 @@
+// Linear projection y = x . W.  The reference reserves this header as an empty
+// namespace (kuiper/include/op/matmul.h:1-11) and the LayerMatmul tag (op/layer.h:14).
+//
+// Quantised (is_quant_layer): INT4-AWQ.  weight slot 0 = qweight Int32 [K, N/8],
+// slot 1 = qzeros Int32 [K/group, N/8], set_scales() = Fp16 [K/group, N],
+// set_group_size(128); input [M, K], output [M, N].
+// Plain: weight slot 0 = Bf16 [N, K] (one row per output, the lm_head layout).
+//
+// Optional residual: with set_residual(true) the layer takes a second input [M, N] and
+// writes output = input2 + x . W in the same kernel (the output may be that tensor).
+#ifndef KUIPER_INCLUDE_OP_MATMUL_H
+#define KUIPER_INCLUDE_OP_MATMUL_H
+
+#include "base/cuda_config.h"
+#include "op/layer.h"
+
+namespace op {
+class MatmulLayer : public LayerParam {
+public:
+    // dim0 = output width N, dim1 = input width K
+    explicit MatmulLayer(base::DeviceType device_type, int32_t dim0, int32_t dim1, bool is_quant_layer = false);
+
+    base::Status check() const override;
+    using Layer::forward;  // keep the N-ary overloads visible next to the override
+    base::Status forward() override;
+
+    void set_residual(bool has_residual);
+    // scratch of the split-K kernel: kernel::matmul_quant_workspace_bytes(M, K, N) bytes, zero-initialised once
+    void set_workspace(const tensor::Tensor& workspace);
+    // how the INT4 kernel rounds x: 1 = fp16 operand (default), 0 = fp32 operand
+    void set_act_mode(int32_t act_mode) { act_mode_ = act_mode; }
+
+    int32_t out_features() const { return dim0_; }
+    int32_t in_features() const { return dim1_; }
+
+protected:
+    base::DataType weight_data_type(int32_t idx) const override;
+
+private:
+    int32_t dim0_ = 0;
+    int32_t dim1_ = 0;
+    bool has_residual_ = false;
+    int32_t act_mode_ = 1;
+    tensor::Tensor workspace_;
+};
+}  // namespace op
+
+#endif  // KUIPER_INCLUDE_OP_MATMUL_H

@@ -1,0 +1,33 @@
+// Grouped-query attention over the KV cache (flash-decoding: split KV + log-sum-exp
+// combine).  Placeholder in the reference: kuiper/include/op/mha.h:1-11, tag LayerMHA
+// (op/layer.h:16).
+//
+// inputs : 0 q [M, Nq*D] Fp32, 1 seq_len [M] Int32 (row m attends to positions
+//          [0, seq_len[m])), 2 slot [M] Int32
+// output : 0 [M, Nq*D] Fp32
+// caches : set_cache(k, v): Bf16 [n_slots, Nkv, max_seq, D]; set_workspace(): scratch of
+//          kernel::mha_workspace_bytes(...) bytes, zero-initialised once
+#ifndef KUIPER_INCLUDE_OP_MHA_H
+#define KUIPER_INCLUDE_OP_MHA_H
+
+#include "base/cuda_config.h"
+#include "op/layer.h"
+
+namespace op {
+class MultiHeadAttention : public Layer {
+public:
+    explicit MultiHeadAttention(base::DeviceType device_type, int32_t head_num, int32_t kv_head_num,
+                                int32_t head_size);
+    base::Status check() const override;
+    using Layer::forward;  // keep the N-ary overloads visible next to the override
+    base::Status forward() override;
+    void set_cache(const tensor::Tensor& key_cache, const tensor::Tensor& value_cache);
+    void set_workspace(const tensor::Tensor& workspace);
+
+private:
+    int32_t head_num_ = 0, kv_head_num_ = 0, head_size_ = 0;
+    tensor::Tensor key_cache_, value_cache_, workspace_;
+};
+}  // namespace op
+
+#endif  // KUIPER_INCLUDE_OP_MHA_H

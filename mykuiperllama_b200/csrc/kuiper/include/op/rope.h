@@ -1,0 +1,34 @@
+// Per-head q/k RMSNorm, half-split rotary embedding and KV-cache append in one layer.
+// Placeholder in the reference: kuiper/include/op/rope.h:1-10, tag LayerRope (op/layer.h:15).
+//
+// inputs : 0 qkv [M, (Nq+2Nkv)*D] Fp32, 1 pos [M] Int32, 2 slot [M] Int32,
+//          3 cos [max_seq, D/2] Fp32, 4 sin [max_seq, D/2] Fp32
+// output : 0 q [M, Nq*D] Fp32
+// weights: 0 q_norm Bf16 [D], 1 k_norm Bf16 [D]
+// caches : set_cache(k, v): Bf16 [n_slots, Nkv, max_seq, D] for this layer
+#ifndef KUIPER_INCLUDE_OP_ROPE_H
+#define KUIPER_INCLUDE_OP_ROPE_H
+
+#include "op/layer.h"
+
+namespace op {
+class RoPELayer : public LayerParam {
+public:
+    explicit RoPELayer(base::DeviceType device_type, int32_t head_num, int32_t kv_head_num, int32_t head_size,
+                       float eps = 1e-6f);
+    base::Status check() const override;
+    using Layer::forward;  // keep the N-ary overloads visible next to the override
+    base::Status forward() override;
+    void set_cache(const tensor::Tensor& key_cache, const tensor::Tensor& value_cache);
+
+protected:
+    base::DataType weight_data_type(int32_t idx) const override;
+
+private:
+    int32_t head_num_ = 0, kv_head_num_ = 0, head_size_ = 0;
+    float eps_ = 1e-6f;
+    tensor::Tensor key_cache_, value_cache_;
+};
+}  // namespace op
+
+#endif  // KUIPER_INCLUDE_OP_ROPE_H

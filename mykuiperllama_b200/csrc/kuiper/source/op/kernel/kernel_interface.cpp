@@ -1,0 +1,186 @@
+// Kernel registry: wraps each C-ABI entry point (include/kuiper_b200.h) in the
+// Tensor-level signature the layers call, and hands it out per device like the
+// reference's get_add_kernel (kuiper/source/op/kernel/kernel_interface.cpp:6-14).
+// Preconditions are CHECKed the way add_kernel_cu does (add_kernel.cu:16-26), and a
+// non-zero C-ABI status is fatal, mirroring its CHECK on cudaGetLastError (:50-51).
+#include "kernel_interface.h"
+
+#include "kuiper_b200.h"
+
+namespace kernel {
+namespace {
+
+using tensor::Tensor;
+
+#define KERNEL_OK(call)                                                              \
+    do {                                                                             \
+        int rc__ = (call);                                                           \
+        CHECK_EQ(rc__, 0) << #call << " failed: " << kuiper_last_error();           \
+    } while (0)
+
+inline kuiper_stream_t as_stream(void* s) { return reinterpret_cast<kuiper_stream_t>(s); }
+
+void require_cuda(const Tensor& t, const char* what) {
+    CHECK(!t.is_empty()) << what << " is empty";
+    CHECK(t.device_type() == base::DeviceType::DeviceCUDA) << what << " is not on the CUDA device";
+}
+
+template <typename T>
+T* out_ptr(const Tensor& t) {
+    return const_cast<T*>(t.ptr<T>());
+}
+
+void add_kernel_cu(const Tensor& input1, const Tensor& input2, const Tensor& output, void* stream) {
+    require_cuda(input1, "add input1");
+    require_cuda(input2, "add input2");
+    require_cuda(output, "add output");
+    CHECK_EQ(input1.size(), output.size());
+    CHECK_EQ(input2.size(), output.size());
+    KERNEL_OK(kuiper_add_f32(input1.ptr<float>(), input2.ptr<float>(), out_ptr<float>(output), int64_t(output.size()),
+                             as_stream(stream)));
+}
+
+void matmul_kernel_cu(const Tensor& input, const Tensor& weight, const Tensor& output, void* stream) {
+    require_cuda(input, "matmul input");
+    require_cuda(weight, "matmul weight");
+    require_cuda(output, "matmul output");
+    CHECK_EQ(weight.dims_size(), 2);
+    const int32_t N = weight.get_dim(0), K = weight.get_dim(1);
+    CHECK_EQ(input.size() % size_t(K), size_t(0));
+    const int32_t M = int32_t(input.size() / size_t(K));
+    CHECK_EQ(output.size(), size_t(M) * size_t(N));
+    KERNEL_OK(kuiper_bf16_gemv_f32(input.ptr<float>(), weight.ptr<uint16_t>(), out_ptr<float>(output), M, K, N,
+                                   as_stream(stream)));
+}
+
+void matmul_kernel_quant_cu(const Tensor& input, const Tensor& qweight, const Tensor& qzeros, const Tensor& scales,
+                            const Tensor& output, const Tensor* residual, int32_t group_size, int32_t act_mode,
+                            const Tensor& workspace, void* stream) {
+    require_cuda(input, "matmul input");
+    require_cuda(qweight, "matmul qweight");
+    require_cuda(qzeros, "matmul qzeros");
+    require_cuda(scales, "matmul scales");
+    require_cuda(output, "matmul output");
+    CHECK_EQ(qweight.dims_size(), 2);
+    const int32_t K = qweight.get_dim(0), N = qweight.get_dim(1) * 8;
+    CHECK_EQ(input.size() % size_t(K), size_t(0));
+    const int32_t M = int32_t(input.size() / size_t(K));
+    CHECK_EQ(output.size(), size_t(M) * size_t(N));
+    if (residual) {
+        require_cuda(*residual, "matmul residual");
+        CHECK_EQ(residual->size(), output.size());
+    }
+    KERNEL_OK(kuiper_awq_gemv_f32(input.ptr<float>(), qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(),
+                                  scales.ptr<uint16_t>(), out_ptr<float>(output),
+                                  residual ? residual->ptr<float>() : nullptr, M, K, N, group_size, act_mode,
+                                  out_ptr<void>(workspace), workspace.byte_size(), as_stream(stream)));
+}
+
+void rmsnorm_kernel_cu(const Tensor& input, const Tensor& weight, const Tensor& output, float eps, void* stream) {
+    require_cuda(input, "rmsnorm input");
+    require_cuda(weight, "rmsnorm weight");
+    require_cuda(output, "rmsnorm output");
+    const int32_t H = int32_t(weight.size());
+    CHECK_EQ(input.size() % size_t(H), size_t(0));
+    CHECK_EQ(input.size(), output.size());
+    KERNEL_OK(kuiper_rmsnorm_f32(input.ptr<float>(), weight.ptr<uint16_t>(), out_ptr<float>(output),
+                                 int32_t(input.size() / size_t(H)), H, eps, as_stream(stream)));
+}
+
+void rope_kernel_cu(const Tensor& qkv, const Tensor& q_norm, const Tensor& k_norm, const Tensor& cos_cache,
+                    const Tensor& sin_cache, const Tensor& pos, const Tensor& slot, const Tensor& q_out,
+                    const Tensor& key_cache, const Tensor& value_cache, int32_t head_num, int32_t kv_head_num,
+                    int32_t head_size, float eps, void* stream) {
+    require_cuda(qkv, "rope qkv");
+    require_cuda(q_out, "rope q_out");
+    require_cuda(key_cache, "rope key cache");
+    require_cuda(value_cache, "rope value cache");
+    CHECK_EQ(key_cache.dims_size(), 4);  // [n_slots, kv_heads, max_seq, head_size]
+    const int32_t row = (head_num + 2 * kv_head_num) * head_size;
+    CHECK_EQ(qkv.size() % size_t(row), size_t(0));
+    const int32_t M = int32_t(qkv.size() / size_t(row));
+    CHECK_GE(pos.size(), size_t(M));
+    CHECK_GE(slot.size(), size_t(M));
+    KERNEL_OK(kuiper_qknorm_rope_kvwrite(qkv.ptr<float>(), q_norm.ptr<uint16_t>(), k_norm.ptr<uint16_t>(),
+                                         cos_cache.ptr<float>(), sin_cache.ptr<float>(), pos.ptr<int32_t>(),
+                                         slot.ptr<int32_t>(), M, head_num, kv_head_num, head_size, eps,
+                                         key_cache.get_dim(2), key_cache.get_dim(0), out_ptr<float>(q_out),
+                                         out_ptr<uint16_t>(key_cache), out_ptr<uint16_t>(value_cache), as_stream(stream)));
+}
+
+void mha_kernel_cu(const Tensor& query, const Tensor& key_cache, const Tensor& value_cache, const Tensor& seq_len,
+                   const Tensor& slot, const Tensor& output, int32_t head_num, int32_t kv_head_num, int32_t head_size,
+                   const Tensor& workspace, void* stream) {
+    require_cuda(query, "mha query");
+    require_cuda(output, "mha output");
+    require_cuda(key_cache, "mha key cache");
+    require_cuda(value_cache, "mha value cache");
+    CHECK_EQ(key_cache.dims_size(), 4);
+    const int32_t row = head_num * head_size;
+    CHECK_EQ(query.size() % size_t(row), size_t(0));
+    const int32_t M = int32_t(query.size() / size_t(row));
+    CHECK_EQ(output.size(), query.size());
+    KERNEL_OK(kuiper_flash_decode(query.ptr<float>(), key_cache.ptr<uint16_t>(), value_cache.ptr<uint16_t>(),
+                                  seq_len.ptr<int32_t>(), slot.ptr<int32_t>(), out_ptr<float>(output), M, head_num,
+                                  kv_head_num, head_size, key_cache.get_dim(2), key_cache.get_dim(0),
+                                  out_ptr<void>(workspace), workspace.byte_size(), as_stream(stream)));
+}
+
+void swiglu_kernel_cu(const Tensor& gate_up, const Tensor& output, void* stream) {
+    require_cuda(gate_up, "swiglu input");
+    require_cuda(output, "swiglu output");
+    CHECK_EQ(gate_up.size(), output.size() * 2);
+    const int32_t I = output.get_dim(output.dims_size() - 1);
+    KERNEL_OK(kuiper_swiglu_f32(gate_up.ptr<float>(), out_ptr<float>(output), int32_t(output.size() / size_t(I)), I,
+                                as_stream(stream)));
+}
+
+void emb_kernel_cu(const Tensor& tokens, const Tensor& table, const Tensor& output, int32_t vocab_size, void* stream) {
+    require_cuda(tokens, "embedding tokens");
+    require_cuda(table, "embedding table");
+    require_cuda(output, "embedding output");
+    const int32_t H = table.get_dim(1);
+    CHECK_EQ(output.size() % size_t(H), size_t(0));
+    const int32_t M = int32_t(output.size() / size_t(H));
+    CHECK_GE(tokens.size(), size_t(M));
+    KERNEL_OK(kuiper_embedding_bf16(tokens.ptr<int32_t>(), table.ptr<uint16_t>(), out_ptr<float>(output), M, H,
+                                    vocab_size, as_stream(stream)));
+}
+
+void argmax_kernel_cu(const Tensor& logits, const Tensor& next, void* stream) {
+    require_cuda(logits, "argmax logits");
+    require_cuda(next, "argmax output");
+    const int32_t V = logits.get_dim(logits.dims_size() - 1);
+    const int32_t M = int32_t(logits.size() / size_t(V));
+    CHECK_GE(next.size(), size_t(M));
+    KERNEL_OK(kuiper_argmax_f32(logits.ptr<float>(), out_ptr<int32_t>(next), M, V, as_stream(stream)));
+}
+
+template <typename Fn>
+Fn pick(base::DeviceType device_type, Fn cuda_fn, const char* name) {
+    if (device_type == base::DeviceType::DeviceCUDA) return cuda_fn;
+    LOG(FATAL) << "No " << name << " kernel for device type " << int(device_type)
+               << ": this engine has CUDA kernels only.";
+    return nullptr;
+}
+
+}  // namespace
+
+AddKernel get_add_kernel(base::DeviceType d) { return pick<AddKernel>(d, add_kernel_cu, "add"); }
+MatmulKernel get_matmul_kernel(base::DeviceType d) { return pick<MatmulKernel>(d, matmul_kernel_cu, "matmul"); }
+MatmulKernelQuant get_matmul_kernel_quant(base::DeviceType d) {
+    return pick<MatmulKernelQuant>(d, matmul_kernel_quant_cu, "quantised matmul");
+}
+RMSNormKernel get_rmsnorm_kernel(base::DeviceType d) { return pick<RMSNormKernel>(d, rmsnorm_kernel_cu, "rmsnorm"); }
+RoPEKernel get_rope_kernel(base::DeviceType d) { return pick<RoPEKernel>(d, rope_kernel_cu, "rope"); }
+MHAKernel get_mha_kernel(base::DeviceType d) { return pick<MHAKernel>(d, mha_kernel_cu, "mha"); }
+SwigluKernel get_swiglu_kernel(base::DeviceType d) { return pick<SwigluKernel>(d, swiglu_kernel_cu, "swiglu"); }
+EmbeddingKernel get_emb_kernel(base::DeviceType d) { return pick<EmbeddingKernel>(d, emb_kernel_cu, "embedding"); }
+ArgmaxKernel get_argmax_kernel(base::DeviceType d) { return pick<ArgmaxKernel>(d, argmax_kernel_cu, "argmax"); }
+
+size_t matmul_quant_workspace_bytes(int32_t M, int32_t K, int32_t N) { return kuiper_awq_gemv_workspace_bytes(M, K, N); }
+size_t mha_workspace_bytes(int32_t M, int32_t head_num, int32_t head_size, int32_t max_seq) {
+    return kuiper_flash_decode_workspace_bytes(M, head_num, head_size, max_seq);
+}
+
+}  // namespace kernel

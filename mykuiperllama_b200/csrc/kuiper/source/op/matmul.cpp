@@ -1,0 +1,81 @@
+// MatmulLayer: y = x . W for INT4-AWQ (dequant-fused GEMV) and bf16 weights.
+#include "op/matmul.h"
+
+#include "kernel/kernel_interface.h"
+
+namespace op {
+
+MatmulLayer::MatmulLayer(base::DeviceType device_type, int32_t dim0, int32_t dim1, bool is_quant_layer)
+    : LayerParam(device_type, LayerType::LayerMatmul, is_quant_layer, "Matmul"), dim0_(dim0), dim1_(dim1) {
+    reset_input_size(1);
+    reset_output_size(1);
+    reset_weights_size(is_quant_layer ? 2 : 1);
+    if (is_quant_layer) group_size_ = 128;
+}
+
+base::DataType MatmulLayer::weight_data_type(int32_t) const {
+    return is_quant_layer_ ? base::DataType::DataTypeInt32 : base::DataType::DataTypeBf16;
+}
+
+void MatmulLayer::set_residual(bool has_residual) {
+    has_residual_ = has_residual;
+    reset_input_size(has_residual ? 2 : 1);
+}
+
+void MatmulLayer::set_workspace(const tensor::Tensor& workspace) { workspace_ = workspace; }
+
+base::Status MatmulLayer::check() const {
+    const tensor::Tensor& x = get_input(0);
+    base::Status status = check_tensor(x, device_type_, data_type_);
+    if (!status) {
+        LOG(ERROR) << "The input tensor error in the matmul layer.";
+        return status;
+    }
+    if (x.size() % size_t(dim1_) != 0) return base::error::invalid_argument("The input width is not the layer's dim1.");
+    const size_t M = x.size() / size_t(dim1_);
+    status = check_tensor(get_output(0), device_type_, data_type_);
+    if (status && get_output(0).size() != M * size_t(dim0_))
+        status = base::error::invalid_argument("The output tensor has a wrong element count.");
+    if (!status) {
+        LOG(ERROR) << "The output tensor error in the matmul layer.";
+        return status;
+    }
+    if (has_residual_) {
+        status = check_tensor(get_input(1), device_type_, data_type_);
+        if (status && get_input(1).size() != M * size_t(dim0_))
+            status = base::error::invalid_argument("The residual tensor has a wrong element count.");
+        if (!status) return status;
+    }
+    if (is_quant_layer_) {
+        if (group_size_ <= 0 || dim1_ % group_size_ != 0)
+            return base::error::invalid_argument("The group size does not divide the input width.");
+        status = check_tensor_with_dim(get_weight(0), device_type_, base::DataType::DataTypeInt32, dim1_, dim0_ / 8);
+        if (!status) return status;
+        status = check_tensor_with_dim(get_weight(1), device_type_, base::DataType::DataTypeInt32, dim1_ / group_size_,
+                                       dim0_ / 8);
+        if (!status) return status;
+        status = check_tensor_with_dim(scales_, device_type_, base::DataType::DataTypeFp16, dim1_ / group_size_, dim0_);
+        if (!status) return status;
+    } else {
+        status = check_tensor_with_dim(get_weight(0), device_type_, base::DataType::DataTypeBf16, dim0_, dim1_);
+        if (!status) return status;
+    }
+    return base::error::success();
+}
+
+base::Status MatmulLayer::forward() {
+    base::Status status = check();
+    if (!status) return status;
+    if (device_type_ == base::DeviceType::DeviceCUDA) CHECK_NE(cuda_config_, nullptr);
+    if (is_quant_layer_) {
+        kernel::get_matmul_kernel_quant(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),
+                                                      has_residual_ ? &get_input(1) : nullptr, group_size_, act_mode_,
+                                                      workspace_, stream());
+    } else {
+        if (has_residual_) return base::error::function_not_implement("residual on a bf16 matmul");
+        kernel::get_matmul_kernel(device_type_)(get_input(0), get_weight(0), get_output(0), stream());
+    }
+    return base::error::success();
+}
+
+}  // namespace op

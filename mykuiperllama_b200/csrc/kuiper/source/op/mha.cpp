@@ -1,0 +1,59 @@
+// MultiHeadAttention: GQA flash-decoding over the KV cache.
+#include "op/mha.h"
+
+#include "kernel/kernel_interface.h"
+
+namespace op {
+
+MultiHeadAttention::MultiHeadAttention(base::DeviceType device_type, int32_t head_num, int32_t kv_head_num,
+                                       int32_t head_size)
+    : Layer(device_type, LayerType::LayerMHA, "MultiHead"),
+      head_num_(head_num), kv_head_num_(kv_head_num), head_size_(head_size) {
+    reset_input_size(3);
+    reset_output_size(1);
+}
+
+void MultiHeadAttention::set_cache(const tensor::Tensor& key_cache, const tensor::Tensor& value_cache) {
+    key_cache_ = key_cache;
+    value_cache_ = value_cache;
+}
+
+void MultiHeadAttention::set_workspace(const tensor::Tensor& workspace) { workspace_ = workspace; }
+
+base::Status MultiHeadAttention::check() const {
+    const int32_t row = head_num_ * head_size_;
+    base::Status status = check_tensor(get_input(0), device_type_, data_type_);
+    if (status && get_input(0).size() % size_t(row) != 0)
+        status = base::error::invalid_argument("The query tensor has a wrong width.");
+    if (!status) {
+        LOG(ERROR) << "The query tensor error in the mha layer.";
+        return status;
+    }
+    const size_t M = get_input(0).size() / size_t(row);
+    for (int i = 1; i <= 2; i++) {
+        status = check_tensor(get_input(i), device_type_, base::DataType::DataTypeInt32);
+        if (status && get_input(i).size() < M) status = base::error::invalid_argument("seq_len / slot tensor is too short.");
+        if (!status) return status;
+    }
+    status = check_tensor(get_output(0), device_type_, data_type_);
+    if (status && get_output(0).size() != get_input(0).size())
+        status = base::error::invalid_argument("The output tensor has a wrong element count.");
+    if (!status) return status;
+    for (const tensor::Tensor* c : {&key_cache_, &value_cache_}) {
+        status = check_tensor(*c, device_type_, base::DataType::DataTypeBf16);
+        if (status && (c->dims_size() != 4 || c->get_dim(1) != kv_head_num_ || c->get_dim(3) != head_size_))
+            status = base::error::invalid_argument("The KV cache has a wrong shape.");
+        if (!status) return status;
+    }
+    return base::error::success();
+}
+
+base::Status MultiHeadAttention::forward() {
+    base::Status status = check();
+    if (!status) return status;
+    kernel::get_mha_kernel(device_type_)(get_input(0), key_cache_, value_cache_, get_input(1), get_input(2),
+                                         get_output(0), head_num_, kv_head_num_, head_size_, workspace_, stream());
+    return base::error::success();
+}
+
+}  // namespace op

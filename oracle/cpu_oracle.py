@@ -267,14 +267,16 @@ class OracleModel:
         self._h = C.c_void_p(lib().orc_model_create(C.byref(c), _p(weights["embed"]), _p(weights["final_norm"]),
                                                     _p(weights["lm_head"]), arr))
 
-    def forward(self, tokens, pos, slot=None, acc_double=True, want_logits=True):
+    def forward(self, tokens, pos, slot=None, acc_double=True, want_logits=True, logit_rows=None):
+        """One pass over the rows; logits / greedy ids for the last ``logit_rows`` rows (default all)."""
         tokens = np.ascontiguousarray(tokens, np.int32)
         pos = np.ascontiguousarray(pos, np.int32)
         M = tokens.size
+        R = M if logit_rows is None else logit_rows
         slot = np.zeros(M, np.int32) if slot is None else np.ascontiguousarray(slot, np.int32)
-        logits = np.empty((M, self.cfg.vocab), np.float32) if want_logits else None
-        nxt = np.empty(M, np.int32)
-        lib().orc_model_forward(self._h, _p(tokens), _p(pos), _p(slot), M, int(acc_double),
+        logits = np.empty((R, self.cfg.vocab), np.float32) if want_logits else None
+        nxt = np.empty(R, np.int32)
+        lib().orc_model_forward(self._h, _p(tokens), _p(pos), _p(slot), M, int(acc_double), R,
                                 _p(logits) if want_logits else None, _p(nxt))
         return logits, nxt
 

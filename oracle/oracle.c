@@ -237,33 +237,39 @@ void orc_awq_gemv(const float* x, const int32_t* qweight, const int32_t* qzeros,
     float* xr = (float*)malloc((size_t)M * K * sizeof(float));
     ORC_CHECK(xr);
     for (int64_t i = 0; i < (int64_t)M * K; i++) xr[i] = round_act(x[i], act_round);
-    /* one task per packed word column: 8 outputs, dequantised on the fly */
+    /* one task per packed word column: 8 outputs; each weight is dequantised once and
+       applied to all M rows */
 #pragma omp parallel for schedule(static)
     for (int j = 0; j < NW; j++) {
-        for (int m = 0; m < M; m++) {
-            double accd[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            float accf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int g = 0; g < K / group; g++) {
-                uint32_t zw = (uint32_t)qzeros[(int64_t)g * NW + j];
-                float s[8];
-                int z[8];
-                for (int i = 0; i < 8; i++) {
-                    z[i] = (int)((zw >> (4 * i)) & 0xfu);
-                    s[i] = orc_f16_to_f32(scales_f16[(int64_t)g * N + 8 * j + ORD[i]]);
-                }
-                for (int k = g * group; k < (g + 1) * group; k++) {
-                    uint32_t w = (uint32_t)qweight[(int64_t)k * NW + j];
+        double* accd = (double*)calloc((size_t)M * 8, sizeof(double));
+        float* accf = (float*)calloc((size_t)M * 8, sizeof(float));
+        ORC_CHECK(accd && accf);
+        for (int g = 0; g < K / group; g++) {
+            uint32_t zw = (uint32_t)qzeros[(int64_t)g * NW + j];
+            float s[8];
+            int z[8];
+            for (int i = 0; i < 8; i++) {
+                z[i] = (int)((zw >> (4 * i)) & 0xfu);
+                s[i] = orc_f16_to_f32(scales_f16[(int64_t)g * N + 8 * j + ORD[i]]);
+            }
+            for (int k = g * group; k < (g + 1) * group; k++) {
+                uint32_t w = (uint32_t)qweight[(int64_t)k * NW + j];
+                float wv[8];
+                for (int i = 0; i < 8; i++) wv[i] = (float)((int)((w >> (4 * i)) & 0xfu) - z[i]) * s[i];
+                for (int m = 0; m < M; m++) {
                     float xv = xr[(int64_t)m * K + k];
-                    for (int i = 0; i < 8; i++) {
-                        float wv = (float)((int)((w >> (4 * i)) & 0xfu) - z[i]) * s[i];
-                        if (acc_double) accd[i] += (double)xv * (double)wv;
-                        else accf[i] += xv * wv;
-                    }
+                    if (acc_double)
+                        for (int i = 0; i < 8; i++) accd[m * 8 + i] += (double)xv * (double)wv[i];
+                    else
+                        for (int i = 0; i < 8; i++) accf[m * 8 + i] += xv * wv[i];
                 }
             }
-            for (int i = 0; i < 8; i++)
-                y[(int64_t)m * N + 8 * j + ORD[i]] = acc_double ? (float)accd[i] : accf[i];
         }
+        for (int m = 0; m < M; m++)
+            for (int i = 0; i < 8; i++)
+                y[(int64_t)m * N + 8 * j + ORD[i]] = acc_double ? (float)accd[m * 8 + i] : accf[m * 8 + i];
+        free(accd);
+        free(accf);
     }
     free(xr);
 }
@@ -469,7 +475,7 @@ const uint16_t* orc_model_kcache(const orc_model* m) { return m->kcache; }
 const uint16_t* orc_model_vcache(const orc_model* m) { return m->vcache; }
 
 void orc_model_forward(orc_model* mdl, const int32_t* tokens, const int32_t* pos, const int32_t* slot,
-                       int M, int acc_double, float* logits, int32_t* next) {
+                       int M, int acc_double, int logit_rows, float* logits, int32_t* next) {
     const orc_config* c = &mdl->cfg;
     int H = c->hidden, D = c->head_dim, Nq = c->n_q_heads, Nkv = c->n_kv_heads, I = c->inter;
     int QKV = (Nq + 2 * Nkv) * D;
@@ -508,12 +514,14 @@ void orc_model_forward(orc_model* mdl, const int32_t* tokens, const int32_t* pos
         orc_awq_gemv(act, w->down_qw, w->down_qz, w->down_s, proj, M, I, H, c->group, acc_double, c->act_round);
         orc_add(h, proj, h, (int64_t)M * H);
     }
-    if (logits || next) {
-        float* lg = logits ? logits : (float*)malloc(sizeof(float) * (size_t)M * c->vocab);
+    if ((logits || next) && logit_rows > 0) {
+        ORC_CHECK(logit_rows <= M);
+        int r0 = M - logit_rows; /* logits for the last logit_rows rows only */
+        float* lg = logits ? logits : (float*)malloc(sizeof(float) * (size_t)logit_rows * c->vocab);
         ORC_CHECK(lg);
-        orc_rmsnorm(h, mdl->final_norm, xn, M, H, c->eps);
-        orc_bf16_gemv(xn, mdl->lm_head, lg, M, H, c->vocab, acc_double);
-        if (next) orc_argmax(lg, M, c->vocab, next);
+        orc_rmsnorm(h + (size_t)r0 * H, mdl->final_norm, xn, logit_rows, H, c->eps);
+        orc_bf16_gemv(xn, mdl->lm_head, lg, logit_rows, H, c->vocab, acc_double);
+        if (next) orc_argmax(lg, logit_rows, c->vocab, next);
         if (!logits) free(lg);
     }
     free(h); free(xn); free(qkv); free(q); free(att); free(proj); free(gu); free(act); free(seq);

@@ -119,10 +119,11 @@ void orc_model_destroy(orc_model* m);
 /*
  * One forward pass over M tokens (tokens[m] at position pos[m] of sequence slot[m]);
  * rows are processed in order so a prompt chunk sees its own earlier tokens.
- * logits [M,V] fp32 (may be NULL), next [M] greedy ids (may be NULL).
+ * Logits are computed for the last logit_rows rows only: logits [logit_rows,V] fp32
+ * (may be NULL), next [logit_rows] greedy ids (may be NULL).
  */
 void orc_model_forward(orc_model* m, const int32_t* tokens, const int32_t* pos, const int32_t* slot,
-                       int M, int acc_double, float* logits, int32_t* next);
+                       int M, int acc_double, int logit_rows, float* logits, int32_t* next);
 /* copies of the bf16 caches for inspection: [L][max_batch][Nkv][max_seq][D] */
 const uint16_t* orc_model_kcache(const orc_model* m);
 const uint16_t* orc_model_vcache(const orc_model* m);
