@@ -216,7 +216,7 @@ awq_gemv_kernel(const GemvParams p) {
 #pragma unroll
         for (int r = 0; r < kBatch; r++)
 #pragma unroll
-            for (int m = 0; m < MT; m++) xv[r][m] = __ldg(p.x + size_t(m) * p.K + k0 + warp + (b * kBatch + r) * kWarps);
+            for (int m = 0; m < MT; m++) xv[r][m] = __ldcg(p.x + size_t(m) * p.K + k0 + warp + (b * kBatch + r) * kWarps);
 #pragma unroll
         for (int r = 0; r < kBatch; r++) {
             acc.row(w[r], z, xv[r]);
@@ -293,7 +293,7 @@ awq_gemv_kernel(const GemvParams p) {
         for (int m = 0; m < MT; m++) {
             float4 s = sum[m];
             if (p.residual) {
-                float4 r = *reinterpret_cast<const float4*>(p.residual + size_t(m) * p.N + col);
+                float4 r = __ldcg(reinterpret_cast<const float4*>(p.residual + size_t(m) * p.N + col));
                 s.x += r.x; s.y += r.y; s.z += r.z; s.w += r.w;
             }
             *reinterpret_cast<float4*>(p.y + size_t(m) * p.N + col) = s;
@@ -337,6 +337,7 @@ __global__ void awq_gemv_generic_kernel(const float* x, const int32_t* qw, const
 
 int g_force_rows = 0;  // tuning override: rows per thread (4, 8 or 16); 0 = heuristic
 int g_force_math = -1;
+int g_force_impl = 0;  // 0: persistent TMA kernel where it applies; 1: always the register-staged kernel
 
 int pick_rows(int K, int N) {
     if (g_force_rows == 4 || g_force_rows == 8 || g_force_rows == 16) return g_force_rows;
@@ -366,7 +367,7 @@ int launch(const GemvParams& p, cudaStream_t stream) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_pdl_enabled ? 1 : 0;
     cudaError_t err = cudaLaunchKernelEx(&cfg, kern, p);
     if (err != cudaSuccess) {
         set_error("awq_gemv launch failed: %s", cudaGetErrorString(err));
@@ -399,7 +400,14 @@ int launch_mode(const GemvParams& p, int mode, int rows, cudaStream_t stream) {
 void awq_gemv_set_tuning(const char* key, int value) {
     if (!strcmp(key, "gemv_rows")) g_force_rows = value;
     if (!strcmp(key, "gemv_math")) g_force_math = value;
+    if (!strcmp(key, "gemv_impl")) g_force_impl = value;
 }
+
+// persistent TMA-fed variant (awq_gemv_tma.cu)
+size_t awq_gemv_tma_workspace_bytes(int K, int N);
+bool awq_gemv_tma_supported(int K, int N);
+int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
+                        const float* residual, int rows, int K, int N, void* workspace, cudaStream_t stream);
 
 }  // namespace kuiper
 
@@ -411,7 +419,9 @@ extern "C" size_t kuiper_awq_gemv_workspace_bytes(int M, int K, int N) {
     const size_t slices = size_t(K) / 32;
     const size_t partial = slices * 2 * size_t(N) * sizeof(float);
     const size_t counters = size_t((N + kTileCols - 1) / kTileCols) * sizeof(int);
-    return ((counters + 255) / 256) * 256 + partial;
+    const size_t legacy = ((counters + 255) / 256) * 256 + partial;
+    const size_t tma = awq_gemv_tma_workspace_bytes(K, N);
+    return legacy > tma ? legacy : tma;
 }
 
 extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
@@ -434,6 +444,25 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
                 residual ? residual + size_t(m) * N : nullptr, K, N);
         }
         return launch_status("awq_gemv_generic");
+    }
+
+    KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(qweight) & 15) == 0 && (reinterpret_cast<uintptr_t>(qzeros) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(scales) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(x) & 3) == 0 && (!residual || (reinterpret_cast<uintptr_t>(residual) & 15) == 0),
+                   "awq_gemv: tensors must be 16-byte aligned");
+    const bool want_tma = g_force_impl == 0 && g_force_math < 0 && act_mode == KUIPER_ACT_FP16 && awq_gemv_tma_supported(K, N);
+    if (want_tma) {
+        KUIPER_REQUIRE(workspace != nullptr && workspace_bytes >= awq_gemv_tma_workspace_bytes(K, N),
+                       "awq_gemv: workspace of %zu bytes is too small", workspace_bytes);
+        KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, "awq_gemv: workspace must be 16-byte aligned");
+        for (int m0 = 0; m0 < M;) {
+            const int mt = (M - m0 >= 2) ? 2 : 1;
+            int rc = awq_gemv_tma_launch(x + size_t(m0) * K, qweight, qzeros, scales, y + size_t(m0) * N,
+                                         residual ? residual + size_t(m0) * N : nullptr, mt, K, N, workspace, st);
+            if (rc != KUIPER_OK) return rc;
+            m0 += mt;
+        }
+        return KUIPER_OK;
     }
 
     const int rows = pick_rows(K, N);

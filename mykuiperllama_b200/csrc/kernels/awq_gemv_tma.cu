@@ -1,0 +1,501 @@
+// Persistent, TMA-fed INT4-AWQ GEMV for sm_100a (decode, one or two token rows).
+//
+// The weight [K, N/8] int32 is cut into units of 32 rows x 1024 columns (16 KB).  Units
+// are numbered column-tile major / K minor and dealt out in contiguous runs to a grid of
+// one CTA per SM, so every SM streams the same number of bytes (+-1 unit) whatever the
+// matrix shape.  Inside a CTA one producer thread keeps a ring of 16 KB shared-memory
+// stages full with cp.async.bulk.tensor (2-D tensor map over the native AWQ layout,
+// box 32 rows x 128 words, out-of-range columns zero filled), completion tracked by
+// mbarriers; 16 consumer warps drain it.  The producer starts before the programmatic
+// dependent-launch wait, so the weight stream of this GEMV overlaps the previous kernel.
+//
+// Consumer thread (cg, rg): columns 16*cg .. 16*cg+15 of the tile (two packed words, one
+// 8-byte shared-memory read per row), rows rg, rg+8, rg+16, rg+24 of each unit.  The
+// activation vector lives in shared memory as fp16; products (q - z) * x are exact and
+// are accumulated in fp32 (fma.rn.f32.f16); the fp16 group scale is applied when a
+// 128-row group ends.  When a CTA's run leaves a column tile the 8 row groups are reduced
+// through shared memory and the CTA's partial row goes to the workspace slot
+// (cta + tile); the last CTA to arrive at a tile adds the slots in order (deterministic
+// result), adds the residual and writes y.
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit failed polls the thread records
+// an error code in the workspace and leaves the loop.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace kuiper {
+namespace {
+
+constexpr int kConsumerWarps = 16;
+constexpr int kConsumers = kConsumerWarps * 32;   // 512
+constexpr int kThreadsTma = kConsumers + 32;      // + producer warp
+constexpr int kUnitRows = 32;
+constexpr int kTileWords = 128;                   // 1024 columns
+constexpr int kTileColsTma = kTileWords * 8;
+constexpr int kStageBytes = kUnitRows * kTileWords * 4;  // 16 KB
+constexpr uint32_t kMagicTma = 0x64006400u;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+struct TmaGemvParams {
+    const float* x;        // [MT, K]
+    float* y;              // [MT, N]
+    const float* residual; // [MT, N] or null
+    const uint2* qz;       // zeros, 8-byte pairs: [K/128][N/16]
+    const __half* scales;  // [K/128][N]
+    float* partial;        // [slots][MT][1024]
+    int* counters;         // [tiles]
+    int* error;            // one word, 0 = ok
+    int K, N, tiles, upt;  // upt = units per tile = K / 32
+    long long U;           // total units
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// bounded wait: false after kSpinLimit unsuccessful polls
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kSpinLimit; spin++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
+
+__device__ __forceinline__ float fma_f16_tma(uint16_t a, uint16_t b, float c) {
+    float d;
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(a), "h"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ __half2 u2h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+__device__ __forceinline__ uint32_t h22u(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+
+// (1024 + z) pairs for the low nibbles, -(64 + z) pairs for the high nibbles of one zero word
+struct ZeroPairs {
+    __half2 lo0, hi0, lo1, hi1;
+};
+__device__ __forceinline__ ZeroPairs make_zero_pairs(uint32_t zw) {
+    ZeroPairs z;
+    const __half2 neg_sixteenth = __floats2half2_rn(-0.0625f, -0.0625f);
+    z.lo0 = u2h2((zw & 0x000f000fu) | kMagicTma);
+    z.hi0 = __hmul2(u2h2((zw & 0x00f000f0u) | kMagicTma), neg_sixteenth);
+    const uint32_t z8 = zw >> 8;
+    z.lo1 = u2h2((z8 & 0x000f000fu) | kMagicTma);
+    z.hi1 = __hmul2(u2h2((z8 & 0x00f000f0u) | kMagicTma), neg_sixteenth);
+    return z;
+}
+
+// acc[m][0..7] += x[m] * (q - z) for the 8 columns of one packed word
+template <int MT>
+__device__ __forceinline__ void word_fma(uint32_t w, const ZeroPairs& z, const uint16_t (&xh)[MT], float (*acc)[16], int base) {
+    const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+    const uint32_t w8 = w >> 8;
+    const uint32_t d[4] = {
+        h22u(__hsub2(u2h2((w & 0x000f000fu) | kMagicTma), z.lo0)),
+        h22u(__hfma2(u2h2((w & 0x00f000f0u) | kMagicTma), sixteenth, z.hi0)),
+        h22u(__hsub2(u2h2((w8 & 0x000f000fu) | kMagicTma), z.lo1)),
+        h22u(__hfma2(u2h2((w8 & 0x00f000f0u) | kMagicTma), sixteenth, z.hi1)),
+    };
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint16_t a = uint16_t(d[i] & 0xffffu), b = uint16_t(d[i] >> 16);
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            acc[m][base + 2 * i] = fma_f16_tma(a, xh[m], acc[m][base + 2 * i]);
+            acc[m][base + 2 * i + 1] = fma_f16_tma(b, xh[m], acc[m][base + 2 * i + 1]);
+        }
+    }
+}
+
+template <int MT, int STAGES>
+__global__ void __launch_bounds__(kThreadsTma, 1)
+awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    // TMA destinations want 128-byte alignment; the launch reserves 128 spare bytes for this
+    unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    unsigned char* stages = smem;                                             // STAGES x 16 KB
+    float4* red = reinterpret_cast<float4*>(smem + STAGES * kStageBytes);      // [8][MT][256] float4
+    uint16_t* xh = reinterpret_cast<uint16_t*>(smem + STAGES * kStageBytes + 8 * MT * 1024 * 4);  // [MT][K] fp16
+    __shared__ uint64_t full_bar[STAGES];
+    __shared__ uint64_t empty_bar[STAGES];
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const long long C = gridDim.x;
+    const long long u0 = (long long)blockIdx.x * p.U / C;
+    const long long u1 = (long long)(blockIdx.x + 1) * p.U / C;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kConsumerWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            int t = int(u0 / p.upt), kb = int(u0 - (long long)t * p.upt);
+            uint32_t it = 0;
+            bool ok = true;
+            for (long long u = u0; u < u1; u++, it++) {
+                const int s = it % STAGES;
+                const uint32_t parity = (it / STAGES) & 1u;
+                if (!mbar_wait(&empty_bar[s], parity ^ 1u)) {
+                    atomicExch(p.error, 1);
+                    ok = false;
+                    break;
+                }
+                mbar_expect_tx(&full_bar[s], kStageBytes);
+                tma_load_2d(stages + s * kStageBytes, &tmap, t * kTileWords, kb * kUnitRows, &full_bar[s]);
+                if (++kb == p.upt) { kb = 0; t++; }
+            }
+            if (!ok) {
+                // give copies already issued a bounded chance to land before the CTA goes away
+                for (int s = 0; s < STAGES; s++) mbar_wait(&full_bar[s], 0);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int cg = tid & 63;   // 16-column group inside the tile
+    const int rg = tid >> 6;   // row group 0..7
+    pdl_wait();
+    for (int i = tid; i < MT * p.K; i += kConsumers) xh[i] = __half_as_ushort(__float2half_rn(__ldcg(p.x + i)));
+    consumer_sync();
+
+    int t = int(u0 / p.upt), kb = int(u0 - (long long)t * p.upt);
+    const int groups = p.K >> 7;
+    const int zstride = p.N >> 4;  // uint2 per zero row
+
+    // raw zero / scale words of a (tile, group) for this thread's 16 columns; zeros outside N
+    auto load_consts = [&](int tile, int g, uint2& zraw, uint4& s0, uint4& s1) {
+        const int col = tile * kTileColsTma + cg * 16;
+        if (col < p.N) {
+            zraw = __ldg(p.qz + size_t(g) * zstride + (col >> 4));
+            const uint4* sp = reinterpret_cast<const uint4*>(p.scales + size_t(g) * p.N + col);
+            s0 = __ldg(sp);
+            s1 = __ldg(sp + 1);
+        } else {
+            zraw = make_uint2(0, 0);
+            s0 = make_uint4(0, 0, 0, 0);
+            s1 = make_uint4(0, 0, 0, 0);
+        }
+    };
+
+    uint2 z_next = make_uint2(0, 0);
+    uint4 sa_next = make_uint4(0, 0, 0, 0), sb_next = sa_next, sa_cur, sb_cur;
+    load_consts(t, kb >> 2, z_next, sa_cur, sb_cur);
+    ZeroPairs z0 = make_zero_pairs(z_next.x), z1 = make_zero_pairs(z_next.y);
+    auto prefetch_following = [&](int tile, int g) {
+        // the group after (tile, g) in unit order, if this CTA's run reaches it
+        int ng = g + 1, nt = tile;
+        if (ng == groups) { ng = 0; nt++; }
+        if ((long long)nt * p.upt + ng * 4 < u1) load_consts(nt, ng, z_next, sa_next, sb_next);
+    };
+    prefetch_following(t, kb >> 2);
+
+    float acc_g[MT][16], acc_t[MT][16];
+#pragma unroll
+    for (int m = 0; m < MT; m++)
+#pragma unroll
+        for (int c = 0; c < 16; c++) { acc_g[m][c] = 0.f; acc_t[m][c] = 0.f; }
+
+    uint32_t it = 0;
+    bool dead = false;  // a wait ran out: keep walking the barriers so nobody hangs, the result is void
+    for (long long u = u0; u < u1; u++, it++) {
+        const int s = it % STAGES;
+        const uint32_t parity = (it / STAGES) & 1u;
+        if (!dead && !mbar_wait(&full_bar[s], parity)) {
+            atomicExch(p.error, 2);
+            dead = true;
+        }
+        const unsigned char* sp = stages + s * kStageBytes + rg * 512 + cg * 8;
+        uint2 w[4];
+        uint16_t xv[4][MT];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            w[i] = *reinterpret_cast<const uint2*>(sp + i * 8 * 512);
+#pragma unroll
+            for (int m = 0; m < MT; m++) xv[i][m] = xh[m * p.K + kb * kUnitRows + rg + 8 * i];
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);  // the stage is in registers now
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            word_fma<MT>(w[i].x, z0, xv[i], acc_g, 0);
+            word_fma<MT>(w[i].y, z1, xv[i], acc_g, 8);
+        }
+
+        const bool group_end = (kb & 3) == 3;
+        const bool run_end = (u + 1 == u1);
+        const bool tile_end = (kb + 1 == p.upt);
+        if (group_end || run_end) {
+            // apply the group's fp16 scales once
+            const uint32_t sraw[8] = {sa_cur.x, sa_cur.y, sa_cur.z, sa_cur.w, sb_cur.x, sb_cur.y, sb_cur.z, sb_cur.w};
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const float2 sc = __half22float2(u2h2(sraw[c]));
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    acc_t[m][2 * c] = fmaf(acc_g[m][2 * c], sc.x, acc_t[m][2 * c]);
+                    acc_t[m][2 * c + 1] = fmaf(acc_g[m][2 * c + 1], sc.y, acc_t[m][2 * c + 1]);
+                    acc_g[m][2 * c] = 0.f;
+                    acc_g[m][2 * c + 1] = 0.f;
+                }
+            }
+            if (!run_end) {
+                // rotate in the constants of the next group and start fetching the one after
+                z0 = make_zero_pairs(z_next.x);
+                z1 = make_zero_pairs(z_next.y);
+                sa_cur = sa_next;
+                sb_cur = sb_next;
+                int ng = (kb >> 2) + 1, nt = t;
+                if (ng == groups) { ng = 0; nt++; }
+                prefetch_following(nt, ng);
+            }
+        }
+
+        if (tile_end || run_end) {
+            // ---- this CTA's contribution to column tile t is complete: reduce the 8 row groups
+#pragma unroll
+            for (int m = 0; m < MT; m++)
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    red[(rg * MT + m) * 256 + cg * 4 + ((j + (cg >> 1)) & 3)] =
+                        make_float4(acc_t[m][4 * j], acc_t[m][4 * j + 1], acc_t[m][4 * j + 2], acc_t[m][4 * j + 3]);
+#pragma unroll
+            for (int m = 0; m < MT; m++)
+#pragma unroll
+                for (int c = 0; c < 16; c++) acc_t[m][c] = 0.f;
+            consumer_sync();
+
+            // contributors of this tile: CTAs owning its first and last unit
+            const long long first_u = (long long)t * p.upt, last_u = first_u + p.upt - 1;
+            const int c_first = int(((first_u + 1) * C - 1) / p.U);
+            const int c_last = int(((last_u + 1) * C - 1) / p.U);
+            const int n_contrib = c_last - c_first + 1;
+
+            const bool worker = tid < 256 * MT;
+            const int m = tid >> 8, f = tid & 255;  // row and float4 index owned in the epilogue
+            const int fcg = f >> 2, fj = f & 3;
+            const int col = t * kTileColsTma + f * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (worker) {
+#pragma unroll
+                for (int r = 0; r < 8; r++) {
+                    const float4 a = red[(r * MT + m) * 256 + fcg * 4 + ((fj + (fcg >> 1)) & 3)];
+                    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                }
+            }
+            bool finish = true;  // whether this CTA writes y for the tile
+            if (n_contrib > 1) {
+                if (worker)
+                    *reinterpret_cast<float4*>(p.partial + (size_t(blockIdx.x + t) * MT + m) * kTileColsTma + f * 4) = v;
+                __threadfence();
+                consumer_sync();
+                if (tid == 0) {
+                    const int prev = atomicAdd(p.counters + t, 1);
+                    s_last = (prev == n_contrib - 1);
+                    if (s_last) p.counters[t] = 0;
+                }
+                consumer_sync();
+                finish = s_last != 0;
+                if (finish) {
+                    __threadfence();
+                    if (worker) {
+                        v = make_float4(0.f, 0.f, 0.f, 0.f);
+                        for (int c = c_first; c <= c_last; c++) {
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(
+                                p.partial + (size_t(c + t) * MT + m) * kTileColsTma + f * 4));
+                            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                        }
+                    }
+                }
+            }
+            if (finish && worker && col < p.N) {
+                if (p.residual) {
+                    const float4 r = __ldcg(reinterpret_cast<const float4*>(p.residual + size_t(m) * p.N + col));
+                    v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+                }
+                *reinterpret_cast<float4*>(p.y + size_t(m) * p.N + col) = v;
+            }
+            consumer_sync();  // red is reused by the next tile
+        }
+        if (++kb == p.upt) { kb = 0; t++; }
+    }
+}
+
+// ---------------------------------------------------------------- host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    int K, N;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && K == o.K && N == o.N; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ (size_t(k.K) * 1000003u) ^ (size_t(k.N) * 8191u);
+    }
+};
+
+// tensor map of a weight matrix: inner dimension N/8 words, outer K rows, box 128 x 32
+bool get_tensor_map(const int32_t* qweight, int K, int N, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{qweight, K, N};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cuuint64_t(N / 8), cuuint64_t(K)};
+    const cuuint64_t strides[1] = {cuuint64_t(N / 8) * 4};
+    const cuuint32_t box[2] = {kTileWords, kUnitRows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap map;
+    CUresult rc = fn(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<int32_t*>(qweight), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return false;
+    if (cache.size() > 16384) cache.clear();
+    cache.emplace(key, map);
+    *out = map;
+    return true;
+}
+
+int g_sm_count = 0;
+int sm_count() {
+    if (g_sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    return g_sm_count;
+}
+
+template <int MT, int STAGES>
+int launch_tma(const CUtensorMap& map, const TmaGemvParams& p, int ctas, cudaStream_t stream) {
+    auto kern = awq_gemv_tma_kernel<MT, STAGES>;
+    const size_t smem = 128 + size_t(STAGES) * kStageBytes + size_t(8) * MT * 1024 * 4 + size_t(MT) * p.K * 2;
+    static size_t configured = 0;
+    if (configured < smem) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+            set_error("awq_gemv_tma: cannot reserve %zu bytes of shared memory", smem);
+            return KUIPER_INTERNAL_ERROR;
+        }
+        configured = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas, 1, 1);
+    cfg.blockDim = dim3(kThreadsTma, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl_enabled ? 1 : 0;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, kern, map, p);
+    if (err != cudaSuccess) {
+        set_error("awq_gemv_tma launch failed: %s", cudaGetErrorString(err));
+        return KUIPER_INTERNAL_ERROR;
+    }
+    return KUIPER_OK;
+}
+
+}  // namespace
+
+// Workspace layout of the TMA kernel: [counters: tiles ints][error word][partial slots].
+size_t awq_gemv_tma_workspace_bytes(int K, int N) {
+    const size_t tiles = size_t(N + kTileColsTma - 1) / kTileColsTma;
+    const size_t head = ((tiles + 1) * sizeof(int) + 255) / 256 * 256;
+    const size_t slots = size_t(sm_count()) + tiles;  // slot index = cta + tile
+    return head + slots * 2 * kTileColsTma * sizeof(float);
+}
+
+bool awq_gemv_tma_supported(int K, int N) {
+    return N % 32 == 0 && K % 128 == 0 && K <= 16384 && encode_fn() != nullptr;
+}
+
+// rows: 1 or 2 token rows starting at x / y / residual
+int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
+                        const float* residual, int rows, int K, int N, void* workspace, cudaStream_t stream) {
+    CUtensorMap map;
+    if (!get_tensor_map(qweight, K, N, &map)) {
+        set_error("awq_gemv_tma: tensor map encoding failed");
+        return KUIPER_INTERNAL_ERROR;
+    }
+    TmaGemvParams p;
+    p.x = x;
+    p.y = y;
+    p.residual = residual;
+    p.qz = reinterpret_cast<const uint2*>(qzeros);
+    p.scales = reinterpret_cast<const __half*>(scales);
+    p.K = K;
+    p.N = N;
+    p.tiles = (N + kTileColsTma - 1) / kTileColsTma;
+    p.upt = K / kUnitRows;
+    p.U = (long long)p.tiles * p.upt;
+    const size_t head = ((size_t(p.tiles) + 1) * sizeof(int) + 255) / 256 * 256;
+    p.counters = reinterpret_cast<int*>(workspace);
+    p.error = p.counters + p.tiles;
+    p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + head);
+    long long ctas = sm_count();
+    if (ctas > p.U) ctas = p.U;
+    if (rows == 2) return launch_tma<2, 6>(map, p, int(ctas), stream);
+    return launch_tma<1, 8>(map, p, int(ctas), stream);
+}
+
+}  // namespace kuiper

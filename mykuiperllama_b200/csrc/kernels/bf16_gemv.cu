@@ -96,7 +96,7 @@ int launch(const float* x, const uint16_t* W, float* y, int K, int N, cudaStream
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_pdl_enabled ? 1 : 0;
     cudaError_t err = cudaLaunchKernelEx(&cfg, kern, x, W, y, K, N);
     if (err != cudaSuccess) {
         set_error("bf16_gemv launch failed: %s", cudaGetErrorString(err));

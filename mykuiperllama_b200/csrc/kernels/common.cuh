@@ -11,6 +11,9 @@
 
 namespace kuiper {
 
+// tuning: 0 launches every kernel without the programmatic-dependent-launch attribute
+extern int g_pdl_enabled;
+
 // thread-local text behind kuiper_last_error()
 void set_error(const char* fmt, ...);
 

@@ -10,6 +10,8 @@
 
 namespace kuiper {
 
+int g_pdl_enabled = 1;
+
 static thread_local char g_error[512] = "";
 
 void set_error(const char* fmt, ...) {
@@ -200,6 +202,7 @@ extern "C" const char* kuiper_last_error(void) { return g_error; }
 
 extern "C" int kuiper_set_tuning(const char* key, int value) {
     if (!key) return KUIPER_INVALID_ARGUMENT;
+    if (!strcmp(key, "pdl")) g_pdl_enabled = value;
     awq_gemv_set_tuning(key, value);
     flash_decode_set_tuning(key, value);
     return KUIPER_OK;

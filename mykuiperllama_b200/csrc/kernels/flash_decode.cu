@@ -315,7 +315,7 @@ extern "C" int kuiper_flash_decode(const float* q, const uint16_t* kcache, const
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g_pdl_enabled ? 1 : 0;
     cudaError_t err;
     switch (R) {
         case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<1>, p); break;
