@@ -413,16 +413,79 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- kernel microbenchmarks
+def run_gemv_micro(args):
+    """INT4-AWQ GEMV alone (config 1 of the workload list and the model-sized shapes): M=1, distinct weight
+    matrices totalling more than L2 are visited in turn inside one CUDA graph, so every launch streams from HBM."""
+    import torch
+    from mykuiperllama_b200 import capi
+    torch.cuda.set_device(0)
+    K, N = (int(v) for v in args.shape.lower().split("x"))
+    if args.gemv_impl is not None:
+        capi.set_tuning("gemv_impl", args.gemv_impl)
+    per = int4_bytes(K, N) + 4 * K + 4 * N
+    n = args.mats or max(2, min(256, (512 << 20) // per))
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0)
+    qw = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), dtype=torch.int32, device="cuda", generator=gen) for _ in range(n)]
+    qz = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 128, N // 8), dtype=torch.int32, device="cuda", generator=gen) for _ in range(n)]
+    sc = [(torch.rand((K // 128, N), device="cuda", generator=gen) * 0.018 + 0.002).half() for _ in range(n)]
+    x = torch.randn((1, K), device="cuda", generator=gen)
+    y = torch.empty((1, N), device="cuda")
+    ws = capi.awq_gemv_workspace(1, K, N)
+
+    def sweep():
+        for i in range(n):
+            capi.awq_gemv(x, qw[i], qz[i], sc[i], workspace=ws, out=y)
+
+    for _ in range(args.warmup):
+        sweep()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        sweep()
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    with ClockSampler(0) as clocks:
+        for _ in range(args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+    ms = float(np.median(times))
+    gbs = per * n / (ms * 1e-3) / 1e9
+    peak, kind = measured_peak_gbs()
+    print(json.dumps({
+        "metric": "INT4-AWQ GEMV HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 weights (AWQ g128), fp16 x operand, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"single INT4-AWQ GEMV M=1 K={K} N={N} g128", "distinct_matrices": n,
+                   "l2_policy": f"{n} matrices ({per * n >> 20} MiB) visited in turn: larger than L2"},
+        "roofline": {"bound": "hbm", "kernel": "awq_gemv", "achieved": gbs, "peak": peak, "peak_kind": kind, "unit": "GB/s",
+                     "frac": gbs / peak, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS, "traffic": None,
+                     "avg_us_per_launch": ms * 1e3 / n, "avg_bytes_per_launch": per},
+        "gpu_launches": n * args.steps, "clocks": clocks.summary()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["gemv"])
+    ap.add_argument("--shape", default="2048x2048", help="KxN of the gemv microbenchmark")
+    ap.add_argument("--mats", type=int, default=0, help="distinct weight matrices in the gemv microbenchmark (0 = 512 MiB worth)")
+    ap.add_argument("--gemv-impl", type=int, default=None, help="0 persistent TMA kernel, 1 register-staged kernel")
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "engine":
         args.warmup = 3
+    if args.workload == "gemv":
+        run_gemv_micro(args)
+        return
     cfg, prompt_len, _, _, desc = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

@@ -77,6 +77,10 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         c.hidden_dim % (c.tp_size * c.group_size) || c.dim % c.group_size || c.max_rows < c.max_batch)
         return base::error::invalid_argument("model dimensions do not divide (heads / tp / group / rows)");
 
+    int n_devices = 0;
+    if (cudaGetDeviceCount(&n_devices) != cudaSuccess || n_devices == 0)
+        return base::error::internal_error("no CUDA device is visible: the engine has no CPU path");
+
     device_type_ = device_type;
     cuda_config_ = std::make_shared<kernel::CudaConfig>();
     cuda_config_->create();
