@@ -87,6 +87,18 @@ KUIPER_API int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
                         int M, int K, int N, int group, int act_mode,
                         void* workspace, size_t workspace_bytes, kuiper_stream_t stream);
 
+/*
+ * y[M,N] += x[M,K] . dequant(qweight): the engine's fast path.  The caller guarantees that y already
+ * holds the addend (the residual stream, or zeros); partial rows are added with vector float
+ * reductions, so no workspace is needed and there is no ordered combine at the end, at the price of
+ * a summation order (last bits) that can differ from run to run.  Needs N % 32 == 0.
+ */
+KUIPER_API int kuiper_awq_gemv_accum_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
+                                         const uint16_t* scales, float* y, int M, int K, int N, int group,
+                                         kuiper_stream_t stream);
+/* health check (synchronises): 5 if a bounded wait inside the pipelined GEMV ever ran out on this device */
+KUIPER_API int kuiper_awq_gemv_status(void);
+
 /* ---- BF16 GEMV (lm_head): W bf16 [N, K], y[M,N] = x[M,K] . W^T ---- */
 KUIPER_API int kuiper_bf16_gemv_f32(const float* x, const uint16_t* W, float* y, int M, int K, int N,
                          kuiper_stream_t stream);
@@ -102,13 +114,14 @@ KUIPER_API int kuiper_rmsnorm_f32(const float* x, const uint16_t* w, float* y, i
  * (half-split pairing (i, i+D/2)); pos[M], slot[M] int32 on the device.
  * q_out [M, Nq, D] fp32; k, v rounded to bf16 into cache[(slot*Nkv + h)*max_seq + pos][D];
  * the caches hold n_slots sequences; pos and slot are clamped into range on the device.
- * D must be 128.
+ * D must be 128.  clear_input != 0 zeroes qkv after it has been read (the buffer is then
+ * ready for the next kuiper_awq_gemv_accum_f32 into it).
  */
-KUIPER_API int kuiper_qknorm_rope_kvwrite(const float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
+KUIPER_API int kuiper_qknorm_rope_kvwrite(float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
                                const float* cos_t, const float* sin_t, const int32_t* pos,
                                const int32_t* slot, int M, int Nq, int Nkv, int D, float eps,
                                int max_seq, int n_slots, float* q_out, uint16_t* kcache,
-                               uint16_t* vcache, kuiper_stream_t stream);
+                               uint16_t* vcache, int clear_input, kuiper_stream_t stream);
 
 /* ---- GQA flash-decoding: placeholder kuiper/include/op/mha.h:1-11 ---- */
 /*
@@ -125,8 +138,8 @@ KUIPER_API int kuiper_flash_decode(const float* q, const uint16_t* kcache, const
                         void* workspace, size_t workspace_bytes, kuiper_stream_t stream);
 
 /* ---- SwiGLU: placeholder kuiper/include/op/swiglu.h:1-10 ---- */
-/* out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]; gate_up is [M, 2I] */
-KUIPER_API int kuiper_swiglu_f32(const float* gate_up, float* out, int M, int I, kuiper_stream_t stream);
+/* out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]; gate_up is [M, 2I]; clear_input != 0 zeroes gate_up afterwards */
+KUIPER_API int kuiper_swiglu_f32(float* gate_up, float* out, int M, int I, int clear_input, kuiper_stream_t stream);
 
 /* ---- embedding gather: placeholder kuiper/include/op/embedding.h:1-10 ---- */
 KUIPER_API int kuiper_embedding_bf16(const int32_t* tokens, const uint16_t* table, float* out, int M, int H,

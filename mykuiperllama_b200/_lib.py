@@ -38,13 +38,15 @@ KERNEL_API = {
     "kuiper_awq_gemv_workspace_bytes": (_sz, [_i32, _i32, _i32]),
     "kuiper_workspace_init": (_i32, [_vp, _sz, _vp]),
     "kuiper_awq_gemv_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
+    "kuiper_awq_gemv_accum_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "kuiper_awq_gemv_status": (_i32, []),
     "kuiper_bf16_gemv_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_rmsnorm_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _vp]),
     "kuiper_qknorm_rope_kvwrite": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _i32,
-                                          _vp, _vp, _vp, _vp]),
+                                          _vp, _vp, _vp, _i32, _vp]),
     "kuiper_flash_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32]),
     "kuiper_flash_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
-    "kuiper_swiglu_f32": (_i32, [_vp, _vp, _i32, _i32, _vp]),
+    "kuiper_swiglu_f32": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_embedding_bf16": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_argmax_f32": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "kuiper_decode_advance": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),

@@ -75,6 +75,20 @@ def awq_gemv(x, qweight, qzeros, scales, workspace=None, residual=None, out=None
     return out
 
 
+def awq_gemv_accum(x, qweight, qzeros, scales, y, group=128):
+    """y += x . W (y holds the addend); returns y."""
+    _dev(x, qweight, qzeros, scales, y)
+    M, K = x.shape
+    N = qweight.shape[1] * 8
+    check(kernels().kuiper_awq_gemv_accum_f32(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(y), M, K, N, group,
+                                              _stream()))
+    return y
+
+
+def awq_gemv_status() -> None:
+    check(kernels().kuiper_awq_gemv_status())
+
+
 def bf16_gemv(x, W, out=None):
     _dev(x, W, out)
     M, K = x.shape
@@ -92,7 +106,7 @@ def rmsnorm(x, w, eps=1e-6, out=None):
     return out
 
 
-def qknorm_rope_kvwrite(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, Nq, Nkv, D, eps, kcache, vcache):
+def qknorm_rope_kvwrite(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, Nq, Nkv, D, eps, kcache, vcache, clear_input=False):
     """kcache / vcache: [n_slots, Nkv, max_seq, D] bf16, updated in place; returns q [M, Nq, D]."""
     _dev(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, kcache, vcache)
     M = qkv.shape[0]
@@ -100,7 +114,7 @@ def qknorm_rope_kvwrite(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, Nq, Nk
     q = torch.empty((M, Nq, D), dtype=torch.float32, device=qkv.device)
     check(kernels().kuiper_qknorm_rope_kvwrite(_ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_t), _ptr(sin_t),
                                                _ptr(pos), _ptr(slot), M, Nq, Nkv, D, eps, max_seq, n_slots,
-                                               _ptr(q), _ptr(kcache), _ptr(vcache), _stream()))
+                                               _ptr(q), _ptr(kcache), _ptr(vcache), int(clear_input), _stream()))
     return q
 
 
@@ -121,11 +135,11 @@ def flash_decode(q, kcache, vcache, seq_len, slot, workspace=None, out=None):
     return out
 
 
-def swiglu(gate_up, out=None):
+def swiglu(gate_up, out=None, clear_input=False):
     _dev(gate_up, out)
     M, I2 = gate_up.shape
     out = torch.empty((M, I2 // 2), dtype=torch.float32, device=gate_up.device) if out is None else out
-    check(kernels().kuiper_swiglu_f32(_ptr(gate_up), _ptr(out), M, I2 // 2, _stream()))
+    check(kernels().kuiper_swiglu_f32(_ptr(gate_up), _ptr(out), M, I2 // 2, int(clear_input), _stream()))
     return out
 
 

@@ -397,17 +397,22 @@ int launch_mode(const GemvParams& p, int mode, int rows, cudaStream_t stream) {
 }  // namespace
 
 // tuning hooks used by the benchmark sweeps
+void awq_gemv_tma_set_tuning(const char* key, int value);
+
 void awq_gemv_set_tuning(const char* key, int value) {
     if (!strcmp(key, "gemv_rows")) g_force_rows = value;
     if (!strcmp(key, "gemv_math")) g_force_math = value;
     if (!strcmp(key, "gemv_impl")) g_force_impl = value;
+    awq_gemv_tma_set_tuning(key, value);
 }
 
 // persistent TMA-fed variant (awq_gemv_tma.cu)
 size_t awq_gemv_tma_workspace_bytes(int K, int N);
 bool awq_gemv_tma_supported(int K, int N);
+int awq_gemv_tma_status();
 int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
-                        const float* residual, int rows, int K, int N, void* workspace, cudaStream_t stream);
+                        const float* residual, int rows, int K, int N, void* workspace, bool accumulate,
+                        cudaStream_t stream);
 
 }  // namespace kuiper
 
@@ -458,7 +463,7 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
         for (int m0 = 0; m0 < M;) {
             const int mt = (M - m0 >= 2) ? 2 : 1;
             int rc = awq_gemv_tma_launch(x + size_t(m0) * K, qweight, qzeros, scales, y + size_t(m0) * N,
-                                         residual ? residual + size_t(m0) * N : nullptr, mt, K, N, workspace, st);
+                                         residual ? residual + size_t(m0) * N : nullptr, mt, K, N, workspace, false, st);
             if (rc != KUIPER_OK) return rc;
             m0 += mt;
         }
@@ -502,4 +507,33 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
         m0 += mt;
     }
     return KUIPER_OK;
+}
+
+extern "C" int kuiper_awq_gemv_accum_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
+                                         const uint16_t* scales, float* y, int M, int K, int N, int group,
+                                         kuiper_stream_t stream) {
+    KUIPER_REQUIRE(x && qweight && qzeros && scales && y, "awq_gemv_accum: null tensor pointer");
+    KUIPER_REQUIRE(M > 0 && K > 0 && N > 0, "awq_gemv_accum: empty shape M=%d K=%d N=%d", M, K, N);
+    KUIPER_REQUIRE(group == 128, "awq_gemv_accum: group size %d is not supported (128 only)", group);
+    KUIPER_REQUIRE(K % 128 == 0 && N % 32 == 0, "awq_gemv_accum: needs K %% 128 == 0 and N %% 32 == 0 (K=%d N=%d)", K, N);
+    KUIPER_REQUIRE(((reinterpret_cast<uintptr_t>(qweight) | reinterpret_cast<uintptr_t>(qzeros) | reinterpret_cast<uintptr_t>(scales) |
+                     reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x)) & 15) == 0,
+                   "awq_gemv_accum: tensors must be 16-byte aligned");
+    KUIPER_REQUIRE(awq_gemv_tma_supported(K, N), "awq_gemv_accum: tensor-map support is unavailable");
+    cudaStream_t st = as_stream(stream);
+    for (int m0 = 0; m0 < M;) {
+        const int mt = (M - m0 >= 2) ? 2 : 1;
+        int rc = awq_gemv_tma_launch(x + size_t(m0) * K, qweight, qzeros, scales, y + size_t(m0) * N, nullptr, mt, K, N,
+                                     nullptr, true, st);
+        if (rc != KUIPER_OK) return rc;
+        m0 += mt;
+    }
+    return KUIPER_OK;
+}
+
+extern "C" int kuiper_awq_gemv_status(void) {
+    const int v = awq_gemv_tma_status();
+    if (v == 0) return KUIPER_OK;
+    set_error("awq_gemv: a bounded pipeline wait ran out (code %d)", v);
+    return KUIPER_INTERNAL_ERROR;
 }

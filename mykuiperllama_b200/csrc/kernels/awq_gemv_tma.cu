@@ -10,8 +10,9 @@
 // dependent-launch wait, so the weight stream of this GEMV overlaps the previous kernel.
 //
 // Consumer thread (cg, rg): columns 16*cg .. 16*cg+15 of the tile (two packed words, one
-// 8-byte shared-memory read per row), rows rg, rg+8, rg+16, rg+24 of each unit.  The
-// activation vector lives in shared memory as fp16; products (q - z) * x are exact and
+// 8-byte shared-memory read per row), rows 8*rg .. 8*rg+7 of each unit.  The
+// activations of those rows are read from global memory (L2) one unit ahead and rounded to
+// fp16; products (q - z) * x are exact and
 // are accumulated in fp32 (fma.rn.f32.f16); the fp16 group scale is applied when a
 // 128-row group ends.  When a CTA's run leaves a column tile the 8 row groups are reduced
 // through shared memory and the CTA's partial row goes to the workspace slot
@@ -22,6 +23,7 @@
 // an error code in the workspace and leaves the loop.
 #include <cuda.h>
 
+#include <cstring>
 #include <mutex>
 #include <unordered_map>
 
@@ -30,8 +32,10 @@
 namespace kuiper {
 namespace {
 
-constexpr int kConsumerWarps = 16;
-constexpr int kConsumers = kConsumerWarps * 32;   // 512
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumers = kConsumerWarps * 32;   // 256
+constexpr int kRowGroups = kConsumers / 64;       // 4 row groups of 8 rows per unit
+constexpr int kCtasPerSm = 2;                     // half an SM per CTA, so that the next kernel can move in early
 constexpr int kThreadsTma = kConsumers + 32;      // + producer warp
 constexpr int kUnitRows = 32;
 constexpr int kTileWords = 128;                   // 1024 columns
@@ -39,6 +43,9 @@ constexpr int kTileColsTma = kTileWords * 8;
 constexpr int kStageBytes = kUnitRows * kTileWords * 4;  // 16 KB
 constexpr uint32_t kMagicTma = 0x64006400u;
 constexpr uint32_t kSpinLimit = 1u << 22;
+
+// set when a bounded mbarrier wait ran out (1 producer, 2 consumer); read by kuiper_awq_gemv_status()
+__device__ int g_gemv_wait_error = 0;
 
 struct TmaGemvParams {
     const float* x;        // [MT, K]
@@ -48,7 +55,6 @@ struct TmaGemvParams {
     const __half* scales;  // [K/128][N]
     float* partial;        // [slots][MT][1024]
     int* counters;         // [tiles]
-    int* error;            // one word, 0 = ok
     int K, N, tiles, upt;  // upt = units per tile = K / 32
     long long U;           // total units
 };
@@ -111,9 +117,11 @@ __device__ __forceinline__ ZeroPairs make_zero_pairs(uint32_t zw) {
     return z;
 }
 
-// acc[m][0..7] += x[m] * (q - z) for the 8 columns of one packed word
-template <int MT>
-__device__ __forceinline__ void word_fma(uint32_t w, const ZeroPairs& z, const uint16_t (&xh)[MT], float (*acc)[16], int base) {
+// acc[m][base..base+7] += x[m] * (q - z) for the 8 columns of one packed word.  The two halves of a
+// dequantised pair are split inside the asm block so that no separate extraction is emitted.
+template <int MT, bool XHI>
+__device__ __forceinline__ void word_fma(uint32_t w, const ZeroPairs& z, const uint32_t (&xpair)[MT], float (*acc)[16], int base) {
+    // xpair[m] holds two fp16 activations; XHI picks the upper one
     const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
     const uint32_t w8 = w >> 8;
     const uint32_t d[4] = {
@@ -124,33 +132,48 @@ __device__ __forceinline__ void word_fma(uint32_t w, const ZeroPairs& z, const u
     };
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const uint16_t a = uint16_t(d[i] & 0xffffu), b = uint16_t(d[i] >> 16);
 #pragma unroll
         for (int m = 0; m < MT; m++) {
-            acc[m][base + 2 * i] = fma_f16_tma(a, xh[m], acc[m][base + 2 * i]);
-            acc[m][base + 2 * i + 1] = fma_f16_tma(b, xh[m], acc[m][base + 2 * i + 1]);
+            if (XHI)
+                asm("{\n\t.reg .b16 lo, hi, xl, xh;\n\t"
+                    "mov.b32 {lo, hi}, %2;\n\t"
+                    "mov.b32 {xl, xh}, %3;\n\t"
+                    "fma.rn.f32.f16 %0, lo, xh, %0;\n\t"
+                    "fma.rn.f32.f16 %1, hi, xh, %1;\n\t}"
+                    : "+f"(acc[m][base + 2 * i]), "+f"(acc[m][base + 2 * i + 1])
+                    : "r"(d[i]), "r"(xpair[m]));
+            else
+                asm("{\n\t.reg .b16 lo, hi, xl, xh;\n\t"
+                    "mov.b32 {lo, hi}, %2;\n\t"
+                    "mov.b32 {xl, xh}, %3;\n\t"
+                    "fma.rn.f32.f16 %0, lo, xl, %0;\n\t"
+                    "fma.rn.f32.f16 %1, hi, xl, %1;\n\t}"
+                    : "+f"(acc[m][base + 2 * i]), "+f"(acc[m][base + 2 * i + 1])
+                    : "r"(d[i]), "r"(xpair[m]));
         }
     }
 }
 
-template <int MT, int STAGES>
-__global__ void __launch_bounds__(kThreadsTma, 1)
+// ACCUM: y += x.W with vector float reductions (no cross-CTA ordering, no tail); the caller guarantees
+// that y holds the addend (residual stream or zeros).  Otherwise y = x.W (+ residual) with the
+// deterministic slot / arrival-counter combine.
+template <int MT, int STAGES, bool ACCUM, bool NOMATH = false>
+__global__ void __launch_bounds__(kThreadsTma, (MT == 1 ? kCtasPerSm : 1))
 awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParams p) {
     extern __shared__ unsigned char smem_raw[];
     // TMA destinations want 128-byte alignment; the launch reserves 128 spare bytes for this
     unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     unsigned char* stages = smem;                                             // STAGES x 16 KB
-    float4* red = reinterpret_cast<float4*>(smem + STAGES * kStageBytes);      // [8][MT][256] float4
-    uint16_t* xh = reinterpret_cast<uint16_t*>(smem + STAGES * kStageBytes + 8 * MT * 1024 * 4);  // [MT][K] fp16
+    float4* red = reinterpret_cast<float4*>(smem + STAGES * kStageBytes);      // [kRowGroups][MT][256] float4
     __shared__ uint64_t full_bar[STAGES];
     __shared__ uint64_t empty_bar[STAGES];
     __shared__ int s_last;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    const long long C = gridDim.x;
-    const long long u0 = (long long)blockIdx.x * p.U / C;
-    const long long u1 = (long long)(blockIdx.x + 1) * p.U / C;
+    const int C = gridDim.x;
+    const int u0 = int((long long)blockIdx.x * p.U / C);
+    const int u1 = int((long long)(blockIdx.x + 1) * p.U / C);
 
     if (tid == 0) {
 #pragma unroll
@@ -166,24 +189,24 @@ awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParam
     if (warp == kConsumerWarps) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            int t = int(u0 / p.upt), kb = int(u0 - (long long)t * p.upt);
-            uint32_t it = 0;
+            int t = u0 / p.upt, kb = u0 - t * p.upt;
+            int s = 0;
+            uint32_t parity = 0;
             bool ok = true;
-            for (long long u = u0; u < u1; u++, it++) {
-                const int s = it % STAGES;
-                const uint32_t parity = (it / STAGES) & 1u;
+            for (int u = u0; u < u1; u++) {
                 if (!mbar_wait(&empty_bar[s], parity ^ 1u)) {
-                    atomicExch(p.error, 1);
+                    atomicExch(&g_gemv_wait_error, 1);
                     ok = false;
                     break;
                 }
                 mbar_expect_tx(&full_bar[s], kStageBytes);
                 tma_load_2d(stages + s * kStageBytes, &tmap, t * kTileWords, kb * kUnitRows, &full_bar[s]);
                 if (++kb == p.upt) { kb = 0; t++; }
+                if (++s == STAGES) { s = 0; parity ^= 1u; }
             }
             if (!ok) {
                 // give copies already issued a bounded chance to land before the CTA goes away
-                for (int s = 0; s < STAGES; s++) mbar_wait(&full_bar[s], 0);
+                for (int q = 0; q < STAGES; q++) mbar_wait(&full_bar[q], 0);
             }
         }
         return;
@@ -191,14 +214,13 @@ awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParam
 
     // ---------------------------------------------------------------- consumers
     const int cg = tid & 63;   // 16-column group inside the tile
-    const int rg = tid >> 6;   // row group 0..7
-    pdl_wait();
-    for (int i = tid; i < MT * p.K; i += kConsumers) xh[i] = __half_as_ushort(__float2half_rn(__ldcg(p.x + i)));
-    consumer_sync();
+    const int rg = tid >> 6;   // row group: rows 8*rg .. 8*rg+7 of every unit
+    pdl_wait();                // x, y and the workspace belong to the previous kernel until here
 
-    int t = int(u0 / p.upt), kb = int(u0 - (long long)t * p.upt);
     const int groups = p.K >> 7;
     const int zstride = p.N >> 4;  // uint2 per zero row
+    const unsigned char* my_stage = stages + rg * 8 * 512 + cg * 8;
+    const float* my_x = p.x + rg * 8;
 
     // raw zero / scale words of a (tile, group) for this thread's 16 columns; zeros outside N
     auto load_consts = [&](int tile, int g, uint2& zraw, uint4& s0, uint4& s1) {
@@ -214,18 +236,28 @@ awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParam
             s1 = make_uint4(0, 0, 0, 0);
         }
     };
+    // the 8 activations of this thread's rows of unit kb, rounded to fp16 and packed in pairs
+    auto load_x = [&](int kb, uint4 (&xr)[MT]) {
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            const float4* xp = reinterpret_cast<const float4*>(my_x + size_t(m) * p.K + kb * kUnitRows);
+            const float4 a = __ldcg(xp), b = __ldcg(xp + 1);
+            xr[m].x = h22u(__floats2half2_rn(a.x, a.y));
+            xr[m].y = h22u(__floats2half2_rn(a.z, a.w));
+            xr[m].z = h22u(__floats2half2_rn(b.x, b.y));
+            xr[m].w = h22u(__floats2half2_rn(b.z, b.w));
+        }
+    };
+
+    int t = u0 / p.upt, kb = u0 - t * p.upt;
+    int units_left = u1 - u0;
 
     uint2 z_next = make_uint2(0, 0);
     uint4 sa_next = make_uint4(0, 0, 0, 0), sb_next = sa_next, sa_cur, sb_cur;
     load_consts(t, kb >> 2, z_next, sa_cur, sb_cur);
     ZeroPairs z0 = make_zero_pairs(z_next.x), z1 = make_zero_pairs(z_next.y);
-    auto prefetch_following = [&](int tile, int g) {
-        // the group after (tile, g) in unit order, if this CTA's run reaches it
-        int ng = g + 1, nt = tile;
-        if (ng == groups) { ng = 0; nt++; }
-        if ((long long)nt * p.upt + ng * 4 < u1) load_consts(nt, ng, z_next, sa_next, sb_next);
-    };
-    prefetch_following(t, kb >> 2);
+    uint4 xr[MT];
+    load_x(kb, xr);
 
     float acc_g[MT][16], acc_t[MT][16];
 #pragma unroll
@@ -233,37 +265,64 @@ awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParam
 #pragma unroll
         for (int c = 0; c < 16; c++) { acc_g[m][c] = 0.f; acc_t[m][c] = 0.f; }
 
-    uint32_t it = 0;
+    int s = 0;
+    uint32_t parity = 0;
     bool dead = false;  // a wait ran out: keep walking the barriers so nobody hangs, the result is void
-    for (long long u = u0; u < u1; u++, it++) {
-        const int s = it % STAGES;
-        const uint32_t parity = (it / STAGES) & 1u;
-        if (!dead && !mbar_wait(&full_bar[s], parity)) {
-            atomicExch(p.error, 2);
-            dead = true;
-        }
-        const unsigned char* sp = stages + s * kStageBytes + rg * 512 + cg * 8;
-        uint2 w[4];
-        uint16_t xv[4][MT];
+    while (units_left > 0) {
+        // ---- one column tile: units kb .. kb + seg - 1 of tile t
+        int seg = min(p.upt - kb, units_left);
+        units_left -= seg;
+        while (seg > 0) {
+            // ---- one quantisation group (up to 4 units)
+            const int gu = min(4 - (kb & 3), seg);
+            seg -= gu;
+            const bool more = (seg > 0) || (units_left > 0);
+            if (more) {
+                // constants of the next group this CTA will visit, fetched while this one is processed
+                int ng = (kb >> 2) + 1, nt = t;
+                if (ng == groups) { ng = 0; nt++; }
+                load_consts(nt, ng, z_next, sa_next, sb_next);
+            }
+            for (int j = 0; j < gu; j++) {
+                if (!dead && !mbar_wait(&full_bar[s], parity)) {
+                    atomicExch(&g_gemv_wait_error, 2);
+                    dead = true;
+                }
+                const unsigned char* sp = my_stage + s * kStageBytes;
+                uint2 w[8];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            w[i] = *reinterpret_cast<const uint2*>(sp + i * 8 * 512);
+                for (int i = 0; i < 8; i++) w[i] = *reinterpret_cast<const uint2*>(sp + i * 512);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[s]);  // the stage is in registers now
+                if (++s == STAGES) { s = 0; parity ^= 1u; }
+                uint32_t xa[MT], xb[MT], xc[MT], xd[MT];
 #pragma unroll
-            for (int m = 0; m < MT; m++) xv[i][m] = xh[m * p.K + kb * kUnitRows + rg + 8 * i];
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[s]);  // the stage is in registers now
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            word_fma<MT>(w[i].x, z0, xv[i], acc_g, 0);
-            word_fma<MT>(w[i].y, z1, xv[i], acc_g, 8);
-        }
-
-        const bool group_end = (kb & 3) == 3;
-        const bool run_end = (u + 1 == u1);
-        const bool tile_end = (kb + 1 == p.upt);
-        if (group_end || run_end) {
-            // apply the group's fp16 scales once
+                for (int m = 0; m < MT; m++) { xa[m] = xr[m].x; xb[m] = xr[m].y; xc[m] = xr[m].z; xd[m] = xr[m].w; }
+                // activations of the next unit this thread will see (same tile or the start of the next one)
+                kb++;
+                if (j + 1 < gu || more) load_x(kb == p.upt ? 0 : kb, xr);
+                if (NOMATH) {  // measurement aid: keep the loads alive, skip the arithmetic
+                    acc_g[0][0] += __uint_as_float((w[0].x ^ w[1].x ^ w[2].x ^ w[3].x ^ w[4].y ^ w[5].y ^ w[6].y ^ w[7].y ^ xa[0] ^ xd[0]) & 0x3fffffffu);
+                    continue;
+                }
+                word_fma<MT, false>(w[0].x, z0, xa, acc_g, 0);
+                word_fma<MT, false>(w[0].y, z1, xa, acc_g, 8);
+                word_fma<MT, true>(w[1].x, z0, xa, acc_g, 0);
+                word_fma<MT, true>(w[1].y, z1, xa, acc_g, 8);
+                word_fma<MT, false>(w[2].x, z0, xb, acc_g, 0);
+                word_fma<MT, false>(w[2].y, z1, xb, acc_g, 8);
+                word_fma<MT, true>(w[3].x, z0, xb, acc_g, 0);
+                word_fma<MT, true>(w[3].y, z1, xb, acc_g, 8);
+                word_fma<MT, false>(w[4].x, z0, xc, acc_g, 0);
+                word_fma<MT, false>(w[4].y, z1, xc, acc_g, 8);
+                word_fma<MT, true>(w[5].x, z0, xc, acc_g, 0);
+                word_fma<MT, true>(w[5].y, z1, xc, acc_g, 8);
+                word_fma<MT, false>(w[6].x, z0, xd, acc_g, 0);
+                word_fma<MT, false>(w[6].y, z1, xd, acc_g, 8);
+                word_fma<MT, true>(w[7].x, z0, xd, acc_g, 0);
+                word_fma<MT, true>(w[7].y, z1, xd, acc_g, 8);
+            }
+            // ---- group done: apply its fp16 scales once
             const uint32_t sraw[8] = {sa_cur.x, sa_cur.y, sa_cur.z, sa_cur.w, sb_cur.x, sb_cur.y, sb_cur.z, sb_cur.w};
 #pragma unroll
             for (int c = 0; c < 8; c++) {
@@ -276,54 +335,60 @@ awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParam
                     acc_g[m][2 * c + 1] = 0.f;
                 }
             }
-            if (!run_end) {
-                // rotate in the constants of the next group and start fetching the one after
+            if (more) {
                 z0 = make_zero_pairs(z_next.x);
                 z1 = make_zero_pairs(z_next.y);
                 sa_cur = sa_next;
                 sb_cur = sb_next;
-                int ng = (kb >> 2) + 1, nt = t;
-                if (ng == groups) { ng = 0; nt++; }
-                prefetch_following(nt, ng);
             }
         }
 
-        if (tile_end || run_end) {
-            // ---- this CTA's contribution to column tile t is complete: reduce the 8 row groups
+        // ---- this CTA's contribution to column tile t is complete: reduce the row groups
 #pragma unroll
-            for (int m = 0; m < MT; m++)
+        for (int m = 0; m < MT; m++)
 #pragma unroll
-                for (int j = 0; j < 4; j++)
-                    red[(rg * MT + m) * 256 + cg * 4 + ((j + (cg >> 1)) & 3)] =
-                        make_float4(acc_t[m][4 * j], acc_t[m][4 * j + 1], acc_t[m][4 * j + 2], acc_t[m][4 * j + 3]);
+            for (int j = 0; j < 4; j++)
+                red[(rg * MT + m) * 256 + cg * 4 + ((j + (cg >> 1)) & 3)] =
+                    make_float4(acc_t[m][4 * j], acc_t[m][4 * j + 1], acc_t[m][4 * j + 2], acc_t[m][4 * j + 3]);
 #pragma unroll
-            for (int m = 0; m < MT; m++)
+        for (int m = 0; m < MT; m++)
 #pragma unroll
-                for (int c = 0; c < 16; c++) acc_t[m][c] = 0.f;
-            consumer_sync();
+            for (int c = 0; c < 16; c++) acc_t[m][c] = 0.f;
+        consumer_sync();
 
+        // thread f owns float4 f of the tile (columns 4f .. 4f+3) for every token row
+        const int f = tid;
+        const int fcg = f >> 2, fj = f & 3;
+        const int col = t * kTileColsTma + f * 4;
+        float4 v[MT];
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            v[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r < kRowGroups; r++) {
+                const float4 a = red[(r * MT + m) * 256 + fcg * 4 + ((fj + (fcg >> 1)) & 3)];
+                v[m].x += a.x; v[m].y += a.y; v[m].z += a.z; v[m].w += a.w;
+            }
+        }
+        if (ACCUM) {
+            if (col < p.N) {
+#pragma unroll
+                for (int m = 0; m < MT; m++)
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.y + size_t(m) * p.N + col),
+                                 "f"(v[m].x), "f"(v[m].y), "f"(v[m].z), "f"(v[m].w)
+                                 : "memory");
+            }
+        } else {
             // contributors of this tile: CTAs owning its first and last unit
             const long long first_u = (long long)t * p.upt, last_u = first_u + p.upt - 1;
             const int c_first = int(((first_u + 1) * C - 1) / p.U);
             const int c_last = int(((last_u + 1) * C - 1) / p.U);
             const int n_contrib = c_last - c_first + 1;
-
-            const bool worker = tid < 256 * MT;
-            const int m = tid >> 8, f = tid & 255;  // row and float4 index owned in the epilogue
-            const int fcg = f >> 2, fj = f & 3;
-            const int col = t * kTileColsTma + f * 4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (worker) {
-#pragma unroll
-                for (int r = 0; r < 8; r++) {
-                    const float4 a = red[(r * MT + m) * 256 + fcg * 4 + ((fj + (fcg >> 1)) & 3)];
-                    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
-                }
-            }
             bool finish = true;  // whether this CTA writes y for the tile
             if (n_contrib > 1) {
-                if (worker)
-                    *reinterpret_cast<float4*>(p.partial + (size_t(blockIdx.x + t) * MT + m) * kTileColsTma + f * 4) = v;
+#pragma unroll
+                for (int m = 0; m < MT; m++)
+                    *reinterpret_cast<float4*>(p.partial + (size_t(blockIdx.x + t) * MT + m) * kTileColsTma + f * 4) = v[m];
                 __threadfence();
                 consumer_sync();
                 if (tid == 0) {
@@ -335,26 +400,42 @@ awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParam
                 finish = s_last != 0;
                 if (finish) {
                     __threadfence();
-                    if (worker) {
-                        v = make_float4(0.f, 0.f, 0.f, 0.f);
-                        for (int c = c_first; c <= c_last; c++) {
-                            const float4 a = __ldcg(reinterpret_cast<const float4*>(
-                                p.partial + (size_t(c + t) * MT + m) * kTileColsTma + f * 4));
-                            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+                    // slots are added in CTA order (deterministic); loads are issued eight at a time
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                        const float* base = p.partial + (size_t(t) * MT + m) * kTileColsTma + f * 4;
+                        int c = c_first;
+                        for (; c + 8 <= c_last + 1; c += 8) {
+                            float4 a[8];
+#pragma unroll
+                            for (int q = 0; q < 8; q++)
+                                a[q] = __ldcg(reinterpret_cast<const float4*>(base + size_t(c + q) * MT * kTileColsTma));
+#pragma unroll
+                            for (int q = 0; q < 8; q++) { sum.x += a[q].x; sum.y += a[q].y; sum.z += a[q].z; sum.w += a[q].w; }
                         }
+                        for (; c <= c_last; c++) {
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(base + size_t(c) * MT * kTileColsTma));
+                            sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+                        }
+                        v[m] = sum;
                     }
                 }
             }
-            if (finish && worker && col < p.N) {
-                if (p.residual) {
-                    const float4 r = __ldcg(reinterpret_cast<const float4*>(p.residual + size_t(m) * p.N + col));
-                    v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+            if (finish && col < p.N) {
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    if (p.residual) {
+                        const float4 r = __ldcg(reinterpret_cast<const float4*>(p.residual + size_t(m) * p.N + col));
+                        v[m].x += r.x; v[m].y += r.y; v[m].z += r.z; v[m].w += r.w;
+                    }
+                    *reinterpret_cast<float4*>(p.y + size_t(m) * p.N + col) = v[m];
                 }
-                *reinterpret_cast<float4*>(p.y + size_t(m) * p.N + col) = v;
             }
-            consumer_sync();  // red is reused by the next tile
         }
-        if (++kb == p.upt) { kb = 0; t++; }
+        consumer_sync();  // red is reused by the next tile
+        kb = 0;
+        t++;
     }
 }
 
@@ -425,10 +506,12 @@ int sm_count() {
     return g_sm_count;
 }
 
-template <int MT, int STAGES>
+int g_tma_nomath = 0;
+
+template <int MT, int STAGES, bool ACCUM, bool NOMATH = false>
 int launch_tma(const CUtensorMap& map, const TmaGemvParams& p, int ctas, cudaStream_t stream) {
-    auto kern = awq_gemv_tma_kernel<MT, STAGES>;
-    const size_t smem = 128 + size_t(STAGES) * kStageBytes + size_t(8) * MT * 1024 * 4 + size_t(MT) * p.K * 2;
+    auto kern = awq_gemv_tma_kernel<MT, STAGES, ACCUM, NOMATH>;
+    const size_t smem = 128 + size_t(STAGES) * kStageBytes + size_t(kRowGroups) * MT * 1024 * 4;
     static size_t configured = 0;
     if (configured < smem) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
@@ -457,21 +540,33 @@ int launch_tma(const CUtensorMap& map, const TmaGemvParams& p, int ctas, cudaStr
 
 }  // namespace
 
+// 0 if no bounded wait of the TMA kernel has ever run out on the current device (synchronises)
+int awq_gemv_tma_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemv_wait_error, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
+void awq_gemv_tma_set_tuning(const char* key, int value) {
+    if (!strcmp(key, "gemv_nomath")) g_tma_nomath = value;
+}
+
 // Workspace layout of the TMA kernel: [counters: tiles ints][error word][partial slots].
 size_t awq_gemv_tma_workspace_bytes(int K, int N) {
     const size_t tiles = size_t(N + kTileColsTma - 1) / kTileColsTma;
     const size_t head = ((tiles + 1) * sizeof(int) + 255) / 256 * 256;
-    const size_t slots = size_t(sm_count()) + tiles;  // slot index = cta + tile
+    const size_t slots = size_t(sm_count()) * kCtasPerSm + tiles;  // slot index = cta + tile
     return head + slots * 2 * kTileColsTma * sizeof(float);
 }
 
 bool awq_gemv_tma_supported(int K, int N) {
-    return N % 32 == 0 && K % 128 == 0 && K <= 16384 && encode_fn() != nullptr;
+    return N % 32 == 0 && K % 128 == 0 && encode_fn() != nullptr;
 }
 
 // rows: 1 or 2 token rows starting at x / y / residual
 int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
-                        const float* residual, int rows, int K, int N, void* workspace, cudaStream_t stream) {
+                        const float* residual, int rows, int K, int N, void* workspace, bool accumulate,
+                        cudaStream_t stream) {
     CUtensorMap map;
     if (!get_tensor_map(qweight, K, N, &map)) {
         set_error("awq_gemv_tma: tensor map encoding failed");
@@ -489,13 +584,21 @@ int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* q
     p.upt = K / kUnitRows;
     p.U = (long long)p.tiles * p.upt;
     const size_t head = ((size_t(p.tiles) + 1) * sizeof(int) + 255) / 256 * 256;
+    if (!accumulate && workspace == nullptr) {
+        set_error("awq_gemv_tma: the ordered combine needs a workspace");
+        return KUIPER_INVALID_ARGUMENT;
+    }
     p.counters = reinterpret_cast<int*>(workspace);
-    p.error = p.counters + p.tiles;
     p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + head);
-    long long ctas = sm_count();
+    long long ctas = (long long)sm_count() * (rows == 1 ? kCtasPerSm : 1);
     if (ctas > p.U) ctas = p.U;
-    if (rows == 2) return launch_tma<2, 6>(map, p, int(ctas), stream);
-    return launch_tma<1, 8>(map, p, int(ctas), stream);
+    if (accumulate) {
+        if (rows == 2) return launch_tma<2, 4, true>(map, p, int(ctas), stream);
+        if (g_tma_nomath) return launch_tma<1, 5, true, true>(map, p, int(ctas), stream);
+        return launch_tma<1, 5, true>(map, p, int(ctas), stream);
+    }
+    if (rows == 2) return launch_tma<2, 4, false>(map, p, int(ctas), stream);
+    return launch_tma<1, 5, false>(map, p, int(ctas), stream);
 }
 
 }  // namespace kuiper

@@ -67,13 +67,17 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* x, const uint
 }
 
 // ---------------------------------------------------------------- swiglu
-__global__ void swiglu_kernel(const float* gate_up, float* out, int M, int I) {
+__global__ void swiglu_kernel(float* gate_up, float* out, int M, int I, int clear_input) {
     pdl_wait();
     const int64_t total = int64_t(M) * I;
     for (int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += int64_t(gridDim.x) * blockDim.x) {
         const int64_t m = idx / I, i = idx - m * I;
         const float g = gate_up[m * 2 * I + i], u = gate_up[m * 2 * I + I + i];
         out[idx] = (g / (1.0f + expf(-g))) * u;
+        if (clear_input) {  // leave the projection buffer zeroed for the next accumulating matmul
+            gate_up[m * 2 * I + i] = 0.f;
+            gate_up[m * 2 * I + I + i] = 0.f;
+        }
     }
 }
 
@@ -235,10 +239,10 @@ extern "C" int kuiper_rmsnorm_f32(const float* x, const uint16_t* w, float* y, i
     return launch_status("rmsnorm");
 }
 
-extern "C" int kuiper_swiglu_f32(const float* gate_up, float* out, int M, int I, kuiper_stream_t stream) {
+extern "C" int kuiper_swiglu_f32(float* gate_up, float* out, int M, int I, int clear_input, kuiper_stream_t stream) {
     KUIPER_REQUIRE(gate_up && out, "swiglu: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && I > 0, "swiglu: empty shape M=%d I=%d", M, I);
-    swiglu_kernel<<<grid_for(int64_t(M) * I, 256), 256, 0, as_stream(stream)>>>(gate_up, out, M, I);
+    swiglu_kernel<<<grid_for(int64_t(M) * I, 256), 256, 0, as_stream(stream)>>>(gate_up, out, M, I, clear_input);
     return launch_status("swiglu");
 }
 

@@ -247,7 +247,7 @@ flash_decode_kernel(const FlashParams p) {
 
 int pick_splits(int M, int Nkv, int max_seq) {
     if (g_force_splits > 0) return g_force_splits;
-    const int by_len = (max_seq + 255) / 256;  // at least 256 rows per slice
+    const int by_len = (max_seq + 63) / 64;  // a slice is at least one 64-row step of the CTA
     int want = (148 * 4 + M * Nkv - 1) / (M * Nkv);
     int s = want < by_len ? want : by_len;
     if (s < 1) s = 1;

@@ -14,22 +14,25 @@ namespace {
 constexpr int kD = 128;
 
 __global__ void __launch_bounds__(128)
-qknorm_rope_kvwrite_kernel(const float* qkv, const uint16_t* __restrict__ q_norm_w, const uint16_t* __restrict__ k_norm_w,
+qknorm_rope_kvwrite_kernel(float* qkv, const uint16_t* __restrict__ q_norm_w, const uint16_t* __restrict__ k_norm_w,
                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int32_t* pos,
                            const int32_t* slot, int M, int Nq, int Nkv, float eps, int max_seq, int n_slots, float* q_out,
-                           uint16_t* kcache, uint16_t* vcache) {
+                           uint16_t* kcache, uint16_t* vcache, int clear_input) {
     pdl_wait();
     const int heads = Nq + 2 * Nkv;
     const int wid = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (wid >= M * heads) return;
     const int lane = threadIdx.x & 31;
     const int m = wid / heads, h = wid - m * heads;
-    const float* src = qkv + (size_t(m) * heads + h) * kD;
+    float* src = qkv + (size_t(m) * heads + h) * kD;
     int p = pos[m];
     p = p < 0 ? 0 : (p >= max_seq ? max_seq - 1 : p);  // clamp: never write outside the cache
     int sl = slot[m];
     sl = sl < 0 ? 0 : (sl >= n_slots ? n_slots - 1 : sl);
     const float a0 = src[lane], a1 = src[lane + 32], b0 = src[lane + 64], b1 = src[lane + 96];
+    if (clear_input) {  // leave the projection buffer zeroed for the next accumulating matmul
+        src[lane] = 0.f; src[lane + 32] = 0.f; src[lane + 64] = 0.f; src[lane + 96] = 0.f;
+    }
 
     if (h >= Nq + Nkv) {  // value head: plain bf16 store
         uint16_t* dst = vcache + ((size_t(sl) * Nkv + (h - Nq - Nkv)) * max_seq + p) * kD;
@@ -74,17 +77,17 @@ qknorm_rope_kvwrite_kernel(const float* qkv, const uint16_t* __restrict__ q_norm
 
 using namespace kuiper;
 
-extern "C" int kuiper_qknorm_rope_kvwrite(const float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
+extern "C" int kuiper_qknorm_rope_kvwrite(float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
                                           const float* cos_t, const float* sin_t, const int32_t* pos,
                                           const int32_t* slot, int M, int Nq, int Nkv, int D, float eps,
                                           int max_seq, int n_slots, float* q_out, uint16_t* kcache, uint16_t* vcache,
-                                          kuiper_stream_t stream) {
+                                          int clear_input, kuiper_stream_t stream) {
     KUIPER_REQUIRE(qkv && q_norm_w && k_norm_w && cos_t && sin_t && pos && slot && q_out && kcache && vcache,
                    "qknorm_rope: null tensor pointer");
     KUIPER_REQUIRE(D == kD, "qknorm_rope: head_dim %d is not supported (128 only)", D);
     KUIPER_REQUIRE(M > 0 && Nq > 0 && Nkv > 0 && max_seq > 0 && n_slots > 0, "qknorm_rope: empty shape");
     const int warps = M * (Nq + 2 * Nkv);
     qknorm_rope_kvwrite_kernel<<<(warps + 3) / 4, 128, 0, as_stream(stream)>>>(
-        qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, M, Nq, Nkv, eps, max_seq, n_slots, q_out, kcache, vcache);
+        qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, M, Nq, Nkv, eps, max_seq, n_slots, q_out, kcache, vcache, clear_input);
     return launch_status("qknorm_rope_kvwrite");
 }

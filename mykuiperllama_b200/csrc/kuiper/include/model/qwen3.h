@@ -83,6 +83,7 @@ private:
     std::unique_ptr<sampler::ArgmaxSampler> sampler_;
     std::vector<bool> layer_loaded_;
     bool globals_loaded_ = false;
+    bool accumulate_ = false;  // projections run in accumulate mode (see init)
 
     // pinned staging for the host <-> device token traffic
     int32_t* host_stage_ = nullptr;

@@ -25,6 +25,9 @@ public:
     base::Status forward() override;
 
     void set_residual(bool has_residual);
+    // accumulate mode (quantised layers): output += x . W, the output tensor already holds the addend
+    // (residual stream or zeros); no workspace, unordered fp32 summation
+    void set_accumulate(bool accumulate) { accumulate_ = accumulate; }
     // scratch of the split-K kernel: kernel::matmul_quant_workspace_bytes(M, K, N) bytes, zero-initialised once
     void set_workspace(const tensor::Tensor& workspace);
     // how the INT4 kernel rounds x: 1 = fp16 operand (default), 0 = fp32 operand
@@ -40,6 +43,7 @@ private:
     int32_t dim0_ = 0;
     int32_t dim1_ = 0;
     bool has_residual_ = false;
+    bool accumulate_ = false;
     int32_t act_mode_ = 1;
     tensor::Tensor workspace_;
 };

@@ -20,6 +20,8 @@ public:
     using Layer::forward;  // keep the N-ary overloads visible next to the override
     base::Status forward() override;
     void set_cache(const tensor::Tensor& key_cache, const tensor::Tensor& value_cache);
+    // zero the qkv input after reading it (it then serves as the addend of an accumulating matmul)
+    void set_clear_input(bool clear) { clear_input_ = clear; }
 
 protected:
     base::DataType weight_data_type(int32_t idx) const override;
@@ -27,6 +29,7 @@ protected:
 private:
     int32_t head_num_ = 0, kv_head_num_ = 0, head_size_ = 0;
     float eps_ = 1e-6f;
+    bool clear_input_ = false;
     tensor::Tensor key_cache_, value_cache_;
 };
 }  // namespace op

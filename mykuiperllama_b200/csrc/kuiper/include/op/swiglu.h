@@ -11,11 +11,13 @@ class SwiGLULayer : public Layer {
 public:
     explicit SwiGLULayer(base::DeviceType device_type, int32_t hidden_dim);
     base::Status check() const override;
+    void set_clear_input(bool clear) { clear_input_ = clear; }  // zero gate|up after reading it
     using Layer::forward;  // keep the N-ary overloads visible next to the override
     base::Status forward() override;
 
 private:
     int32_t hidden_dim_ = 0;
+    bool clear_input_ = false;
 };
 }  // namespace op
 

@@ -136,6 +136,9 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::MHAWorkspace, dev(DataType::DataTypeInt8, {int32_t(ws_mha)})));
     CUDA_OK(cudaMemset(get_buffer(ModelBufferType::MatmulWorkspace).ptr<void>(), 0, ws_mm));
     CUDA_OK(cudaMemset(get_buffer(ModelBufferType::MHAWorkspace).ptr<void>(), 0, ws_mha));
+    // accumulating projections need their output buffers zero before the first pass
+    CUDA_OK(cudaMemset(get_buffer(ModelBufferType::QKVOutput).ptr<void>(), 0, get_buffer(ModelBufferType::QKVOutput).byte_size()));
+    CUDA_OK(cudaMemset(get_buffer(ModelBufferType::W1Output).ptr<void>(), 0, get_buffer(ModelBufferType::W1Output).byte_size()));
     for (ModelBufferType b : {ModelBufferType::InputTokens, ModelBufferType::InputPos, ModelBufferType::SeqLen,
                               ModelBufferType::SeqSlot, ModelBufferType::NextTokens})
         CUDA_OK(cudaMemset(get_buffer(b).ptr<void>(), 0, size_t(R) * 4));
@@ -177,6 +180,9 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     };
     // with tensor parallelism only rank 0 folds the residual into its partial sum
     const bool fold_residual = c.tp_size == 1 || c.tp_rank == 0;
+    // Single GPU, fp16-operand mode: every projection accumulates into its output (the residual stream for O
+    // and down; a buffer that its consumer left zeroed for QKV and gate|up), which needs no ordered combine.
+    accumulate_ = c.tp_size == 1 && c.act_mode == 1 && QKV % 32 == 0 && H % 32 == 0 && (2 * I) % 32 == 0;
 
     layers_.resize(size_t(c.layer_num));
     layer_loaded_.assign(size_t(c.layer_num), false);
@@ -184,9 +190,10 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         L.input_norm = make_norm(H);
         L.post_norm = make_norm(H);
         L.qkv = make_quant(sh_qkv, false);
-        L.o = make_quant(sh_o, fold_residual);
+        L.o = make_quant(sh_o, fold_residual && !accumulate_);
         L.gate_up = make_quant(sh_gu, false);
-        L.down = make_quant(sh_down, fold_residual);
+        L.down = make_quant(sh_down, fold_residual && !accumulate_);
+        for (op::MatmulLayer* m : {L.qkv.get(), L.o.get(), L.gate_up.get(), L.down.get()}) m->set_accumulate(accumulate_);
         L.key_cache = dev(DataType::DataTypeBf16, {c.max_batch, Hkv, c.max_seq_len, D});
         L.value_cache = dev(DataType::DataTypeBf16, {c.max_batch, Hkv, c.max_seq_len, D});
         CUDA_OK(cudaMemset(L.key_cache.ptr<void>(), 0, L.key_cache.byte_size()));
@@ -196,12 +203,14 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         STATUS_CHECK(L.rope->set_weight(0, dev(DataType::DataTypeBf16, {D})));
         STATUS_CHECK(L.rope->set_weight(1, dev(DataType::DataTypeBf16, {D})));
         L.rope->set_cache(L.key_cache, L.value_cache);
+        L.rope->set_clear_input(accumulate_);
         L.mha = std::make_unique<op::MultiHeadAttention>(device_type_, Hq, Hkv, D);
         L.mha->set_cuda_config(cuda_config_);
         L.mha->set_cache(L.key_cache, L.value_cache);
         L.mha->set_workspace(get_buffer(ModelBufferType::MHAWorkspace));
         L.swiglu = std::make_unique<op::SwiGLULayer>(device_type_, I);
         L.swiglu->set_cuda_config(cuda_config_);
+        L.swiglu->set_clear_input(accumulate_);
     }
     embedding_ = std::make_unique<op::EmbeddingLayer>(device_type_, H, c.vocab_size);
     embedding_->set_cuda_config(cuda_config_);
@@ -353,7 +362,7 @@ base::Status Qwen3Model::run_pass(int32_t M) {
 
     // row-split projection: out = h + x.W summed over ranks
     auto project_and_reduce = [&](op::MatmulLayer& layer, const Tensor& x) -> base::Status {
-        if (!tp) return layer.forward(x, h, h);
+        if (!tp) return accumulate_ ? layer.forward(x, h) : layer.forward(x, h, h);
         RETURN_IF_ERROR(fold_residual ? layer.forward(x, h, h_alt) : layer.forward(x, h_alt));
         RETURN_IF_ERROR(communicator_->all_reduce_sum(const_cast<float*>(h_alt.ptr<float>()), size_t(M) * H, stream()));
         std::swap(h, h_alt);

@@ -76,6 +76,23 @@ void matmul_kernel_quant_cu(const Tensor& input, const Tensor& qweight, const Te
                                   out_ptr<void>(workspace), workspace.byte_size(), as_stream(stream)));
 }
 
+void matmul_kernel_quant_accum_cu(const Tensor& input, const Tensor& qweight, const Tensor& qzeros, const Tensor& scales,
+                                  const Tensor& output, int32_t group_size, void* stream) {
+    require_cuda(input, "matmul input");
+    require_cuda(qweight, "matmul qweight");
+    require_cuda(qzeros, "matmul qzeros");
+    require_cuda(scales, "matmul scales");
+    require_cuda(output, "matmul output");
+    CHECK_EQ(qweight.dims_size(), 2);
+    const int32_t K = qweight.get_dim(0), N = qweight.get_dim(1) * 8;
+    CHECK_EQ(input.size() % size_t(K), size_t(0));
+    const int32_t M = int32_t(input.size() / size_t(K));
+    CHECK_EQ(output.size(), size_t(M) * size_t(N));
+    KERNEL_OK(kuiper_awq_gemv_accum_f32(input.ptr<float>(), qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(),
+                                        scales.ptr<uint16_t>(), out_ptr<float>(output), M, K, N, group_size,
+                                        as_stream(stream)));
+}
+
 void rmsnorm_kernel_cu(const Tensor& input, const Tensor& weight, const Tensor& output, float eps, void* stream) {
     require_cuda(input, "rmsnorm input");
     require_cuda(weight, "rmsnorm weight");
@@ -90,7 +107,7 @@ void rmsnorm_kernel_cu(const Tensor& input, const Tensor& weight, const Tensor& 
 void rope_kernel_cu(const Tensor& qkv, const Tensor& q_norm, const Tensor& k_norm, const Tensor& cos_cache,
                     const Tensor& sin_cache, const Tensor& pos, const Tensor& slot, const Tensor& q_out,
                     const Tensor& key_cache, const Tensor& value_cache, int32_t head_num, int32_t kv_head_num,
-                    int32_t head_size, float eps, void* stream) {
+                    int32_t head_size, float eps, bool clear_input, void* stream) {
     require_cuda(qkv, "rope qkv");
     require_cuda(q_out, "rope q_out");
     require_cuda(key_cache, "rope key cache");
@@ -101,11 +118,12 @@ void rope_kernel_cu(const Tensor& qkv, const Tensor& q_norm, const Tensor& k_nor
     const int32_t M = int32_t(qkv.size() / size_t(row));
     CHECK_GE(pos.size(), size_t(M));
     CHECK_GE(slot.size(), size_t(M));
-    KERNEL_OK(kuiper_qknorm_rope_kvwrite(qkv.ptr<float>(), q_norm.ptr<uint16_t>(), k_norm.ptr<uint16_t>(),
+    KERNEL_OK(kuiper_qknorm_rope_kvwrite(out_ptr<float>(qkv), q_norm.ptr<uint16_t>(), k_norm.ptr<uint16_t>(),
                                          cos_cache.ptr<float>(), sin_cache.ptr<float>(), pos.ptr<int32_t>(),
                                          slot.ptr<int32_t>(), M, head_num, kv_head_num, head_size, eps,
                                          key_cache.get_dim(2), key_cache.get_dim(0), out_ptr<float>(q_out),
-                                         out_ptr<uint16_t>(key_cache), out_ptr<uint16_t>(value_cache), as_stream(stream)));
+                                         out_ptr<uint16_t>(key_cache), out_ptr<uint16_t>(value_cache), clear_input ? 1 : 0,
+                                         as_stream(stream)));
 }
 
 void mha_kernel_cu(const Tensor& query, const Tensor& key_cache, const Tensor& value_cache, const Tensor& seq_len,
@@ -126,13 +144,13 @@ void mha_kernel_cu(const Tensor& query, const Tensor& key_cache, const Tensor& v
                                   out_ptr<void>(workspace), workspace.byte_size(), as_stream(stream)));
 }
 
-void swiglu_kernel_cu(const Tensor& gate_up, const Tensor& output, void* stream) {
+void swiglu_kernel_cu(const Tensor& gate_up, const Tensor& output, bool clear_input, void* stream) {
     require_cuda(gate_up, "swiglu input");
     require_cuda(output, "swiglu output");
     CHECK_EQ(gate_up.size(), output.size() * 2);
     const int32_t I = output.get_dim(output.dims_size() - 1);
-    KERNEL_OK(kuiper_swiglu_f32(gate_up.ptr<float>(), out_ptr<float>(output), int32_t(output.size() / size_t(I)), I,
-                                as_stream(stream)));
+    KERNEL_OK(kuiper_swiglu_f32(out_ptr<float>(gate_up), out_ptr<float>(output), int32_t(output.size() / size_t(I)), I,
+                                clear_input ? 1 : 0, as_stream(stream)));
 }
 
 void emb_kernel_cu(const Tensor& tokens, const Tensor& table, const Tensor& output, int32_t vocab_size, void* stream) {
@@ -170,6 +188,9 @@ AddKernel get_add_kernel(base::DeviceType d) { return pick<AddKernel>(d, add_ker
 MatmulKernel get_matmul_kernel(base::DeviceType d) { return pick<MatmulKernel>(d, matmul_kernel_cu, "matmul"); }
 MatmulKernelQuant get_matmul_kernel_quant(base::DeviceType d) {
     return pick<MatmulKernelQuant>(d, matmul_kernel_quant_cu, "quantised matmul");
+}
+MatmulKernelQuantAccum get_matmul_kernel_quant_accum(base::DeviceType d) {
+    return pick<MatmulKernelQuantAccum>(d, matmul_kernel_quant_accum_cu, "accumulating quantised matmul");
 }
 RMSNormKernel get_rmsnorm_kernel(base::DeviceType d) { return pick<RMSNormKernel>(d, rmsnorm_kernel_cu, "rmsnorm"); }
 RoPEKernel get_rope_kernel(base::DeviceType d) { return pick<RoPEKernel>(d, rope_kernel_cu, "rope"); }

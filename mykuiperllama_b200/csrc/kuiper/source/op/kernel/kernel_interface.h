@@ -29,6 +29,11 @@ using MatmulKernelQuant = void (*)(const tensor::Tensor& input, const tensor::Te
                                    const tensor::Tensor& output, const tensor::Tensor* residual, int32_t group_size,
                                    int32_t act_mode, const tensor::Tensor& workspace, void* stream);
 
+// output[M,N] += input[M,K] . dequant(...): the output already holds the addend (residual stream or zeros)
+using MatmulKernelQuantAccum = void (*)(const tensor::Tensor& input, const tensor::Tensor& qweight,
+                                        const tensor::Tensor& qzeros, const tensor::Tensor& scales,
+                                        const tensor::Tensor& output, int32_t group_size, void* stream);
+
 using RMSNormKernel = void (*)(const tensor::Tensor& input, const tensor::Tensor& weight, const tensor::Tensor& output,
                                float eps, void* stream);
 
@@ -36,14 +41,14 @@ using RoPEKernel = void (*)(const tensor::Tensor& qkv, const tensor::Tensor& q_n
                             const tensor::Tensor& cos_cache, const tensor::Tensor& sin_cache, const tensor::Tensor& pos,
                             const tensor::Tensor& slot, const tensor::Tensor& q_out, const tensor::Tensor& key_cache,
                             const tensor::Tensor& value_cache, int32_t head_num, int32_t kv_head_num, int32_t head_size,
-                            float eps, void* stream);
+                            float eps, bool clear_input, void* stream);
 
 using MHAKernel = void (*)(const tensor::Tensor& query, const tensor::Tensor& key_cache, const tensor::Tensor& value_cache,
                            const tensor::Tensor& seq_len, const tensor::Tensor& slot, const tensor::Tensor& output,
                            int32_t head_num, int32_t kv_head_num, int32_t head_size, const tensor::Tensor& workspace,
                            void* stream);
 
-using SwigluKernel = void (*)(const tensor::Tensor& gate_up, const tensor::Tensor& output, void* stream);
+using SwigluKernel = void (*)(const tensor::Tensor& gate_up, const tensor::Tensor& output, bool clear_input, void* stream);
 
 using EmbeddingKernel = void (*)(const tensor::Tensor& tokens, const tensor::Tensor& table, const tensor::Tensor& output,
                                  int32_t vocab_size, void* stream);
@@ -53,6 +58,7 @@ using ArgmaxKernel = void (*)(const tensor::Tensor& logits, const tensor::Tensor
 AddKernel get_add_kernel(base::DeviceType device_type);
 MatmulKernel get_matmul_kernel(base::DeviceType device_type);
 MatmulKernelQuant get_matmul_kernel_quant(base::DeviceType device_type);
+MatmulKernelQuantAccum get_matmul_kernel_quant_accum(base::DeviceType device_type);
 RMSNormKernel get_rmsnorm_kernel(base::DeviceType device_type);
 RoPEKernel get_rope_kernel(base::DeviceType device_type);
 MHAKernel get_mha_kernel(base::DeviceType device_type);

@@ -67,7 +67,11 @@ base::Status MatmulLayer::forward() {
     base::Status status = check();
     if (!status) return status;
     if (device_type_ == base::DeviceType::DeviceCUDA) CHECK_NE(cuda_config_, nullptr);
-    if (is_quant_layer_) {
+    if (is_quant_layer_ && accumulate_) {
+        if (has_residual_) return base::error::invalid_argument("accumulate mode takes no residual input");
+        kernel::get_matmul_kernel_quant_accum(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),
+                                                            group_size_, stream());
+    } else if (is_quant_layer_) {
         kernel::get_matmul_kernel_quant(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),
                                                       has_residual_ ? &get_input(1) : nullptr, group_size_, act_mode_,
                                                       workspace_, stream());

@@ -61,7 +61,7 @@ base::Status RoPELayer::forward() {
     if (!status) return status;
     kernel::get_rope_kernel(device_type_)(get_input(0), get_weight(0), get_weight(1), get_input(3), get_input(4),
                                           get_input(1), get_input(2), get_output(0), key_cache_, value_cache_, head_num_,
-                                          kv_head_num_, head_size_, eps_, stream());
+                                          kv_head_num_, head_size_, eps_, clear_input_, stream());
     return base::error::success();
 }
 

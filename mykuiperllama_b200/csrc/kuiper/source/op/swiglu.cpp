@@ -30,7 +30,7 @@ base::Status SwiGLULayer::check() const {
 base::Status SwiGLULayer::forward() {
     base::Status status = check();
     if (!status) return status;
-    kernel::get_swiglu_kernel(device_type_)(get_input(0), get_output(0), stream());
+    kernel::get_swiglu_kernel(device_type_)(get_input(0), get_output(0), clear_input_, stream());
     return base::error::success();
 }
 

@@ -108,6 +108,27 @@ def test_awq_gemv_shapes(cuda, oracle, M, K, N, rows):
     assert err <= 1e-3
 
 
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (1, 4096, 6144), (1, 12288, 4096), (2, 1024, 3072), (3, 256, 1056), (1, 128, 32),
+                                   (1, 2560, 2560)])
+def test_awq_gemv_accumulate_mode(cuda, oracle, M, K, N):
+    # y += x.W on top of an addend already in y (the engine's path: residual stream or zeros)
+    rng = np.random.default_rng(K + N + M)
+    q, z, s = awq_random(rng, K, N)
+    qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    addend = rng.standard_normal((M, N)).astype(np.float32)
+    ref = oracle.awq_gemv(x, qw, qz, su, act_round=oracle.ROUND_FP16).astype(np.float64) + addend
+    y = dev(addend)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        cuda.awq_gemv_accum(dev(x), dev(qw), dev(qz), dev(su, torch.float16), y)
+    side.synchronize()
+    err = rel_err(y.cpu().numpy(), ref)
+    assert err <= SPEC_TOL and err <= 2e-6  # only the (unordered) fp32 summation differs from the mirrored oracle
+    cuda.awq_gemv_status()
+
+
 def test_awq_gemv_ragged_width_uses_generic_kernel(cuda, oracle):
     err, *_ = _gemv_case(cuda, oracle, np.random.default_rng(5), 2, 256, 40, 1, residual=True)
     assert err <= 2e-6
@@ -180,6 +201,25 @@ def test_swiglu(cuda, oracle):
     ref = np.stack([oracle.swiglu(gu[m, :3072], gu[m, 3072:]) for m in range(3)])
     y = cuda.swiglu(dev(gu)).cpu().numpy()
     assert rel_err(y, ref) <= 1e-6
+
+
+def test_swiglu_and_rope_can_clear_their_input(cuda, oracle):
+    # the accumulating matmuls need their output buffer zero again after the consumer has read it
+    rng = np.random.default_rng(12)
+    gu = dev((rng.standard_normal((2, 2 * 512)) * 3).astype(np.float32))
+    ref = cuda.swiglu(gu.clone()).cpu().numpy()
+    out = cuda.swiglu(gu, clear_input=True)
+    assert np.array_equal(out.cpu().numpy(), ref) and float(gu.abs().max()) == 0.0
+    Nq, Nkv, D = 4, 2, 128
+    qkv = dev(rng.standard_normal((3, (Nq + 2 * Nkv) * D)).astype(np.float32))
+    qn = dev(oracle.f32_to_bf16(np.ones(D, np.float32)))
+    cos_t, sin_t = oracle.rope_tables(16, D, 1e6)
+    pos, slot = dev(np.array([0, 1, 2], np.int32)), dev(np.zeros(3, np.int32))
+    kc = torch.zeros((1, Nkv, 16, D), dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    q1 = cuda.qknorm_rope_kvwrite(qkv.clone(), qn, qn, dev(cos_t), dev(sin_t), pos, slot, Nq, Nkv, D, 1e-6, kc.clone(), vc.clone())
+    q2 = cuda.qknorm_rope_kvwrite(qkv, qn, qn, dev(cos_t), dev(sin_t), pos, slot, Nq, Nkv, D, 1e-6, kc, vc, clear_input=True)
+    assert torch.equal(q1, q2) and float(qkv.abs().max()) == 0.0
 
 
 def test_embedding_is_exact(cuda, oracle):
