@@ -480,6 +480,7 @@ def main():
     ap.add_argument("--mats", type=int, default=0, help="distinct weight matrices in the gemv microbenchmark (0 = 512 MiB worth)")
     ap.add_argument("--gemv-impl", type=int, default=None, help="0 persistent TMA kernel, 1 register-staged kernel")
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--prompt", type=int, default=None, help="override the workload's prompt length (profiling aid)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "engine":
         args.warmup = 3
@@ -487,6 +488,9 @@ def main():
         run_gemv_micro(args)
         return
     cfg, prompt_len, _, _, desc = WORKLOADS[args.workload]
+    if args.prompt is not None:
+        prompt_len = args.prompt
+        desc += f" (prompt overridden to {prompt_len} tokens)"
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":

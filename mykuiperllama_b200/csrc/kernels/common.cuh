@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <utility>
 
 #include "kuiper_b200.h"
 
@@ -28,6 +29,33 @@ void set_error(const char* fmt, ...);
 // after a launch: map a launch failure onto the InternalError status
 inline int launch_status(const char* what) {
     cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        set_error("%s launch failed: %s", what, cudaGetErrorString(err));
+        return KUIPER_INTERNAL_ERROR;
+    }
+    return KUIPER_OK;
+}
+
+// Launch with the programmatic-dependent-launch attribute: the kernel may be scheduled while its
+// predecessor in the stream is still running, so it must call pdl_wait() before touching anything
+// the predecessor produces (every kernel of this library does, at its top or after a prefetch).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl_enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+inline int pdl_status(cudaError_t err, const char* what) {
     if (err != cudaSuccess) {
         set_error("%s launch failed: %s", what, cudaGetErrorString(err));
         return KUIPER_INTERNAL_ERROR;

@@ -31,6 +31,7 @@ namespace {
 // per thread (add_kernel.cu:4-12).
 __global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
                            int64_t n, int vec_ok) {
+    pdl_launch_dependents();
     pdl_wait();
     const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
@@ -44,30 +45,70 @@ __global__ void add_kernel(const float* __restrict__ a, const float* __restrict_
 }
 
 // ---------------------------------------------------------------- rmsnorm
-// one CTA per token row
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* x, const uint16_t* __restrict__ w, float* y, int H,
-                                                      float eps) {
-    __shared__ float s_part[8];
+// One CTA of 1024 threads per token row.  The row is read once, with every load of a thread issued
+// before the first use (a single CTA is latency bound, so rounds of dependent loads are what costs).
+constexpr int kNormThreads = 1024;
+constexpr int kNormVec = 4;  // float4 per thread held in registers: rows up to 16384 wide
+
+__device__ __forceinline__ float block_sum_1024(float v, float* s_part) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float tot = (threadIdx.x & 31) < (kNormThreads / 32) ? s_part[threadIdx.x & 31] : 0.f;
+    return warp_sum(tot);  // every warp reduces the 32 partials itself: same order, same value everywhere
+}
+
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const float* x, const uint16_t* __restrict__ w, float* y, int H,
+                                                               float eps) {
+    __shared__ float s_part[kNormThreads / 32];
+    pdl_launch_dependents();
     pdl_wait();
     const float* xr = x + size_t(blockIdx.x) * H;
     float* yr = y + size_t(blockIdx.x) * H;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = xr[i];
-        ss = fmaf(v, v, ss);
-    }
-    ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.f;
+    const int t = threadIdx.x;
+    if ((H & 3) == 0 && H <= kNormThreads * kNormVec * 4 && (reinterpret_cast<uintptr_t>(xr) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(yr) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 7) == 0) {
+        const int n4 = H >> 2;
+        float4 v[kNormVec];
+        uint2 wv[kNormVec];
 #pragma unroll
-    for (int i = 0; i < 8; i++) tot += s_part[i];
-    const float rstd = 1.0f / sqrtf(tot / float(H) + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = (xr[i] * rstd) * bf16_bits_to_float(w[i]);
+        for (int j = 0; j < kNormVec; j++) {
+            const int i = t + j * kNormThreads;
+            v[j] = i < n4 ? __ldcg(reinterpret_cast<const float4*>(xr) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            wv[j] = i < n4 ? __ldg(reinterpret_cast<const uint2*>(w) + i) : make_uint2(0, 0);
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < kNormVec; j++) {
+            ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+            ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+        }
+        const float rstd = 1.0f / sqrtf(block_sum_1024(ss, s_part) / float(H) + eps);
+#pragma unroll
+        for (int j = 0; j < kNormVec; j++) {
+            const int i = t + j * kNormThreads;
+            if (i < n4) {
+                float4 o;
+                o.x = (v[j].x * rstd) * bf16_lo(wv[j].x); o.y = (v[j].y * rstd) * bf16_hi(wv[j].x);
+                o.z = (v[j].z * rstd) * bf16_lo(wv[j].y); o.w = (v[j].w * rstd) * bf16_hi(wv[j].y);
+                reinterpret_cast<float4*>(yr)[i] = o;
+            }
+        }
+        return;
+    }
+    // any width / alignment: two scalar passes
+    float ss = 0.f;
+    for (int i = t; i < H; i += kNormThreads) {
+        const float a = xr[i];
+        ss = fmaf(a, a, ss);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum_1024(ss, s_part) / float(H) + eps);
+    for (int i = t; i < H; i += kNormThreads) yr[i] = (xr[i] * rstd) * bf16_bits_to_float(w[i]);
 }
 
 // ---------------------------------------------------------------- swiglu
 __global__ void swiglu_kernel(float* gate_up, float* out, int M, int I, int clear_input) {
+    pdl_launch_dependents();
     pdl_wait();
     const int64_t total = int64_t(M) * I;
     for (int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += int64_t(gridDim.x) * blockDim.x) {
@@ -83,6 +124,7 @@ __global__ void swiglu_kernel(float* gate_up, float* out, int M, int I, int clea
 
 // ---------------------------------------------------------------- embedding
 __global__ void embedding_kernel(const int32_t* tokens, const uint16_t* __restrict__ table, float* out, int H, int vocab) {
+    pdl_launch_dependents();
     pdl_wait();
     int tok = tokens[blockIdx.x];
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);  // clamp: never read outside the table
@@ -91,23 +133,50 @@ __global__ void embedding_kernel(const int32_t* tokens, const uint16_t* __restri
 }
 
 // ---------------------------------------------------------------- argmax
-// one CTA per row; ties go to the lowest index
+// one CTA of 1024 threads per row; ties go to the lowest index.  Eight 16-byte loads are in flight
+// per thread so that the single CTA is bandwidth bound, not latency bound.
+__device__ __forceinline__ void argmax_take(float v, int i, float& best, int& bi) {
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+}
+
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int32_t* out, int V) {
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
+    pdl_launch_dependents();
     pdl_wait();
     const float* l = logits + size_t(blockIdx.x) * V;
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        float v = l[i];
-        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    const int t = threadIdx.x;
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(l) & 15) == 0) {
+        const int n4 = V >> 2;
+        constexpr int kU = 8;
+        int i = t;
+        for (; i + (kU - 1) * 1024 < n4; i += kU * 1024) {
+            float4 v[kU];
+#pragma unroll
+            for (int u = 0; u < kU; u++) v[u] = __ldcg(reinterpret_cast<const float4*>(l) + i + u * 1024);
+#pragma unroll
+            for (int u = 0; u < kU; u++) {
+                const int b = (i + u * 1024) * 4;
+                argmax_take(v[u].x, b, best, bi); argmax_take(v[u].y, b + 1, best, bi);
+                argmax_take(v[u].z, b + 2, best, bi); argmax_take(v[u].w, b + 3, best, bi);
+            }
+        }
+        for (; i < n4; i += 1024) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(l) + i);
+            argmax_take(v.x, i * 4, best, bi); argmax_take(v.y, i * 4 + 1, best, bi);
+            argmax_take(v.z, i * 4 + 2, best, bi); argmax_take(v.w, i * 4 + 3, best, bi);
+        }
+        done = n4 * 4;
     }
+    for (int i = done + t; i < V; i += 1024) argmax_take(l[i], i, best, bi);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         float ov = __shfl_xor_sync(0xffffffffu, best, o);
         int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        argmax_take(ov, oi, best, bi);
     }
     if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = bi; }
     __syncthreads();
@@ -119,7 +188,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int32
         for (int o = 16; o > 0; o >>= 1) {
             float ov = __shfl_xor_sync(0xffffffffu, best, o);
             int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+            argmax_take(ov, oi, best, bi);
         }
         if (threadIdx.x == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;  // all-NaN row -> 0
     }
@@ -180,6 +249,7 @@ __global__ void awq_dequant_kernel(const int32_t* __restrict__ qw, const int32_t
 // ---------------------------------------------------------------- decode bookkeeping
 __global__ void decode_advance_kernel(int32_t* tokens, const int32_t* next, int32_t* pos, int32_t* seq_len, int B,
                                       int max_seq) {
+    pdl_launch_dependents();
     pdl_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
@@ -227,38 +297,34 @@ extern "C" int kuiper_add_f32(const float* a, const float* b, float* out, int64_
     KUIPER_REQUIRE(a && b && out, "add: null tensor pointer");
     KUIPER_REQUIRE(n > 0, "add: empty tensor");
     const int vec_ok = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-    add_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, as_stream(stream)>>>(a, b, out, n, vec_ok);
-    return launch_status("add");
+    return pdl_status(launch_pdl(add_kernel, dim3(grid_for((n + 3) / 4, 256)), dim3(256), 0, as_stream(stream), a, b, out, n, vec_ok), "add");
 }
 
 extern "C" int kuiper_rmsnorm_f32(const float* x, const uint16_t* w, float* y, int M, int H, float eps,
                                   kuiper_stream_t stream) {
     KUIPER_REQUIRE(x && w && y, "rmsnorm: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && H > 0, "rmsnorm: empty shape M=%d H=%d", M, H);
-    rmsnorm_kernel<<<M, 256, 0, as_stream(stream)>>>(x, w, y, H, eps);
-    return launch_status("rmsnorm");
+    return pdl_status(launch_pdl(rmsnorm_kernel, dim3(M), dim3(kNormThreads), 0, as_stream(stream), x, w, y, H, eps), "rmsnorm");
 }
 
 extern "C" int kuiper_swiglu_f32(float* gate_up, float* out, int M, int I, int clear_input, kuiper_stream_t stream) {
     KUIPER_REQUIRE(gate_up && out, "swiglu: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && I > 0, "swiglu: empty shape M=%d I=%d", M, I);
-    swiglu_kernel<<<grid_for(int64_t(M) * I, 256), 256, 0, as_stream(stream)>>>(gate_up, out, M, I, clear_input);
-    return launch_status("swiglu");
+    return pdl_status(launch_pdl(swiglu_kernel, dim3(grid_for(int64_t(M) * I, 256)), dim3(256), 0, as_stream(stream), gate_up, out, M, I,
+                                 clear_input), "swiglu");
 }
 
 extern "C" int kuiper_embedding_bf16(const int32_t* tokens, const uint16_t* table, float* out, int M, int H,
                                      int vocab, kuiper_stream_t stream) {
     KUIPER_REQUIRE(tokens && table && out, "embedding: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && H > 0 && vocab > 0, "embedding: empty shape M=%d H=%d vocab=%d", M, H, vocab);
-    embedding_kernel<<<M, 256, 0, as_stream(stream)>>>(tokens, table, out, H, vocab);
-    return launch_status("embedding");
+    return pdl_status(launch_pdl(embedding_kernel, dim3(M), dim3(256), 0, as_stream(stream), tokens, table, out, H, vocab), "embedding");
 }
 
 extern "C" int kuiper_argmax_f32(const float* logits, int32_t* out, int M, int V, kuiper_stream_t stream) {
     KUIPER_REQUIRE(logits && out, "argmax: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && V > 0, "argmax: empty shape M=%d V=%d", M, V);
-    argmax_kernel<<<M, 1024, 0, as_stream(stream)>>>(logits, out, V);
-    return launch_status("argmax");
+    return pdl_status(launch_pdl(argmax_kernel, dim3(M), dim3(1024), 0, as_stream(stream), logits, out, V), "argmax");
 }
 
 extern "C" int kuiper_awq_unpack_u8(const int32_t* qweight, uint8_t* out, int K, int N, kuiper_stream_t stream) {
@@ -301,6 +367,6 @@ extern "C" int kuiper_decode_advance(int32_t* tokens, const int32_t* next, int32
                                      int B, int max_seq, kuiper_stream_t stream) {
     KUIPER_REQUIRE(tokens && next && pos && seq_len, "decode_advance: null tensor pointer");
     KUIPER_REQUIRE(B > 0 && max_seq > 0, "decode_advance: empty shape");
-    decode_advance_kernel<<<(B + 127) / 128, 128, 0, as_stream(stream)>>>(tokens, next, pos, seq_len, B, max_seq);
-    return launch_status("decode_advance");
+    return pdl_status(launch_pdl(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, as_stream(stream), tokens, next, pos,
+                                 seq_len, B, max_seq), "decode_advance");
 }

@@ -230,18 +230,49 @@ flash_decode_kernel(const FlashParams p) {
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // ---- final combine by the last CTA: fetch every slice's (max, sum) at once, turn them into
+    // weights in shared memory, then add the partial outputs in slice order with eight loads in flight
+    __shared__ float s_w[64 * R];   // weight of slice sp for head h at [sp * R + h]
+    __shared__ float s_l[64 * R];   // softmax denominators of the slices
+    __shared__ float s_den[R];
+    for (int i = t; i < p.S * R; i += kWarps * 32) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (pbase * R + i) * 2));
+        s_w[i] = ml.x;  // slice maximum
+        s_l[i] = ml.y;
+    }
+    __syncthreads();
+    if (t < R) {
+        float nm = -INFINITY;
+        for (int sp = 0; sp < p.S; sp++) nm = fmaxf(nm, s_w[sp * R + t]);
+        s_den[t] = nm;
+    }
+    __syncthreads();
+    for (int i = t; i < p.S * R; i += kWarps * 32) {
+        const float wm = s_w[i], nm = s_den[i % R];
+        s_w[i] = (wm == -INFINITY) ? 0.f : __expf(wm - nm);
+    }
+    __syncthreads();
+    if (t < R) {
+        float den = 0.f;
+        for (int sp = 0; sp < p.S; sp++) den += s_l[sp * R + t] * s_w[sp * R + t];
+        s_den[t] = den;
+    }
+    __syncthreads();
 #pragma unroll
     for (int h = 0; h < R; h++) {
-        float nm = -INFINITY;
-        for (int sp = 0; sp < p.S; sp++) nm = fmaxf(nm, __ldcg(p.part_ml + ((pbase + sp) * R + h) * 2));
-        float acc = 0.f, ssum = 0.f;
-        for (int sp = 0; sp < p.S; sp++) {
-            const float wm = __ldcg(p.part_ml + ((pbase + sp) * R + h) * 2);
-            const float c = (wm == -INFINITY) ? 0.f : __expf(wm - nm);
-            acc += __ldcg(p.part_o + ((pbase + sp) * R + h) * kD + t) * c;
-            ssum += __ldcg(p.part_ml + ((pbase + sp) * R + h) * 2 + 1) * c;
+        float acc = 0.f;
+        const float* po = p.part_o + (pbase * R + h) * kD + t;
+        int sp = 0;
+        for (; sp + 8 <= p.S; sp += 8) {
+            float a[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) a[q] = __ldcg(po + size_t(sp + q) * R * kD);
+#pragma unroll
+            for (int q = 0; q < 8; q++) acc = fmaf(a[q], s_w[(sp + q) * R + h], acc);
         }
-        p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + t] = ssum > 0.f ? acc / ssum : 0.f;
+        for (; sp < p.S; sp++) acc = fmaf(__ldcg(po + size_t(sp) * R * kD), s_w[sp * R + h], acc);
+        const float den = s_den[h];
+        p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + t] = den > 0.f ? acc / den : 0.f;
     }
 }
 

@@ -18,6 +18,7 @@ qknorm_rope_kvwrite_kernel(float* qkv, const uint16_t* __restrict__ q_norm_w, co
                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int32_t* pos,
                            const int32_t* slot, int M, int Nq, int Nkv, float eps, int max_seq, int n_slots, float* q_out,
                            uint16_t* kcache, uint16_t* vcache, int clear_input) {
+    pdl_launch_dependents();
     pdl_wait();
     const int heads = Nq + 2 * Nkv;
     const int wid = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -87,7 +88,8 @@ extern "C" int kuiper_qknorm_rope_kvwrite(float* qkv, const uint16_t* q_norm_w, 
     KUIPER_REQUIRE(D == kD, "qknorm_rope: head_dim %d is not supported (128 only)", D);
     KUIPER_REQUIRE(M > 0 && Nq > 0 && Nkv > 0 && max_seq > 0 && n_slots > 0, "qknorm_rope: empty shape");
     const int warps = M * (Nq + 2 * Nkv);
-    qknorm_rope_kvwrite_kernel<<<(warps + 3) / 4, 128, 0, as_stream(stream)>>>(
-        qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, M, Nq, Nkv, eps, max_seq, n_slots, q_out, kcache, vcache, clear_input);
-    return launch_status("qknorm_rope_kvwrite");
+    return pdl_status(launch_pdl(qknorm_rope_kvwrite_kernel, dim3((warps + 3) / 4), dim3(128), 0, as_stream(stream), qkv, q_norm_w,
+                                 k_norm_w, cos_t, sin_t, pos, slot, M, Nq, Nkv, eps, max_seq, n_slots, q_out, kcache, vcache,
+                                 clear_input),
+                      "qknorm_rope_kvwrite");
 }
