@@ -99,6 +99,24 @@ KUIPER_API int kuiper_awq_gemv_accum_f32(const float* x, const int32_t* qweight,
 /* health check (synchronises): 5 if a bounded wait inside the pipelined GEMV ever ran out on this device */
 KUIPER_API int kuiper_awq_gemv_status(void);
 
+/*
+ * The INT4 GEMV once more, for callers that must not allocate: no counterpart in the reference (its
+ * kernels take caller-owned tensors only and it has no split-K scratch at all).  Meant for code that
+ * runs after the application has committed all device memory to its own pool, or inside a loop where
+ * cudaMalloc and the synchronisation it implies are ruled out.  The scratch of the ordered combine
+ * lives in a fixed array inside the library image (kuiper_awq_gemv_noalloc_scratch_bytes(), about
+ * 2.1 MiB held per GPU for the life of the process); the call itself allocates nothing, on the host
+ * or on the device.  Limits: N <= 32768, N % 32 == 0, K % 128 == 0, group 128, M <= 8; other sizes
+ * return 7.  Same result as kuiper_awq_gemv_f32 up to fp32 summation order.  The first call on a
+ * device resolves the array's device address: issue it before any stream capture.  All calls on a
+ * device share the array, so calls that may overlap on the GPU race; its counters are cleared at the
+ * start of each call.
+ */
+KUIPER_API size_t kuiper_awq_gemv_noalloc_scratch_bytes(void);
+KUIPER_API int kuiper_awq_gemv_f32_noalloc(const float* x, const int32_t* qweight, const int32_t* qzeros,
+                                           const uint16_t* scales, float* y, const float* residual,
+                                           int M, int K, int N, int group, kuiper_stream_t stream);
+
 /* ---- BF16 GEMV (lm_head): W bf16 [N, K], y[M,N] = x[M,K] . W^T ---- */
 KUIPER_API int kuiper_bf16_gemv_f32(const float* x, const uint16_t* W, float* y, int M, int K, int N,
                          kuiper_stream_t stream);

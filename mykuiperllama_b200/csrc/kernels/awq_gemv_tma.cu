@@ -601,4 +601,123 @@ int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* q
     return launch_tma<1, 5, false>(map, p, int(ctas), stream);
 }
 
+// ---------------------------------------------------------------- entry point that allocates nothing
+//
+// Some callers cannot hand this library a workspace: code that runs after the host application has
+// given every byte of device memory to its own pool, or inside a serving loop where cudaMalloc (and
+// the device-wide synchronisation it implies) is not an option.  For them the ordered-combine GEMV is
+// offered once more with its scratch (arrival counters + partial-row slots) in a fixed array that is
+// part of the library image: every GPU that loads the library holds kNoAllocScratchBytes for it until
+// the process exits.
+namespace {
+
+constexpr int kNoAllocMaxN = 32768;                       // 32 column tiles
+constexpr int kNoAllocMaxCtas = 512;                      // partial-row slots: one per CTA + one per tile
+constexpr size_t kNoAllocHeadBytes = 256;                 // arrival counters (32 ints), padded
+constexpr size_t kNoAllocScratchBytes =
+    kNoAllocHeadBytes + size_t(kNoAllocMaxCtas + kNoAllocMaxN / kTileColsTma) * kTileColsTma * sizeof(float);  // 2 228 480 B
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+std::mutex g_noalloc_mu;
+
+// The array's name is only a host-side stand-in; the address the kernel needs comes from the runtime,
+// once per device, with that device current.
+int noalloc_scratch(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_error("awq_gemv_noalloc: cannot identify the current device");
+        return KUIPER_INTERNAL_ERROR;
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (err != cudaSuccess || ptr == nullptr) {
+            set_error("awq_gemv_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(err));
+            return KUIPER_INTERNAL_ERROR;
+        }
+        g_noalloc_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_ptr[dev];
+    return KUIPER_OK;
+}
+
+// tensor map built on the stack: nothing is cached, nothing is allocated
+bool encode_tensor_map_once(const int32_t* qweight, int K, int N, CUtensorMap* out) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cuuint64_t(N / 8), cuuint64_t(K)};
+    const cuuint64_t strides[1] = {cuuint64_t(N / 8) * 4};
+    const cuuint32_t box[2] = {kTileWords, kUnitRows};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<int32_t*>(qweight), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
 }  // namespace kuiper
+
+using namespace kuiper;
+
+extern "C" size_t kuiper_awq_gemv_noalloc_scratch_bytes(void) { return kNoAllocScratchBytes; }
+
+// y[M,N] = x[M,K] . dequant(qweight) (+ residual), same result as kuiper_awq_gemv_f32 up to the order of the
+// fp32 partial sums, without a caller workspace and without any allocation.
+//  - limits: N <= 32768, N % 32 == 0, K % 128 == 0, group 128, M <= 8; anything else is rejected with status 7;
+//  - the first call on a device looks up the scratch array's device address (and sets the kernel's shared
+//    memory attribute); make that first call before starting a stream capture;
+//  - all calls on a device share the one scratch array: calls that can overlap on the GPU (different streams,
+//    or a captured graph replayed concurrently) race on it.  The counters it holds are cleared at the start of
+//    every call, so a call that was cut short does not poison the next one.
+extern "C" int kuiper_awq_gemv_f32_noalloc(const float* x, const int32_t* qweight, const int32_t* qzeros,
+                                           const uint16_t* scales, float* y, const float* residual, int M, int K, int N,
+                                           int group, kuiper_stream_t stream) {
+    KUIPER_REQUIRE(x && qweight && qzeros && scales && y, "awq_gemv_noalloc: null tensor pointer");
+    KUIPER_REQUIRE(M > 0 && K > 0 && N > 0, "awq_gemv_noalloc: empty shape M=%d K=%d N=%d", M, K, N);
+    KUIPER_REQUIRE(group == 128, "awq_gemv_noalloc: group size %d is not supported (128 only)", group);
+    KUIPER_REQUIRE(K % 128 == 0 && N % 32 == 0, "awq_gemv_noalloc: needs K %% 128 == 0 and N %% 32 == 0 (K=%d N=%d)", K, N);
+    KUIPER_REQUIRE(N <= kNoAllocMaxN, "awq_gemv_noalloc: N=%d exceeds the built-in scratch (max N %d)", N, kNoAllocMaxN);
+    KUIPER_REQUIRE(M <= 8, "awq_gemv_noalloc: M=%d exceeds the limit of 8 token rows", M);
+    KUIPER_REQUIRE(((reinterpret_cast<uintptr_t>(qweight) | reinterpret_cast<uintptr_t>(qzeros) | reinterpret_cast<uintptr_t>(scales) |
+                     reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual)) & 15) == 0,
+                   "awq_gemv_noalloc: tensors must be 16-byte aligned");
+    void* scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc != KUIPER_OK) return rc;
+    CUtensorMap map;
+    if (!encode_tensor_map_once(qweight, K, N, &map)) {
+        set_error("awq_gemv_noalloc: tensor map encoding failed");
+        return KUIPER_INTERNAL_ERROR;
+    }
+    cudaStream_t st = as_stream(stream);
+    TmaGemvParams p;
+    p.qz = reinterpret_cast<const uint2*>(qzeros);
+    p.scales = reinterpret_cast<const __half*>(scales);
+    p.K = K;
+    p.N = N;
+    p.tiles = (N + kTileColsTma - 1) / kTileColsTma;
+    p.upt = K / kUnitRows;
+    p.U = (long long)p.tiles * p.upt;
+    p.counters = reinterpret_cast<int*>(scratch);
+    p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + kNoAllocHeadBytes);
+    long long ctas = (long long)sm_count() * kCtasPerSm;
+    if (ctas > kNoAllocMaxCtas) ctas = kNoAllocMaxCtas;
+    if (ctas > p.U) ctas = p.U;
+    for (int m = 0; m < M; m++) {  // one token row per launch: a slot then holds a single partial row
+        cudaError_t err = cudaMemsetAsync(scratch, 0, kNoAllocHeadBytes, st);
+        if (err != cudaSuccess) {
+            set_error("awq_gemv_noalloc: clearing the counters failed: %s", cudaGetErrorString(err));
+            return KUIPER_INTERNAL_ERROR;
+        }
+        p.x = x + size_t(m) * K;
+        p.y = y + size_t(m) * N;
+        p.residual = residual ? residual + size_t(m) * N : nullptr;
+        rc = launch_tma<1, 5, false>(map, p, int(ctas), st);
+        if (rc != KUIPER_OK) return rc;
+    }
+    return KUIPER_OK;
+}
