@@ -248,7 +248,7 @@ def gemv_roofline(cfg, tp, layers_kept, iters=3):
     from mykuiperllama_b200 import capi
     shapes = layer_shapes(cfg, tp)
     x = {n: torch.randn((1, K), device="cuda") for n, (K, N) in shapes.items()}
-    y = {n: torch.empty((1, N), device="cuda") for n, (K, N) in shapes.items()}
+    y = {n: torch.zeros((1, N), device="cuda") for n, (K, N) in shapes.items()}
     ws = capi.awq_gemv_workspace(1, max(K for K, _ in shapes.values()), max(N for _, N in shapes.values()))
     L = cfg["n_layers"]
 
@@ -256,7 +256,7 @@ def gemv_roofline(cfg, tp, layers_kept, iters=3):
         for l in range(L):
             lw = layers_kept[l % len(layers_kept)]
             for n in ("qkv", "o", "gu", "down"):
-                capi.awq_gemv(x[n], lw[f"{n}_qw"], lw[f"{n}_qz"], lw[f"{n}_s"], workspace=ws, out=y[n])
+                capi.awq_gemv_accum(x[n], lw[f"{n}_qw"], lw[f"{n}_qz"], lw[f"{n}_s"], y[n])  # the engine's path
 
     one_token()
     torch.cuda.synchronize()
@@ -394,7 +394,7 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
     if world == 1:
         per_launch_bytes, per_launch_s, launches = gemv_roofline(cfg, 1, keep)
         achieved = per_launch_bytes / per_launch_s / 1e9
-        line["roofline"] = {"bound": "hbm", "kernel": "awq_gemv_kernel", "achieved": achieved, "peak": peak,
+        line["roofline"] = {"bound": "hbm", "kernel": "awq_gemv_tma_kernel<1,5,accumulate>", "achieved": achieved, "peak": peak,
                             "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS, "traffic": None,
                             "launches_per_token": launches, "avg_bytes_per_launch": int(per_launch_bytes),
@@ -421,7 +421,9 @@ def run_gemv_micro(args):
     from mykuiperllama_b200 import capi
     torch.cuda.set_device(0)
     K, N = (int(v) for v in args.shape.lower().split("x"))
-    if args.gemv_impl is not None:
+    if args.gemv_impl is None:
+        args.gemv_impl = 2
+    if args.gemv_impl in (0, 1):
         capi.set_tuning("gemv_impl", args.gemv_impl)
     per = int4_bytes(K, N) + 4 * K + 4 * N
     n = args.mats or max(2, min(256, (512 << 20) // per))
@@ -431,12 +433,15 @@ def run_gemv_micro(args):
     qz = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 128, N // 8), dtype=torch.int32, device="cuda", generator=gen) for _ in range(n)]
     sc = [(torch.rand((K // 128, N), device="cuda", generator=gen) * 0.018 + 0.002).half() for _ in range(n)]
     x = torch.randn((1, K), device="cuda", generator=gen)
-    y = torch.empty((1, N), device="cuda")
+    y = torch.zeros((1, N), device="cuda")
     ws = capi.awq_gemv_workspace(1, K, N)
 
     def sweep():
         for i in range(n):
-            capi.awq_gemv(x, qw[i], qz[i], sc[i], workspace=ws, out=y)
+            if args.gemv_impl == 2:
+                capi.awq_gemv_accum(x, qw[i], qz[i], sc[i], y)
+            else:
+                capi.awq_gemv(x, qw[i], qz[i], sc[i], workspace=ws, out=y)
 
     for _ in range(args.warmup):
         sweep()
@@ -478,7 +483,7 @@ def main():
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["gemv"])
     ap.add_argument("--shape", default="2048x2048", help="KxN of the gemv microbenchmark")
     ap.add_argument("--mats", type=int, default=0, help="distinct weight matrices in the gemv microbenchmark (0 = 512 MiB worth)")
-    ap.add_argument("--gemv-impl", type=int, default=None, help="0 persistent TMA kernel, 1 register-staged kernel")
+    ap.add_argument("--gemv-impl", type=int, default=None, help="2 accumulate mode of the TMA kernel (engine path, default), 0 its ordered combine, 1 register-staged kernel")
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--prompt", type=int, default=None, help="override the workload's prompt length (profiling aid)")
     args = ap.parse_args()
