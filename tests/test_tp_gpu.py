@@ -1,0 +1,20 @@
+"""Tensor-parallel engine on 2 GPUs (one process per GPU, NCCL all-reduce after the row-split projections)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_tensor_parallel_matches_oracle():
+    env = dict(os.environ, OMP_NUM_THREADS="4", NCCL_NVLS_ENABLE="0")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29577", os.path.join(ROOT, "tests", "tp_worker.py")],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    assert "tp-rank0-ok" in res.stdout and "tp-rank1-ok" in res.stdout
