@@ -288,10 +288,10 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    B = 1
+    B = max(1, args.batch)
     steps_total = args.warmup + args.steps
     max_seq = prompt_len + 2 * steps_total + 16
-    ecfg = eng_mod.EngineConfig(**cfg, max_seq=max_seq, max_batch=B, max_rows=8, tp_rank=rank, tp_size=world)
+    ecfg = eng_mod.EngineConfig(**cfg, max_seq=max_seq, max_batch=B, max_rows=max(8, B), tp_rank=rank, tp_size=world)
     eng = eng_mod.Qwen3Engine(ecfg)
 
     gen = torch.Generator(device=device)
@@ -317,7 +317,7 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
     rng = np.random.default_rng(7)
     prompt = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
     t0 = time.perf_counter()
-    first = eng.prefill(prompt, slot=0)
+    firsts = [eng.prefill(np.roll(prompt, b), slot=b) for b in range(B)]  # a different prompt per sequence
     prefill_s = time.perf_counter() - t0
 
     stream = torch.cuda.ExternalStream(eng.stream, device=device)
@@ -328,7 +328,7 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         torch.cuda.synchronize()
 
     # ---- device-resident loop: value
-    eng.decode_begin([first], [prompt_len], [0])
+    eng.decode_begin(firsts, [prompt_len] * B, list(range(B)))
     eng.decode_step(args.warmup)
     eng.synchronize()
     barrier()
@@ -345,12 +345,12 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     value = args.steps * B / (ms * 1e-3)
-    tok_after = int(eng.decode_read(1)[0])
+    tok_after = eng.decode_read(B)
 
     # ---- end to end: host token in, host token out, every step
     pos_now = prompt_len + steps_total
-    eng.decode_begin([tok_after], [pos_now], [0])
-    tok = np.array([tok_after], np.int32)
+    eng.decode_begin(tok_after, [pos_now] * B, list(range(B)))
+    tok = np.array(tok_after, np.int32)
     for _ in range(args.warmup):
         tok = eng.decode_predict(tok)
     barrier()
@@ -381,7 +381,7 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights (AWQ g128), fp16 x operand, fp32 accumulate",
         "data": "synthetic",
-        "config": {"workload": desc, "batch": B, "prompt_tokens": prompt_len, "context_during_timing": ctx_mid,
+        "config": {"workload": desc if B == 1 else desc.replace("batch 1", f"batch {B}"), "batch": B, "prompt_tokens": prompt_len, "context_during_timing": ctx_mid,
                    "parallelism": f"tp{world}", "l2_policy": "inputs larger than L2 (weights streamed once per token)",
                    "prefill_s": round(prefill_s, 3)},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
@@ -475,22 +475,82 @@ def run_gemv_micro(args):
         "gpu_launches": n * args.steps, "clocks": clocks.summary()}), flush=True)
 
 
+def run_attn_micro(args):
+    """GQA flash-decoding alone (config 3 of the workload list): 32 query heads over 8 KV heads, head_dim 128, bf16
+    cache ~N(0,1); distinct caches totalling more than L2 are visited in turn, so the KV rows stream from HBM."""
+    import torch
+    from mykuiperllama_b200 import capi
+    torch.cuda.set_device(0)
+    B, L, Nq, Nkv, D = max(1, args.batch), args.kv_len, 32, 8, 128
+    kv_bytes = B * 2 * Nkv * L * D * 2
+    n = max(2, min(64, (384 << 20) // kv_bytes + 1))
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0)
+    kc = [torch.randn((B, Nkv, L, D), device="cuda", generator=gen).bfloat16() for _ in range(n)]
+    vc = [torch.randn((B, Nkv, L, D), device="cuda", generator=gen).bfloat16() for _ in range(n)]
+    q = torch.randn((B, Nq, D), device="cuda", generator=gen)
+    out = torch.empty_like(q)
+    seq = torch.full((B,), L, dtype=torch.int32, device="cuda")
+    slot = torch.arange(B, dtype=torch.int32, device="cuda")
+    ws = capi.flash_decode_workspace(B, Nq, D, L)
+
+    def sweep():
+        for i in range(n):
+            capi.flash_decode(q, kc[i], vc[i], seq, slot, workspace=ws, out=out)
+
+    for _ in range(args.warmup):
+        sweep()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        sweep()
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    with ClockSampler(0) as clocks:
+        for _ in range(args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+    ms = float(np.median(times))
+    gbs = kv_bytes * n / (ms * 1e-3) / 1e9
+    peak, kind = measured_peak_gbs()
+    print(json.dumps({
+        "metric": "GQA flash-decoding KV-read GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 KV cache, fp32 softmax and accumulation", "data": "synthetic",
+        "config": {"workload": f"flash-decoding batch {B}, 32 q heads / 8 kv heads, head_dim 128, KV length {L}",
+                   "distinct_caches": n, "l2_policy": f"{n} caches ({kv_bytes * n >> 20} MiB) visited in turn: larger than L2"},
+        "roofline": {"bound": "hbm", "kernel": "flash_decode_kernel<4>", "achieved": gbs, "peak": peak, "peak_kind": kind,
+                     "unit": "GB/s", "frac": gbs / peak, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS, "traffic": None,
+                     "avg_us_per_launch": ms * 1e3 / n, "avg_bytes_per_launch": kv_bytes},
+        "gpu_launches": n * args.steps, "clocks": clocks.summary()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["gemv"])
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["gemv", "attn"])
+    ap.add_argument("--kv-len", type=int, default=4096, help="KV length of the attn microbenchmark")
     ap.add_argument("--shape", default="2048x2048", help="KxN of the gemv microbenchmark")
     ap.add_argument("--mats", type=int, default=0, help="distinct weight matrices in the gemv microbenchmark (0 = 512 MiB worth)")
     ap.add_argument("--gemv-impl", type=int, default=None, help="2 accumulate mode of the TMA kernel (engine path, default), 0 its ordered combine, 1 register-staged kernel")
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (config 4 of the workload list uses 16)")
     ap.add_argument("--prompt", type=int, default=None, help="override the workload's prompt length (profiling aid)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "engine":
         args.warmup = 3
     if args.workload == "gemv":
         run_gemv_micro(args)
+        return
+    if args.workload == "attn":
+        run_attn_micro(args)
         return
     cfg, prompt_len, _, _, desc = WORKLOADS[args.workload]
     if args.prompt is not None:

@@ -96,6 +96,14 @@ KUIPER_API int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
 KUIPER_API int kuiper_awq_gemv_accum_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
                                          const uint16_t* scales, float* y, int M, int K, int N, int group,
                                          kuiper_stream_t stream);
+/*
+ * Same, with the RMSNorm of the input fused in: y[M,N] += RMSNorm(h[M,K]; norm_w, eps) . dequant(qweight).
+ * h is the un-normalised row (the residual stream); norm_w is bf16 [K].  Replaces an rmsnorm call + a matmul call.
+ */
+KUIPER_API int kuiper_rmsnorm_awq_gemv_accum_f32(const float* h, const uint16_t* norm_w, float eps,
+                                                 const int32_t* qweight, const int32_t* qzeros,
+                                                 const uint16_t* scales, float* y, int M, int K, int N, int group,
+                                                 kuiper_stream_t stream);
 /* health check (synchronises): 5 if a bounded wait inside the pipelined GEMV ever ran out on this device */
 KUIPER_API int kuiper_awq_gemv_status(void);
 

@@ -39,6 +39,7 @@ KERNEL_API = {
     "kuiper_workspace_init": (_i32, [_vp, _sz, _vp]),
     "kuiper_awq_gemv_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "kuiper_awq_gemv_accum_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "kuiper_rmsnorm_awq_gemv_accum_f32": (_i32, [_vp, _vp, _f32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_awq_gemv_status": (_i32, []),
     "kuiper_awq_gemv_noalloc_scratch_bytes": (_sz, []),
     "kuiper_awq_gemv_f32_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),

@@ -85,6 +85,16 @@ def awq_gemv_accum(x, qweight, qzeros, scales, y, group=128):
     return y
 
 
+def rmsnorm_awq_gemv_accum(h, norm_w, eps, qweight, qzeros, scales, y, group=128):
+    """y += RMSNorm(h) . W (y holds the addend); returns y."""
+    _dev(h, norm_w, qweight, qzeros, scales, y)
+    M, K = h.shape
+    N = qweight.shape[1] * 8
+    check(kernels().kuiper_rmsnorm_awq_gemv_accum_f32(_ptr(h), _ptr(norm_w), eps, _ptr(qweight), _ptr(qzeros), _ptr(scales),
+                                                      _ptr(y), M, K, N, group, _stream()))
+    return y
+
+
 def awq_gemv_status() -> None:
     check(kernels().kuiper_awq_gemv_status())
 

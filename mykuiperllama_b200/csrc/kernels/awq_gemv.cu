@@ -412,7 +412,7 @@ bool awq_gemv_tma_supported(int K, int N);
 int awq_gemv_tma_status();
 int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
                         const float* residual, int rows, int K, int N, void* workspace, bool accumulate,
-                        cudaStream_t stream);
+                        const uint16_t* norm_w, float eps, cudaStream_t stream);
 
 }  // namespace kuiper
 
@@ -463,7 +463,7 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
         for (int m0 = 0; m0 < M;) {
             const int mt = (M - m0 >= 2) ? 2 : 1;
             int rc = awq_gemv_tma_launch(x + size_t(m0) * K, qweight, qzeros, scales, y + size_t(m0) * N,
-                                         residual ? residual + size_t(m0) * N : nullptr, mt, K, N, workspace, false, st);
+                                         residual ? residual + size_t(m0) * N : nullptr, mt, K, N, workspace, false, nullptr, 0.f, st);
             if (rc != KUIPER_OK) return rc;
             m0 += mt;
         }
@@ -509,9 +509,9 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
     return KUIPER_OK;
 }
 
-extern "C" int kuiper_awq_gemv_accum_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
-                                         const uint16_t* scales, float* y, int M, int K, int N, int group,
-                                         kuiper_stream_t stream) {
+static int awq_gemv_accum_common(const float* x, const uint16_t* norm_w, float eps, const int32_t* qweight,
+                                 const int32_t* qzeros, const uint16_t* scales, float* y, int M, int K, int N, int group,
+                                 kuiper_stream_t stream) {
     KUIPER_REQUIRE(x && qweight && qzeros && scales && y, "awq_gemv_accum: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && K > 0 && N > 0, "awq_gemv_accum: empty shape M=%d K=%d N=%d", M, K, N);
     KUIPER_REQUIRE(group == 128, "awq_gemv_accum: group size %d is not supported (128 only)", group);
@@ -524,11 +524,25 @@ extern "C" int kuiper_awq_gemv_accum_f32(const float* x, const int32_t* qweight,
     for (int m0 = 0; m0 < M;) {
         const int mt = (M - m0 >= 2) ? 2 : 1;
         int rc = awq_gemv_tma_launch(x + size_t(m0) * K, qweight, qzeros, scales, y + size_t(m0) * N, nullptr, mt, K, N,
-                                     nullptr, true, st);
+                                     nullptr, true, norm_w, eps, st);
         if (rc != KUIPER_OK) return rc;
         m0 += mt;
     }
     return KUIPER_OK;
+}
+
+extern "C" int kuiper_awq_gemv_accum_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
+                                         const uint16_t* scales, float* y, int M, int K, int N, int group,
+                                         kuiper_stream_t stream) {
+    return awq_gemv_accum_common(x, nullptr, 0.f, qweight, qzeros, scales, y, M, K, N, group, stream);
+}
+
+extern "C" int kuiper_rmsnorm_awq_gemv_accum_f32(const float* h, const uint16_t* norm_w, float eps, const int32_t* qweight,
+                                                 const int32_t* qzeros, const uint16_t* scales, float* y, int M, int K,
+                                                 int N, int group, kuiper_stream_t stream) {
+    KUIPER_REQUIRE(norm_w != nullptr, "rmsnorm_awq_gemv_accum: null norm weight");
+    KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(norm_w) & 15) == 0, "rmsnorm_awq_gemv_accum: norm weight must be 16-byte aligned");
+    return awq_gemv_accum_common(h, norm_w, eps, qweight, qzeros, scales, y, M, K, N, group, stream);
 }
 
 extern "C" int kuiper_awq_gemv_status(void) {

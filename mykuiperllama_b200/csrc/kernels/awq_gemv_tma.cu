@@ -55,6 +55,8 @@ struct TmaGemvParams {
     const __half* scales;  // [K/128][N]
     float* partial;        // [slots][MT][1024]
     int* counters;         // [tiles]
+    const uint16_t* norm_w; // bf16 [K]: fused RMSNorm weight of the input (NORM kernels), else null
+    float eps;
     int K, N, tiles, upt;  // upt = units per tile = K / 32
     long long U;           // total units
 };
@@ -119,9 +121,8 @@ __device__ __forceinline__ ZeroPairs make_zero_pairs(uint32_t zw) {
 
 // acc[m][base..base+7] += x[m] * (q - z) for the 8 columns of one packed word.  The two halves of a
 // dequantised pair are split inside the asm block so that no separate extraction is emitted.
-template <int MT, bool XHI>
-__device__ __forceinline__ void word_fma(uint32_t w, const ZeroPairs& z, const uint32_t (&xpair)[MT], float (*acc)[16], int base) {
-    // xpair[m] holds two fp16 activations; XHI picks the upper one
+template <int MT>
+__device__ __forceinline__ void word_fma(uint32_t w, const ZeroPairs& z, const uint16_t (&xh)[MT], float (*acc)[16], int base) {
     const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
     const uint32_t w8 = w >> 8;
     const uint32_t d[4] = {
@@ -134,30 +135,22 @@ __device__ __forceinline__ void word_fma(uint32_t w, const ZeroPairs& z, const u
     for (int i = 0; i < 4; i++) {
 #pragma unroll
         for (int m = 0; m < MT; m++) {
-            if (XHI)
-                asm("{\n\t.reg .b16 lo, hi, xl, xh;\n\t"
-                    "mov.b32 {lo, hi}, %2;\n\t"
-                    "mov.b32 {xl, xh}, %3;\n\t"
-                    "fma.rn.f32.f16 %0, lo, xh, %0;\n\t"
-                    "fma.rn.f32.f16 %1, hi, xh, %1;\n\t}"
-                    : "+f"(acc[m][base + 2 * i]), "+f"(acc[m][base + 2 * i + 1])
-                    : "r"(d[i]), "r"(xpair[m]));
-            else
-                asm("{\n\t.reg .b16 lo, hi, xl, xh;\n\t"
-                    "mov.b32 {lo, hi}, %2;\n\t"
-                    "mov.b32 {xl, xh}, %3;\n\t"
-                    "fma.rn.f32.f16 %0, lo, xl, %0;\n\t"
-                    "fma.rn.f32.f16 %1, hi, xl, %1;\n\t}"
-                    : "+f"(acc[m][base + 2 * i]), "+f"(acc[m][base + 2 * i + 1])
-                    : "r"(d[i]), "r"(xpair[m]));
+            asm("{\n\t.reg .b16 lo, hi;\n\t"
+                "mov.b32 {lo, hi}, %2;\n\t"
+                "fma.rn.f32.f16 %0, lo, %3, %0;\n\t"
+                "fma.rn.f32.f16 %1, hi, %3, %1;\n\t}"
+                : "+f"(acc[m][base + 2 * i]), "+f"(acc[m][base + 2 * i + 1])
+                : "r"(d[i]), "h"(xh[m]));
         }
     }
 }
 
+// NORM: the input row is the residual stream h and the matmul operand is RMSNorm(h) = (h * rstd) * norm_w,
+// formed on the fly (every CTA computes rstd from the whole row itself, which is cheaper than a kernel).
 // ACCUM: y += x.W with vector float reductions (no cross-CTA ordering, no tail); the caller guarantees
 // that y holds the addend (residual stream or zeros).  Otherwise y = x.W (+ residual) with the
 // deterministic slot / arrival-counter combine.
-template <int MT, int STAGES, bool ACCUM, bool NOMATH = false>
+template <int MT, int STAGES, bool ACCUM, bool NOMATH = false, bool NORM = false>
 __global__ void __launch_bounds__(kThreadsTma, (MT == 1 ? kCtasPerSm : 1))
 awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParams p) {
     extern __shared__ unsigned char smem_raw[];
@@ -222,6 +215,42 @@ awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParam
     const unsigned char* my_stage = stages + rg * 8 * 512 + cg * 8;
     const float* my_x = p.x + rg * 8;
 
+    float rstd[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) rstd[m] = 1.f;
+    if (NORM) {
+        // sum of squares of the whole input row, by all consumer threads, 4 x 16-byte loads in flight each
+        float* s_part = reinterpret_cast<float*>(red);  // [MT][kConsumerWarps], free until the first tile ends
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            const float4* hp = reinterpret_cast<const float4*>(p.x + size_t(m) * p.K);
+            const int n4 = p.K >> 2;
+            float ss = 0.f;
+            for (int i = tid; i < n4; i += 4 * kConsumers) {
+                float4 v[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+                    v[q] = (i + q * kConsumers < n4) ? __ldcg(hp + i + q * kConsumers) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    ss = fmaf(v[q].x, v[q].x, ss); ss = fmaf(v[q].y, v[q].y, ss);
+                    ss = fmaf(v[q].z, v[q].z, ss); ss = fmaf(v[q].w, v[q].w, ss);
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) s_part[m * kConsumerWarps + warp] = ss;
+        }
+        consumer_sync();
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            float tot = 0.f;
+#pragma unroll
+            for (int q = 0; q < kConsumerWarps; q++) tot += s_part[m * kConsumerWarps + q];
+            rstd[m] = 1.0f / sqrtf(tot / float(p.K) + p.eps);
+        }
+        consumer_sync();  // red is free again
+    }
+
     // raw zero / scale words of a (tile, group) for this thread's 16 columns; zeros outside N
     auto load_consts = [&](int tile, int g, uint2& zraw, uint4& s0, uint4& s1) {
         const int col = tile * kTileColsTma + cg * 16;
@@ -241,7 +270,14 @@ awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParam
 #pragma unroll
         for (int m = 0; m < MT; m++) {
             const float4* xp = reinterpret_cast<const float4*>(my_x + size_t(m) * p.K + kb * kUnitRows);
-            const float4 a = __ldcg(xp), b = __ldcg(xp + 1);
+            float4 a = __ldcg(xp), b = __ldcg(xp + 1);
+            if (NORM) {
+                const uint4 wn = __ldg(reinterpret_cast<const uint4*>(p.norm_w + rg * 8 + kb * kUnitRows));
+                a.x = (a.x * rstd[m]) * bf16_lo(wn.x); a.y = (a.y * rstd[m]) * bf16_hi(wn.x);
+                a.z = (a.z * rstd[m]) * bf16_lo(wn.y); a.w = (a.w * rstd[m]) * bf16_hi(wn.y);
+                b.x = (b.x * rstd[m]) * bf16_lo(wn.z); b.y = (b.y * rstd[m]) * bf16_hi(wn.z);
+                b.z = (b.z * rstd[m]) * bf16_lo(wn.w); b.w = (b.w * rstd[m]) * bf16_hi(wn.w);
+            }
             xr[m].x = h22u(__floats2half2_rn(a.x, a.y));
             xr[m].y = h22u(__floats2half2_rn(a.z, a.w));
             xr[m].z = h22u(__floats2half2_rn(b.x, b.y));
@@ -295,32 +331,29 @@ awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParam
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty_bar[s]);  // the stage is in registers now
                 if (++s == STAGES) { s = 0; parity ^= 1u; }
-                uint32_t xa[MT], xb[MT], xc[MT], xd[MT];
+                // the eight fp16 activations of this thread's rows, one 16-bit register each
+                uint16_t x16[8][MT];
 #pragma unroll
-                for (int m = 0; m < MT; m++) { xa[m] = xr[m].x; xb[m] = xr[m].y; xc[m] = xr[m].z; xd[m] = xr[m].w; }
+                for (int m = 0; m < MT; m++) {
+                    const uint32_t pr[4] = {xr[m].x, xr[m].y, xr[m].z, xr[m].w};
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        x16[2 * q][m] = uint16_t(pr[q] & 0xffffu);
+                        x16[2 * q + 1][m] = uint16_t(pr[q] >> 16);
+                    }
+                }
                 // activations of the next unit this thread will see (same tile or the start of the next one)
                 kb++;
                 if (j + 1 < gu || more) load_x(kb == p.upt ? 0 : kb, xr);
                 if (NOMATH) {  // measurement aid: keep the loads alive, skip the arithmetic
-                    acc_g[0][0] += __uint_as_float((w[0].x ^ w[1].x ^ w[2].x ^ w[3].x ^ w[4].y ^ w[5].y ^ w[6].y ^ w[7].y ^ xa[0] ^ xd[0]) & 0x3fffffffu);
+                    acc_g[0][0] += __uint_as_float((w[0].x ^ w[1].x ^ w[2].x ^ w[3].x ^ w[4].y ^ w[5].y ^ w[6].y ^ w[7].y ^ x16[0][0] ^ x16[7][0]) & 0x3fffffffu);
                     continue;
                 }
-                word_fma<MT, false>(w[0].x, z0, xa, acc_g, 0);
-                word_fma<MT, false>(w[0].y, z1, xa, acc_g, 8);
-                word_fma<MT, true>(w[1].x, z0, xa, acc_g, 0);
-                word_fma<MT, true>(w[1].y, z1, xa, acc_g, 8);
-                word_fma<MT, false>(w[2].x, z0, xb, acc_g, 0);
-                word_fma<MT, false>(w[2].y, z1, xb, acc_g, 8);
-                word_fma<MT, true>(w[3].x, z0, xb, acc_g, 0);
-                word_fma<MT, true>(w[3].y, z1, xb, acc_g, 8);
-                word_fma<MT, false>(w[4].x, z0, xc, acc_g, 0);
-                word_fma<MT, false>(w[4].y, z1, xc, acc_g, 8);
-                word_fma<MT, true>(w[5].x, z0, xc, acc_g, 0);
-                word_fma<MT, true>(w[5].y, z1, xc, acc_g, 8);
-                word_fma<MT, false>(w[6].x, z0, xd, acc_g, 0);
-                word_fma<MT, false>(w[6].y, z1, xd, acc_g, 8);
-                word_fma<MT, true>(w[7].x, z0, xd, acc_g, 0);
-                word_fma<MT, true>(w[7].y, z1, xd, acc_g, 8);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    word_fma<MT>(w[i].x, z0, x16[i], acc_g, 0);
+                    word_fma<MT>(w[i].y, z1, x16[i], acc_g, 8);
+                }
             }
             // ---- group done: apply its fp16 scales once
             const uint32_t sraw[8] = {sa_cur.x, sa_cur.y, sa_cur.z, sa_cur.w, sb_cur.x, sb_cur.y, sb_cur.z, sb_cur.w};
@@ -508,9 +541,9 @@ int sm_count() {
 
 int g_tma_nomath = 0;
 
-template <int MT, int STAGES, bool ACCUM, bool NOMATH = false>
+template <int MT, int STAGES, bool ACCUM, bool NOMATH = false, bool NORM = false>
 int launch_tma(const CUtensorMap& map, const TmaGemvParams& p, int ctas, cudaStream_t stream) {
-    auto kern = awq_gemv_tma_kernel<MT, STAGES, ACCUM, NOMATH>;
+    auto kern = awq_gemv_tma_kernel<MT, STAGES, ACCUM, NOMATH, NORM>;
     const size_t smem = 128 + size_t(STAGES) * kStageBytes + size_t(kRowGroups) * MT * 1024 * 4;
     static size_t configured = 0;
     if (configured < smem) {
@@ -566,7 +599,7 @@ bool awq_gemv_tma_supported(int K, int N) {
 // rows: 1 or 2 token rows starting at x / y / residual
 int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
                         const float* residual, int rows, int K, int N, void* workspace, bool accumulate,
-                        cudaStream_t stream) {
+                        const uint16_t* norm_w, float eps, cudaStream_t stream) {
     CUtensorMap map;
     if (!get_tensor_map(qweight, K, N, &map)) {
         set_error("awq_gemv_tma: tensor map encoding failed");
@@ -578,6 +611,8 @@ int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* q
     p.residual = residual;
     p.qz = reinterpret_cast<const uint2*>(qzeros);
     p.scales = reinterpret_cast<const __half*>(scales);
+    p.norm_w = norm_w;
+    p.eps = eps;
     p.K = K;
     p.N = N;
     p.tiles = (N + kTileColsTma - 1) / kTileColsTma;
@@ -592,6 +627,14 @@ int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* q
     p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + head);
     long long ctas = (long long)sm_count() * (rows == 1 ? kCtasPerSm : 1);
     if (ctas > p.U) ctas = p.U;
+    if (accumulate && norm_w) {
+        if (rows == 2) return launch_tma<2, 4, true, false, true>(map, p, int(ctas), stream);
+        return launch_tma<1, 5, true, false, true>(map, p, int(ctas), stream);
+    }
+    if (norm_w) {
+        set_error("awq_gemv_tma: the fused input norm exists in accumulate mode only");
+        return KUIPER_INVALID_ARGUMENT;
+    }
     if (accumulate) {
         if (rows == 2) return launch_tma<2, 4, true>(map, p, int(ctas), stream);
         if (g_tma_nomath) return launch_tma<1, 5, true, true>(map, p, int(ctas), stream);
@@ -697,6 +740,8 @@ extern "C" int kuiper_awq_gemv_f32_noalloc(const float* x, const int32_t* qweigh
     TmaGemvParams p;
     p.qz = reinterpret_cast<const uint2*>(qzeros);
     p.scales = reinterpret_cast<const __half*>(scales);
+    p.norm_w = nullptr;
+    p.eps = 0.f;
     p.K = K;
     p.N = N;
     p.tiles = (N + kTileColsTma - 1) / kTileColsTma;

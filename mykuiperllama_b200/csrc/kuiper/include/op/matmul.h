@@ -28,6 +28,12 @@ public:
     // accumulate mode (quantised layers): output += x . W, the output tensor already holds the addend
     // (residual stream or zeros); no workspace, unordered fp32 summation
     void set_accumulate(bool accumulate) { accumulate_ = accumulate; }
+    // accumulate mode only: the input is an un-normalised row and the layer applies RMSNorm(input; weight, eps)
+    // inside the matmul kernel (weight bf16 [dim1]); saves the separate norm launch
+    void set_input_norm(const tensor::Tensor& weight, float eps) {
+        input_norm_ = weight;
+        input_norm_eps_ = eps;
+    }
     // scratch of the split-K kernel: kernel::matmul_quant_workspace_bytes(M, K, N) bytes, zero-initialised once
     void set_workspace(const tensor::Tensor& workspace);
     // how the INT4 kernel rounds x: 1 = fp16 operand (default), 0 = fp32 operand
@@ -44,6 +50,8 @@ private:
     int32_t dim1_ = 0;
     bool has_residual_ = false;
     bool accumulate_ = false;
+    tensor::Tensor input_norm_;
+    float input_norm_eps_ = 1e-6f;
     int32_t act_mode_ = 1;
     tensor::Tensor workspace_;
 };

@@ -194,6 +194,11 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         L.gate_up = make_quant(sh_gu, false);
         L.down = make_quant(sh_down, fold_residual && !accumulate_);
         for (op::MatmulLayer* m : {L.qkv.get(), L.o.get(), L.gate_up.get(), L.down.get()}) m->set_accumulate(accumulate_);
+        if (accumulate_) {
+            // the two pre-norms run inside the projections that consume them
+            L.qkv->set_input_norm(L.input_norm->get_weight(0), c.eps);
+            L.gate_up->set_input_norm(L.post_norm->get_weight(0), c.eps);
+        }
         L.key_cache = dev(DataType::DataTypeBf16, {c.max_batch, Hkv, c.max_seq_len, D});
         L.value_cache = dev(DataType::DataTypeBf16, {c.max_batch, Hkv, c.max_seq_len, D});
         CUDA_OK(cudaMemset(L.key_cache.ptr<void>(), 0, L.key_cache.byte_size()));
@@ -371,13 +376,21 @@ base::Status Qwen3Model::run_pass(int32_t M) {
 
     RETURN_IF_ERROR(embedding_->forward(tokens, h));
     for (Qwen3Layer& L : layers_) {
-        RETURN_IF_ERROR(L.input_norm->forward(h, xn));
-        RETURN_IF_ERROR(L.qkv->forward(xn, qkv));
+        if (accumulate_) {
+            RETURN_IF_ERROR(L.qkv->forward(h, qkv));  // RMSNorm fused into the projection
+        } else {
+            RETURN_IF_ERROR(L.input_norm->forward(h, xn));
+            RETURN_IF_ERROR(L.qkv->forward(xn, qkv));
+        }
         RETURN_IF_ERROR(L.rope->forward(qkv, pos, slot, cos_t, sin_t, q));
         RETURN_IF_ERROR(L.mha->forward(q, seq_len, slot, att));
         RETURN_IF_ERROR(project_and_reduce(*L.o, att));
-        RETURN_IF_ERROR(L.post_norm->forward(h, xn2));
-        RETURN_IF_ERROR(L.gate_up->forward(xn2, gu));
+        if (accumulate_) {
+            RETURN_IF_ERROR(L.gate_up->forward(h, gu));
+        } else {
+            RETURN_IF_ERROR(L.post_norm->forward(h, xn2));
+            RETURN_IF_ERROR(L.gate_up->forward(xn2, gu));
+        }
         RETURN_IF_ERROR(L.swiglu->forward(gu, act));
         RETURN_IF_ERROR(project_and_reduce(*L.down, act));
     }

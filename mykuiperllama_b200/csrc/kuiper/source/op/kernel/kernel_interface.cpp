@@ -77,7 +77,8 @@ void matmul_kernel_quant_cu(const Tensor& input, const Tensor& qweight, const Te
 }
 
 void matmul_kernel_quant_accum_cu(const Tensor& input, const Tensor& qweight, const Tensor& qzeros, const Tensor& scales,
-                                  const Tensor& output, int32_t group_size, void* stream) {
+                                  const Tensor& output, int32_t group_size, const Tensor* input_norm_weight, float eps,
+                                  void* stream) {
     require_cuda(input, "matmul input");
     require_cuda(qweight, "matmul qweight");
     require_cuda(qzeros, "matmul qzeros");
@@ -88,6 +89,14 @@ void matmul_kernel_quant_accum_cu(const Tensor& input, const Tensor& qweight, co
     CHECK_EQ(input.size() % size_t(K), size_t(0));
     const int32_t M = int32_t(input.size() / size_t(K));
     CHECK_EQ(output.size(), size_t(M) * size_t(N));
+    if (input_norm_weight) {
+        require_cuda(*input_norm_weight, "matmul input norm weight");
+        CHECK_EQ(input_norm_weight->size(), size_t(K));
+        KERNEL_OK(kuiper_rmsnorm_awq_gemv_accum_f32(input.ptr<float>(), input_norm_weight->ptr<uint16_t>(), eps,
+                                                    qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(), scales.ptr<uint16_t>(),
+                                                    out_ptr<float>(output), M, K, N, group_size, as_stream(stream)));
+        return;
+    }
     KERNEL_OK(kuiper_awq_gemv_accum_f32(input.ptr<float>(), qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(),
                                         scales.ptr<uint16_t>(), out_ptr<float>(output), M, K, N, group_size,
                                         as_stream(stream)));

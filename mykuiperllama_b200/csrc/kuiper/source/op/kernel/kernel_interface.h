@@ -29,10 +29,12 @@ using MatmulKernelQuant = void (*)(const tensor::Tensor& input, const tensor::Te
                                    const tensor::Tensor& output, const tensor::Tensor* residual, int32_t group_size,
                                    int32_t act_mode, const tensor::Tensor& workspace, void* stream);
 
-// output[M,N] += input[M,K] . dequant(...): the output already holds the addend (residual stream or zeros)
+// output[M,N] += input[M,K] . dequant(...): the output already holds the addend (residual stream or zeros).
+// With input_norm_weight (bf16 [K]) the operand is RMSNorm(input) formed inside the kernel.
 using MatmulKernelQuantAccum = void (*)(const tensor::Tensor& input, const tensor::Tensor& qweight,
                                         const tensor::Tensor& qzeros, const tensor::Tensor& scales,
-                                        const tensor::Tensor& output, int32_t group_size, void* stream);
+                                        const tensor::Tensor& output, int32_t group_size,
+                                        const tensor::Tensor* input_norm_weight, float eps, void* stream);
 
 using RMSNormKernel = void (*)(const tensor::Tensor& input, const tensor::Tensor& weight, const tensor::Tensor& output,
                                float eps, void* stream);

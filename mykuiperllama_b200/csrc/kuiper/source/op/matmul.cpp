@@ -70,7 +70,8 @@ base::Status MatmulLayer::forward() {
     if (is_quant_layer_ && accumulate_) {
         if (has_residual_) return base::error::invalid_argument("accumulate mode takes no residual input");
         kernel::get_matmul_kernel_quant_accum(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),
-                                                            group_size_, stream());
+                                                            group_size_, input_norm_.is_empty() ? nullptr : &input_norm_,
+                                                            input_norm_eps_, stream());
     } else if (is_quant_layer_) {
         kernel::get_matmul_kernel_quant(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),
                                                       has_residual_ ? &get_input(1) : nullptr, group_size_, act_mode_,

@@ -129,6 +129,23 @@ def test_awq_gemv_accumulate_mode(cuda, oracle, M, K, N):
     cuda.awq_gemv_status()
 
 
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 6144), (2, 1024, 2048), (1, 2560, 1056), (3, 256, 1024)])
+def test_rmsnorm_fused_into_accumulating_gemv(cuda, oracle, M, K, N):
+    rng = np.random.default_rng(K * 5 + N + M)
+    q, z, s = awq_random(rng, K, N)
+    qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
+    h = (rng.standard_normal((M, K)) * 2.5).astype(np.float32)
+    nw = oracle.f32_to_bf16((1 + 0.1 * rng.standard_normal(K)).astype(np.float32))
+    addend = rng.standard_normal((M, N)).astype(np.float32)
+    xn = oracle.rmsnorm(h, nw, 1e-6)
+    ref = oracle.awq_gemv(xn, qw, qz, su).astype(np.float64) + addend  # un-rounded operand: the workload's reference
+    y = dev(addend)
+    cuda.rmsnorm_awq_gemv_accum(dev(h), dev(nw), 1e-6, dev(qw), dev(qz), dev(su, torch.float16), y)
+    torch.cuda.synchronize()
+    err = rel_err(y.cpu().numpy(), ref)
+    assert err <= SPEC_TOL and err <= 1e-3
+
+
 def test_awq_gemv_ragged_width_uses_generic_kernel(cuda, oracle):
     err, *_ = _gemv_case(cuda, oracle, np.random.default_rng(5), 2, 256, 40, 1, residual=True)
     assert err <= 2e-6
