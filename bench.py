@@ -291,7 +291,7 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
     B = max(1, args.batch)
     steps_total = args.warmup + args.steps
     max_seq = prompt_len + 2 * steps_total + 16
-    ecfg = eng_mod.EngineConfig(**cfg, max_seq=max_seq, max_batch=B, max_rows=max(8, B), tp_rank=rank, tp_size=world)
+    ecfg = eng_mod.EngineConfig(**cfg, max_seq=max_seq, max_batch=B, max_rows=max(128, B), tp_rank=rank, tp_size=world)
     eng = eng_mod.Qwen3Engine(ecfg)
 
     gen = torch.Generator(device=device)

@@ -125,6 +125,19 @@ KUIPER_API int kuiper_awq_gemv_f32_noalloc(const float* x, const int32_t* qweigh
                                            const uint16_t* scales, float* y, const float* residual,
                                            int M, int K, int N, int group, kuiper_stream_t stream);
 
+/* ---- INT4-AWQ GEMM on the tcgen05 tensor cores, for M >= 16 token rows (prefill, batched decode).
+ * Same placeholder as the GEMV (kuiper/include/op/matmul.h:1-11).  x is rounded to fp16, the weight
+ * (q - z) * s is rounded to fp16, accumulation is fp32 in tensor memory.
+ *   accumulate == 0, residual == NULL : y  = x . W
+ *   accumulate == 0, residual != NULL : y  = x . W + residual   (residual may alias y)
+ *   accumulate != 0                   : y += x . W              (summation order fixed: deterministic)
+ * Any M > 0 is accepted (rows are padded to 128 inside the kernel); K % 128 == 0, N % 8 == 0.
+ * kuiper_awq_gemm_status() synchronously reads the kernel's bounded-wait error word. ---- */
+KUIPER_API int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
+                                   const uint16_t* scales, float* y, const float* residual, int accumulate,
+                                   int M, int K, int N, int group, kuiper_stream_t stream);
+KUIPER_API int kuiper_awq_gemm_status(void);
+
 /* ---- BF16 GEMV (lm_head): W bf16 [N, K], y[M,N] = x[M,K] . W^T ---- */
 KUIPER_API int kuiper_bf16_gemv_f32(const float* x, const uint16_t* W, float* y, int M, int K, int N,
                          kuiper_stream_t stream);

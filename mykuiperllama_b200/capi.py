@@ -95,6 +95,23 @@ def rmsnorm_awq_gemv_accum(h, norm_w, eps, qweight, qzeros, scales, y, group=128
     return y
 
 
+def awq_gemm(x, qweight, qzeros, scales, y=None, residual=None, accumulate=False, group=128):
+    """Tensor-core INT4 GEMM for M >= 16 rows: y = x . W (+ residual), or y += x . W."""
+    _dev(x, qweight, qzeros, scales)
+    M, K = x.shape
+    N = qweight.shape[1] * 8
+    if y is None:
+        y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    check(kernels().kuiper_awq_gemm_f32(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(y),
+                                        _ptr(residual) if residual is not None else None, int(bool(accumulate)),
+                                        M, K, N, group, _stream()))
+    return y
+
+
+def awq_gemm_status() -> None:
+    check(kernels().kuiper_awq_gemm_status())
+
+
 def awq_gemv_status() -> None:
     check(kernels().kuiper_awq_gemv_status())
 

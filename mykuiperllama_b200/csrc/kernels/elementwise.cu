@@ -23,6 +23,7 @@ void set_error(const char* fmt, ...) {
 
 void awq_gemv_set_tuning(const char* key, int value);
 void flash_decode_set_tuning(const char* key, int value);
+void awq_gemm_set_tuning(const char* key, int value);
 
 namespace {
 
@@ -279,6 +280,7 @@ extern "C" int kuiper_set_tuning(const char* key, int value) {
     if (!strcmp(key, "pdl")) g_pdl_enabled = value;
     awq_gemv_set_tuning(key, value);
     flash_decode_set_tuning(key, value);
+    awq_gemm_set_tuning(key, value);
     return KUIPER_OK;
 }
 

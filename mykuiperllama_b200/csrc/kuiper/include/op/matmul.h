@@ -34,6 +34,12 @@ public:
         input_norm_ = weight;
         input_norm_eps_ = eps;
     }
+    // where RMSNorm(input) is written when the row count takes the tensor-core path, which has no fused norm
+    // ([max rows, dim1] fp32)
+    void set_norm_scratch(const tensor::Tensor& scratch) { norm_scratch_ = scratch; }
+    // quantised layers, fp16-operand mode: inputs of at least this many rows go to the tcgen05 GEMM
+    // instead of the GEMV (0 = never)
+    void set_gemm_min_rows(int32_t rows) { gemm_min_rows_ = rows; }
     // scratch of the split-K kernel: kernel::matmul_quant_workspace_bytes(M, K, N) bytes, zero-initialised once
     void set_workspace(const tensor::Tensor& workspace);
     // how the INT4 kernel rounds x: 1 = fp16 operand (default), 0 = fp32 operand
@@ -54,6 +60,8 @@ private:
     float input_norm_eps_ = 1e-6f;
     int32_t act_mode_ = 1;
     tensor::Tensor workspace_;
+    tensor::Tensor norm_scratch_;
+    int32_t gemm_min_rows_ = 16;
 };
 }  // namespace op
 

@@ -198,6 +198,9 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
             // the two pre-norms run inside the projections that consume them
             L.qkv->set_input_norm(L.input_norm->get_weight(0), c.eps);
             L.gate_up->set_input_norm(L.post_norm->get_weight(0), c.eps);
+            // passes of 16 rows or more take the tensor-core path, which wants the normed rows materialised
+            L.qkv->set_norm_scratch(get_buffer(ModelBufferType::OutputRMSNorm));
+            L.gate_up->set_norm_scratch(get_buffer(ModelBufferType::FFNRMSNorm));
         }
         L.key_cache = dev(DataType::DataTypeBf16, {c.max_batch, Hkv, c.max_seq_len, D});
         L.value_cache = dev(DataType::DataTypeBf16, {c.max_batch, Hkv, c.max_seq_len, D});

@@ -102,6 +102,25 @@ void matmul_kernel_quant_accum_cu(const Tensor& input, const Tensor& qweight, co
                                         as_stream(stream)));
 }
 
+void matmul_kernel_quant_gemm_cu(const Tensor& input, const Tensor& qweight, const Tensor& qzeros, const Tensor& scales,
+                                 const Tensor& output, const Tensor* residual, bool accumulate, int32_t group_size,
+                                 void* stream) {
+    require_cuda(input, "matmul input");
+    require_cuda(qweight, "matmul qweight");
+    require_cuda(qzeros, "matmul qzeros");
+    require_cuda(scales, "matmul scales");
+    require_cuda(output, "matmul output");
+    if (residual) require_cuda(*residual, "matmul residual");
+    CHECK_EQ(qweight.dims_size(), 2);
+    const int32_t K = qweight.get_dim(0), N = qweight.get_dim(1) * 8;
+    CHECK_EQ(input.size() % size_t(K), size_t(0));
+    const int32_t M = int32_t(input.size() / size_t(K));
+    CHECK_EQ(output.size(), size_t(M) * size_t(N));
+    KERNEL_OK(kuiper_awq_gemm_f32(input.ptr<float>(), qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(), scales.ptr<uint16_t>(),
+                                  out_ptr<float>(output), residual ? residual->ptr<float>() : nullptr, accumulate ? 1 : 0, M,
+                                  K, N, group_size, as_stream(stream)));
+}
+
 void rmsnorm_kernel_cu(const Tensor& input, const Tensor& weight, const Tensor& output, float eps, void* stream) {
     require_cuda(input, "rmsnorm input");
     require_cuda(weight, "rmsnorm weight");
@@ -200,6 +219,9 @@ MatmulKernelQuant get_matmul_kernel_quant(base::DeviceType d) {
 }
 MatmulKernelQuantAccum get_matmul_kernel_quant_accum(base::DeviceType d) {
     return pick<MatmulKernelQuantAccum>(d, matmul_kernel_quant_accum_cu, "accumulating quantised matmul");
+}
+MatmulKernelQuantGemm get_matmul_kernel_quant_gemm(base::DeviceType d) {
+    return pick<MatmulKernelQuantGemm>(d, matmul_kernel_quant_gemm_cu, "tensor-core quantised matmul");
 }
 RMSNormKernel get_rmsnorm_kernel(base::DeviceType d) { return pick<RMSNormKernel>(d, rmsnorm_kernel_cu, "rmsnorm"); }
 RoPEKernel get_rope_kernel(base::DeviceType d) { return pick<RoPEKernel>(d, rope_kernel_cu, "rope"); }

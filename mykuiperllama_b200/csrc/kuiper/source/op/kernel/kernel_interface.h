@@ -36,6 +36,12 @@ using MatmulKernelQuantAccum = void (*)(const tensor::Tensor& input, const tenso
                                         const tensor::Tensor& output, int32_t group_size,
                                         const tensor::Tensor* input_norm_weight, float eps, void* stream);
 
+// Tensor-core path for M >= 16 rows: output = input . dequant(...) (+ residual), or output += ... when accumulate.
+using MatmulKernelQuantGemm = void (*)(const tensor::Tensor& input, const tensor::Tensor& qweight,
+                                       const tensor::Tensor& qzeros, const tensor::Tensor& scales,
+                                       const tensor::Tensor& output, const tensor::Tensor* residual, bool accumulate,
+                                       int32_t group_size, void* stream);
+
 using RMSNormKernel = void (*)(const tensor::Tensor& input, const tensor::Tensor& weight, const tensor::Tensor& output,
                                float eps, void* stream);
 
@@ -61,6 +67,7 @@ AddKernel get_add_kernel(base::DeviceType device_type);
 MatmulKernel get_matmul_kernel(base::DeviceType device_type);
 MatmulKernelQuant get_matmul_kernel_quant(base::DeviceType device_type);
 MatmulKernelQuantAccum get_matmul_kernel_quant_accum(base::DeviceType device_type);
+MatmulKernelQuantGemm get_matmul_kernel_quant_gemm(base::DeviceType device_type);
 RMSNormKernel get_rmsnorm_kernel(base::DeviceType device_type);
 RoPEKernel get_rope_kernel(base::DeviceType device_type);
 MHAKernel get_mha_kernel(base::DeviceType device_type);

@@ -67,7 +67,25 @@ base::Status MatmulLayer::forward() {
     base::Status status = check();
     if (!status) return status;
     if (device_type_ == base::DeviceType::DeviceCUDA) CHECK_NE(cuda_config_, nullptr);
-    if (is_quant_layer_ && accumulate_) {
+    const int32_t M = int32_t(get_input(0).size() / size_t(dim1_));
+    if (is_quant_layer_ && act_mode_ == 1 && gemm_min_rows_ > 0 && M >= gemm_min_rows_) {
+        // enough rows for the tensor cores: x and the dequantised weight go through tcgen05 as fp16
+        if (accumulate_ && has_residual_) return base::error::invalid_argument("accumulate mode takes no residual input");
+        const tensor::Tensor* x = &get_input(0);
+        tensor::Tensor normed;
+        if (accumulate_ && !input_norm_.is_empty()) {
+            if (norm_scratch_.is_empty() || norm_scratch_.size() < get_input(0).size())
+                return base::error::invalid_argument("the tensor-core path needs a norm scratch of the input's size");
+            normed = tensor::Tensor(base::DataType::DataTypeFp32, std::vector<int32_t>{M, dim1_}, false, nullptr,
+                                    const_cast<float*>(norm_scratch_.ptr<float>()));
+            normed.set_device_type(device_type_);
+            kernel::get_rmsnorm_kernel(device_type_)(get_input(0), input_norm_, normed, input_norm_eps_, stream());
+            x = &normed;
+        }
+        kernel::get_matmul_kernel_quant_gemm(device_type_)(*x, get_weight(0), get_weight(1), scales_, get_output(0),
+                                                           has_residual_ ? &get_input(1) : nullptr, accumulate_,
+                                                           group_size_, stream());
+    } else if (is_quant_layer_ && accumulate_) {
         if (has_residual_) return base::error::invalid_argument("accumulate mode takes no residual input");
         kernel::get_matmul_kernel_quant_accum(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),
                                                             group_size_, input_norm_.is_empty() ? nullptr : &input_norm_,

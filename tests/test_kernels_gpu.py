@@ -190,6 +190,61 @@ def test_awq_gemv_rejects_bad_arguments(cuda):
     assert e.value.code == 7
 
 
+# ----------------------------------------------------------------------------- INT4 GEMM (tcgen05), M >= 16
+@pytest.mark.parametrize("M,K,N", [(16, 128, 128), (16, 256, 136), (100, 1024, 384), (128, 4096, 1024), (129, 512, 256),
+                                   (300, 1024, 4104), (16, 4096, 6144), (64, 3072, 1024)])
+def test_awq_gemm_tensor_core(cuda, oracle, M, K, N):
+    rng = np.random.default_rng(M + K + N)
+    q, z, s = awq_random(rng, K, N)
+    qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    ref = oracle.awq_gemv(x, qw, qz, su, act_round=oracle.ROUND_FP16).astype(np.float64)
+    tx, tqw, tqz, ts = dev(x), dev(qw), dev(qz), dev(su, torch.float16)
+    y = cuda.awq_gemm(tx, tqw, tqz, ts)
+    y_res = cuda.awq_gemm(tx, tqw, tqz, ts, residual=dev(res))
+    y_acc = dev(res)
+    cuda.awq_gemm(tx, tqw, tqz, ts, y=y_acc, accumulate=True)
+    torch.cuda.synchronize()
+    # the weight (q - z) * s is rounded to fp16 before the tensor-core product: ~2^-11 per weight on top of the GEMV's error
+    err = rel_err(y.cpu().numpy(), ref)
+    assert err <= SPEC_TOL and err <= 1e-3
+    assert rel_err(y_res.cpu().numpy(), ref + res) <= 1e-3
+    assert torch.equal(y_acc, y_res)  # same tile, same order: bit-identical
+    again = cuda.awq_gemm(tx, tqw, tqz, ts)
+    torch.cuda.synchronize()
+    assert torch.equal(again, y)  # fixed summation order: deterministic
+    cuda.awq_gemm_status()
+
+
+def test_awq_gemm_agrees_with_gemv_rows(cuda, oracle):
+    # the batched-decode switch (M >= 16 -> GEMM) must not move results beyond the fp16 weight rounding
+    rng = np.random.default_rng(77)
+    M, K, N = 16, 1024, 2048
+    q, z, s = awq_random(rng, K, N)
+    tqw, tqz, ts = dev(oracle.awq_pack(q)), dev(oracle.awq_pack(z)), dev(s.view(np.uint16), torch.float16)
+    x = dev(rng.standard_normal((M, K)).astype(np.float32))
+    y = cuda.awq_gemm(x, tqw, tqz, ts)
+    rows = torch.cat([cuda.awq_gemv(x[i:i + 8].contiguous(), tqw, tqz, ts) for i in range(0, M, 8)])
+    torch.cuda.synchronize()
+    assert rel_err(y.cpu().numpy(), rows.cpu().numpy()) <= 1e-3
+
+
+def test_awq_gemm_rejects_bad_arguments(cuda):
+    from mykuiperllama_b200._lib import KuiperError
+    qz = torch.zeros((2, 4), dtype=torch.int32, device="cuda")
+    s = torch.zeros((2, 32), dtype=torch.float16, device="cuda")
+    with pytest.raises(KuiperError) as e:  # K not a multiple of the group
+        cuda.awq_gemm(torch.zeros((16, 192), device="cuda"), torch.zeros((192, 4), dtype=torch.int32, device="cuda"), qz, s)
+    assert e.value.code == 7
+    x = torch.zeros((16, 256), device="cuda")
+    qw = torch.zeros((256, 4), dtype=torch.int32, device="cuda")
+    with pytest.raises(KuiperError) as e:  # accumulate and residual at once
+        cuda.awq_gemm(x, qw, qz, s, y=torch.zeros((16, 32), device="cuda"), residual=torch.zeros((16, 32), device="cuda"),
+                      accumulate=True)
+    assert e.value.code == 7
+
+
 # ----------------------------------------------------------------------------- BF16 GEMV
 @pytest.mark.parametrize("M,K,N", [(1, 1024, 5000), (1, 2560, 1001), (3, 4096, 2048), (4, 1024, 777), (7, 520, 64)])
 def test_bf16_gemv(cuda, oracle, M, K, N):
