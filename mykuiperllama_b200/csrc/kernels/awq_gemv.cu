@@ -337,7 +337,7 @@ __global__ void awq_gemv_generic_kernel(const float* x, const int32_t* qw, const
 
 int g_force_rows = 0;  // tuning override: rows per thread (4, 8 or 16); 0 = heuristic
 int g_force_math = -1;
-int g_force_impl = 0;  // 0: persistent TMA kernel where it applies; 1: always the register-staged kernel
+int g_force_impl = 0;  // 0: persistent tensor-core kernel where it applies; 2: persistent SIMT kernel; 1: register-staged kernel
 
 int pick_rows(int K, int N) {
     if (g_force_rows == 4 || g_force_rows == 8 || g_force_rows == 16) return g_force_rows;
@@ -398,12 +398,14 @@ int launch_mode(const GemvParams& p, int mode, int rows, cudaStream_t stream) {
 
 // tuning hooks used by the benchmark sweeps
 void awq_gemv_tma_set_tuning(const char* key, int value);
+void awq_gemv_mma_set_tuning(const char* key, int value);
 
 void awq_gemv_set_tuning(const char* key, int value) {
     if (!strcmp(key, "gemv_rows")) g_force_rows = value;
     if (!strcmp(key, "gemv_math")) g_force_math = value;
     if (!strcmp(key, "gemv_impl")) g_force_impl = value;
     awq_gemv_tma_set_tuning(key, value);
+    awq_gemv_mma_set_tuning(key, value);
 }
 
 // persistent TMA-fed variant (awq_gemv_tma.cu)
@@ -411,6 +413,14 @@ size_t awq_gemv_tma_workspace_bytes(int K, int N);
 bool awq_gemv_tma_supported(int K, int N);
 int awq_gemv_tma_status();
 int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
+                        const float* residual, int rows, int K, int N, void* workspace, bool accumulate,
+                        const uint16_t* norm_w, float eps, cudaStream_t stream);
+
+// persistent TMA-fed variant with the dot products on the tensor cores (awq_gemv_mma.cu)
+bool awq_gemv_mma_supported(int K, int N);
+int awq_gemv_mma_status();
+int awq_gemv_mma_max_rows(bool accumulate);
+int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
                         const float* residual, int rows, int K, int N, void* workspace, bool accumulate,
                         const uint16_t* norm_w, float eps, cudaStream_t stream);
 
@@ -455,15 +465,18 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
                        (reinterpret_cast<uintptr_t>(scales) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(x) & 3) == 0 && (!residual || (reinterpret_cast<uintptr_t>(residual) & 15) == 0),
                    "awq_gemv: tensors must be 16-byte aligned");
-    const bool want_tma = g_force_impl == 0 && g_force_math < 0 && act_mode == KUIPER_ACT_FP16 && awq_gemv_tma_supported(K, N);
+    const bool want_tma = (g_force_impl == 0 || g_force_impl == 2) && g_force_math < 0 && act_mode == KUIPER_ACT_FP16 &&
+                          awq_gemv_tma_supported(K, N);
     if (want_tma) {
+        const bool mma = g_force_impl == 0 && awq_gemv_mma_supported(K, N);
         KUIPER_REQUIRE(workspace != nullptr && workspace_bytes >= awq_gemv_tma_workspace_bytes(K, N),
                        "awq_gemv: workspace of %zu bytes is too small", workspace_bytes);
         KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, "awq_gemv: workspace must be 16-byte aligned");
         for (int m0 = 0; m0 < M;) {
             const int mt = (M - m0 >= 2) ? 2 : 1;
-            int rc = awq_gemv_tma_launch(x + size_t(m0) * K, qweight, qzeros, scales, y + size_t(m0) * N,
-                                         residual ? residual + size_t(m0) * N : nullptr, mt, K, N, workspace, false, nullptr, 0.f, st);
+            int rc = (mma ? awq_gemv_mma_launch : awq_gemv_tma_launch)(
+                x + size_t(m0) * K, qweight, qzeros, scales, y + size_t(m0) * N, residual ? residual + size_t(m0) * N : nullptr,
+                mt, K, N, workspace, false, nullptr, 0.f, st);
             if (rc != KUIPER_OK) return rc;
             m0 += mt;
         }
@@ -521,10 +534,13 @@ static int awq_gemv_accum_common(const float* x, const uint16_t* norm_w, float e
                    "awq_gemv_accum: tensors must be 16-byte aligned");
     KUIPER_REQUIRE(awq_gemv_tma_supported(K, N), "awq_gemv_accum: tensor-map support is unavailable");
     cudaStream_t st = as_stream(stream);
+    const bool mma = g_force_impl != 2 && awq_gemv_mma_supported(K, N);
+    const int max_rows = mma ? awq_gemv_mma_max_rows(true) : 2;
     for (int m0 = 0; m0 < M;) {
-        const int mt = (M - m0 >= 2) ? 2 : 1;
-        int rc = awq_gemv_tma_launch(x + size_t(m0) * K, qweight, qzeros, scales, y + size_t(m0) * N, nullptr, mt, K, N,
-                                     nullptr, true, norm_w, eps, st);
+        const int mt = (M - m0 >= max_rows) ? max_rows : (M - m0);
+        int rc = (mma ? awq_gemv_mma_launch : awq_gemv_tma_launch)(x + size_t(m0) * K, qweight, qzeros, scales,
+                                                                   y + size_t(m0) * N, nullptr, mt, K, N, nullptr, true, norm_w,
+                                                                   eps, st);
         if (rc != KUIPER_OK) return rc;
         m0 += mt;
     }
@@ -546,7 +562,8 @@ extern "C" int kuiper_rmsnorm_awq_gemv_accum_f32(const float* h, const uint16_t*
 }
 
 extern "C" int kuiper_awq_gemv_status(void) {
-    const int v = awq_gemv_tma_status();
+    int v = awq_gemv_tma_status();
+    if (v == 0) v = awq_gemv_mma_status();
     if (v == 0) return KUIPER_OK;
     set_error("awq_gemv: a bounded pipeline wait ran out (code %d)", v);
     return KUIPER_INTERNAL_ERROR;
