@@ -104,6 +104,14 @@ KUIPER_API int kuiper_rmsnorm_awq_gemv_accum_f32(const float* h, const uint16_t*
                                                  const int32_t* qweight, const int32_t* qzeros,
                                                  const uint16_t* scales, float* y, int M, int K, int N, int group,
                                                  kuiper_stream_t stream);
+/*
+ * Same as kuiper_awq_gemv_accum_f32 with SwiGLU fused in: gate_up is [M, 2K] (gate | up) and the operand is
+ * x = silu(gate) * up in fp32 (the formula of kuiper_swiglu_f32), rounded to fp16: y[M,N] += x . dequant(qweight).
+ * gate_up is only read.  Replaces a swiglu call + a matmul call.
+ */
+KUIPER_API int kuiper_swiglu_awq_gemv_accum_f32(const float* gate_up, const int32_t* qweight, const int32_t* qzeros,
+                                                const uint16_t* scales, float* y, int M, int K, int N, int group,
+                                                kuiper_stream_t stream);
 /* health check (synchronises): 5 if a bounded wait inside the pipelined GEMV ever ran out on this device */
 KUIPER_API int kuiper_awq_gemv_status(void);
 
@@ -154,13 +162,17 @@ KUIPER_API int kuiper_rmsnorm_f32(const float* x, const uint16_t* w, float* y, i
  * q_out [M, Nq, D] fp32; k, v rounded to bf16 into cache[(slot*Nkv + h)*max_seq + pos][D];
  * the caches hold n_slots sequences; pos and slot are clamped into range on the device.
  * D must be 128.  clear_input != 0 zeroes qkv after it has been read (the buffer is then
- * ready for the next kuiper_awq_gemv_accum_f32 into it).
+ * ready for the next kuiper_awq_gemv_accum_f32 into it).  clear_extra (may be NULL with count 0):
+ * clear_extra_count floats (a multiple of 4, 16-byte aligned) that the kernel zeroes on the side - the
+ * engine passes the gate|up projection buffer, whose consumer is fused into the down projection and
+ * cannot clear it itself.
  */
 KUIPER_API int kuiper_qknorm_rope_kvwrite(float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
                                const float* cos_t, const float* sin_t, const int32_t* pos,
                                const int32_t* slot, int M, int Nq, int Nkv, int D, float eps,
                                int max_seq, int n_slots, float* q_out, uint16_t* kcache,
-                               uint16_t* vcache, int clear_input, kuiper_stream_t stream);
+                               uint16_t* vcache, int clear_input, float* clear_extra,
+                               int64_t clear_extra_count, kuiper_stream_t stream);
 
 /* ---- GQA flash-decoding: placeholder kuiper/include/op/mha.h:1-11 ---- */
 /*

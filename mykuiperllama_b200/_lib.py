@@ -40,6 +40,7 @@ KERNEL_API = {
     "kuiper_awq_gemv_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "kuiper_awq_gemv_accum_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_rmsnorm_awq_gemv_accum_f32": (_i32, [_vp, _vp, _f32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "kuiper_swiglu_awq_gemv_accum_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_awq_gemv_status": (_i32, []),
     "kuiper_awq_gemv_noalloc_scratch_bytes": (_sz, []),
     "kuiper_awq_gemv_f32_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
@@ -48,7 +49,7 @@ KERNEL_API = {
     "kuiper_bf16_gemv_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_rmsnorm_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _vp]),
     "kuiper_qknorm_rope_kvwrite": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _i32,
-                                          _vp, _vp, _vp, _i32, _vp]),
+                                          _vp, _vp, _vp, _i32, _vp, _i64, _vp]),
     "kuiper_flash_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32]),
     "kuiper_flash_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "kuiper_swiglu_f32": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),

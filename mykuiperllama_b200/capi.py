@@ -95,6 +95,17 @@ def rmsnorm_awq_gemv_accum(h, norm_w, eps, qweight, qzeros, scales, y, group=128
     return y
 
 
+def swiglu_awq_gemv_accum(gate_up, qweight, qzeros, scales, y, group=128):
+    """y += (silu(gate) * up) . W with gate_up = [M, 2K]; returns y."""
+    _dev(gate_up, qweight, qzeros, scales, y)
+    M = gate_up.shape[0]
+    K = gate_up.shape[1] // 2
+    N = qweight.shape[1] * 8
+    check(kernels().kuiper_swiglu_awq_gemv_accum_f32(_ptr(gate_up), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(y), M, K, N,
+                                                     group, _stream()))
+    return y
+
+
 def awq_gemm(x, qweight, qzeros, scales, y=None, residual=None, accumulate=False, group=128):
     """Tensor-core INT4 GEMM for M >= 16 rows: y = x . W (+ residual), or y += x . W."""
     _dev(x, qweight, qzeros, scales)
@@ -133,15 +144,19 @@ def rmsnorm(x, w, eps=1e-6, out=None):
     return out
 
 
-def qknorm_rope_kvwrite(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, Nq, Nkv, D, eps, kcache, vcache, clear_input=False):
-    """kcache / vcache: [n_slots, Nkv, max_seq, D] bf16, updated in place; returns q [M, Nq, D]."""
-    _dev(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, kcache, vcache)
+def qknorm_rope_kvwrite(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, Nq, Nkv, D, eps, kcache, vcache, clear_input=False,
+                        clear_extra=None):
+    """kcache / vcache: [n_slots, Nkv, max_seq, D] bf16, updated in place; returns q [M, Nq, D].
+    clear_extra: an fp32 tensor the kernel zeroes on the side."""
+    _dev(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, slot, kcache, vcache, clear_extra)
     M = qkv.shape[0]
     n_slots, _, max_seq, _ = kcache.shape
     q = torch.empty((M, Nq, D), dtype=torch.float32, device=qkv.device)
     check(kernels().kuiper_qknorm_rope_kvwrite(_ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_t), _ptr(sin_t),
                                                _ptr(pos), _ptr(slot), M, Nq, Nkv, D, eps, max_seq, n_slots,
-                                               _ptr(q), _ptr(kcache), _ptr(vcache), int(clear_input), _stream()))
+                                               _ptr(q), _ptr(kcache), _ptr(vcache), int(clear_input),
+                                               _ptr(clear_extra) if clear_extra is not None else None,
+                                               clear_extra.numel() if clear_extra is not None else 0, _stream()))
     return q
 
 

@@ -422,7 +422,7 @@ int awq_gemv_mma_status();
 int awq_gemv_mma_max_rows(bool accumulate);
 int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
                         const float* residual, int rows, int K, int N, void* workspace, bool accumulate,
-                        const uint16_t* norm_w, float eps, cudaStream_t stream);
+                        const uint16_t* norm_w, float eps, bool swiglu, cudaStream_t stream);
 
 }  // namespace kuiper
 
@@ -474,9 +474,11 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
         KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, "awq_gemv: workspace must be 16-byte aligned");
         for (int m0 = 0; m0 < M;) {
             const int mt = (M - m0 >= 2) ? 2 : 1;
-            int rc = (mma ? awq_gemv_mma_launch : awq_gemv_tma_launch)(
-                x + size_t(m0) * K, qweight, qzeros, scales, y + size_t(m0) * N, residual ? residual + size_t(m0) * N : nullptr,
-                mt, K, N, workspace, false, nullptr, 0.f, st);
+            const float* xm = x + size_t(m0) * K;
+            float* ym = y + size_t(m0) * N;
+            const float* rm = residual ? residual + size_t(m0) * N : nullptr;
+            int rc = mma ? awq_gemv_mma_launch(xm, qweight, qzeros, scales, ym, rm, mt, K, N, workspace, false, nullptr, 0.f, false, st)
+                         : awq_gemv_tma_launch(xm, qweight, qzeros, scales, ym, rm, mt, K, N, workspace, false, nullptr, 0.f, st);
             if (rc != KUIPER_OK) return rc;
             m0 += mt;
         }
@@ -522,7 +524,7 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
     return KUIPER_OK;
 }
 
-static int awq_gemv_accum_common(const float* x, const uint16_t* norm_w, float eps, const int32_t* qweight,
+static int awq_gemv_accum_common(const float* x, const uint16_t* norm_w, float eps, bool swiglu, const int32_t* qweight,
                                  const int32_t* qzeros, const uint16_t* scales, float* y, int M, int K, int N, int group,
                                  kuiper_stream_t stream) {
     KUIPER_REQUIRE(x && qweight && qzeros && scales && y, "awq_gemv_accum: null tensor pointer");
@@ -535,12 +537,14 @@ static int awq_gemv_accum_common(const float* x, const uint16_t* norm_w, float e
     KUIPER_REQUIRE(awq_gemv_tma_supported(K, N), "awq_gemv_accum: tensor-map support is unavailable");
     cudaStream_t st = as_stream(stream);
     const bool mma = g_force_impl != 2 && awq_gemv_mma_supported(K, N);
+    KUIPER_REQUIRE(mma || !swiglu, "awq_gemv_accum: the fused SwiGLU needs the tensor-core kernel");
     const int max_rows = mma ? awq_gemv_mma_max_rows(true) : 2;
     for (int m0 = 0; m0 < M;) {
         const int mt = (M - m0 >= max_rows) ? max_rows : (M - m0);
-        int rc = (mma ? awq_gemv_mma_launch : awq_gemv_tma_launch)(x + size_t(m0) * K, qweight, qzeros, scales,
-                                                                   y + size_t(m0) * N, nullptr, mt, K, N, nullptr, true, norm_w,
-                                                                   eps, st);
+        const float* xm = x + size_t(m0) * K * (swiglu ? 2 : 1);
+        float* ym = y + size_t(m0) * N;
+        int rc = mma ? awq_gemv_mma_launch(xm, qweight, qzeros, scales, ym, nullptr, mt, K, N, nullptr, true, norm_w, eps, swiglu, st)
+                     : awq_gemv_tma_launch(xm, qweight, qzeros, scales, ym, nullptr, mt, K, N, nullptr, true, norm_w, eps, st);
         if (rc != KUIPER_OK) return rc;
         m0 += mt;
     }
@@ -550,7 +554,7 @@ static int awq_gemv_accum_common(const float* x, const uint16_t* norm_w, float e
 extern "C" int kuiper_awq_gemv_accum_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
                                          const uint16_t* scales, float* y, int M, int K, int N, int group,
                                          kuiper_stream_t stream) {
-    return awq_gemv_accum_common(x, nullptr, 0.f, qweight, qzeros, scales, y, M, K, N, group, stream);
+    return awq_gemv_accum_common(x, nullptr, 0.f, false, qweight, qzeros, scales, y, M, K, N, group, stream);
 }
 
 extern "C" int kuiper_rmsnorm_awq_gemv_accum_f32(const float* h, const uint16_t* norm_w, float eps, const int32_t* qweight,
@@ -558,7 +562,13 @@ extern "C" int kuiper_rmsnorm_awq_gemv_accum_f32(const float* h, const uint16_t*
                                                  int N, int group, kuiper_stream_t stream) {
     KUIPER_REQUIRE(norm_w != nullptr, "rmsnorm_awq_gemv_accum: null norm weight");
     KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(norm_w) & 15) == 0, "rmsnorm_awq_gemv_accum: norm weight must be 16-byte aligned");
-    return awq_gemv_accum_common(h, norm_w, eps, qweight, qzeros, scales, y, M, K, N, group, stream);
+    return awq_gemv_accum_common(h, norm_w, eps, false, qweight, qzeros, scales, y, M, K, N, group, stream);
+}
+
+extern "C" int kuiper_swiglu_awq_gemv_accum_f32(const float* gate_up, const int32_t* qweight, const int32_t* qzeros,
+                                                const uint16_t* scales, float* y, int M, int K, int N, int group,
+                                                kuiper_stream_t stream) {
+    return awq_gemv_accum_common(gate_up, nullptr, 0.f, true, qweight, qzeros, scales, y, M, K, N, group, stream);
 }
 
 extern "C" int kuiper_awq_gemv_status(void) {

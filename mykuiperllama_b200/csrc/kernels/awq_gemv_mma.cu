@@ -63,6 +63,7 @@ struct MmaGemvParams {
     int* counters;          // ordered mode: [tiles]
     const uint16_t* norm_w; // bf16 [K] or null
     float eps;
+    int swiglu;             // != 0: x is a gate|up row [MT, 2K] and the operand is silu(gate) * up
     int K, N, tiles, upt;   // upt = units per tile = K / 32
     long long U;            // total units
 };
@@ -124,12 +125,49 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1,
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+template <int IMM>
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
+    return v;
+}
+template <int IMM>
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(IMM));
+    return v;
+}
+// w >> 8 as a multiply-high: runs on the FMA pipe and leaves the half-rate integer pipe to the masks
+__device__ __forceinline__ uint32_t shr8(uint32_t w) {
+    uint32_t v;
+    asm("mul.hi.u32 %0, %1, 16777216;" : "=r"(v) : "r"(w));
+    return v;
+}
+__device__ __forceinline__ bool bar_try(uint32_t addr, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+__device__ __noinline__ bool bar_wait_addr(uint32_t addr, uint32_t parity) {
+    for (uint32_t spin = 0; spin < kSpinLimitM; spin++)
+        if (bar_try(addr, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bar_arrive_addr(uint32_t addr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
+}
 __device__ __forceinline__ float2 halves_to_floats(uint32_t u) { return __half22float2(*reinterpret_cast<__half2*>(&u)); }
 
 // MT token rows (1..4).  ACCUM: y += x.W with vector float reductions, the caller guarantees that y holds the
 // addend.  Otherwise y = x.W (+ residual) through workspace slots and arrival counters, summed in CTA order.
 // NORM: the operand is RMSNorm(x) = (x * rstd) * norm_w, formed by the activation warp.
-template <int MT, int STAGES, bool ACCUM, bool NORM, bool NOMATH = false>
+template <int MT, int STAGES, bool ACCUM, bool NORM, int PROBE = 0>
 __global__ void __launch_bounds__(kThreadsMma, kCtasPerSmMma)
 awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParams p) {
     // B-fragment rows of the 2*MT live column slots, one row of zeros for the other lanes, per-token sums
@@ -178,6 +216,12 @@ awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParam
                     ok = false;
                     break;
                 }
+                if (PROBE == 2) {  // measurement aid: no weight traffic at all, the consumers run on stale shared memory
+                    bar_arrive(&full_bar[s]);
+                    if (++kb == p.upt) { kb = 0; t++; }
+                    if (++s == STAGES) { s = 0; parity ^= 1u; }
+                    continue;
+                }
                 bar_expect_tx(&full_bar[s], kStageBytesM);
 #pragma unroll
                 for (int b = 0; b < 4; b++)
@@ -211,7 +255,14 @@ awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParam
         auto fetch = [&](int kblock, float (&v)[MT]) {
 #pragma unroll
             for (int m = 0; m < MT; m++) {
-                float a = __ldcg(p.x + size_t(m) * p.K + kblock * kUnitRowsM + lane);
+                float a;
+                if (p.swiglu) {
+                    const float* gp = p.x + size_t(m) * 2 * p.K + kblock * kUnitRowsM + lane;
+                    const float gate = __ldcg(gp), up = __ldcg(gp + p.K);
+                    a = (gate / (1.0f + expf(-gate))) * up;
+                } else {
+                    a = __ldcg(p.x + size_t(m) * p.K + kblock * kUnitRowsM + lane);
+                }
                 if (NORM) {
                     const uint16_t wn = __ldg(p.norm_w + kblock * kUnitRowsM + lane);
                     a = (a * rstd[m]) * __uint_as_float(uint32_t(wn) << 16);
@@ -319,11 +370,14 @@ awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParam
     };
 
     int t = u0 / p.upt, kb = u0 - t * p.upt;
-    int units_left = u1 - u0;
 
-    uint32_t z_cur[2], z_next[2] = {0u, 0u};
-    uint4 s_cur[2], s_next[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    // constants of the current group and of the one after it (fetched a whole group ahead)
+    uint32_t z_cur[2], z_next[2];
+    uint4 s_cur[2], s_next[2];
     load_consts(t, kb >> 2, z_cur, s_cur);
+    int nt = t, ng = (kb >> 2) + 1;  // the group after the current one on this CTA's path
+    if (ng == groups) { ng = 0; nt++; }
+    load_consts(nt, ng, z_next, s_next);
 
     float acc_g[2][2][4];  // [block][mma][fragment]: raw nibble sums of the current group; columns 4*mma + fragment
     float acc_t[2][8];     // scaled total of the current tile
@@ -336,92 +390,99 @@ awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParam
         for (int i = 0; i < 4; i++) { acc_g[cbi][0][i] = 0.f; acc_g[cbi][1][i] = 0.f; }
     }
 
+    // 32-bit shared-memory addresses that walk the ring with the stage index
+    const uint32_t stage0 = sm_u32(stages), xstage0 = sm_u32(xstages) + xoff;
+    const uint32_t full0 = sm_u32(&full_bar[0]), empty0 = sm_u32(&empty_bar[0]);
+    const uint32_t sum_rel = uint32_t((2 * MT + 1) * kXRowStride + (owner ? tig : 0) * 4) - xoff;
+    uint32_t sbase = stage0, xbase = xstage0, fbar = full0, ebar = empty0;
     int s = 0;
     uint32_t parity = 0;
     bool dead = false;  // a wait ran out: keep walking so that nobody hangs, the result is void
-    while (units_left > 0) {
-        // ---- one column tile: units kb .. kb + seg - 1 of tile t
-        int seg = min(p.upt - kb, units_left);
-        units_left -= seg;
-        while (seg > 0) {
-            // ---- one quantisation group (up to 4 units)
-            const int gu = min(4 - (kb & 3), seg);
-            seg -= gu;
-            const bool more = (seg > 0) || (units_left > 0);
-            if (more) {
-                int ng = (kb >> 2) + 1, nt = t;
-                if (ng == groups) { ng = 0; nt++; }
-                load_consts(nt, ng, z_next, s_next);
+    for (int u = u0; u < u1; u++) {
+        if (!dead && !bar_try(fbar, parity) && !bar_wait_addr(fbar, parity)) {
+            atomicExch(&g_gemv_mma_wait_error, 2);
+            dead = true;
+        }
+        // the unit is taken in two halves of 16 rows so that only half of it is live in registers at a time;
+        // the stage is released after the second half has been read
+        const uint32_t a00 = sbase + off0[0], a10 = sbase + off1[0], a01 = sbase + off0[1], a11 = sbase + off1[1];
+        uint32_t w0[2][2], w1[2][2];
+        uint2 xb[2];
+        auto math = [&]() {
+            if (PROBE == 1) {  // measurement aid: keep the loads alive, skip the arithmetic
+                uint32_t v = 0;
+#pragma unroll
+                for (int rb = 0; rb < 2; rb++) v ^= w0[0][rb] ^ w1[0][rb] ^ w0[1][rb] ^ w1[1][rb] ^ xb[rb].x ^ xb[rb].y;
+                acc_g[0][0][0] += __uint_as_float(v & 0x3fffffffu);
+                return;
             }
-            for (int j = 0; j < gu; j++) {
-                if (!dead && !bar_wait(&full_bar[s], parity)) {
-                    atomicExch(&g_gemv_mma_wait_error, 2);
-                    dead = true;
-                }
-                const unsigned char* st = stages + s * kStageBytesM;
-                const unsigned char* xs = xstages + s * kXStage;
-                uint32_t w0[2][4], w1[2][4];
-                uint2 xb[4];
 #pragma unroll
-                for (int rb = 0; rb < 4; rb++) {
+            for (int rb = 0; rb < 2; rb++) {
 #pragma unroll
-                    for (int cbi = 0; cbi < 2; cbi++) {
-                        w0[cbi][rb] = *reinterpret_cast<const uint32_t*>(st + off0[cbi] + rb * 1024);
-                        w1[cbi][rb] = *reinterpret_cast<const uint32_t*>(st + off1[cbi] + rb * 1024);
-                    }
-                    xb[rb] = *reinterpret_cast<const uint2*>(xs + xoff + rb * 32);
-                }
-                if (owner) gsum += *reinterpret_cast<const float*>(xs + (2 * MT + 1) * kXRowStride + tig * 4);
-                __syncwarp();
-                if (lane == 0) bar_arrive(&empty_bar[s]);  // the stage is in registers now
-                if (++s == STAGES) { s = 0; parity ^= 1u; }
-                kb++;
-                if (NOMATH) {  // measurement aid: keep the loads alive, skip the arithmetic
-                    uint32_t v = 0;
-#pragma unroll
-                    for (int rb = 0; rb < 4; rb++) v ^= w0[0][rb] ^ w1[0][rb] ^ w0[1][rb] ^ w1[1][rb] ^ xb[rb].x ^ xb[rb].y;
-                    acc_g[0][0][0] += __uint_as_float(v & 0x3fffffffu);
-                    continue;
-                }
-#pragma unroll
-                for (int rb = 0; rb < 4; rb++) {
-#pragma unroll
-                    for (int cbi = 0; cbi < 2; cbi++) {
-                        const uint32_t a = w0[cbi][rb], b = w1[cbi][rb];
-                        const uint32_t a8 = a >> 8, b8 = b >> 8;
-                        // fragment rows g / g+8 = column pairs (0,1) / (2,3), then (4,5) / (6,7)
-                        mma_f16(acc_g[cbi][0], a & 0x000f000fu, a & 0x00f000f0u, b & 0x000f000fu, b & 0x00f000f0u, xb[rb].x, xb[rb].y);
-                        mma_f16(acc_g[cbi][1], a8 & 0x000f000fu, a8 & 0x00f000f0u, b8 & 0x000f000fu, b8 & 0x00f000f0u, xb[rb].x, xb[rb].y);
-                    }
+                for (int cbi = 0; cbi < 2; cbi++) {
+                    const uint32_t a = w0[cbi][rb], b = w1[cbi][rb];
+                    const uint32_t a8 = a >> 8, b8 = b >> 8;
+                    // fragment rows g / g+8 = column pairs (0,1) / (2,3), then (4,5) / (6,7)
+                    mma_f16(acc_g[cbi][0], a & 0x000f000fu, a & 0x00f000f0u, b & 0x000f000fu, b & 0x00f000f0u, xb[rb].x, xb[rb].y);
+                    mma_f16(acc_g[cbi][1], a8 & 0x000f000fu, a8 & 0x00f000f0u, b8 & 0x000f000fu, b8 & 0x00f000f0u, xb[rb].x, xb[rb].y);
                 }
             }
-            // ---- group done: take the zero point back out and apply the fp16 scales.  Both the nibble sums and the
-            //      zero pairs carry the factor 2^-24 (columns 0,1,4,5 of a word) or 2^-20 (columns 2,3,6,7); it is
-            //      removed once per tile, which is exact (a power of two).
+        };
+        w0[0][0] = lds32<0>(a00);    w1[0][0] = lds32<0>(a10);    w0[1][0] = lds32<0>(a01);    w1[1][0] = lds32<0>(a11);
+        w0[0][1] = lds32<1024>(a00); w1[0][1] = lds32<1024>(a10); w0[1][1] = lds32<1024>(a01); w1[1][1] = lds32<1024>(a11);
+        xb[0] = lds64<0>(xbase);
+        xb[1] = lds64<32>(xbase);
+        {
+            const float unit_sum = __uint_as_float(lds32<0>(xbase + sum_rel));
+            gsum += owner ? unit_sum : 0.f;
+        }
+        math();
+        w0[0][0] = lds32<2048>(a00); w1[0][0] = lds32<2048>(a10); w0[1][0] = lds32<2048>(a01); w1[1][0] = lds32<2048>(a11);
+        w0[0][1] = lds32<3072>(a00); w1[0][1] = lds32<3072>(a10); w0[1][1] = lds32<3072>(a01); w1[1][1] = lds32<3072>(a11);
+        xb[0] = lds64<64>(xbase);
+        xb[1] = lds64<96>(xbase);
+        __syncwarp();
+        if (lane == 0) bar_arrive_addr(ebar);  // the stage is in registers now
+        if (++s == STAGES) {
+            s = 0; parity ^= 1u; sbase = stage0; xbase = xstage0; fbar = full0; ebar = empty0;
+        } else {
+            sbase += kStageBytesM; xbase += kXStage; fbar += 8; ebar += 8;
+        }
+        kb++;
+        math();
+        const bool tile_end = kb == p.upt;
+        const bool run_end = u + 1 == u1;
+        if ((kb & 3) != 0 && !run_end) continue;
+
+        // ---- group done (or the run ends inside it): take the zero point back out and apply the fp16 scales.  Both
+        //      the nibble sums and the zero pairs carry the factor 2^-24 (columns 0,1,4,5 of a word) or 2^-20
+        //      (columns 2,3,6,7); it is removed once per tile, which is exact (a power of two).
 #pragma unroll
-            for (int cbi = 0; cbi < 2; cbi++) {
-                const uint32_t zw = z_cur[cbi], z8 = zw >> 8;
-                const float2 zf[4] = {halves_to_floats(zw & 0x000f000fu), halves_to_floats(zw & 0x00f000f0u),
-                                      halves_to_floats(z8 & 0x000f000fu), halves_to_floats(z8 & 0x00f000f0u)};
-                const float2 sf[4] = {halves_to_floats(s_cur[cbi].x), halves_to_floats(s_cur[cbi].y),
-                                      halves_to_floats(s_cur[cbi].z), halves_to_floats(s_cur[cbi].w)};
+        for (int cbi = 0; cbi < 2; cbi++) {
+            const uint32_t zw = z_cur[cbi], z8 = zw >> 8;
+            const float2 zf[4] = {halves_to_floats(zw & 0x000f000fu), halves_to_floats(zw & 0x00f000f0u),
+                                  halves_to_floats(z8 & 0x000f000fu), halves_to_floats(z8 & 0x00f000f0u)};
+            const float2 sf[4] = {halves_to_floats(s_cur[cbi].x), halves_to_floats(s_cur[cbi].y),
+                                  halves_to_floats(s_cur[cbi].z), halves_to_floats(s_cur[cbi].w)};
 #pragma unroll
-                for (int pr = 0; pr < 4; pr++) {
-                    // pair pr = columns 2pr, 2pr+1 sits in mma pr>>1, fragment entries 2*(pr&1), 2*(pr&1)+1
-                    float& a0 = acc_g[cbi][pr >> 1][2 * (pr & 1)];
-                    float& a1 = acc_g[cbi][pr >> 1][2 * (pr & 1) + 1];
-                    acc_t[cbi][2 * pr] = fmaf(fmaf(-zf[pr].x, gsum, a0), sf[pr].x, acc_t[cbi][2 * pr]);
-                    acc_t[cbi][2 * pr + 1] = fmaf(fmaf(-zf[pr].y, gsum, a1), sf[pr].y, acc_t[cbi][2 * pr + 1]);
-                    a0 = 0.f;
-                    a1 = 0.f;
-                }
-            }
-            gsum = 0.f;
-            if (more) {
-#pragma unroll
-                for (int cbi = 0; cbi < 2; cbi++) { z_cur[cbi] = z_next[cbi]; s_cur[cbi] = s_next[cbi]; }
+            for (int pr = 0; pr < 4; pr++) {
+                // pair pr = columns 2pr, 2pr+1 sits in mma pr>>1, fragment entries 2*(pr&1), 2*(pr&1)+1
+                float& a0 = acc_g[cbi][pr >> 1][2 * (pr & 1)];
+                float& a1 = acc_g[cbi][pr >> 1][2 * (pr & 1) + 1];
+                acc_t[cbi][2 * pr] = fmaf(fmaf(-zf[pr].x, gsum, a0), sf[pr].x, acc_t[cbi][2 * pr]);
+                acc_t[cbi][2 * pr + 1] = fmaf(fmaf(-zf[pr].y, gsum, a1), sf[pr].y, acc_t[cbi][2 * pr + 1]);
+                a0 = 0.f;
+                a1 = 0.f;
             }
         }
+        gsum = 0.f;
+        if (!run_end) {
+#pragma unroll
+            for (int cbi = 0; cbi < 2; cbi++) { z_cur[cbi] = z_next[cbi]; s_cur[cbi] = s_next[cbi]; }
+            if (++ng == groups) { ng = 0; nt++; }
+            load_consts(nt, ng, z_next, s_next);  // clamped to zeros past the last tile
+        }
+        if (!tile_end && !run_end) continue;
 
         // ---- this CTA's contribution to column tile t is complete
 #pragma unroll
@@ -595,10 +656,11 @@ int sm_count_mma() {
 }
 
 int g_mma_nomath = 0;
+int g_mma_stages = 0;
 
-template <int MT, int STAGES, bool ACCUM, bool NORM, bool NOMATH = false>
+template <int MT, int STAGES, bool ACCUM, bool NORM, int PROBE = 0>
 int launch_mma(const CUtensorMap& map, const MmaGemvParams& p, int ctas, cudaStream_t stream) {
-    auto kern = awq_gemv_mma_kernel<MT, STAGES, ACCUM, NORM, NOMATH>;
+    auto kern = awq_gemv_mma_kernel<MT, STAGES, ACCUM, NORM, PROBE>;
     constexpr int kXStage = (2 * MT + 1) * kXRowStride + 16 * MT;
     const size_t smem = 1024 + size_t(STAGES) * kStageBytesM + ((size_t(STAGES) * kXStage + 15) & ~size_t(15)) +
                         (ACCUM ? 0 : size_t(MT) * kTileColsM * sizeof(float));
@@ -642,6 +704,7 @@ int launch_mma_rows(int rows, const CUtensorMap& map, const MmaGemvParams& p, in
 
 void awq_gemv_mma_set_tuning(const char* key, int value) {
     if (!strcmp(key, "gemv_nomath")) g_mma_nomath = value;
+    if (!strcmp(key, "gemv_stages")) g_mma_stages = value;
 }
 
 int awq_gemv_mma_status() {
@@ -660,7 +723,7 @@ int awq_gemv_mma_max_rows(bool accumulate) { return accumulate ? 4 : 2; }
 // [counters: tiles ints, padded to 256 bytes][partial slots: (CTAs + tiles) x 2 x 1024 floats].
 int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
                         const float* residual, int rows, int K, int N, void* workspace, bool accumulate,
-                        const uint16_t* norm_w, float eps, cudaStream_t stream) {
+                        const uint16_t* norm_w, float eps, bool swiglu, cudaStream_t stream) {
     if (rows < 1 || rows > awq_gemv_mma_max_rows(accumulate)) {
         set_error("awq_gemv_mma: %d token rows in one launch", rows);
         return KUIPER_INVALID_ARGUMENT;
@@ -678,6 +741,7 @@ int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* q
     p.scales = reinterpret_cast<const __half*>(scales);
     p.norm_w = norm_w;
     p.eps = eps;
+    p.swiglu = swiglu ? 1 : 0;
     p.K = K;
     p.N = N;
     p.tiles = (N + kTileColsM - 1) / kTileColsM;
@@ -692,12 +756,16 @@ int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* q
     p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + head);
     long long ctas = (long long)sm_count_mma() * kCtasPerSmMma;
     if (ctas > p.U) ctas = p.U;
-    if (norm_w && !accumulate) {
-        set_error("awq_gemv_mma: the fused input norm exists in accumulate mode only");
+    if ((norm_w || swiglu) && !accumulate) {
+        set_error("awq_gemv_mma: the fused input norm / SwiGLU exist in accumulate mode only");
         return KUIPER_INVALID_ARGUMENT;
     }
     if (accumulate && norm_w) return launch_mma_rows<true, true>(rows, map, p, int(ctas), stream);
-    if (accumulate && g_mma_nomath && rows == 1) return launch_mma<1, 5, true, false, true>(map, p, int(ctas), stream);
+    if (accumulate && g_mma_nomath == 1 && rows == 1) return launch_mma<1, 5, true, false, 1>(map, p, int(ctas), stream);
+    if (accumulate && g_mma_nomath == 2 && rows == 1) return launch_mma<1, 5, true, false, 2>(map, p, int(ctas), stream);
+    if (accumulate && !norm_w && rows == 1 && g_mma_stages == 3) return launch_mma<1, 3, true, false>(map, p, int(ctas), stream);
+    if (accumulate && !norm_w && rows == 1 && g_mma_stages == 4) return launch_mma<1, 4, true, false>(map, p, int(ctas), stream);
+    if (accumulate && !norm_w && rows == 1 && g_mma_stages == 6) return launch_mma<1, 6, true, false>(map, p, int(ctas), stream);
     if (accumulate) return launch_mma_rows<true, false>(rows, map, p, int(ctas), stream);
     if (rows == 2) return launch_mma<2, 5, false, false>(map, p, int(ctas), stream);
     return launch_mma<1, 5, false, false>(map, p, int(ctas), stream);

@@ -17,9 +17,13 @@ __global__ void __launch_bounds__(128)
 qknorm_rope_kvwrite_kernel(float* qkv, const uint16_t* __restrict__ q_norm_w, const uint16_t* __restrict__ k_norm_w,
                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int32_t* pos,
                            const int32_t* slot, int M, int Nq, int Nkv, float eps, int max_seq, int n_slots, float* q_out,
-                           uint16_t* kcache, uint16_t* vcache, int clear_input) {
+                           uint16_t* kcache, uint16_t* vcache, int clear_input, float4* clear_extra, int clear_extra_vec4) {
     pdl_launch_dependents();
     pdl_wait();
+    // optional side job: zero another buffer (the gate|up projection output, which nothing uses at this point of a
+    // layer and which the next accumulating matmul into it wants zeroed)
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < clear_extra_vec4; i += gridDim.x * blockDim.x)
+        clear_extra[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     const int heads = Nq + 2 * Nkv;
     const int wid = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (wid >= M * heads) return;
@@ -82,7 +86,12 @@ extern "C" int kuiper_qknorm_rope_kvwrite(float* qkv, const uint16_t* q_norm_w, 
                                           const float* cos_t, const float* sin_t, const int32_t* pos,
                                           const int32_t* slot, int M, int Nq, int Nkv, int D, float eps,
                                           int max_seq, int n_slots, float* q_out, uint16_t* kcache, uint16_t* vcache,
-                                          int clear_input, kuiper_stream_t stream) {
+                                          int clear_input, float* clear_extra, int64_t clear_extra_count,
+                                          kuiper_stream_t stream) {
+    KUIPER_REQUIRE(clear_extra_count >= 0 && (clear_extra_count == 0 || clear_extra), "qknorm_rope: bad extra buffer");
+    KUIPER_REQUIRE(clear_extra_count % 4 == 0 && (reinterpret_cast<uintptr_t>(clear_extra) & 15) == 0 &&
+                       clear_extra_count / 4 <= 0x7fffffff,
+                   "qknorm_rope: the extra buffer must be 16-byte aligned with a multiple of 4 floats");
     KUIPER_REQUIRE(qkv && q_norm_w && k_norm_w && cos_t && sin_t && pos && slot && q_out && kcache && vcache,
                    "qknorm_rope: null tensor pointer");
     KUIPER_REQUIRE(D == kD, "qknorm_rope: head_dim %d is not supported (128 only)", D);
@@ -90,6 +99,6 @@ extern "C" int kuiper_qknorm_rope_kvwrite(float* qkv, const uint16_t* q_norm_w, 
     const int warps = M * (Nq + 2 * Nkv);
     return pdl_status(launch_pdl(qknorm_rope_kvwrite_kernel, dim3((warps + 3) / 4), dim3(128), 0, as_stream(stream), qkv, q_norm_w,
                                  k_norm_w, cos_t, sin_t, pos, slot, M, Nq, Nkv, eps, max_seq, n_slots, q_out, kcache, vcache,
-                                 clear_input),
+                                 clear_input, reinterpret_cast<float4*>(clear_extra), int(clear_extra_count / 4)),
                       "qknorm_rope_kvwrite");
 }

@@ -34,8 +34,11 @@ public:
         input_norm_ = weight;
         input_norm_eps_ = eps;
     }
-    // where RMSNorm(input) is written when the row count takes the tensor-core path, which has no fused norm
-    // ([max rows, dim1] fp32)
+    // accumulate mode only: the input is a gate|up row [M, 2*dim1] and the layer applies SwiGLU inside the matmul
+    // kernel (operand = silu(gate) * up); saves the separate activation launch.  The input is only read.
+    void set_input_swiglu(bool on) { input_swiglu_ = on; }
+    // where RMSNorm(input) / SwiGLU(input) is written when the row count takes the tensor-core path, which has
+    // no fused prologue ([max rows, dim1] fp32)
     void set_norm_scratch(const tensor::Tensor& scratch) { norm_scratch_ = scratch; }
     // quantised layers, fp16-operand mode: inputs of at least this many rows go to the tcgen05 GEMM
     // instead of the GEMV (0 = never)
@@ -56,6 +59,7 @@ private:
     int32_t dim1_ = 0;
     bool has_residual_ = false;
     bool accumulate_ = false;
+    bool input_swiglu_ = false;
     tensor::Tensor input_norm_;
     float input_norm_eps_ = 1e-6f;
     int32_t act_mode_ = 1;

@@ -22,6 +22,13 @@ public:
     void set_cache(const tensor::Tensor& key_cache, const tensor::Tensor& value_cache);
     // zero the qkv input after reading it (it then serves as the addend of an accumulating matmul)
     void set_clear_input(bool clear) { clear_input_ = clear; }
+    // another Fp32 buffer the kernel zeroes on the side (an empty tensor switches it off); the model passes the
+    // gate|up projection output, which is idle while this layer runs
+    // row_elems: floats per token row; the kernel clears as many rows as the pass has
+    void set_clear_extra(const tensor::Tensor& buffer, int32_t row_elems) {
+        clear_extra_ = buffer;
+        clear_extra_row_ = row_elems;
+    }
 
 protected:
     base::DataType weight_data_type(int32_t idx) const override;
@@ -30,7 +37,8 @@ private:
     int32_t head_num_ = 0, kv_head_num_ = 0, head_size_ = 0;
     float eps_ = 1e-6f;
     bool clear_input_ = false;
-    tensor::Tensor key_cache_, value_cache_;
+    tensor::Tensor key_cache_, value_cache_, clear_extra_;
+    int32_t clear_extra_row_ = 0;
 };
 }  // namespace op
 

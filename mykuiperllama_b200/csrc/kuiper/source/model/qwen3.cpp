@@ -201,6 +201,9 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
             // passes of 16 rows or more take the tensor-core path, which wants the normed rows materialised
             L.qkv->set_norm_scratch(get_buffer(ModelBufferType::OutputRMSNorm));
             L.gate_up->set_norm_scratch(get_buffer(ModelBufferType::FFNRMSNorm));
+            // SwiGLU runs inside the down projection, which only reads the gate|up buffer
+            L.down->set_input_swiglu(true);
+            L.down->set_norm_scratch(get_buffer(ModelBufferType::W2Output));
         }
         L.key_cache = dev(DataType::DataTypeBf16, {c.max_batch, Hkv, c.max_seq_len, D});
         L.value_cache = dev(DataType::DataTypeBf16, {c.max_batch, Hkv, c.max_seq_len, D});
@@ -212,6 +215,8 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         STATUS_CHECK(L.rope->set_weight(1, dev(DataType::DataTypeBf16, {D})));
         L.rope->set_cache(L.key_cache, L.value_cache);
         L.rope->set_clear_input(accumulate_);
+        // ... so this layer's rotary kernel zeroes that buffer for the next gate|up projection to accumulate into
+        if (accumulate_) L.rope->set_clear_extra(get_buffer(ModelBufferType::W1Output), 2 * I);
         L.mha = std::make_unique<op::MultiHeadAttention>(device_type_, Hq, Hkv, D);
         L.mha->set_cuda_config(cuda_config_);
         L.mha->set_cache(L.key_cache, L.value_cache);
@@ -394,8 +399,12 @@ base::Status Qwen3Model::run_pass(int32_t M) {
             RETURN_IF_ERROR(L.post_norm->forward(h, xn2));
             RETURN_IF_ERROR(L.gate_up->forward(xn2, gu));
         }
-        RETURN_IF_ERROR(L.swiglu->forward(gu, act));
-        RETURN_IF_ERROR(project_and_reduce(*L.down, act));
+        if (accumulate_) {
+            RETURN_IF_ERROR(project_and_reduce(*L.down, gu));  // SwiGLU fused into the projection
+        } else {
+            RETURN_IF_ERROR(L.swiglu->forward(gu, act));
+            RETURN_IF_ERROR(project_and_reduce(*L.down, act));
+        }
     }
     if (logit_rows_ > 0) {
         // logits only for the last logit_rows_ rows of the pass

@@ -78,7 +78,7 @@ void matmul_kernel_quant_cu(const Tensor& input, const Tensor& qweight, const Te
 
 void matmul_kernel_quant_accum_cu(const Tensor& input, const Tensor& qweight, const Tensor& qzeros, const Tensor& scales,
                                   const Tensor& output, int32_t group_size, const Tensor* input_norm_weight, float eps,
-                                  void* stream) {
+                                  bool input_swiglu, void* stream) {
     require_cuda(input, "matmul input");
     require_cuda(qweight, "matmul qweight");
     require_cuda(qzeros, "matmul qzeros");
@@ -86,9 +86,17 @@ void matmul_kernel_quant_accum_cu(const Tensor& input, const Tensor& qweight, co
     require_cuda(output, "matmul output");
     CHECK_EQ(qweight.dims_size(), 2);
     const int32_t K = qweight.get_dim(0), N = qweight.get_dim(1) * 8;
-    CHECK_EQ(input.size() % size_t(K), size_t(0));
-    const int32_t M = int32_t(input.size() / size_t(K));
+    const size_t in_row = size_t(K) * (input_swiglu ? 2 : 1);
+    CHECK_EQ(input.size() % in_row, size_t(0));
+    const int32_t M = int32_t(input.size() / in_row);
     CHECK_EQ(output.size(), size_t(M) * size_t(N));
+    if (input_swiglu) {
+        CHECK(input_norm_weight == nullptr);
+        KERNEL_OK(kuiper_swiglu_awq_gemv_accum_f32(input.ptr<float>(), qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(),
+                                                   scales.ptr<uint16_t>(), out_ptr<float>(output), M, K, N, group_size,
+                                                   as_stream(stream)));
+        return;
+    }
     if (input_norm_weight) {
         require_cuda(*input_norm_weight, "matmul input norm weight");
         CHECK_EQ(input_norm_weight->size(), size_t(K));
@@ -135,8 +143,9 @@ void rmsnorm_kernel_cu(const Tensor& input, const Tensor& weight, const Tensor& 
 void rope_kernel_cu(const Tensor& qkv, const Tensor& q_norm, const Tensor& k_norm, const Tensor& cos_cache,
                     const Tensor& sin_cache, const Tensor& pos, const Tensor& slot, const Tensor& q_out,
                     const Tensor& key_cache, const Tensor& value_cache, int32_t head_num, int32_t kv_head_num,
-                    int32_t head_size, float eps, bool clear_input, void* stream) {
+                    int32_t head_size, float eps, bool clear_input, const Tensor* clear_extra, void* stream) {
     require_cuda(qkv, "rope qkv");
+    if (clear_extra) require_cuda(*clear_extra, "rope extra buffer");
     require_cuda(q_out, "rope q_out");
     require_cuda(key_cache, "rope key cache");
     require_cuda(value_cache, "rope value cache");
@@ -151,7 +160,8 @@ void rope_kernel_cu(const Tensor& qkv, const Tensor& q_norm, const Tensor& k_nor
                                          slot.ptr<int32_t>(), M, head_num, kv_head_num, head_size, eps,
                                          key_cache.get_dim(2), key_cache.get_dim(0), out_ptr<float>(q_out),
                                          out_ptr<uint16_t>(key_cache), out_ptr<uint16_t>(value_cache), clear_input ? 1 : 0,
-                                         as_stream(stream)));
+                                         clear_extra ? out_ptr<float>(*clear_extra) : nullptr,
+                                         clear_extra ? int64_t(clear_extra->size()) : 0, as_stream(stream)));
 }
 
 void mha_kernel_cu(const Tensor& query, const Tensor& key_cache, const Tensor& value_cache, const Tensor& seq_len,

@@ -31,10 +31,12 @@ using MatmulKernelQuant = void (*)(const tensor::Tensor& input, const tensor::Te
 
 // output[M,N] += input[M,K] . dequant(...): the output already holds the addend (residual stream or zeros).
 // With input_norm_weight (bf16 [K]) the operand is RMSNorm(input) formed inside the kernel.
+// With input_swiglu the input is a gate|up row [M, 2K] and the operand is silu(gate) * up (no norm then).
 using MatmulKernelQuantAccum = void (*)(const tensor::Tensor& input, const tensor::Tensor& qweight,
                                         const tensor::Tensor& qzeros, const tensor::Tensor& scales,
                                         const tensor::Tensor& output, int32_t group_size,
-                                        const tensor::Tensor* input_norm_weight, float eps, void* stream);
+                                        const tensor::Tensor* input_norm_weight, float eps, bool input_swiglu,
+                                        void* stream);
 
 // Tensor-core path for M >= 16 rows: output = input . dequant(...) (+ residual), or output += ... when accumulate.
 using MatmulKernelQuantGemm = void (*)(const tensor::Tensor& input, const tensor::Tensor& qweight,
@@ -49,7 +51,7 @@ using RoPEKernel = void (*)(const tensor::Tensor& qkv, const tensor::Tensor& q_n
                             const tensor::Tensor& cos_cache, const tensor::Tensor& sin_cache, const tensor::Tensor& pos,
                             const tensor::Tensor& slot, const tensor::Tensor& q_out, const tensor::Tensor& key_cache,
                             const tensor::Tensor& value_cache, int32_t head_num, int32_t kv_head_num, int32_t head_size,
-                            float eps, bool clear_input, void* stream);
+                            float eps, bool clear_input, const tensor::Tensor* clear_extra, void* stream);
 
 using MHAKernel = void (*)(const tensor::Tensor& query, const tensor::Tensor& key_cache, const tensor::Tensor& value_cache,
                            const tensor::Tensor& seq_len, const tensor::Tensor& slot, const tensor::Tensor& output,

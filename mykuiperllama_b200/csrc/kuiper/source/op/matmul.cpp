@@ -31,8 +31,9 @@ base::Status MatmulLayer::check() const {
         LOG(ERROR) << "The input tensor error in the matmul layer.";
         return status;
     }
-    if (x.size() % size_t(dim1_) != 0) return base::error::invalid_argument("The input width is not the layer's dim1.");
-    const size_t M = x.size() / size_t(dim1_);
+    const size_t in_row = size_t(dim1_) * (input_swiglu_ ? 2 : 1);
+    if (x.size() % in_row != 0) return base::error::invalid_argument("The input width is not the layer's dim1.");
+    const size_t M = x.size() / in_row;
     status = check_tensor(get_output(0), device_type_, data_type_);
     if (status && get_output(0).size() != M * size_t(dim0_))
         status = base::error::invalid_argument("The output tensor has a wrong element count.");
@@ -67,19 +68,24 @@ base::Status MatmulLayer::forward() {
     base::Status status = check();
     if (!status) return status;
     if (device_type_ == base::DeviceType::DeviceCUDA) CHECK_NE(cuda_config_, nullptr);
-    const int32_t M = int32_t(get_input(0).size() / size_t(dim1_));
+    const int32_t M = int32_t(get_input(0).size() / (size_t(dim1_) * (input_swiglu_ ? 2 : 1)));
+    if (input_swiglu_ && !(is_quant_layer_ && accumulate_ && input_norm_.is_empty()))
+        return base::error::invalid_argument("the fused SwiGLU input needs a quantised layer in accumulate mode without a norm");
     if (is_quant_layer_ && act_mode_ == 1 && gemm_min_rows_ > 0 && M >= gemm_min_rows_) {
         // enough rows for the tensor cores: x and the dequantised weight go through tcgen05 as fp16
         if (accumulate_ && has_residual_) return base::error::invalid_argument("accumulate mode takes no residual input");
         const tensor::Tensor* x = &get_input(0);
         tensor::Tensor normed;
-        if (accumulate_ && !input_norm_.is_empty()) {
-            if (norm_scratch_.is_empty() || norm_scratch_.size() < get_input(0).size())
-                return base::error::invalid_argument("the tensor-core path needs a norm scratch of the input's size");
+        if (accumulate_ && (!input_norm_.is_empty() || input_swiglu_)) {
+            if (norm_scratch_.is_empty() || norm_scratch_.size() < size_t(M) * size_t(dim1_))
+                return base::error::invalid_argument("the tensor-core path needs a scratch of the operand's size");
             normed = tensor::Tensor(base::DataType::DataTypeFp32, std::vector<int32_t>{M, dim1_}, false, nullptr,
                                     const_cast<float*>(norm_scratch_.ptr<float>()));
             normed.set_device_type(device_type_);
-            kernel::get_rmsnorm_kernel(device_type_)(get_input(0), input_norm_, normed, input_norm_eps_, stream());
+            if (input_swiglu_)
+                kernel::get_swiglu_kernel(device_type_)(get_input(0), normed, false, stream());
+            else
+                kernel::get_rmsnorm_kernel(device_type_)(get_input(0), input_norm_, normed, input_norm_eps_, stream());
             x = &normed;
         }
         kernel::get_matmul_kernel_quant_gemm(device_type_)(*x, get_weight(0), get_weight(1), scales_, get_output(0),
@@ -89,7 +95,7 @@ base::Status MatmulLayer::forward() {
         if (has_residual_) return base::error::invalid_argument("accumulate mode takes no residual input");
         kernel::get_matmul_kernel_quant_accum(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),
                                                             group_size_, input_norm_.is_empty() ? nullptr : &input_norm_,
-                                                            input_norm_eps_, stream());
+                                                            input_norm_eps_, input_swiglu_, stream());
     } else if (is_quant_layer_) {
         kernel::get_matmul_kernel_quant(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),
                                                       has_residual_ ? &get_input(1) : nullptr, group_size_, act_mode_,

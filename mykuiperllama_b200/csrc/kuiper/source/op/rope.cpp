@@ -59,9 +59,20 @@ base::Status RoPELayer::check() const {
 base::Status RoPELayer::forward() {
     base::Status status = check();
     if (!status) return status;
+    tensor::Tensor extra;
+    if (!clear_extra_.is_empty() && clear_extra_row_ > 0) {
+        const int32_t row = (head_num_ + 2 * kv_head_num_) * head_size_;
+        const int32_t M = int32_t(get_input(0).size() / size_t(row));
+        if (size_t(M) * size_t(clear_extra_row_) > clear_extra_.size())
+            return base::error::invalid_argument("the extra buffer is smaller than the pass");
+        extra = tensor::Tensor(base::DataType::DataTypeFp32, std::vector<int32_t>{M, clear_extra_row_}, false, nullptr,
+                               const_cast<float*>(clear_extra_.ptr<float>()));
+        extra.set_device_type(device_type_);
+    }
     kernel::get_rope_kernel(device_type_)(get_input(0), get_weight(0), get_weight(1), get_input(3), get_input(4),
                                           get_input(1), get_input(2), get_output(0), key_cache_, value_cache_, head_num_,
-                                          kv_head_num_, head_size_, eps_, clear_input_, stream());
+                                          kv_head_num_, head_size_, eps_, clear_input_,
+                                          extra.is_empty() ? nullptr : &extra, stream());
     return base::error::success();
 }
 

@@ -146,6 +146,25 @@ def test_rmsnorm_fused_into_accumulating_gemv(cuda, oracle, M, K, N):
     assert err <= SPEC_TOL and err <= 1e-3
 
 
+@pytest.mark.parametrize("M,K,N", [(1, 12288, 4096), (2, 1024, 2048), (4, 3072, 1024), (1, 256, 1056)])
+def test_swiglu_fused_into_accumulating_gemv(cuda, oracle, M, K, N):
+    # y += (silu(gate) * up) . W: the activation is formed by the kernel's activation warp, gate|up is only read
+    rng = np.random.default_rng(M + K + N)
+    q, z, s = awq_random(rng, K, N)
+    qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
+    gu = rng.standard_normal((M, 2 * K)).astype(np.float32)
+    addend = rng.standard_normal((M, N)).astype(np.float32)
+    act = np.stack([oracle.swiglu(gu[m, :K], gu[m, K:]) for m in range(M)])
+    ref = oracle.awq_gemv(act, qw, qz, su, act_round=oracle.ROUND_FP16).astype(np.float64) + addend
+    y, tgu = dev(addend), dev(gu)
+    cuda.swiglu_awq_gemv_accum(tgu, dev(qw), dev(qz), dev(su, torch.float16), y)
+    torch.cuda.synchronize()
+    err = rel_err(y.cpu().numpy(), ref)
+    assert err <= SPEC_TOL and err <= 1e-5  # expf may differ by an ulp between host and device
+    assert np.array_equal(tgu.cpu().numpy(), gu)
+    cuda.awq_gemv_status()
+
+
 def test_awq_gemv_ragged_width_uses_generic_kernel(cuda, oracle):
     err, *_ = _gemv_case(cuda, oracle, np.random.default_rng(5), 2, 256, 40, 1, residual=True)
     assert err <= 2e-6
@@ -292,6 +311,22 @@ def test_swiglu_and_rope_can_clear_their_input(cuda, oracle):
     q1 = cuda.qknorm_rope_kvwrite(qkv.clone(), qn, qn, dev(cos_t), dev(sin_t), pos, slot, Nq, Nkv, D, 1e-6, kc.clone(), vc.clone())
     q2 = cuda.qknorm_rope_kvwrite(qkv, qn, qn, dev(cos_t), dev(sin_t), pos, slot, Nq, Nkv, D, 1e-6, kc, vc, clear_input=True)
     assert torch.equal(q1, q2) and float(qkv.abs().max()) == 0.0
+
+
+def test_rope_kernel_clears_a_side_buffer(cuda, oracle):
+    rng = np.random.default_rng(9)
+    M, Nq, Nkv, D = 2, 4, 2, 128
+    qkv = dev(rng.standard_normal((M, (Nq + 2 * Nkv) * D)).astype(np.float32))
+    w = dev(oracle.f32_to_bf16(np.ones(D, np.float32)))
+    cos_t, sin_t = (dev(t) for t in oracle.rope_tables(16, D, 1e6))
+    kc = torch.zeros((1, Nkv, 16, D), dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    side = torch.ones((M, 1000), device="cuda")
+    keep = torch.ones(64, device="cuda")
+    cuda.qknorm_rope_kvwrite(qkv, w, w, cos_t, sin_t, dev(np.array([3, 4], np.int32)), dev(np.zeros(2, np.int32)), Nq, Nkv, D,
+                             1e-6, kc, vc, clear_input=True, clear_extra=side)
+    torch.cuda.synchronize()
+    assert float(side.abs().max()) == 0.0 and float(qkv.abs().max()) == 0.0 and float(keep.min()) == 1.0
 
 
 def test_embedding_is_exact(cuda, oracle):
