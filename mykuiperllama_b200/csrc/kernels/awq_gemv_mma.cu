@@ -50,6 +50,7 @@ constexpr int kBoxBytes = kBoxWords * 4 * kUnitRowsM;   // 4 KB
 constexpr int kStageBytesM = 4 * kBoxBytes;             // 16 KB
 constexpr int kXRowStride = 160;                // bytes between the B-fragment rows of two column slots
 constexpr uint32_t kSpinLimitM = 1u << 22;
+constexpr int kStagesM = 3;                     // ring depth: deeper rings measured slower (more queued loads at start)
 
 __device__ int g_gemv_mma_wait_error = 0;
 
@@ -693,10 +694,10 @@ int launch_mma(const CUtensorMap& map, const MmaGemvParams& p, int ctas, cudaStr
 template <bool ACCUM, bool NORM>
 int launch_mma_rows(int rows, const CUtensorMap& map, const MmaGemvParams& p, int ctas, cudaStream_t stream) {
     switch (rows) {
-        case 1: return launch_mma<1, 5, ACCUM, NORM>(map, p, ctas, stream);
-        case 2: return launch_mma<2, 5, ACCUM, NORM>(map, p, ctas, stream);
-        case 3: return launch_mma<3, 5, ACCUM, NORM>(map, p, ctas, stream);
-        default: return launch_mma<4, 5, ACCUM, NORM>(map, p, ctas, stream);
+        case 1: return launch_mma<1, kStagesM, ACCUM, NORM>(map, p, ctas, stream);
+        case 2: return launch_mma<2, kStagesM, ACCUM, NORM>(map, p, ctas, stream);
+        case 3: return launch_mma<3, kStagesM, ACCUM, NORM>(map, p, ctas, stream);
+        default: return launch_mma<4, kStagesM, ACCUM, NORM>(map, p, ctas, stream);
     }
 }
 
@@ -761,14 +762,14 @@ int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* q
         return KUIPER_INVALID_ARGUMENT;
     }
     if (accumulate && norm_w) return launch_mma_rows<true, true>(rows, map, p, int(ctas), stream);
-    if (accumulate && g_mma_nomath == 1 && rows == 1) return launch_mma<1, 5, true, false, 1>(map, p, int(ctas), stream);
-    if (accumulate && g_mma_nomath == 2 && rows == 1) return launch_mma<1, 5, true, false, 2>(map, p, int(ctas), stream);
-    if (accumulate && !norm_w && rows == 1 && g_mma_stages == 3) return launch_mma<1, 3, true, false>(map, p, int(ctas), stream);
+    if (accumulate && g_mma_nomath == 1 && rows == 1) return launch_mma<1, kStagesM, true, false, 1>(map, p, int(ctas), stream);
+    if (accumulate && g_mma_nomath == 2 && rows == 1) return launch_mma<1, kStagesM, true, false, 2>(map, p, int(ctas), stream);
+    if (accumulate && !norm_w && rows == 1 && g_mma_stages == 5) return launch_mma<1, 5, true, false>(map, p, int(ctas), stream);
     if (accumulate && !norm_w && rows == 1 && g_mma_stages == 4) return launch_mma<1, 4, true, false>(map, p, int(ctas), stream);
     if (accumulate && !norm_w && rows == 1 && g_mma_stages == 6) return launch_mma<1, 6, true, false>(map, p, int(ctas), stream);
     if (accumulate) return launch_mma_rows<true, false>(rows, map, p, int(ctas), stream);
-    if (rows == 2) return launch_mma<2, 5, false, false>(map, p, int(ctas), stream);
-    return launch_mma<1, 5, false, false>(map, p, int(ctas), stream);
+    if (rows == 2) return launch_mma<2, kStagesM, false, false>(map, p, int(ctas), stream);
+    return launch_mma<1, kStagesM, false, false>(map, p, int(ctas), stream);
 }
 
 }  // namespace kuiper
