@@ -58,8 +58,11 @@ flash_decode_kernel(const FlashParams p) {
     int sl = p.slot[m];
     sl = sl < 0 ? 0 : (sl >= p.n_slots ? p.n_slots - 1 : sl);
     // slice of the KV range owned by this CTA, in units of 64 rows
-    const int blocks = (L + 63) / 64;
+    const int blocks = max((L + 63) / 64, 1);
     const int per = (blocks + p.S - 1) / p.S;
+    // splits that have rows; the others leave at once and are not waited for
+    const int n_active = (blocks + per - 1) / per;
+    if (split >= n_active) return;
     const int begin = split * per * 64;
     const int end = min(L, begin + per * 64);
 
@@ -204,7 +207,7 @@ flash_decode_kernel(const FlashParams p) {
         fo[h] = acc; fm[h] = nm; fs[h] = ssum;
     }
 
-    if (p.S == 1) {
+    if (n_active == 1) {
 #pragma unroll
         for (int h = 0; h < R; h++)
             p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + t] = fs[h] > 0.f ? fo[h] / fs[h] : 0.f;
@@ -224,55 +227,57 @@ flash_decode_kernel(const FlashParams p) {
     __syncthreads();
     if (t == 0) {
         const int prev = atomicAdd(p.counters + m * p.Nkv + kvh, 1);
-        s_last = (prev == p.S - 1);
+        s_last = (prev == n_active - 1);
         if (s_last) p.counters[m * p.Nkv + kvh] = 0;
     }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // ---- final combine by the last CTA: fetch every slice's (max, sum) at once, turn them into
-    // weights in shared memory, then add the partial outputs in slice order with eight loads in flight
+    // ---- final combine by the last CTA.  Weights first: warp w takes heads w, w + 4, ...; lane l holds the
+    // (max, sum) of slices l and l + 32, so the maximum and the denominator are two warp reductions.
     __shared__ float s_w[64 * R];   // weight of slice sp for head h at [sp * R + h]
-    __shared__ float s_l[64 * R];   // softmax denominators of the slices
     __shared__ float s_den[R];
-    for (int i = t; i < p.S * R; i += kWarps * 32) {
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (pbase * R + i) * 2));
-        s_w[i] = ml.x;  // slice maximum
-        s_l[i] = ml.y;
+    for (int h = warp; h < R; h += kWarps) {
+        float2 ml0 = make_float2(-INFINITY, 0.f), ml1 = ml0;
+        if (lane < n_active) ml0 = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((pbase + lane) * R + h) * 2));
+        if (lane + 32 < n_active) ml1 = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((pbase + lane + 32) * R + h) * 2));
+        const float nm = warp_max(fmaxf(ml0.x, ml1.x));
+        const float w0 = (ml0.x == -INFINITY) ? 0.f : __expf(ml0.x - nm);
+        const float w1 = (ml1.x == -INFINITY) ? 0.f : __expf(ml1.x - nm);
+        const float den = warp_sum(ml0.y * w0 + ml1.y * w1);
+        s_w[lane * R + h] = w0;
+        s_w[(lane + 32) * R + h] = w1;
+        if (lane == 0) s_den[h] = den;
     }
     __syncthreads();
-    if (t < R) {
-        float nm = -INFINITY;
-        for (int sp = 0; sp < p.S; sp++) nm = fmaxf(nm, s_w[sp * R + t]);
-        s_den[t] = nm;
+    // then the partial outputs in slice order, eight slices of every head in flight per thread
+    float acc[R];
+#pragma unroll
+    for (int h = 0; h < R; h++) acc[h] = 0.f;
+    const float* po = p.part_o + pbase * R * kD + t;
+    int sp = 0;
+    for (; sp + 8 <= n_active; sp += 8) {
+        float a[8][R];
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+#pragma unroll
+            for (int h = 0; h < R; h++) a[q][h] = __ldcg(po + (size_t(sp + q) * R + h) * kD);
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+#pragma unroll
+            for (int h = 0; h < R; h++) acc[h] = fmaf(a[q][h], s_w[(sp + q) * R + h], acc[h]);
     }
-    __syncthreads();
-    for (int i = t; i < p.S * R; i += kWarps * 32) {
-        const float wm = s_w[i], nm = s_den[i % R];
-        s_w[i] = (wm == -INFINITY) ? 0.f : __expf(wm - nm);
+    for (; sp < n_active; sp++) {
+        float a[R];
+#pragma unroll
+        for (int h = 0; h < R; h++) a[h] = __ldcg(po + (size_t(sp) * R + h) * kD);
+#pragma unroll
+        for (int h = 0; h < R; h++) acc[h] = fmaf(a[h], s_w[sp * R + h], acc[h]);
     }
-    __syncthreads();
-    if (t < R) {
-        float den = 0.f;
-        for (int sp = 0; sp < p.S; sp++) den += s_l[sp * R + t] * s_w[sp * R + t];
-        s_den[t] = den;
-    }
-    __syncthreads();
 #pragma unroll
     for (int h = 0; h < R; h++) {
-        float acc = 0.f;
-        const float* po = p.part_o + (pbase * R + h) * kD + t;
-        int sp = 0;
-        for (; sp + 8 <= p.S; sp += 8) {
-            float a[8];
-#pragma unroll
-            for (int q = 0; q < 8; q++) a[q] = __ldcg(po + size_t(sp + q) * R * kD);
-#pragma unroll
-            for (int q = 0; q < 8; q++) acc = fmaf(a[q], s_w[(sp + q) * R + h], acc);
-        }
-        for (; sp < p.S; sp++) acc = fmaf(__ldcg(po + size_t(sp) * R * kD), s_w[sp * R + h], acc);
         const float den = s_den[h];
-        p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + t] = den > 0.f ? acc / den : 0.f;
+        p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + t] = den > 0.f ? acc[h] / den : 0.f;
     }
 }
 
