@@ -181,11 +181,16 @@ KUIPER_API int kuiper_qknorm_rope_kvwrite(float* qkv, const uint16_t* q_norm_w, 
  * CTAs and the partial (max, sum, out) triples are merged with a log-sum-exp combine.
  * workspace: kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq) bytes, counters zeroed once
  * with kuiper_workspace_init.  D must be 128, Nq/Nkv in {1,2,4,8}.
+ * fresh_rows: -1 = the kernel touches nothing before the stream's previous kernel has completed.
+ * fresh_rows = F >= 0 is a promise by the caller: seq_len, slot and every cache row below
+ * seq_len[m] - F were final before the previous kernel on the stream started (that kernel appended
+ * at most the newest F rows of a sequence and produced q).  The kernel then fetches those rows
+ * under programmatic dependent launch while the previous kernel is still finishing.
  */
 KUIPER_API size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq);
 KUIPER_API int kuiper_flash_decode(const float* q, const uint16_t* kcache, const uint16_t* vcache,
                         const int32_t* seq_len, const int32_t* slot, float* out,
-                        int M, int Nq, int Nkv, int D, int max_seq, int n_slots,
+                        int M, int Nq, int Nkv, int D, int max_seq, int n_slots, int fresh_rows,
                         void* workspace, size_t workspace_bytes, kuiper_stream_t stream);
 
 /* ---- SwiGLU: placeholder kuiper/include/op/swiglu.h:1-10 ---- */

@@ -165,7 +165,7 @@ def flash_decode_workspace(M, Nq, D, max_seq, device="cuda"):
     return torch.zeros(max(n, 16), dtype=torch.uint8, device=device)
 
 
-def flash_decode(q, kcache, vcache, seq_len, slot, workspace=None, out=None):
+def flash_decode(q, kcache, vcache, seq_len, slot, workspace=None, out=None, fresh_rows=-1):
     _dev(q, kcache, vcache, seq_len, slot, workspace, out)
     M, Nq, D = q.shape
     n_slots, Nkv, max_seq, _ = kcache.shape
@@ -173,7 +173,8 @@ def flash_decode(q, kcache, vcache, seq_len, slot, workspace=None, out=None):
         workspace = flash_decode_workspace(M, Nq, D, max_seq, q.device)
     out = torch.empty_like(q) if out is None else out
     check(kernels().kuiper_flash_decode(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(seq_len), _ptr(slot), _ptr(out),
-                                        M, Nq, Nkv, D, max_seq, n_slots, _ptr(workspace), workspace.numel(), _stream()))
+                                        M, Nq, Nkv, D, max_seq, n_slots, fresh_rows, _ptr(workspace), workspace.numel(),
+                                        _stream()))
     return out
 
 

@@ -25,6 +25,7 @@ constexpr int kWarps = 4;
 constexpr int kRowsPerStep = 8;  // row slots per half warp per step
 
 int g_force_splits = 0;
+int g_flash_early = 1;  // 0: ignore fresh_rows, touch nothing before the dependent-launch wait
 
 struct FlashParams {
     const float* q;       // [M, Nq, 128]
@@ -37,6 +38,7 @@ struct FlashParams {
     float* part_ml;       // [M, Nkv, S, R, 2]
     int* counters;        // [M * Nkv]
     int M, Nq, Nkv, max_seq, n_slots, S;
+    int fresh_rows;       // cache rows >= seq_len - fresh_rows may still be in flight from the previous kernel; < 0: all
 };
 
 template <int R>
@@ -51,24 +53,65 @@ flash_decode_kernel(const FlashParams p) {
     const int half = lane >> 4, li = lane & 15;  // half warp and lane within it
 
     pdl_launch_dependents();
-    pdl_wait();
+    // With fresh_rows >= 0 the caller vouches that every cache row below seq_len - fresh_rows was final before the
+    // work that this grid may overtake under programmatic dependent launch was enqueued, so those rows are fetched
+    // while the previous kernel (the one that appends the newest rows and produces q) is still finishing.  seq_len
+    // and slot are read early too, but re-read after the wait: if they changed, the kernel starts over.
+    // With fresh_rows < 0 nothing is touched before the wait.
+    bool waited = p.fresh_rows < 0;
+    if (waited) pdl_wait();
 
-    int L = p.seq_len[m];
-    L = L < 0 ? 0 : (L > p.max_seq ? p.max_seq : L);
-    int sl = p.slot[m];
-    sl = sl < 0 ? 0 : (sl >= p.n_slots ? p.n_slots - 1 : sl);
-    // slice of the KV range owned by this CTA, in units of 64 rows
-    const int blocks = max((L + 63) / 64, 1);
-    const int per = (blocks + p.S - 1) / p.S;
-    // splits that have rows; the others leave at once and are not waited for
-    const int n_active = (blocks + per - 1) / per;
+    int L, sl, n_active, begin, end, base0;
+    const uint16_t *kb, *vb;
+    uint4 kraw[kRowsPerStep], vraw[kRowsPerStep];
+    while (true) {
+        L = __ldcg(p.seq_len + m);
+        sl = __ldcg(p.slot + m);
+        const int L_seen = L, sl_seen = sl;
+        L = L < 0 ? 0 : (L > p.max_seq ? p.max_seq : L);
+        sl = sl < 0 ? 0 : (sl >= p.n_slots ? p.n_slots - 1 : sl);
+        // slice of the KV range owned by this CTA, in units of 64 rows
+        const int blocks = max((L + 63) / 64, 1);
+        const int per = (blocks + p.S - 1) / p.S;
+        // splits that have rows; the others leave at once and are not waited for
+        n_active = (blocks + per - 1) / per;
+        begin = split * per * 64;
+        end = min(L, begin + per * 64);
+        const size_t head_off = (size_t(sl) * p.Nkv + kvh) * p.max_seq * kD;
+        kb = p.kc + head_off;
+        vb = p.vc + head_off;
+        // first step of this warp: rows base0 + half + 2*r; rows below safe_end may be read before the wait
+        base0 = begin + warp * 16;
+        const bool has_rows = split < n_active;
+        const int safe_end = waited ? end : min(end, L - p.fresh_rows);
+#pragma unroll
+        for (int r = 0; r < kRowsPerStep; r++) {
+            const int row = base0 + half + 2 * r;
+            kraw[r] = (has_rows && row < safe_end) ? ld_stream_u4(kb + size_t(row) * kD + li * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int r = 0; r < kRowsPerStep; r++) {
+            const int row = base0 + half + 2 * r;
+            vraw[r] = (has_rows && row < safe_end) ? ld_stream_u4(vb + size_t(row) * kD + li * 8) : make_uint4(0, 0, 0, 0);
+        }
+        if (waited) break;
+        pdl_wait();
+        waited = true;
+        // seq_len / slot themselves may have been written by something this grid was allowed to overtake:
+        // if they changed, start over with nothing assumed
+        if (__ldcg(p.seq_len + m) != L_seen || __ldcg(p.slot + m) != sl_seen) continue;
+        // rows of the first step that the previous kernel may just have written
+#pragma unroll
+        for (int r = 0; r < kRowsPerStep; r++) {
+            const int row = base0 + half + 2 * r;
+            if (has_rows && row >= safe_end && row < end) {
+                kraw[r] = ld_stream_u4(kb + size_t(row) * kD + li * 8);
+                vraw[r] = ld_stream_u4(vb + size_t(row) * kD + li * 8);
+            }
+        }
+        break;
+    }
     if (split >= n_active) return;
-    const int begin = split * per * 64;
-    const int end = min(L, begin + per * 64);
-
-    const size_t head_off = (size_t(sl) * p.Nkv + kvh) * p.max_seq * kD;
-    const uint16_t* kb = p.kc + head_off;
-    const uint16_t* vb = p.vc + head_off;
 
     // q slice of this lane: elements li*8 .. li*8+7 of each of the R heads, pre-scaled
     const float scale = 0.08838834764831845f;  // 1/sqrt(128)
@@ -93,19 +136,20 @@ flash_decode_kernel(const FlashParams p) {
     }
 
     // warp w takes rows begin + w*16 + step*64 + half + 2*r, r = 0..7
-    for (int base = begin + warp * 16; base < end; base += kWarps * 16) {
-        uint4 kraw[kRowsPerStep], vraw[kRowsPerStep];
+    for (int base = base0; base < end; base += kWarps * 16) {
+        if (base != base0) {
 #pragma unroll
-        for (int r = 0; r < kRowsPerStep; r++) {
-            const int row = base + half + 2 * r;
-            const bool ok = row < end;
-            kraw[r] = ok ? ld_stream_u4(kb + size_t(row) * kD + li * 8) : make_uint4(0, 0, 0, 0);
-        }
+            for (int r = 0; r < kRowsPerStep; r++) {
+                const int row = base + half + 2 * r;
+                const bool ok = row < end;
+                kraw[r] = ok ? ld_stream_u4(kb + size_t(row) * kD + li * 8) : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-        for (int r = 0; r < kRowsPerStep; r++) {
-            const int row = base + half + 2 * r;
-            const bool ok = row < end;
-            vraw[r] = ok ? ld_stream_u4(vb + size_t(row) * kD + li * 8) : make_uint4(0, 0, 0, 0);
+            for (int r = 0; r < kRowsPerStep; r++) {
+                const int row = base + half + 2 * r;
+                const bool ok = row < end;
+                vraw[r] = ok ? ld_stream_u4(vb + size_t(row) * kD + li * 8) : make_uint4(0, 0, 0, 0);
+            }
         }
         float s[kRowsPerStep][R];
 #pragma unroll
@@ -297,6 +341,7 @@ size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
 void flash_decode_set_tuning(const char* key, int value) {
     if (!strcmp(key, "flash_splits")) g_force_splits = value;
+    if (!strcmp(key, "flash_early")) g_flash_early = value;
 }
 
 }  // namespace kuiper
@@ -312,7 +357,7 @@ extern "C" size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int 
 
 extern "C" int kuiper_flash_decode(const float* q, const uint16_t* kcache, const uint16_t* vcache,
                                    const int32_t* seq_len, const int32_t* slot, float* out,
-                                   int M, int Nq, int Nkv, int D, int max_seq, int n_slots,
+                                   int M, int Nq, int Nkv, int D, int max_seq, int n_slots, int fresh_rows,
                                    void* workspace, size_t workspace_bytes, kuiper_stream_t stream) {
     KUIPER_REQUIRE(q && kcache && vcache && seq_len && slot && out, "flash_decode: null tensor pointer");
     KUIPER_REQUIRE(D == kD, "flash_decode: head_dim %d is not supported (128 only)", D);
@@ -328,6 +373,7 @@ extern "C" int kuiper_flash_decode(const float* q, const uint16_t* kcache, const
     FlashParams p;
     p.q = q; p.kc = kcache; p.vc = vcache; p.seq_len = seq_len; p.slot = slot; p.out = out;
     p.M = M; p.Nq = Nq; p.Nkv = Nkv; p.max_seq = max_seq; p.n_slots = n_slots;
+    p.fresh_rows = g_flash_early ? fresh_rows : -1;
     p.S = pick_splits(M, Nkv, max_seq);
     if (p.S > 1) {
         KUIPER_REQUIRE(workspace != nullptr, "flash_decode: split KV needs a workspace");

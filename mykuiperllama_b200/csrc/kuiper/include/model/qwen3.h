@@ -66,7 +66,9 @@ public:
     int32_t kernels_per_step() const { return kernels_per_step_; }
 
 private:
-    base::Status run_pass(int32_t M);  // enqueue one pass over the first M rows of the input buffers
+    // enqueue one pass over the first M rows of the input buffers; inputs_settled: positions / slots were on the
+    // device before anything of this pass was enqueued (the decode graph), not copied in by the pass's own memcpys
+    base::Status run_pass(int32_t M, bool inputs_settled = false);
     base::Status upload_rows(const int32_t* tokens, const int32_t* pos, const int32_t* slot, int32_t M);
     base::Status ensure_graph(int32_t B);
     base::Status check_loaded() const;
@@ -91,6 +93,9 @@ private:
     int32_t decode_batch_ = 0;
     int32_t kernels_per_step_ = 0;
     int32_t logit_rows_ = 0;  // rows (counted from the end of a pass) that get logits and a sampled id
+    // the rows of the current pass that share a sequence slot lie within `rows` consecutive positions, so the
+    // attention kernel may fetch all older cache rows before the rotary kernel has finished
+    bool rows_compact_ = false;
 };
 
 }  // namespace model

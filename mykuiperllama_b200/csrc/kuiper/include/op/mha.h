@@ -23,9 +23,14 @@ public:
     base::Status forward() override;
     void set_cache(const tensor::Tensor& key_cache, const tensor::Tensor& value_cache);
     void set_workspace(const tensor::Tensor& workspace);
+    // Promise about the kernel launched just before this layer on the stream: it appended at most the newest
+    // `rows` cache rows of a sequence, everything below seq_len - rows (and seq_len / slot) was final before it
+    // started.  The attention kernel then fetches those rows while that kernel is still finishing.  -1 = no promise.
+    void set_fresh_rows(int32_t rows) { fresh_rows_ = rows; }
 
 private:
     int32_t head_num_ = 0, kv_head_num_ = 0, head_size_ = 0;
+    int32_t fresh_rows_ = -1;
     tensor::Tensor key_cache_, value_cache_, workspace_;
 };
 }  // namespace op

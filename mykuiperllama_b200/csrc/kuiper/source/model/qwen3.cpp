@@ -1,7 +1,9 @@
 // Qwen3-shaped INT4-AWQ decoder on one GPU or one tensor-parallel rank.
 #include "model/qwen3.h"
 
+#include <climits>
 #include <cmath>
+#include <cstdint>
 #include <cstring>
 
 #include "kuiper_b200.h"
@@ -329,6 +331,16 @@ base::Status Qwen3Model::upload_rows(const int32_t* tokens, const int32_t* pos, 
         if (pos[m] < 0 || pos[m] >= config_.max_seq_len) return base::error::invalid_argument("position exceeds max_seq_len");
         if (slot[m] < 0 || slot[m] >= config_.max_batch) return base::error::invalid_argument("sequence slot out of range");
     }
+    {
+        std::vector<int32_t> lo(size_t(config_.max_batch), INT32_MAX), hi(size_t(config_.max_batch), -1);
+        for (int32_t m = 0; m < M; m++) {
+            lo[size_t(slot[m])] = std::min(lo[size_t(slot[m])], pos[m]);
+            hi[size_t(slot[m])] = std::max(hi[size_t(slot[m])], pos[m]);
+        }
+        rows_compact_ = true;
+        for (int32_t b = 0; b < config_.max_batch; b++)
+            if (hi[size_t(b)] >= 0 && hi[size_t(b)] - lo[size_t(b)] >= M) rows_compact_ = false;
+    }
     cudaStream_t s = stream();
     CUDA_OK(cudaStreamSynchronize(s));  // the pinned stage may still feed an earlier copy
     int32_t* st = host_stage_;
@@ -346,7 +358,7 @@ base::Status Qwen3Model::upload_rows(const int32_t* tokens, const int32_t* pos, 
     return base::error::success();
 }
 
-base::Status Qwen3Model::run_pass(int32_t M) {
+base::Status Qwen3Model::run_pass(int32_t M, bool inputs_settled) {
     const ModelConfig& c = config_;
     const int32_t D = c.head_size, H = c.dim;
     const int32_t Hq = local_heads(), Hkv = local_kv_heads(), I = local_hidden();
@@ -391,6 +403,11 @@ base::Status Qwen3Model::run_pass(int32_t M) {
             RETURN_IF_ERROR(L.qkv->forward(xn, qkv));
         }
         RETURN_IF_ERROR(L.rope->forward(qkv, pos, slot, cos_t, sin_t, q));
+        // the rotary kernel just before appended one cache row per token row of this pass; when the rows of a
+        // sequence lie within M consecutive positions, every cache row below seq_len - M is older than this pass.
+        // The promise also covers seq_len / slot, so it is only made when those were settled before the pass
+        // (kernels under programmatic dependent launch may start ahead of earlier copies of the same pass).
+        L.mha->set_fresh_rows(rows_compact_ && inputs_settled ? M : -1);
         RETURN_IF_ERROR(L.mha->forward(q, seq_len, slot, att));
         RETURN_IF_ERROR(project_and_reduce(*L.o, att));
         if (accumulate_) {
@@ -472,12 +489,12 @@ base::Status Qwen3Model::ensure_graph(int32_t B) {
     logit_rows_ = B;
     // one eager pass first: it configures every kernel variant outside the capture and
     // leaves the same cache contents the captured step will write again
-    RETURN_IF_ERROR(run_pass(B));
+    RETURN_IF_ERROR(run_pass(B, true));
     CUDA_OK(cudaStreamSynchronize(s));
 
     cudaGraph_t graph = nullptr;
     CUDA_OK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-    base::Status st = run_pass(B);
+    base::Status st = run_pass(B, true);
     if (st) {
         const int rc = kuiper_decode_advance(get_buffer(ModelBufferType::InputTokens).ptr<int32_t>(),
                                              get_buffer(ModelBufferType::NextTokens).ptr<int32_t>(),

@@ -166,7 +166,7 @@ void rope_kernel_cu(const Tensor& qkv, const Tensor& q_norm, const Tensor& k_nor
 
 void mha_kernel_cu(const Tensor& query, const Tensor& key_cache, const Tensor& value_cache, const Tensor& seq_len,
                    const Tensor& slot, const Tensor& output, int32_t head_num, int32_t kv_head_num, int32_t head_size,
-                   const Tensor& workspace, void* stream) {
+                   int32_t fresh_rows, const Tensor& workspace, void* stream) {
     require_cuda(query, "mha query");
     require_cuda(output, "mha output");
     require_cuda(key_cache, "mha key cache");
@@ -178,7 +178,7 @@ void mha_kernel_cu(const Tensor& query, const Tensor& key_cache, const Tensor& v
     CHECK_EQ(output.size(), query.size());
     KERNEL_OK(kuiper_flash_decode(query.ptr<float>(), key_cache.ptr<uint16_t>(), value_cache.ptr<uint16_t>(),
                                   seq_len.ptr<int32_t>(), slot.ptr<int32_t>(), out_ptr<float>(output), M, head_num,
-                                  kv_head_num, head_size, key_cache.get_dim(2), key_cache.get_dim(0),
+                                  kv_head_num, head_size, key_cache.get_dim(2), key_cache.get_dim(0), fresh_rows,
                                   out_ptr<void>(workspace), workspace.byte_size(), as_stream(stream)));
 }
 

@@ -55,8 +55,8 @@ using RoPEKernel = void (*)(const tensor::Tensor& qkv, const tensor::Tensor& q_n
 
 using MHAKernel = void (*)(const tensor::Tensor& query, const tensor::Tensor& key_cache, const tensor::Tensor& value_cache,
                            const tensor::Tensor& seq_len, const tensor::Tensor& slot, const tensor::Tensor& output,
-                           int32_t head_num, int32_t kv_head_num, int32_t head_size, const tensor::Tensor& workspace,
-                           void* stream);
+                           int32_t head_num, int32_t kv_head_num, int32_t head_size, int32_t fresh_rows,
+                           const tensor::Tensor& workspace, void* stream);
 
 using SwigluKernel = void (*)(const tensor::Tensor& gate_up, const tensor::Tensor& output, bool clear_input, void* stream);
 

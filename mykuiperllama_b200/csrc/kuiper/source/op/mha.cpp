@@ -52,7 +52,8 @@ base::Status MultiHeadAttention::forward() {
     base::Status status = check();
     if (!status) return status;
     kernel::get_mha_kernel(device_type_)(get_input(0), key_cache_, value_cache_, get_input(1), get_input(2),
-                                         get_output(0), head_num_, kv_head_num_, head_size_, workspace_, stream());
+                                         get_output(0), head_num_, kv_head_num_, head_size_, fresh_rows_, workspace_,
+                                         stream());
     return base::error::success();
 }
 

@@ -404,6 +404,24 @@ def test_flash_decode(cuda, oracle, B, Nq, Nkv, lens, splits):
     assert err <= SPEC_TOL and err <= 1e-5
 
 
+def test_flash_decode_early_fetch_matches_conservative_path(cuda, oracle):
+    # fresh_rows = F lets the kernel read cache rows below seq_len - F before the previous kernel has finished;
+    # on a static cache both paths must give the same bits
+    rng = np.random.default_rng(21)
+    B, Nq, Nkv, D, Lmax = 3, 32, 8, 128, 2100
+    kc = torch.randn((B, Nkv, Lmax, D), device="cuda").bfloat16()
+    vc = torch.randn((B, Nkv, Lmax, D), device="cuda").bfloat16()
+    q = dev(rng.standard_normal((B, Nq, D)).astype(np.float32))
+    seq = dev(np.array([2084, 1, 700], np.int32))
+    slot = dev(np.arange(B, dtype=np.int32))
+    ws = cuda.flash_decode_workspace(B, Nq, D, Lmax)
+    ref = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws)
+    for fresh in (0, 1, 3, 5000):
+        got = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws, fresh_rows=fresh)
+        torch.cuda.synchronize()
+        assert torch.equal(got, ref), fresh
+
+
 def test_flash_decode_shared_cache_is_causal_prefill(cuda, oracle):
     # a prompt chunk: every row reads the same sequence, row i sees positions [0, i]
     rng = np.random.default_rng(9)
