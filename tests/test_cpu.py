@@ -170,7 +170,7 @@ def test_kernel_argument_validation_needs_no_gpu():
     assert b"null" in lib.kuiper_last_error()
     assert lib.kuiper_awq_gemv_f32(1, 1, 1, 1, 1, None, 1, 100, 64, 128, 1, None, 0, None) == 7  # K % 128 != 0
     assert lib.kuiper_awq_gemv_f32(1, 1, 1, 1, 1, None, 1, 128, 64, 64, 1, None, 0, None) == 7   # group != 128
-    assert lib.kuiper_flash_decode(1, 1, 1, 1, 1, 1, 1, 6, 4, 128, 64, 1, None, 0, None) == 7    # Nq % Nkv != 0
+    assert lib.kuiper_flash_decode(1, 1, 1, 1, 1, 1, 1, 6, 4, 128, 64, 1, -1, None, 0, None) == 7   # Nq % Nkv != 0
     assert lib.kuiper_bf16_gemv_f32(1, 1, 1, 1, 10, 4, None) == 7                                 # K % 8 != 0
 
 
