@@ -334,10 +334,14 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
+        if args.profile_range:
+            torch.cuda.profiler.start()  # a profiler started with "profile from start off" sees only the timed steps
         e0.record(stream)
         eng.decode_step(args.steps)
         e1.record(stream)
         eng.synchronize()
+        if args.profile_range:
+            torch.cuda.profiler.stop()
         barrier()
     ms = e0.elapsed_time(e1)
     t = torch.tensor([ms], device=device)
@@ -425,6 +429,9 @@ def run_gemv_micro(args):
         args.gemv_impl = 2
     if args.gemv_impl in (0, 1):
         capi.set_tuning("gemv_impl", args.gemv_impl)
+    if args.gemv_impl == 3:  # the first-generation persistent kernel (SIMT products), accumulate mode
+        capi.set_tuning("gemv_impl", 2)
+        args.gemv_impl = 2
     per = int4_bytes(K, N) + 4 * K + 4 * N
     n = args.mats or max(2, min(256, (512 << 20) // per))
     gen = torch.Generator(device="cuda")
@@ -472,6 +479,66 @@ def run_gemv_micro(args):
         "roofline": {"bound": "hbm", "kernel": "awq_gemv", "achieved": gbs, "peak": peak, "peak_kind": kind, "unit": "GB/s",
                      "frac": gbs / peak, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS, "traffic": None,
                      "avg_us_per_launch": ms * 1e3 / n, "avg_bytes_per_launch": per},
+        "gpu_launches": n * args.steps, "clocks": clocks.summary()}), flush=True)
+
+
+def run_gemm_micro(args):
+    """INT4-AWQ GEMM on the tcgen05 tensor cores alone (M >= 16 token rows): distinct weight matrices are visited in
+    turn inside one CUDA graph.  Reports TFLOP/s (2*M*K*N per launch) against the measured dense bf16 peak."""
+    import torch
+    from mykuiperllama_b200 import capi
+    torch.cuda.set_device(0)
+    K, N = (int(v) for v in args.shape.lower().split("x"))
+    M = max(16, args.rows)
+    per = int4_bytes(K, N)
+    n = args.mats or max(2, min(64, (256 << 20) // per))
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0)
+    qw = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), dtype=torch.int32, device="cuda", generator=gen) for _ in range(n)]
+    qz = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 128, N // 8), dtype=torch.int32, device="cuda", generator=gen) for _ in range(n)]
+    sc = [(torch.rand((K // 128, N), device="cuda", generator=gen) * 0.018 + 0.002).half() for _ in range(n)]
+    x = torch.randn((M, K), device="cuda", generator=gen)
+    y = torch.zeros((M, N), device="cuda")
+
+    def sweep():
+        for i in range(n):
+            capi.awq_gemm(x, qw[i], qz[i], sc[i], y=y)
+
+    for _ in range(args.warmup):
+        sweep()
+    torch.cuda.synchronize()
+    capi.awq_gemm_status()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        sweep()
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    with ClockSampler(0) as clocks:
+        for _ in range(args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+    ms = float(np.median(times))
+    tflops = 2.0 * M * K * N * n / (ms * 1e-3) / 1e12
+    peak, kind = 1590.0, "fallback"
+    try:
+        peak, kind = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]), "measured"
+    except Exception:
+        pass
+    print(json.dumps({
+        "metric": "INT4-AWQ GEMM TFLOP/s", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 weights (AWQ g128) dequantised to fp16, fp16 x operand, fp32 accumulate in tensor memory",
+        "data": "synthetic",
+        "config": {"workload": f"single INT4-AWQ GEMM M={M} K={K} N={N} g128", "distinct_matrices": n,
+                   "l2_policy": f"{n} matrices ({per * n >> 20} MiB) visited in turn"},
+        "roofline": {"bound": "tensor", "kernel": "awq_gemm_tc_kernel", "achieved": tflops, "peak": peak, "peak_kind": kind,
+                     "unit": "TFLOP/s", "frac": tflops / peak, "traffic": None, "avg_us_per_launch": ms * 1e3 / n,
+                     "weight_gbs": per * n / (ms * 1e-3) / 1e9},
         "gpu_launches": n * args.steps, "clocks": clocks.summary()}), flush=True)
 
 
@@ -535,19 +602,26 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["gemv", "attn"])
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS) + ["gemv", "gemm", "attn"])
     ap.add_argument("--kv-len", type=int, default=4096, help="KV length of the attn microbenchmark")
     ap.add_argument("--shape", default="2048x2048", help="KxN of the gemv microbenchmark")
+    ap.add_argument("--rows", type=int, default=2048, help="token rows M of the gemm microbenchmark")
     ap.add_argument("--mats", type=int, default=0, help="distinct weight matrices in the gemv microbenchmark (0 = 512 MiB worth)")
-    ap.add_argument("--gemv-impl", type=int, default=None, help="2 accumulate mode of the TMA kernel (engine path, default), 0 its ordered combine, 1 register-staged kernel")
+    ap.add_argument("--gemv-impl", type=int, default=None, help="2 accumulate mode of the tensor-core GEMV (engine path, default), 0 its ordered combine, "
+                         "1 register-staged kernel, 3 first-generation persistent SIMT kernel (accumulate)")
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (config 4 of the workload list uses 16)")
+    ap.add_argument("--profile-range", action="store_true",
+                    help="bracket the timed decode steps with cudaProfilerStart/Stop (for a profiler run with profile-from-start off)")
     ap.add_argument("--prompt", type=int, default=None, help="override the workload's prompt length (profiling aid)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "engine":
         args.warmup = 3
     if args.workload == "gemv":
         run_gemv_micro(args)
+        return
+    if args.workload == "gemm":
+        run_gemm_micro(args)
         return
     if args.workload == "attn":
         run_attn_micro(args)
