@@ -245,41 +245,44 @@ awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParam
         float rstd[MT];
 #pragma unroll
         for (int m = 0; m < MT; m++) rstd[m] = 1.f;
-        if (NORM) {
-            norm_sync();
-#pragma unroll
-            for (int m = 0; m < MT; m++) rstd[m] = s_rstd[m];
-        }
         int kb = u0 % p.upt;
         int s = 0;
         uint32_t parity = 0;
-        auto fetch = [&](int kblock, float (&v)[MT]) {
+        // raw operand rows (SwiGLU applied, norm not yet) and the norm weight of the row
+        auto fetch = [&](int kblock, float (&v)[MT], float& wn) {
 #pragma unroll
             for (int m = 0; m < MT; m++) {
-                float a;
                 if (p.swiglu) {
                     const float* gp = p.x + size_t(m) * 2 * p.K + kblock * kUnitRowsM + lane;
                     const float gate = __ldcg(gp), up = __ldcg(gp + p.K);
-                    a = (gate / (1.0f + expf(-gate))) * up;
+                    v[m] = (gate / (1.0f + expf(-gate))) * up;
                 } else {
-                    a = __ldcg(p.x + size_t(m) * p.K + kblock * kUnitRowsM + lane);
+                    v[m] = __ldcg(p.x + size_t(m) * p.K + kblock * kUnitRowsM + lane);
                 }
-                if (NORM) {
-                    const uint16_t wn = __ldg(p.norm_w + kblock * kUnitRowsM + lane);
-                    a = (a * rstd[m]) * __uint_as_float(uint32_t(wn) << 16);
-                }
-                v[m] = a;
             }
+            wn = NORM ? __uint_as_float(uint32_t(__ldg(p.norm_w + kblock * kUnitRowsM + lane)) << 16) : 1.f;
         };
-        float cur[MT], nxt[MT];
-        if (u0 < u1) fetch(kb, cur);
+        float cur[MT], nxt[MT], cur_w = 1.f, nxt_w = 1.f;
+        if (u0 < u1) fetch(kb, cur, cur_w);
+        bool have_rstd = !NORM;
         for (int u = u0; u < u1; u++) {
             int kb_next = kb + 1;
             if (kb_next == p.upt) kb_next = 0;
-            if (u + 1 < u1) fetch(kb_next, nxt);
+            if (u + 1 < u1) fetch(kb_next, nxt, nxt_w);
+            if (!have_rstd) {
+                // the consumers' sum of squares; the first rows were requested before waiting for it
+                norm_sync();
+#pragma unroll
+                for (int m = 0; m < MT; m++) rstd[m] = s_rstd[m];
+                have_rstd = true;
+            }
             if (!bar_wait_relaxed(&empty_bar[s], parity ^ 1u)) {
                 atomicExch(&g_gemv_mma_wait_error, 3);
                 break;
+            }
+            if (NORM) {
+#pragma unroll
+                for (int m = 0; m < MT; m++) cur[m] = (cur[m] * rstd[m]) * cur_w;
             }
             unsigned char* xs = xstages + s * kXStage;
 #pragma unroll
@@ -296,6 +299,7 @@ awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParam
             if (lane == 0) bar_arrive(&full_bar[s]);
 #pragma unroll
             for (int m = 0; m < MT; m++) cur[m] = nxt[m];
+            cur_w = nxt_w;
             kb = kb_next;
             if (++s == STAGES) { s = 0; parity ^= 1u; }
         }
