@@ -193,6 +193,23 @@ KUIPER_API int kuiper_flash_decode(const float* q, const uint16_t* kcache, const
                         int M, int Nq, int Nkv, int D, int max_seq, int n_slots, int fresh_rows,
                         void* workspace, size_t workspace_bytes, kuiper_stream_t stream);
 
+/*
+ * The two calls above in one kernel, for decode batches: every token row m must belong to a different
+ * sequence slot and seq_len[m] == pos[m] + 1.  Each CTA forms q (per-head RMSNorm + rotary) for its kv
+ * head from the raw projection row in qkv; the CTA whose slice ends the sequence appends the new K / V
+ * row to the caches and uses it.  With clear_input != 0 the last CTA of a (row, kv head) zeroes the
+ * slices of qkv it read; clear_extra / clear_extra_count as in kuiper_qknorm_rope_kvwrite.  fresh_rows
+ * as in kuiper_flash_decode (the newest row is never fetched early: it does not exist yet).
+ * Results are bit-identical to kuiper_qknorm_rope_kvwrite followed by kuiper_flash_decode.
+ */
+KUIPER_API int kuiper_rope_flash_decode(float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
+                                        const float* cos_t, const float* sin_t, const int32_t* pos,
+                                        const int32_t* seq_len, const int32_t* slot, float* out,
+                                        uint16_t* kcache, uint16_t* vcache, int M, int Nq, int Nkv, int D,
+                                        float eps, int max_seq, int n_slots, int fresh_rows, int clear_input,
+                                        float* clear_extra, int64_t clear_extra_count, void* workspace,
+                                        size_t workspace_bytes, kuiper_stream_t stream);
+
 /* ---- SwiGLU: placeholder kuiper/include/op/swiglu.h:1-10 ---- */
 /* out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]; gate_up is [M, 2I]; clear_input != 0 zeroes gate_up afterwards */
 KUIPER_API int kuiper_swiglu_f32(float* gate_up, float* out, int M, int I, int clear_input, kuiper_stream_t stream);

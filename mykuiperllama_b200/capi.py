@@ -178,6 +178,25 @@ def flash_decode(q, kcache, vcache, seq_len, slot, workspace=None, out=None, fre
     return out
 
 
+def rope_flash_decode(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, seq_len, slot, Nq, Nkv, D, eps, kcache, vcache,
+                      workspace=None, out=None, fresh_rows=-1, clear_input=False, clear_extra=None):
+    """q/k-norm + rotary + KV append + flash-decoding in one kernel (decode batches: one row per sequence slot,
+    seq_len == pos + 1); returns the attention output [M, Nq, D]."""
+    _dev(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, seq_len, slot, kcache, vcache, workspace, out, clear_extra)
+    M = qkv.shape[0]
+    n_slots, _, max_seq, _ = kcache.shape
+    if workspace is None:
+        workspace = flash_decode_workspace(M, Nq, D, max_seq, qkv.device)
+    out = torch.empty((M, Nq, D), dtype=torch.float32, device=qkv.device) if out is None else out
+    check(kernels().kuiper_rope_flash_decode(_ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_t), _ptr(sin_t), _ptr(pos),
+                                             _ptr(seq_len), _ptr(slot), _ptr(out), _ptr(kcache), _ptr(vcache), M, Nq, Nkv, D,
+                                             eps, max_seq, n_slots, fresh_rows, int(clear_input),
+                                             _ptr(clear_extra) if clear_extra is not None else None,
+                                             clear_extra.numel() if clear_extra is not None else 0, _ptr(workspace),
+                                             workspace.numel(), _stream()))
+    return out
+
+
 def swiglu(gate_up, out=None, clear_input=False):
     _dev(gate_up, out)
     M, I2 = gate_up.shape

@@ -39,12 +39,54 @@ struct FlashParams {
     int* counters;        // [M * Nkv]
     int M, Nq, Nkv, max_seq, n_slots, S;
     int fresh_rows;       // cache rows >= seq_len - fresh_rows may still be in flight from the previous kernel; < 0: all
+    // fused rotary prologue (FUSED kernels): q and the newest K / V row are produced here from the raw projection
+    float* qkv;                // [M, (Nq + 2 Nkv) * 128] q heads | k heads | v heads
+    const uint16_t* q_norm_w;  // bf16 [128]
+    const uint16_t* k_norm_w;
+    const float* cos_t;        // [max_pos, 64]
+    const float* sin_t;
+    const int32_t* pos;        // [M], seq_len[m] == pos[m] + 1
+    uint16_t* kc_w;            // the caches again, writable
+    uint16_t* vc_w;
+    float4* clear_extra;       // optional side job: zero this buffer
+    int clear_extra_vec4;
+    int clear_qkv;             // zero the slices of qkv this (row, kv head) read once nobody needs them any more
+    float eps;
 };
 
-template <int R>
+// q/k RMSNorm over the head + half-split rotary for one head held by one warp: lane l has elements l, l+32 (first
+// half) and l+64, l+96 (second half).  Same arithmetic, in the same order, as qknorm_rope_kvwrite_kernel.
+__device__ __forceinline__ void head_norm_rope(float a0, float a1, float b0, float b1, const uint16_t* __restrict__ w,
+                                               const float* __restrict__ cos_row, const float* __restrict__ sin_row,
+                                               float eps, int lane, float (&out)[4]) {
+    float ss = a0 * a0;
+    ss = fmaf(a1, a1, ss);
+    ss = fmaf(b0, b0, ss);
+    ss = fmaf(b1, b1, ss);
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss / float(128) + eps);
+    const float x0 = (a0 * rstd) * bf16_bits_to_float(w[lane]);
+    const float x1 = (a1 * rstd) * bf16_bits_to_float(w[lane + 32]);
+    const float y0 = (b0 * rstd) * bf16_bits_to_float(w[lane + 64]);
+    const float y1 = (b1 * rstd) * bf16_bits_to_float(w[lane + 96]);
+    const float c0 = cos_row[lane], s0 = sin_row[lane];
+    const float c1 = cos_row[lane + 32], s1 = sin_row[lane + 32];
+    out[0] = __fsub_rn(__fmul_rn(x0, c0), __fmul_rn(y0, s0));
+    out[1] = __fsub_rn(__fmul_rn(x1, c1), __fmul_rn(y1, s1));
+    out[2] = __fadd_rn(__fmul_rn(y0, c0), __fmul_rn(x0, s0));
+    out[3] = __fadd_rn(__fmul_rn(y1, c1), __fmul_rn(x1, s1));
+}
+
+// a cache row slice; rows this kernel itself wrote must not go through the non-coherent path
+__device__ __forceinline__ uint4 ld_row(const uint16_t* ptr, bool coherent) {
+    return coherent ? __ldcg(reinterpret_cast<const uint4*>(ptr)) : ld_stream_u4(ptr);
+}
+
+template <int R, bool FUSED>
 __global__ void __launch_bounds__(kWarps * 32)
 flash_decode_kernel(const FlashParams p) {
     __shared__ float s_o[kWarps][R][kD];
+    __shared__ float s_q[FUSED ? R : 1][kD];
     __shared__ float s_ml[kWarps][R][2];
     __shared__ int s_last;
 
@@ -61,7 +103,7 @@ flash_decode_kernel(const FlashParams p) {
     bool waited = p.fresh_rows < 0;
     if (waited) pdl_wait();
 
-    int L, sl, n_active, begin, end, base0;
+    int L, sl, n_active, begin, end, base0, fetched_end;
     const uint16_t *kb, *vb;
     uint4 kraw[kRowsPerStep], vraw[kRowsPerStep];
     while (true) {
@@ -83,7 +125,9 @@ flash_decode_kernel(const FlashParams p) {
         // first step of this warp: rows base0 + half + 2*r; rows below safe_end may be read before the wait
         base0 = begin + warp * 16;
         const bool has_rows = split < n_active;
-        const int safe_end = waited ? end : min(end, L - p.fresh_rows);
+        // (fused: the newest row is produced by this kernel, so it is never fetched here)
+        const int safe_end = waited ? (FUSED ? min(end, L - 1) : end) : min(end, L - (FUSED ? max(p.fresh_rows, 1) : p.fresh_rows));
+        fetched_end = safe_end;
 #pragma unroll
         for (int r = 0; r < kRowsPerStep; r++) {
             const int row = base0 + half + 2 * r;
@@ -100,27 +144,83 @@ flash_decode_kernel(const FlashParams p) {
         // seq_len / slot themselves may have been written by something this grid was allowed to overtake:
         // if they changed, start over with nothing assumed
         if (__ldcg(p.seq_len + m) != L_seen || __ldcg(p.slot + m) != sl_seen) continue;
-        // rows of the first step that the previous kernel may just have written
+        break;
+    }
+    if (FUSED) {
+        // side job: zero the buffer the caller named (nothing uses it at this point of a layer)
+        const int ctas = gridDim.x * gridDim.y * gridDim.z;
+        const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        for (int i = cta * (kWarps * 32) + threadIdx.x; i < p.clear_extra_vec4; i += ctas * kWarps * 32)
+            p.clear_extra[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (split >= n_active) return;
+
+    const int heads = p.Nq + 2 * p.Nkv;
+    const int newest = L - 1;  // the row appended by this pass (fused) / by the previous kernel
+    if (FUSED) {
+        int pp = p.pos[m];
+        pp = pp < 0 ? 0 : (pp >= p.max_seq ? p.max_seq - 1 : pp);
+        const float* cos_row = p.cos_t + size_t(pp) * 64;
+        const float* sin_row = p.sin_t + size_t(pp) * 64;
+        // q heads of this kv head: one warp per head
+        for (int h = warp; h < R; h += kWarps) {
+            const float* src = p.qkv + (size_t(m) * heads + kvh * R + h) * kD;
+            float r4[4];
+            head_norm_rope(__ldcg(src + lane), __ldcg(src + lane + 32), __ldcg(src + lane + 64), __ldcg(src + lane + 96),
+                           p.q_norm_w, cos_row, sin_row, p.eps, lane, r4);
+            s_q[h][lane] = r4[0]; s_q[h][lane + 32] = r4[1]; s_q[h][lane + 64] = r4[2]; s_q[h][lane + 96] = r4[3];
+        }
+        // the CTA whose slice holds the newest row appends it: K through norm + rotary, V as it is, both as bf16
+        if (newest >= begin && newest < end) {
+            const size_t row_off = ((size_t(sl) * p.Nkv + kvh) * p.max_seq + pp) * kD;
+            if (warp == kWarps - 1) {
+                const float* src = p.qkv + (size_t(m) * heads + p.Nq + kvh) * kD;
+                float r4[4];
+                head_norm_rope(__ldcg(src + lane), __ldcg(src + lane + 32), __ldcg(src + lane + 64), __ldcg(src + lane + 96),
+                               p.k_norm_w, cos_row, sin_row, p.eps, lane, r4);
+                uint16_t* dst = p.kc_w + row_off;
+                dst[lane] = float_to_bf16_bits(r4[0]);
+                dst[lane + 32] = float_to_bf16_bits(r4[1]);
+                dst[lane + 64] = float_to_bf16_bits(r4[2]);
+                dst[lane + 96] = float_to_bf16_bits(r4[3]);
+            } else if (warp == kWarps - 2) {
+                const float* src = p.qkv + (size_t(m) * heads + p.Nq + p.Nkv + kvh) * kD;
+                uint16_t* dst = p.vc_w + row_off;
+                dst[lane] = float_to_bf16_bits(__ldcg(src + lane));
+                dst[lane + 32] = float_to_bf16_bits(__ldcg(src + lane + 32));
+                dst[lane + 64] = float_to_bf16_bits(__ldcg(src + lane + 64));
+                dst[lane + 96] = float_to_bf16_bits(__ldcg(src + lane + 96));
+            }
+        }
+        __syncthreads();  // s_q is complete; the appended row is visible to the whole CTA
+    }
+    // rows of the first step that were not fetched ahead of the wait
+    {
 #pragma unroll
         for (int r = 0; r < kRowsPerStep; r++) {
             const int row = base0 + half + 2 * r;
-            if (has_rows && row >= safe_end && row < end) {
-                kraw[r] = ld_stream_u4(kb + size_t(row) * kD + li * 8);
-                vraw[r] = ld_stream_u4(vb + size_t(row) * kD + li * 8);
+            if (row >= fetched_end && row < end) {
+                const bool coherent = FUSED && row >= newest;
+                kraw[r] = ld_row(kb + size_t(row) * kD + li * 8, coherent);
+                vraw[r] = ld_row(vb + size_t(row) * kD + li * 8, coherent);
             }
         }
-        break;
     }
-    if (split >= n_active) return;
 
     // q slice of this lane: elements li*8 .. li*8+7 of each of the R heads, pre-scaled
     const float scale = 0.08838834764831845f;  // 1/sqrt(128)
     float qr[R][8];
 #pragma unroll
     for (int h = 0; h < R; h++) {
-        const float* qp = p.q + (size_t(m) * p.Nq + kvh * R + h) * kD + li * 8;
-        const float4 a = __ldcg(reinterpret_cast<const float4*>(qp));
-        const float4 b = __ldcg(reinterpret_cast<const float4*>(qp + 4));
+        float4 a, b;
+        if (FUSED) {
+            a = *reinterpret_cast<const float4*>(&s_q[h][li * 8]);
+            b = *reinterpret_cast<const float4*>(&s_q[h][li * 8 + 4]);
+        } else {
+            const float* qp = p.q + (size_t(m) * p.Nq + kvh * R + h) * kD + li * 8;
+            a = __ldcg(reinterpret_cast<const float4*>(qp));
+            b = __ldcg(reinterpret_cast<const float4*>(qp + 4));
+        }
         qr[h][0] = a.x * scale; qr[h][1] = a.y * scale; qr[h][2] = a.z * scale; qr[h][3] = a.w * scale;
         qr[h][4] = b.x * scale; qr[h][5] = b.y * scale; qr[h][6] = b.z * scale; qr[h][7] = b.w * scale;
     }
@@ -142,13 +242,13 @@ flash_decode_kernel(const FlashParams p) {
             for (int r = 0; r < kRowsPerStep; r++) {
                 const int row = base + half + 2 * r;
                 const bool ok = row < end;
-                kraw[r] = ok ? ld_stream_u4(kb + size_t(row) * kD + li * 8) : make_uint4(0, 0, 0, 0);
+                kraw[r] = ok ? ld_row(kb + size_t(row) * kD + li * 8, FUSED && row >= newest) : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
             for (int r = 0; r < kRowsPerStep; r++) {
                 const int row = base + half + 2 * r;
                 const bool ok = row < end;
-                vraw[r] = ok ? ld_stream_u4(vb + size_t(row) * kD + li * 8) : make_uint4(0, 0, 0, 0);
+                vraw[r] = ok ? ld_row(vb + size_t(row) * kD + li * 8, FUSED && row >= newest) : make_uint4(0, 0, 0, 0);
             }
         }
         float s[kRowsPerStep][R];
@@ -251,10 +351,22 @@ flash_decode_kernel(const FlashParams p) {
         fo[h] = acc; fm[h] = nm; fs[h] = ssum;
     }
 
+    // fused: once every CTA of this (row, kv head) is past its prologue, the raw q / k / v slices can be zeroed for
+    // the next projection that accumulates into the buffer
+    auto clear_raw = [&]() {
+        if (FUSED && p.clear_qkv) {
+            float* row = p.qkv + size_t(m) * heads * kD;
+#pragma unroll
+            for (int h = 0; h < R; h++) row[(kvh * R + h) * kD + t] = 0.f;
+            row[(p.Nq + kvh) * kD + t] = 0.f;
+            row[(p.Nq + p.Nkv + kvh) * kD + t] = 0.f;
+        }
+    };
     if (n_active == 1) {
 #pragma unroll
         for (int h = 0; h < R; h++)
             p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + t] = fs[h] > 0.f ? fo[h] / fs[h] : 0.f;
+        clear_raw();
         return;
     }
 
@@ -323,6 +435,7 @@ flash_decode_kernel(const FlashParams p) {
         const float den = s_den[h];
         p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + t] = den > 0.f ? acc[h] / den : 0.f;
     }
+    clear_raw();
 }
 
 int pick_splits(int M, int Nkv, int max_seq) {
@@ -355,23 +468,15 @@ extern "C" size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int 
            align256(size_t(M) * Nq * S * 2 * sizeof(float));
 }
 
-extern "C" int kuiper_flash_decode(const float* q, const uint16_t* kcache, const uint16_t* vcache,
-                                   const int32_t* seq_len, const int32_t* slot, float* out,
-                                   int M, int Nq, int Nkv, int D, int max_seq, int n_slots, int fresh_rows,
-                                   void* workspace, size_t workspace_bytes, kuiper_stream_t stream) {
-    KUIPER_REQUIRE(q && kcache && vcache && seq_len && slot && out, "flash_decode: null tensor pointer");
+// argument checks, workspace carving and launch shared by the two entry points; `p` arrives with the tensors set
+static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int D, int max_seq, int n_slots, int fresh_rows,
+                        void* workspace, size_t workspace_bytes, kuiper_stream_t stream) {
     KUIPER_REQUIRE(D == kD, "flash_decode: head_dim %d is not supported (128 only)", D);
     KUIPER_REQUIRE(M > 0 && Nq > 0 && Nkv > 0 && max_seq > 0 && n_slots > 0, "flash_decode: empty shape");
     KUIPER_REQUIRE(Nq % Nkv == 0, "flash_decode: Nq=%d is not a multiple of Nkv=%d", Nq, Nkv);
     KUIPER_REQUIRE(M <= 65535 && Nkv <= 65535, "flash_decode: grid too large");
     const int R = Nq / Nkv;
     KUIPER_REQUIRE(R == 1 || R == 2 || R == 4 || R == 8, "flash_decode: group size %d is not supported", R);
-    KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(kcache) & 15) == 0 && (reinterpret_cast<uintptr_t>(vcache) & 15) == 0 &&
-                       (reinterpret_cast<uintptr_t>(q) & 15) == 0,
-                   "flash_decode: q and caches must be 16-byte aligned");
-
-    FlashParams p;
-    p.q = q; p.kc = kcache; p.vc = vcache; p.seq_len = seq_len; p.slot = slot; p.out = out;
     p.M = M; p.Nq = Nq; p.Nkv = Nkv; p.max_seq = max_seq; p.n_slots = n_slots;
     p.fresh_rows = g_flash_early ? fresh_rows : -1;
     p.S = pick_splits(M, Nkv, max_seq);
@@ -399,15 +504,63 @@ extern "C" int kuiper_flash_decode(const float* q, const uint16_t* kcache, const
     cfg.attrs = attr;
     cfg.numAttrs = g_pdl_enabled ? 1 : 0;
     cudaError_t err;
-    switch (R) {
-        case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<1>, p); break;
-        case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<2>, p); break;
-        case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<4>, p); break;
-        default: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<8>, p); break;
+    if (fused) {
+        switch (R) {
+            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<1, true>, p); break;
+            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<2, true>, p); break;
+            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<4, true>, p); break;
+            default: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<8, true>, p); break;
+        }
+    } else {
+        switch (R) {
+            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<1, false>, p); break;
+            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<2, false>, p); break;
+            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<4, false>, p); break;
+            default: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<8, false>, p); break;
+        }
     }
     if (err != cudaSuccess) {
         set_error("flash_decode launch failed: %s", cudaGetErrorString(err));
         return KUIPER_INTERNAL_ERROR;
     }
     return KUIPER_OK;
+}
+
+extern "C" int kuiper_flash_decode(const float* q, const uint16_t* kcache, const uint16_t* vcache,
+                                   const int32_t* seq_len, const int32_t* slot, float* out,
+                                   int M, int Nq, int Nkv, int D, int max_seq, int n_slots, int fresh_rows,
+                                   void* workspace, size_t workspace_bytes, kuiper_stream_t stream) {
+    KUIPER_REQUIRE(q && kcache && vcache && seq_len && slot && out, "flash_decode: null tensor pointer");
+    KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(kcache) & 15) == 0 && (reinterpret_cast<uintptr_t>(vcache) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(q) & 15) == 0,
+                   "flash_decode: q and caches must be 16-byte aligned");
+    FlashParams p = {};
+    p.q = q; p.kc = kcache; p.vc = vcache; p.seq_len = seq_len; p.slot = slot; p.out = out;
+    return flash_launch(p, false, M, Nq, Nkv, D, max_seq, n_slots, fresh_rows, workspace, workspace_bytes, stream);
+}
+
+extern "C" int kuiper_rope_flash_decode(float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w, const float* cos_t,
+                                        const float* sin_t, const int32_t* pos, const int32_t* seq_len, const int32_t* slot,
+                                        float* out, uint16_t* kcache, uint16_t* vcache, int M, int Nq, int Nkv, int D,
+                                        float eps, int max_seq, int n_slots, int fresh_rows, int clear_input,
+                                        float* clear_extra, int64_t clear_extra_count, void* workspace,
+                                        size_t workspace_bytes, kuiper_stream_t stream) {
+    KUIPER_REQUIRE(qkv && q_norm_w && k_norm_w && cos_t && sin_t && pos && seq_len && slot && out && kcache && vcache,
+                   "rope_flash_decode: null tensor pointer");
+    KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(kcache) & 15) == 0 && (reinterpret_cast<uintptr_t>(vcache) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(qkv) & 15) == 0,
+                   "rope_flash_decode: qkv and caches must be 16-byte aligned");
+    KUIPER_REQUIRE(clear_extra_count >= 0 && (clear_extra_count == 0 || clear_extra), "rope_flash_decode: bad extra buffer");
+    KUIPER_REQUIRE(clear_extra_count % 4 == 0 && (reinterpret_cast<uintptr_t>(clear_extra) & 15) == 0 &&
+                       clear_extra_count / 4 <= 0x7fffffff,
+                   "rope_flash_decode: the extra buffer must be 16-byte aligned with a multiple of 4 floats");
+    FlashParams p = {};
+    p.q = nullptr; p.kc = kcache; p.vc = vcache; p.seq_len = seq_len; p.slot = slot; p.out = out;
+    p.qkv = qkv; p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.cos_t = cos_t; p.sin_t = sin_t; p.pos = pos;
+    p.kc_w = kcache; p.vc_w = vcache;
+    p.clear_extra = reinterpret_cast<float4*>(clear_extra);
+    p.clear_extra_vec4 = int(clear_extra_count / 4);
+    p.clear_qkv = clear_input;
+    p.eps = eps;
+    return flash_launch(p, true, M, Nq, Nkv, D, max_seq, n_slots, fresh_rows, workspace, workspace_bytes, stream);
 }

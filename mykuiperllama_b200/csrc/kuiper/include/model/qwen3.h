@@ -96,6 +96,7 @@ private:
     // the rows of the current pass that share a sequence slot lie within `rows` consecutive positions, so the
     // attention kernel may fetch all older cache rows before the rotary kernel has finished
     bool rows_compact_ = false;
+    bool slots_distinct_ = false;  // every row of the current pass has its own sequence slot
 };
 
 }  // namespace model

@@ -30,6 +30,15 @@ public:
         clear_extra_row_ = row_elems;
     }
 
+    // Decode batches only (one token row per sequence slot, seq_len == pos + 1): rotary, KV append and
+    // flash-decoding in one kernel.  Inputs as for forward() plus seq_len; attention_out [M, Nq*D] replaces the q
+    // output; workspace as for op::MultiHeadAttention; fresh_rows as documented there.
+    void set_attention_workspace(const tensor::Tensor& workspace) { attention_workspace_ = workspace; }
+    base::Status forward_with_attention(const tensor::Tensor& qkv, const tensor::Tensor& pos, const tensor::Tensor& slot,
+                                        const tensor::Tensor& cos_cache, const tensor::Tensor& sin_cache,
+                                        const tensor::Tensor& seq_len, const tensor::Tensor& attention_out,
+                                        int32_t fresh_rows);
+
 protected:
     base::DataType weight_data_type(int32_t idx) const override;
 
@@ -37,7 +46,7 @@ private:
     int32_t head_num_ = 0, kv_head_num_ = 0, head_size_ = 0;
     float eps_ = 1e-6f;
     bool clear_input_ = false;
-    tensor::Tensor key_cache_, value_cache_, clear_extra_;
+    tensor::Tensor key_cache_, value_cache_, clear_extra_, attention_workspace_;
     int32_t clear_extra_row_ = 0;
 };
 }  // namespace op

@@ -223,6 +223,7 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         L.mha->set_cuda_config(cuda_config_);
         L.mha->set_cache(L.key_cache, L.value_cache);
         L.mha->set_workspace(get_buffer(ModelBufferType::MHAWorkspace));
+        L.rope->set_attention_workspace(get_buffer(ModelBufferType::MHAWorkspace));
         L.swiglu = std::make_unique<op::SwiGLULayer>(device_type_, I);
         L.swiglu->set_cuda_config(cuda_config_);
         L.swiglu->set_clear_input(accumulate_);
@@ -340,6 +341,12 @@ base::Status Qwen3Model::upload_rows(const int32_t* tokens, const int32_t* pos, 
         rows_compact_ = true;
         for (int32_t b = 0; b < config_.max_batch; b++)
             if (hi[size_t(b)] >= 0 && hi[size_t(b)] - lo[size_t(b)] >= M) rows_compact_ = false;
+        std::vector<char> seen(size_t(config_.max_batch), 0);
+        slots_distinct_ = true;
+        for (int32_t m = 0; m < M; m++) {
+            if (seen[size_t(slot[m])]) slots_distinct_ = false;
+            seen[size_t(slot[m])] = 1;
+        }
     }
     cudaStream_t s = stream();
     CUDA_OK(cudaStreamSynchronize(s));  // the pinned stage may still feed an earlier copy
@@ -402,13 +409,19 @@ base::Status Qwen3Model::run_pass(int32_t M, bool inputs_settled) {
             RETURN_IF_ERROR(L.input_norm->forward(h, xn));
             RETURN_IF_ERROR(L.qkv->forward(xn, qkv));
         }
-        RETURN_IF_ERROR(L.rope->forward(qkv, pos, slot, cos_t, sin_t, q));
-        // the rotary kernel just before appended one cache row per token row of this pass; when the rows of a
-        // sequence lie within M consecutive positions, every cache row below seq_len - M is older than this pass.
-        // The promise also covers seq_len / slot, so it is only made when those were settled before the pass
-        // (kernels under programmatic dependent launch may start ahead of earlier copies of the same pass).
-        L.mha->set_fresh_rows(rows_compact_ && inputs_settled ? M : -1);
-        RETURN_IF_ERROR(L.mha->forward(q, seq_len, slot, att));
+        if (accumulate_ && inputs_settled && slots_distinct_) {
+            // decode batch: rotary, KV append and attention in one kernel; every cache row but the one appended
+            // here is older than this pass
+            RETURN_IF_ERROR(L.rope->forward_with_attention(qkv, pos, slot, cos_t, sin_t, seq_len, att, 1));
+        } else {
+            RETURN_IF_ERROR(L.rope->forward(qkv, pos, slot, cos_t, sin_t, q));
+            // the rotary kernel just before appended one cache row per token row of this pass; when the rows of a
+            // sequence lie within M consecutive positions, every cache row below seq_len - M is older than this pass.
+            // The promise also covers seq_len / slot, so it is only made when those were settled before the pass
+            // (kernels under programmatic dependent launch may start ahead of earlier copies of the same pass).
+            L.mha->set_fresh_rows(rows_compact_ && inputs_settled ? M : -1);
+            RETURN_IF_ERROR(L.mha->forward(q, seq_len, slot, att));
+        }
         RETURN_IF_ERROR(project_and_reduce(*L.o, att));
         if (accumulate_) {
             RETURN_IF_ERROR(L.gate_up->forward(h, gu));

@@ -182,6 +182,34 @@ void mha_kernel_cu(const Tensor& query, const Tensor& key_cache, const Tensor& v
                                   out_ptr<void>(workspace), workspace.byte_size(), as_stream(stream)));
 }
 
+void rope_mha_kernel_cu(const Tensor& qkv, const Tensor& q_norm, const Tensor& k_norm, const Tensor& cos_cache,
+                        const Tensor& sin_cache, const Tensor& pos, const Tensor& seq_len, const Tensor& slot,
+                        const Tensor& output, const Tensor& key_cache, const Tensor& value_cache, int32_t head_num,
+                        int32_t kv_head_num, int32_t head_size, float eps, int32_t fresh_rows, bool clear_input,
+                        const Tensor* clear_extra, const Tensor& workspace, void* stream) {
+    require_cuda(qkv, "rope+mha qkv");
+    require_cuda(output, "rope+mha output");
+    require_cuda(key_cache, "rope+mha key cache");
+    require_cuda(value_cache, "rope+mha value cache");
+    if (clear_extra) require_cuda(*clear_extra, "rope+mha extra buffer");
+    CHECK_EQ(key_cache.dims_size(), 4);  // [n_slots, kv_heads, max_seq, head_size]
+    const int32_t row = (head_num + 2 * kv_head_num) * head_size;
+    CHECK_EQ(qkv.size() % size_t(row), size_t(0));
+    const int32_t M = int32_t(qkv.size() / size_t(row));
+    CHECK_EQ(output.size(), size_t(M) * size_t(head_num) * size_t(head_size));
+    CHECK_GE(pos.size(), size_t(M));
+    CHECK_GE(seq_len.size(), size_t(M));
+    CHECK_GE(slot.size(), size_t(M));
+    KERNEL_OK(kuiper_rope_flash_decode(out_ptr<float>(qkv), q_norm.ptr<uint16_t>(), k_norm.ptr<uint16_t>(),
+                                       cos_cache.ptr<float>(), sin_cache.ptr<float>(), pos.ptr<int32_t>(),
+                                       seq_len.ptr<int32_t>(), slot.ptr<int32_t>(), out_ptr<float>(output),
+                                       out_ptr<uint16_t>(key_cache), out_ptr<uint16_t>(value_cache), M, head_num, kv_head_num,
+                                       head_size, eps, key_cache.get_dim(2), key_cache.get_dim(0), fresh_rows,
+                                       clear_input ? 1 : 0, clear_extra ? out_ptr<float>(*clear_extra) : nullptr,
+                                       clear_extra ? int64_t(clear_extra->size()) : 0, out_ptr<void>(workspace),
+                                       workspace.byte_size(), as_stream(stream)));
+}
+
 void swiglu_kernel_cu(const Tensor& gate_up, const Tensor& output, bool clear_input, void* stream) {
     require_cuda(gate_up, "swiglu input");
     require_cuda(output, "swiglu output");
@@ -236,6 +264,7 @@ MatmulKernelQuantGemm get_matmul_kernel_quant_gemm(base::DeviceType d) {
 RMSNormKernel get_rmsnorm_kernel(base::DeviceType d) { return pick<RMSNormKernel>(d, rmsnorm_kernel_cu, "rmsnorm"); }
 RoPEKernel get_rope_kernel(base::DeviceType d) { return pick<RoPEKernel>(d, rope_kernel_cu, "rope"); }
 MHAKernel get_mha_kernel(base::DeviceType d) { return pick<MHAKernel>(d, mha_kernel_cu, "mha"); }
+RoPEMHAKernel get_rope_mha_kernel(base::DeviceType d) { return pick<RoPEMHAKernel>(d, rope_mha_kernel_cu, "rope+mha"); }
 SwigluKernel get_swiglu_kernel(base::DeviceType d) { return pick<SwigluKernel>(d, swiglu_kernel_cu, "swiglu"); }
 EmbeddingKernel get_emb_kernel(base::DeviceType d) { return pick<EmbeddingKernel>(d, emb_kernel_cu, "embedding"); }
 ArgmaxKernel get_argmax_kernel(base::DeviceType d) { return pick<ArgmaxKernel>(d, argmax_kernel_cu, "argmax"); }

@@ -53,6 +53,14 @@ using RoPEKernel = void (*)(const tensor::Tensor& qkv, const tensor::Tensor& q_n
                             const tensor::Tensor& value_cache, int32_t head_num, int32_t kv_head_num, int32_t head_size,
                             float eps, bool clear_input, const tensor::Tensor* clear_extra, void* stream);
 
+// rotary + KV append + attention in one kernel (decode batches: one row per sequence slot, seq_len == pos + 1)
+using RoPEMHAKernel = void (*)(const tensor::Tensor& qkv, const tensor::Tensor& q_norm, const tensor::Tensor& k_norm,
+                               const tensor::Tensor& cos_cache, const tensor::Tensor& sin_cache, const tensor::Tensor& pos,
+                               const tensor::Tensor& seq_len, const tensor::Tensor& slot, const tensor::Tensor& output,
+                               const tensor::Tensor& key_cache, const tensor::Tensor& value_cache, int32_t head_num,
+                               int32_t kv_head_num, int32_t head_size, float eps, int32_t fresh_rows, bool clear_input,
+                               const tensor::Tensor* clear_extra, const tensor::Tensor& workspace, void* stream);
+
 using MHAKernel = void (*)(const tensor::Tensor& query, const tensor::Tensor& key_cache, const tensor::Tensor& value_cache,
                            const tensor::Tensor& seq_len, const tensor::Tensor& slot, const tensor::Tensor& output,
                            int32_t head_num, int32_t kv_head_num, int32_t head_size, int32_t fresh_rows,
@@ -73,6 +81,7 @@ MatmulKernelQuantGemm get_matmul_kernel_quant_gemm(base::DeviceType device_type)
 RMSNormKernel get_rmsnorm_kernel(base::DeviceType device_type);
 RoPEKernel get_rope_kernel(base::DeviceType device_type);
 MHAKernel get_mha_kernel(base::DeviceType device_type);
+RoPEMHAKernel get_rope_mha_kernel(base::DeviceType device_type);
 SwigluKernel get_swiglu_kernel(base::DeviceType device_type);
 EmbeddingKernel get_emb_kernel(base::DeviceType device_type);
 ArgmaxKernel get_argmax_kernel(base::DeviceType device_type);

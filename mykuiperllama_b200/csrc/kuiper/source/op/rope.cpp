@@ -76,4 +76,36 @@ base::Status RoPELayer::forward() {
     return base::error::success();
 }
 
+base::Status RoPELayer::forward_with_attention(const tensor::Tensor& qkv, const tensor::Tensor& pos,
+                                               const tensor::Tensor& slot, const tensor::Tensor& cos_cache,
+                                               const tensor::Tensor& sin_cache, const tensor::Tensor& seq_len,
+                                               const tensor::Tensor& attention_out, int32_t fresh_rows) {
+    set_input(0, qkv);
+    set_input(1, pos);
+    set_input(2, slot);
+    set_input(3, cos_cache);
+    set_input(4, sin_cache);
+    set_output(0, attention_out);  // same shape as the q output of the plain layer
+    base::Status status = check();
+    if (!status) return status;
+    const int32_t row = (head_num_ + 2 * kv_head_num_) * head_size_;
+    const int32_t M = int32_t(qkv.size() / size_t(row));
+    status = check_tensor(seq_len, device_type_, base::DataType::DataTypeInt32);
+    if (status && seq_len.size() < size_t(M)) status = base::error::invalid_argument("seq_len tensor is too short.");
+    if (!status) return status;
+    tensor::Tensor extra;
+    if (!clear_extra_.is_empty() && clear_extra_row_ > 0) {
+        if (size_t(M) * size_t(clear_extra_row_) > clear_extra_.size())
+            return base::error::invalid_argument("the extra buffer is smaller than the pass");
+        extra = tensor::Tensor(base::DataType::DataTypeFp32, std::vector<int32_t>{M, clear_extra_row_}, false, nullptr,
+                               const_cast<float*>(clear_extra_.ptr<float>()));
+        extra.set_device_type(device_type_);
+    }
+    kernel::get_rope_mha_kernel(device_type_)(qkv, get_weight(0), get_weight(1), cos_cache, sin_cache, pos, seq_len, slot,
+                                              attention_out, key_cache_, value_cache_, head_num_, kv_head_num_, head_size_,
+                                              eps_, fresh_rows, clear_input_, extra.is_empty() ? nullptr : &extra,
+                                              attention_workspace_, stream());
+    return base::error::success();
+}
+
 }  // namespace op

@@ -422,6 +422,37 @@ def test_flash_decode_early_fetch_matches_conservative_path(cuda, oracle):
         assert torch.equal(got, ref), fresh
 
 
+@pytest.mark.parametrize("Nq,Nkv,lens", [(32, 8, [2084, 1, 700]), (16, 8, [65, 64]), (8, 8, [130])])
+def test_rope_fused_into_flash_decode_is_bit_identical(cuda, oracle, Nq, Nkv, lens):
+    # decode batch: one row per slot, seq_len = pos + 1; the fused kernel must reproduce the two-kernel path bit for bit,
+    # caches included, and may clear the raw projection rows and a side buffer
+    rng = np.random.default_rng(31 + Nq)
+    B, D, Lmax = len(lens), 128, 2100
+    kc = torch.randn((B, Nkv, Lmax, D), device="cuda").bfloat16()
+    vc = torch.randn((B, Nkv, Lmax, D), device="cuda").bfloat16()
+    kc2, vc2 = kc.clone(), vc.clone()
+    qkv = dev(rng.standard_normal((B, (Nq + 2 * Nkv) * D)).astype(np.float32))
+    qn = dev(oracle.f32_to_bf16((1 + 0.1 * rng.standard_normal(D)).astype(np.float32)))
+    kn = dev(oracle.f32_to_bf16((1 + 0.1 * rng.standard_normal(D)).astype(np.float32)))
+    cos_t, sin_t = (dev(t) for t in oracle.rope_tables(Lmax, D, 1e6))
+    seq = dev(np.array(lens, np.int32))
+    pos = dev(np.array(lens, np.int32) - 1)
+    slot = dev(np.arange(B, dtype=np.int32))
+    ws = cuda.flash_decode_workspace(B, Nq, D, Lmax)
+    q = cuda.qknorm_rope_kvwrite(qkv.clone(), qn, kn, cos_t, sin_t, pos, slot, Nq, Nkv, D, 1e-6, kc, vc)
+    ref = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws)
+    for fresh in (-1, 1):
+        raw = qkv.clone()
+        side = torch.ones((B, 512), device="cuda")
+        k_f, v_f = kc2.clone(), vc2.clone()
+        got = cuda.rope_flash_decode(raw, qn, kn, cos_t, sin_t, pos, seq, slot, Nq, Nkv, D, 1e-6, k_f, v_f, workspace=ws,
+                                     fresh_rows=fresh, clear_input=True, clear_extra=side)
+        torch.cuda.synchronize()
+        assert torch.equal(got, ref), fresh
+        assert torch.equal(k_f.view(torch.int16), kc.view(torch.int16)) and torch.equal(v_f.view(torch.int16), vc.view(torch.int16))
+        assert float(raw.abs().max()) == 0.0 and float(side.abs().max()) == 0.0
+
+
 def test_flash_decode_shared_cache_is_causal_prefill(cuda, oracle):
     # a prompt chunk: every row reads the same sequence, row i sees positions [0, i]
     rng = np.random.default_rng(9)
