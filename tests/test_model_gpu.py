@@ -138,27 +138,27 @@ def test_engine_rejects_bad_requests(oracle, engine_mod):
         engine_mod.Qwen3Engine(engine_mod.EngineConfig(**{**TINY, "head_dim": 64}))
 
 
-def test_passes_of_16_rows_or_more_use_the_tensor_core_gemm(oracle, engine_mod):
-    """M >= 16 rows switch the INT4 projections to the tcgen05 GEMM (fp16 weights in the product): logits stay
-    within the fp16 weight rounding of the oracle, and a chunked prefill (32 + 8 rows) hands the same cache to decode."""
+def test_passes_of_64_rows_or_more_use_the_tensor_core_gemm(oracle, engine_mod):
+    """M >= 64 rows switch the INT4 projections to the tcgen05 GEMM (fp16 weights in the product): logits stay
+    within the fp16 weight rounding of the oracle, and a chunked prefill (96 + 4 rows) hands the same cache to decode."""
     cfg = {**TINY, "max_seq": 128}
     ocfg = oracle.ModelConfig(**cfg, act_round=oracle.ROUND_FP16)
     weights = make_model_weights(oracle, ocfg, seed=5)
     ref = oracle.OracleModel(ocfg, weights)
-    eng = engine_mod.Qwen3Engine(engine_mod.EngineConfig(**cfg, max_rows=32, act_mode=1))
+    eng = engine_mod.Qwen3Engine(engine_mod.EngineConfig(**cfg, max_rows=96, act_mode=1))
     eng.load(weights)
     rng = np.random.default_rng(6)
-    rows = rng.integers(0, 1000, 20).astype(np.int32)
-    pos = np.arange(20, dtype=np.int32)
+    rows = rng.integers(0, 1000, 70).astype(np.int32)
+    pos = np.arange(70, dtype=np.int32)
     lg_ref, nx_ref = ref.forward(rows, pos)
     lg, nx = eng.predict(rows, pos, want_logits=True)
     assert rel_err(lg, lg_ref) <= 5e-3
     assert np.mean(nx == nx_ref) >= 0.9  # near-ties may flip under the extra rounding
-    prompt = rng.integers(0, 1000, 40).astype(np.int32)
-    lg_ref, nx_ref = ref.forward(prompt, np.arange(40, dtype=np.int32), np.ones(40, np.int32))
+    prompt = rng.integers(0, 1000, 100).astype(np.int32)
+    lg_ref, nx_ref = ref.forward(prompt, np.arange(100, dtype=np.int32), np.ones(100, np.int32))
     first = eng.prefill(prompt, slot=1)
-    lg_ref1, nx_ref1 = ref.forward([first], [40], [1])
-    lg1, nx1 = eng.predict([first], [40], [1], want_logits=True)
+    lg_ref1, nx_ref1 = ref.forward([first], [100], [1])
+    lg1, nx1 = eng.predict([first], [100], [1], want_logits=True)
     assert rel_err(lg1, lg_ref1) <= 5e-3
     from mykuiperllama_b200 import capi
     capi.awq_gemm_status()
