@@ -85,7 +85,8 @@ private:
     std::unique_ptr<sampler::ArgmaxSampler> sampler_;
     std::vector<bool> layer_loaded_;
     bool globals_loaded_ = false;
-    bool accumulate_ = false;  // projections run in accumulate mode (see init)
+    bool accumulate_ = false;       // every projection runs in accumulate mode (single GPU, see init)
+    bool accumulate_cols_ = false;  // the column-split projections (QKV, gate|up) do; true under tensor parallelism too
 
     // pinned staging for the host <-> device token traffic
     int32_t* host_stage_ = nullptr;

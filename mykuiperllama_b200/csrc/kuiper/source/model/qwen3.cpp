@@ -184,7 +184,11 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     const bool fold_residual = c.tp_size == 1 || c.tp_rank == 0;
     // Single GPU, fp16-operand mode: every projection accumulates into its output (the residual stream for O
     // and down; a buffer that its consumer left zeroed for QKV and gate|up), which needs no ordered combine.
-    accumulate_ = c.tp_size == 1 && c.act_mode == 1 && QKV % 32 == 0 && H % 32 == 0 && (2 * I) % 32 == 0;
+    // Under tensor parallelism the row-split projections (O, down) keep the ordered combine - their output is a
+    // partial sum that goes through the all-reduce - while QKV and gate|up, whose outputs stay on the rank, still
+    // accumulate with their pre-norms fused in.
+    accumulate_cols_ = c.act_mode == 1 && QKV % 32 == 0 && H % 32 == 0 && (2 * I) % 32 == 0;
+    accumulate_ = accumulate_cols_ && c.tp_size == 1;
 
     layers_.resize(size_t(c.layer_num));
     layer_loaded_.assign(size_t(c.layer_num), false);
@@ -195,14 +199,17 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         L.o = make_quant(sh_o, fold_residual && !accumulate_);
         L.gate_up = make_quant(sh_gu, false);
         L.down = make_quant(sh_down, fold_residual && !accumulate_);
-        for (op::MatmulLayer* m : {L.qkv.get(), L.o.get(), L.gate_up.get(), L.down.get()}) m->set_accumulate(accumulate_);
-        if (accumulate_) {
+        for (op::MatmulLayer* m : {L.qkv.get(), L.gate_up.get()}) m->set_accumulate(accumulate_cols_);
+        for (op::MatmulLayer* m : {L.o.get(), L.down.get()}) m->set_accumulate(accumulate_);
+        if (accumulate_cols_) {
             // the two pre-norms run inside the projections that consume them
             L.qkv->set_input_norm(L.input_norm->get_weight(0), c.eps);
             L.gate_up->set_input_norm(L.post_norm->get_weight(0), c.eps);
-            // passes of 16 rows or more take the tensor-core path, which wants the normed rows materialised
+            // passes of 64 rows or more take the tensor-core path, which wants the normed rows materialised
             L.qkv->set_norm_scratch(get_buffer(ModelBufferType::OutputRMSNorm));
             L.gate_up->set_norm_scratch(get_buffer(ModelBufferType::FFNRMSNorm));
+        }
+        if (accumulate_) {
             // SwiGLU runs inside the down projection, which only reads the gate|up buffer
             L.down->set_input_swiglu(true);
             L.down->set_norm_scratch(get_buffer(ModelBufferType::W2Output));
@@ -216,7 +223,7 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         STATUS_CHECK(L.rope->set_weight(0, dev(DataType::DataTypeBf16, {D})));
         STATUS_CHECK(L.rope->set_weight(1, dev(DataType::DataTypeBf16, {D})));
         L.rope->set_cache(L.key_cache, L.value_cache);
-        L.rope->set_clear_input(accumulate_);
+        L.rope->set_clear_input(accumulate_cols_);
         // ... so this layer's rotary kernel zeroes that buffer for the next gate|up projection to accumulate into
         if (accumulate_) L.rope->set_clear_extra(get_buffer(ModelBufferType::W1Output), 2 * I);
         L.mha = std::make_unique<op::MultiHeadAttention>(device_type_, Hq, Hkv, D);
@@ -226,7 +233,7 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         L.rope->set_attention_workspace(get_buffer(ModelBufferType::MHAWorkspace));
         L.swiglu = std::make_unique<op::SwiGLULayer>(device_type_, I);
         L.swiglu->set_cuda_config(cuda_config_);
-        L.swiglu->set_clear_input(accumulate_);
+        L.swiglu->set_clear_input(accumulate_cols_);  // used when SwiGLU is not fused into the down projection
     }
     embedding_ = std::make_unique<op::EmbeddingLayer>(device_type_, H, c.vocab_size);
     embedding_->set_cuda_config(cuda_config_);
@@ -403,13 +410,13 @@ base::Status Qwen3Model::run_pass(int32_t M, bool inputs_settled) {
 
     RETURN_IF_ERROR(embedding_->forward(tokens, h));
     for (Qwen3Layer& L : layers_) {
-        if (accumulate_) {
+        if (accumulate_cols_) {
             RETURN_IF_ERROR(L.qkv->forward(h, qkv));  // RMSNorm fused into the projection
         } else {
             RETURN_IF_ERROR(L.input_norm->forward(h, xn));
             RETURN_IF_ERROR(L.qkv->forward(xn, qkv));
         }
-        if (accumulate_ && inputs_settled && slots_distinct_) {
+        if (accumulate_cols_ && inputs_settled && slots_distinct_) {
             // decode batch: rotary, KV append and attention in one kernel; every cache row but the one appended
             // here is older than this pass
             RETURN_IF_ERROR(L.rope->forward_with_attention(qkv, pos, slot, cos_t, sin_t, seq_len, att, 1));
@@ -423,7 +430,7 @@ base::Status Qwen3Model::run_pass(int32_t M, bool inputs_settled) {
             RETURN_IF_ERROR(L.mha->forward(q, seq_len, slot, att));
         }
         RETURN_IF_ERROR(project_and_reduce(*L.o, att));
-        if (accumulate_) {
+        if (accumulate_cols_) {
             RETURN_IF_ERROR(L.gate_up->forward(h, gu));
         } else {
             RETURN_IF_ERROR(L.post_norm->forward(h, xn2));
