@@ -499,10 +499,11 @@ def run_gemm_micro(args):
     sc = [(torch.rand((K // 128, N), device="cuda", generator=gen) * 0.018 + 0.002).half() for _ in range(n)]
     x = torch.randn((M, K), device="cuda", generator=gen)
     y = torch.zeros((M, N), device="cuda")
+    ws = None if args.gemm_impl == 1 else capi.awq_gemm_workspace(M, K)  # None: first-generation kernel
 
     def sweep():
         for i in range(n):
-            capi.awq_gemm(x, qw[i], qz[i], sc[i], y=y)
+            capi.awq_gemm(x, qw[i], qz[i], sc[i], y=y, workspace=ws)
 
     for _ in range(args.warmup):
         sweep()
@@ -606,6 +607,7 @@ def main():
     ap.add_argument("--kv-len", type=int, default=4096, help="KV length of the attn microbenchmark")
     ap.add_argument("--shape", default="2048x2048", help="KxN of the gemv microbenchmark")
     ap.add_argument("--rows", type=int, default=2048, help="token rows M of the gemm microbenchmark")
+    ap.add_argument("--gemm-impl", type=int, default=2, help="2 pipelined 128x256 kernel (default), 1 first-generation kernel")
     ap.add_argument("--mats", type=int, default=0, help="distinct weight matrices in the gemv microbenchmark (0 = 512 MiB worth)")
     ap.add_argument("--gemv-impl", type=int, default=None, help="2 accumulate mode of the tensor-core GEMV (engine path, default), 0 its ordered combine, "
                          "1 register-staged kernel, 3 first-generation persistent SIMT kernel (accumulate)")

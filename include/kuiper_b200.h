@@ -140,10 +140,15 @@ KUIPER_API int kuiper_awq_gemv_f32_noalloc(const float* x, const int32_t* qweigh
  *   accumulate == 0, residual != NULL : y  = x . W + residual   (residual may alias y)
  *   accumulate != 0                   : y += x . W              (summation order fixed: deterministic)
  * Any M > 0 is accepted (rows are padded to 128 inside the kernel); K % 128 == 0, N % 8 == 0.
+ * workspace: kuiper_awq_gemm_workspace_bytes(M, K) bytes (16-byte aligned) for the fp16 copy of x that the
+ * pipelined kernel reads (128 x 256 tiles, three stages); with NULL / too small a workspace the call
+ * falls back to the first-generation kernel, which converts x tile by tile.
  * kuiper_awq_gemm_status() synchronously reads the kernel's bounded-wait error word. ---- */
+KUIPER_API size_t kuiper_awq_gemm_workspace_bytes(int M, int K);
 KUIPER_API int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
                                    const uint16_t* scales, float* y, const float* residual, int accumulate,
-                                   int M, int K, int N, int group, kuiper_stream_t stream);
+                                   int M, int K, int N, int group, void* workspace, size_t workspace_bytes,
+                                   kuiper_stream_t stream);
 KUIPER_API int kuiper_awq_gemm_status(void);
 
 /* ---- BF16 GEMV (lm_head): W bf16 [N, K], y[M,N] = x[M,K] . W^T ---- */

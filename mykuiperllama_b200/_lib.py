@@ -44,7 +44,8 @@ KERNEL_API = {
     "kuiper_awq_gemv_status": (_i32, []),
     "kuiper_awq_gemv_noalloc_scratch_bytes": (_sz, []),
     "kuiper_awq_gemv_f32_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
-    "kuiper_awq_gemm_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "kuiper_awq_gemm_workspace_bytes": (_sz, [_i32, _i32]),
+    "kuiper_awq_gemm_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "kuiper_awq_gemm_status": (_i32, []),
     "kuiper_bf16_gemv_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_rmsnorm_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _vp]),

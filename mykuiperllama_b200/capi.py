@@ -106,16 +106,26 @@ def swiglu_awq_gemv_accum(gate_up, qweight, qzeros, scales, y, group=128):
     return y
 
 
-def awq_gemm(x, qweight, qzeros, scales, y=None, residual=None, accumulate=False, group=128):
-    """Tensor-core INT4 GEMM for M >= 16 rows: y = x . W (+ residual), or y += x . W."""
+def awq_gemm_workspace(M, K, device="cuda"):
+    n = kernels().kuiper_awq_gemm_workspace_bytes(M, K)
+    return torch.empty(max(n, 16), dtype=torch.uint8, device=device)
+
+
+def awq_gemm(x, qweight, qzeros, scales, y=None, residual=None, accumulate=False, group=128, workspace="auto"):
+    """Tensor-core INT4 GEMM for M >= 16 rows: y = x . W (+ residual), or y += x . W.
+    workspace: "auto" allocates the fp16 activation copy of the pipelined kernel, None selects the first-generation
+    kernel, a tensor is used as it is."""
     _dev(x, qweight, qzeros, scales)
     M, K = x.shape
     N = qweight.shape[1] * 8
     if y is None:
         y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    if isinstance(workspace, str):
+        workspace = awq_gemm_workspace(M, K, x.device)
     check(kernels().kuiper_awq_gemm_f32(_ptr(x), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(y),
                                         _ptr(residual) if residual is not None else None, int(bool(accumulate)),
-                                        M, K, N, group, _stream()))
+                                        M, K, N, group, _ptr(workspace) if workspace is not None else None,
+                                        workspace.numel() if workspace is not None else 0, _stream()))
     return y
 
 

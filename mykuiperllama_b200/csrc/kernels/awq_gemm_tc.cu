@@ -276,6 +276,261 @@ __global__ void __launch_bounds__(kGemmThreads, 1) awq_gemm_tc_kernel(const Gemm
     }
 }
 
+// zero-point and scale pairs of one (group, packed column): computed once per tile, used for its eight rows
+struct TileConsts {
+    __half2 z0, z1, z2, z3;  // (1024 + z) pairs for the low nibbles, -(64 + z) pairs for the high nibbles
+    __half2 s0, s1, s2, s3;  // fp16 scales of column pairs (0,1) (2,3) (4,5) (6,7)
+};
+__device__ __forceinline__ TileConsts make_tile_consts(uint32_t zw, const uint4& sraw) {
+    const __half2 neg_sixteenth = __floats2half2_rn(-0.0625f, -0.0625f);
+    const uint32_t z8 = zw >> 8;
+    TileConsts c;
+    c.z0 = tc_u2h2((zw & 0x000f000fu) | kMagicTc);
+    c.z1 = __hmul2(tc_u2h2((zw & 0x00f000f0u) | kMagicTc), neg_sixteenth);
+    c.z2 = tc_u2h2((z8 & 0x000f000fu) | kMagicTc);
+    c.z3 = __hmul2(tc_u2h2((z8 & 0x00f000f0u) | kMagicTc), neg_sixteenth);
+    c.s0 = tc_u2h2(sraw.x); c.s1 = tc_u2h2(sraw.y); c.s2 = tc_u2h2(sraw.z); c.s3 = tc_u2h2(sraw.w);
+    return c;
+}
+__device__ __forceinline__ void dequant_word_consts(uint32_t w, const TileConsts& c, uint32_t (&out)[4]) {
+    const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+    const uint32_t w8 = w >> 8;
+    out[0] = tc_h22u(__hmul2(__hsub2(tc_u2h2((w & 0x000f000fu) | kMagicTc), c.z0), c.s0));
+    out[1] = tc_h22u(__hmul2(__hfma2(tc_u2h2((w & 0x00f000f0u) | kMagicTc), sixteenth, c.z1), c.s1));
+    out[2] = tc_h22u(__hmul2(__hsub2(tc_u2h2((w8 & 0x000f000fu) | kMagicTc), c.z2), c.s2));
+    out[3] = tc_h22u(__hmul2(__hfma2(tc_u2h2((w8 & 0x00f000f0u) | kMagicTc), sixteenth, c.z3), c.s3));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Second generation: 128 x 256 tiles, two CTAs per SM, no global-memory latency on the critical path.
+//   * the activations are converted to fp16 once per call (convert_f16_kernel) and reach shared memory with
+//     cp.async, 16 bytes per (row, K octet), straight into their swizzled position, one tile ahead;
+//   * the packed weights of the next tile are already in registers while the current tile is dequantised;
+//   * a stage is reused only after the tcgen05.commit of the MMAs that read it; two stages of 48 KB, so that two
+//     CTAs share an SM and one's dequantisation overlaps the other's MMAs.
+constexpr int kBN2 = 256;
+constexpr int kStages2 = 2;   // 96 KB per CTA: two CTAs (16 warps, 2 x 256 TMEM columns) share an SM
+constexpr int kStageA2 = kBM * kBK * 2;   // 16 KB
+constexpr int kStageB2 = kBN2 * kBK * 2;  // 32 KB
+
+__global__ void convert_f16_kernel(const float4* __restrict__ x, uint2* __restrict__ out, int64_t n4) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += int64_t(gridDim.x) * blockDim.x) {
+        const float4 v = __ldcg(x + i);
+        out[i] = make_uint2(tc_h22u(__floats2half2_rn(v.x, v.y)), tc_h22u(__floats2half2_rn(v.z, v.w)));
+    }
+}
+
+struct GemmParams2 {
+    GemmParams g;
+    const __half* x16;  // [M, K] fp16 copy of x
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 2) awq_gemm_tc2_kernel(const GemmParams2 pp) {
+    const GemmParams& p = pp.g;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+    unsigned char* sA = smem;                          // kStages2 x 16 KB
+    unsigned char* sB = smem + kStages2 * kStageA2;    // kStages2 x 32 KB
+    __shared__ uint64_t mma_bar[kStages2];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_dead;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * kBN2, m0 = blockIdx.y * kBM;
+    const int NW = p.N >> 3;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < kStages2; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&mma_bar[i])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_dead = 0;
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&s_tmem)), "r"(uint32_t(kBN2))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    const uint32_t idesc = (1u << 4) | (uint32_t(kBN2 >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+    const int nk = p.K / kBK;
+    bool dead = false;
+
+    // ---- this thread's share of a tile; everything that does not depend on the tile is computed here
+    // activations: four 16-byte chunks (row m, K octet koct), global fp16 -> swizzled shared memory
+    const __half* a_src[4];
+    uint32_t a_dst[4], a_bytes[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const int item = q * kGemmThreads + tid;
+        const int koct = item & 7, m = item >> 3;
+        const bool ok = m0 + m < p.M;
+        a_src[q] = pp.x16 + size_t(ok ? m0 + m : 0) * p.K + koct * 8;
+        a_dst[q] = smem_addr(sA) + (m >> 3) * 1024 + (m & 7) * 128 + ((koct ^ (m & 7)) << 4);
+        a_bytes[q] = ok ? 16u : 0u;  // 0: the chunk is zero filled
+    }
+    auto issue_a = [&](int tile, int stage) {
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_dst[q] + stage * kStageA2),
+                         "l"(a_src[q] + tile * kBK), "r"(a_bytes[q])
+                         : "memory");
+    };
+    // weights: packed word column j of the tile (8 output columns), K octet koct (8 rows)
+    const int koct_b = tid & 7, j_b = tid >> 3;
+    const int wcol = (n0 >> 3) + j_b;
+    const bool col_ok = wcol < NW;
+    const uint32_t* w_src = p.qw + (col_ok ? size_t(koct_b * 8) * NW + wcol : 0);  // + tile * kBK * NW + r * NW
+    const uint32_t* z_src = p.qz + (col_ok ? wcol : 0);                            // + group * NW
+    const uint4* s_src = reinterpret_cast<const uint4*>(p.scales + (col_ok ? n0 + j_b * 8 : 0));  // + group * N halves
+    const int tile_words = kBK * NW;
+    auto load_b = [&](int tile, uint32_t (&w)[8], uint32_t& zw, uint4& sraw) {
+        const uint32_t* wp = w_src + size_t(tile) * tile_words;
+        const int g = tile >> 1;  // two 64-row tiles per 128-row group
+#pragma unroll
+        for (int r = 0; r < 8; r++) w[r] = col_ok ? __ldg(wp + r * NW) : 0u;
+        zw = col_ok ? __ldg(z_src + size_t(g) * NW) : 0u;
+        sraw = col_ok ? __ldg(s_src + size_t(g) * (p.N >> 3)) : make_uint4(0, 0, 0, 0);
+    };
+
+    // one tile of the K loop; the packed words of tile `it` are in (w, zw, sraw) and the same registers are
+    // refilled with tile it + 2 as soon as they have been consumed, so a load has two tiles of time to land
+    auto tile_step = [&](int it, uint32_t (&w)[8], uint32_t& zw, uint4& sraw) {
+        const int s = it % kStages2;
+        // ---- dequantise the weight tile into stage s (free: checked one tile ago, when its activations were requested)
+        {
+            uint32_t d[8][4];  // [row][column pair]
+            const TileConsts tc = make_tile_consts(zw, sraw);
+#pragma unroll
+            for (int r = 0; r < 8; r++) dequant_word_consts(w[r], tc, d[r]);
+            if (it + 2 < nk) load_b(it + 2, w, zw, sraw);
+            unsigned char* dst = sB + s * kStageB2 + j_b * 1024;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                const int pr = c >> 1;
+                const uint32_t sel = (c & 1) ? 0x7632u : 0x5410u;
+                uint4 o;  // rows (0,1) (2,3) (4,5) (6,7) of column c
+                o.x = __byte_perm(d[0][pr], d[1][pr], sel);
+                o.y = __byte_perm(d[2][pr], d[3][pr], sel);
+                o.z = __byte_perm(d[4][pr], d[5][pr], sel);
+                o.w = __byte_perm(d[6][pr], d[7][pr], sel);
+                *reinterpret_cast<uint4*>(dst + c * 128 + ((koct_b ^ c) << 4)) = o;
+            }
+        }
+        // ---- request the next tile's activations; its stage is free once the MMAs that last read it have finished
+        //      (by now they had the whole dequantisation above to do so)
+        if (it + 1 < nk) {
+            const int sn = (it + 1) % kStages2;
+            if (it + 1 >= kStages2 && !dead) {
+                if (!tc_mbar_wait(&mma_bar[sn], uint32_t((it + 1) / kStages2 - 1) & 1u)) {
+                    atomicExch(&g_gemm_wait_error, 3);
+                    s_dead = 1;
+                    dead = true;
+                }
+            }
+            issue_a(it + 1, sn);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the newest group: this tile's activations
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        dead = dead || (s_dead != 0);
+        if (tid == 0 && !dead) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_base = smem_addr(sA + s * kStageA2), b_base = smem_addr(sB + s * kStageB2);
+#pragma unroll
+            for (int kk = 0; kk < kBK / 16; kk++) {
+                const uint64_t adesc = make_desc(a_base + kk * 32);
+                const uint64_t bdesc = make_desc(b_base + kk * 32);
+                const uint32_t accumulate = (it > 0 || kk > 0) ? 1u : 0u;
+                asm volatile(
+                    "{\n\t.reg .pred p;\n\t"
+                    "setp.ne.b32 p, %4, 0;\n\t"
+                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                    ::"r"(tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                    : "memory");
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(&mma_bar[s]))
+                         : "memory");
+        }
+    };
+
+    uint32_t w_even[8], w_odd[8], zw_even, zw_odd = 0;
+    uint4 s_even, s_odd = make_uint4(0, 0, 0, 0);
+    issue_a(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    load_b(0, w_even, zw_even, s_even);
+    if (nk > 1) load_b(1, w_odd, zw_odd, s_odd);
+    for (int it = 0; it < nk; it += 2) {
+        tile_step(it, w_even, zw_even, s_even);
+        if (it + 1 < nk) tile_step(it + 1, w_odd, zw_odd, s_odd);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+    // ---- all MMAs done?  (they complete in order: the last commit covers everything)
+    if (!dead) {
+        const int last = nk - 1;
+        if (!tc_mbar_wait(&mma_bar[last % kStages2], uint32_t(last / kStages2) & 1u)) {
+            atomicExch(&g_gemm_wait_error, 4);
+            dead = true;
+        }
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    if (!dead) {
+        // ---- epilogue: warp w reads TMEM lanes 32*(w&3).., columns 128*(w>>2)..; one output row per thread
+        const int row = m0 + (warp & 3) * 32 + lane;
+        const int cbase = (warp >> 2) * 128;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ch++) {
+            uint32_t r[32];
+            const uint32_t taddr = tmem + (uint32_t((warp & 3) * 32) << 16) + uint32_t(cbase + ch * 32);
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                  "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr)
+                : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < p.M) {
+                const int col0 = n0 + cbase + ch * 32;
+                float* yp = p.y + size_t(row) * p.N + col0;
+                const float* rp = p.mode == 1 ? p.residual + size_t(row) * p.N + col0 : (p.mode == 2 ? yp : nullptr);
+#pragma unroll
+                for (int v = 0; v < 8; v++) {
+                    if (col0 + v * 4 < p.N) {
+                        float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                               __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                        if (rp) {
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(rp) + v);
+                            o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
+                        }
+                        reinterpret_cast<float4*>(yp)[v] = o;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kBN2)) : "memory");
+    }
+}
+
 }  // namespace
 
 void awq_gemm_set_tuning(const char* key, int value) {
@@ -295,9 +550,14 @@ extern "C" int kuiper_awq_gemm_status(void) {
     return KUIPER_INTERNAL_ERROR;
 }
 
+extern "C" size_t kuiper_awq_gemm_workspace_bytes(int M, int K) {
+    if (M <= 0 || K <= 0) return 0;
+    return (size_t(M) * size_t(K) * sizeof(__half) + 255) / 256 * 256;  // fp16 copy of the activations
+}
+
 extern "C" int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
                                    float* y, const float* residual, int accumulate, int M, int K, int N, int group,
-                                   kuiper_stream_t stream) {
+                                   void* workspace, size_t workspace_bytes, kuiper_stream_t stream) {
     KUIPER_REQUIRE(x && qweight && qzeros && scales && y, "awq_gemm: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && K > 0 && N > 0, "awq_gemm: empty shape M=%d K=%d N=%d", M, K, N);
     KUIPER_REQUIRE(group == 128, "awq_gemm: group size %d is not supported (128 only)", group);
@@ -315,6 +575,31 @@ extern "C" int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const
     p.residual = residual;
     p.M = M; p.K = K; p.N = N;
     p.mode = accumulate ? 2 : (residual ? 1 : 0);
+    if (workspace != nullptr && workspace_bytes >= kuiper_awq_gemm_workspace_bytes(M, K) &&
+        (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) {
+        // second-generation kernel: activations converted to fp16 once, 128 x 256 tiles
+        const int64_t n4 = int64_t(M) * K / 4;
+        int blocks = int((n4 + 255) / 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        int rc = pdl_status(launch_pdl(convert_f16_kernel, dim3(blocks), dim3(256), 0, as_stream(stream),
+                                       reinterpret_cast<const float4*>(x), reinterpret_cast<uint2*>(workspace), n4),
+                            "awq_gemm convert");
+        if (rc != KUIPER_OK) return rc;
+        GemmParams2 p2;
+        p2.g = p;
+        p2.x16 = reinterpret_cast<const __half*>(workspace);
+        const size_t smem2 = 1024 + size_t(kStages2) * (kStageA2 + kStageB2);
+        static bool configured2 = false;
+        if (!configured2) {
+            if (cudaFuncSetAttribute(awq_gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem2)) != cudaSuccess) {
+                set_error("awq_gemm: cannot reserve %zu bytes of shared memory", smem2);
+                return KUIPER_INTERNAL_ERROR;
+            }
+            configured2 = true;
+        }
+        const dim3 grid2((N + kBN2 - 1) / kBN2, (M + kBM - 1) / kBM, 1);
+        return pdl_status(launch_pdl(awq_gemm_tc2_kernel, grid2, dim3(kGemmThreads), smem2, as_stream(stream), p2), "awq_gemm");
+    }
     const size_t smem = 1024 + 2 * kStageA + 2 * kStageB;
     static bool configured = false;
     if (!configured) {

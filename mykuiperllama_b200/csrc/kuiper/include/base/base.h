@@ -50,6 +50,7 @@ enum class ModelBufferType {
     NextTokens = 35,    // greedy ids on the device
     MatmulWorkspace = 36,
     MHAWorkspace = 37,
+    GemmWorkspace = 38,  // fp16 copy of the activation rows for the tensor-core matmul
 };
 }  // namespace model
 

@@ -46,6 +46,9 @@ public:
     void set_gemm_min_rows(int32_t rows) { gemm_min_rows_ = rows; }
     // scratch of the split-K kernel: kernel::matmul_quant_workspace_bytes(M, K, N) bytes, zero-initialised once
     void set_workspace(const tensor::Tensor& workspace);
+    // scratch of the tensor-core path: kernel::matmul_quant_gemm_workspace_bytes(max rows, dim1) bytes, no
+    // initialisation needed; without it the first-generation GEMM kernel is used
+    void set_gemm_workspace(const tensor::Tensor& workspace) { gemm_workspace_ = workspace; }
     // how the INT4 kernel rounds x: 1 = fp16 operand (default), 0 = fp32 operand
     void set_act_mode(int32_t act_mode) { act_mode_ = act_mode; }
 
@@ -65,6 +68,7 @@ private:
     float input_norm_eps_ = 1e-6f;
     int32_t act_mode_ = 1;
     tensor::Tensor workspace_;
+    tensor::Tensor gemm_workspace_;
     tensor::Tensor norm_scratch_;
     int32_t gemm_min_rows_ = 64;
 };

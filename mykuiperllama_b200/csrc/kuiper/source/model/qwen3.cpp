@@ -96,8 +96,11 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     // ---- capacity of the arena: weights + caches + step buffers + scratch
     const size_t cache_elems = size_t(c.max_batch) * Hkv * c.max_seq_len * D;
     size_t ws_mm = 0;
-    for (const QuantShape& s : {sh_qkv, sh_o, sh_gu, sh_down})
+    size_t ws_gemm = 0;  // fp16 activation rows of the tensor-core path
+    for (const QuantShape& s : {sh_qkv, sh_o, sh_gu, sh_down}) {
         ws_mm = std::max(ws_mm, kernel::matmul_quant_workspace_bytes(2, s.K, s.N));
+        ws_gemm = std::max(ws_gemm, kernel::matmul_quant_gemm_workspace_bytes(R, s.K));
+    }
     const size_t ws_mha = kernel::mha_workspace_bytes(R, Hq, D, c.max_seq_len);
     size_t total = 0;
     total += size_t(c.layer_num) * (sh_qkv.total(g) + sh_o.total(g) + sh_gu.total(g) + sh_down.total(g) +
@@ -110,7 +113,7 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     total += round256(size_t(R) * 2 * I * 4) + round256(size_t(R) * I * 4);
     total += round256(size_t(R) * c.vocab_size * 4);
     total += 2 * round256(size_t(c.max_seq_len) * (D / 2) * 4);
-    total += round256(ws_mm) + round256(ws_mha) + (1u << 20);
+    total += round256(ws_mm) + round256(ws_mha) + round256(ws_gemm) + (1u << 20);
     auto arena = std::make_shared<base::CUDAArenaAllocator>(total);
     weight_alloc_ = arena;
 
@@ -136,6 +139,7 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::SinCache, dev(DataType::DataTypeFp32, {c.max_seq_len, D / 2})));
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::MatmulWorkspace, dev(DataType::DataTypeInt8, {int32_t(ws_mm)})));
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::MHAWorkspace, dev(DataType::DataTypeInt8, {int32_t(ws_mha)})));
+    RETURN_IF_ERROR(insert_buffer(ModelBufferType::GemmWorkspace, dev(DataType::DataTypeInt8, {int32_t(ws_gemm)})));
     CUDA_OK(cudaMemset(get_buffer(ModelBufferType::MatmulWorkspace).ptr<void>(), 0, ws_mm));
     CUDA_OK(cudaMemset(get_buffer(ModelBufferType::MHAWorkspace).ptr<void>(), 0, ws_mha));
     // accumulating projections need their output buffers zero before the first pass
@@ -169,6 +173,7 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         l->set_act_mode(c.act_mode);
         l->set_residual(residual);
         l->set_workspace(get_buffer(ModelBufferType::MatmulWorkspace));
+        l->set_gemm_workspace(get_buffer(ModelBufferType::GemmWorkspace));
         STATUS_CHECK(l->set_weight(0, dev(DataType::DataTypeInt32, {s.K, s.N / 8})));
         STATUS_CHECK(l->set_weight(1, dev(DataType::DataTypeInt32, {s.K / g, s.N / 8})));
         l->set_scales(dev(DataType::DataTypeFp16, {s.K / g, s.N}));

@@ -112,7 +112,7 @@ void matmul_kernel_quant_accum_cu(const Tensor& input, const Tensor& qweight, co
 
 void matmul_kernel_quant_gemm_cu(const Tensor& input, const Tensor& qweight, const Tensor& qzeros, const Tensor& scales,
                                  const Tensor& output, const Tensor* residual, bool accumulate, int32_t group_size,
-                                 void* stream) {
+                                 const Tensor& workspace, void* stream) {
     require_cuda(input, "matmul input");
     require_cuda(qweight, "matmul qweight");
     require_cuda(qzeros, "matmul qzeros");
@@ -126,7 +126,8 @@ void matmul_kernel_quant_gemm_cu(const Tensor& input, const Tensor& qweight, con
     CHECK_EQ(output.size(), size_t(M) * size_t(N));
     KERNEL_OK(kuiper_awq_gemm_f32(input.ptr<float>(), qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(), scales.ptr<uint16_t>(),
                                   out_ptr<float>(output), residual ? residual->ptr<float>() : nullptr, accumulate ? 1 : 0, M,
-                                  K, N, group_size, as_stream(stream)));
+                                  K, N, group_size, workspace.is_empty() ? nullptr : out_ptr<void>(workspace),
+                                  workspace.is_empty() ? 0 : workspace.byte_size(), as_stream(stream)));
 }
 
 void rmsnorm_kernel_cu(const Tensor& input, const Tensor& weight, const Tensor& output, float eps, void* stream) {
@@ -270,6 +271,7 @@ EmbeddingKernel get_emb_kernel(base::DeviceType d) { return pick<EmbeddingKernel
 ArgmaxKernel get_argmax_kernel(base::DeviceType d) { return pick<ArgmaxKernel>(d, argmax_kernel_cu, "argmax"); }
 
 size_t matmul_quant_workspace_bytes(int32_t M, int32_t K, int32_t N) { return kuiper_awq_gemv_workspace_bytes(M, K, N); }
+size_t matmul_quant_gemm_workspace_bytes(int32_t M, int32_t K) { return kuiper_awq_gemm_workspace_bytes(M, K); }
 size_t mha_workspace_bytes(int32_t M, int32_t head_num, int32_t head_size, int32_t max_seq) {
     return kuiper_flash_decode_workspace_bytes(M, head_num, head_size, max_seq);
 }

@@ -42,7 +42,7 @@ using MatmulKernelQuantAccum = void (*)(const tensor::Tensor& input, const tenso
 using MatmulKernelQuantGemm = void (*)(const tensor::Tensor& input, const tensor::Tensor& qweight,
                                        const tensor::Tensor& qzeros, const tensor::Tensor& scales,
                                        const tensor::Tensor& output, const tensor::Tensor* residual, bool accumulate,
-                                       int32_t group_size, void* stream);
+                                       int32_t group_size, const tensor::Tensor& workspace, void* stream);
 
 using RMSNormKernel = void (*)(const tensor::Tensor& input, const tensor::Tensor& weight, const tensor::Tensor& output,
                                float eps, void* stream);
@@ -88,6 +88,7 @@ ArgmaxKernel get_argmax_kernel(base::DeviceType device_type);
 
 // scratch sizes of the two kernels that need a workspace
 size_t matmul_quant_workspace_bytes(int32_t M, int32_t K, int32_t N);
+size_t matmul_quant_gemm_workspace_bytes(int32_t M, int32_t K);  // fp16 activation copy of the tensor-core path
 size_t mha_workspace_bytes(int32_t M, int32_t head_num, int32_t head_size, int32_t max_seq);
 
 }  // namespace kernel

@@ -90,7 +90,7 @@ base::Status MatmulLayer::forward() {
         }
         kernel::get_matmul_kernel_quant_gemm(device_type_)(*x, get_weight(0), get_weight(1), scales_, get_output(0),
                                                            has_residual_ ? &get_input(1) : nullptr, accumulate_,
-                                                           group_size_, stream());
+                                                           group_size_, gemm_workspace_, stream());
     } else if (is_quant_layer_ && accumulate_) {
         if (has_residual_) return base::error::invalid_argument("accumulate mode takes no residual input");
         kernel::get_matmul_kernel_quant_accum(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),

@@ -210,9 +210,10 @@ def test_awq_gemv_rejects_bad_arguments(cuda):
 
 
 # ----------------------------------------------------------------------------- INT4 GEMM (tcgen05), M >= 16
+@pytest.mark.parametrize("gen", [2, 1])
 @pytest.mark.parametrize("M,K,N", [(16, 128, 128), (16, 256, 136), (100, 1024, 384), (128, 4096, 1024), (129, 512, 256),
                                    (300, 1024, 4104), (16, 4096, 6144), (64, 3072, 1024)])
-def test_awq_gemm_tensor_core(cuda, oracle, M, K, N):
+def test_awq_gemm_tensor_core(cuda, oracle, M, K, N, gen):
     rng = np.random.default_rng(M + K + N)
     q, z, s = awq_random(rng, K, N)
     qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
@@ -220,17 +221,18 @@ def test_awq_gemm_tensor_core(cuda, oracle, M, K, N):
     res = rng.standard_normal((M, N)).astype(np.float32)
     ref = oracle.awq_gemv(x, qw, qz, su, act_round=oracle.ROUND_FP16).astype(np.float64)
     tx, tqw, tqz, ts = dev(x), dev(qw), dev(qz), dev(su, torch.float16)
-    y = cuda.awq_gemm(tx, tqw, tqz, ts)
-    y_res = cuda.awq_gemm(tx, tqw, tqz, ts, residual=dev(res))
+    ws = cuda.awq_gemm_workspace(M, K) if gen == 2 else None  # None: first-generation kernel (converts x per tile)
+    y = cuda.awq_gemm(tx, tqw, tqz, ts, workspace=ws)
+    y_res = cuda.awq_gemm(tx, tqw, tqz, ts, residual=dev(res), workspace=ws)
     y_acc = dev(res)
-    cuda.awq_gemm(tx, tqw, tqz, ts, y=y_acc, accumulate=True)
+    cuda.awq_gemm(tx, tqw, tqz, ts, y=y_acc, accumulate=True, workspace=ws)
     torch.cuda.synchronize()
     # the weight (q - z) * s is rounded to fp16 before the tensor-core product: ~2^-11 per weight on top of the GEMV's error
     err = rel_err(y.cpu().numpy(), ref)
     assert err <= SPEC_TOL and err <= 1e-3
     assert rel_err(y_res.cpu().numpy(), ref + res) <= 1e-3
     assert torch.equal(y_acc, y_res)  # same tile, same order: bit-identical
-    again = cuda.awq_gemm(tx, tqw, tqz, ts)
+    again = cuda.awq_gemm(tx, tqw, tqz, ts, workspace=ws)
     torch.cuda.synchronize()
     assert torch.equal(again, y)  # fixed summation order: deterministic
     cuda.awq_gemm_status()
