@@ -151,6 +151,22 @@ KUIPER_API int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const
                                    kuiper_stream_t stream);
 KUIPER_API int kuiper_awq_gemm_status(void);
 
+/* ---- one-shot all-reduce (sum, fp32) over peer-mapped exchange buffers: tensor-parallel decode.  No counterpart in
+ * the reference (it has no multi-GPU code).
+ * Every rank owns an exchange buffer of kuiper_allreduce_buffer_bytes(world, max_count) bytes, zero-initialised once,
+ * 128-byte aligned, and mapped into every other rank's process (CUDA IPC); rank_buffers is a HOST array of `world`
+ * device pointers, entry r = rank r's buffer as this process sees it (entry `rank` = the own buffer).  state: two
+ * zero-initialised uint32 on the device (sequence number, error word), private to the rank.  All ranks must issue
+ * the same sequence of calls with the same count.  data (16-byte aligned, count % 4 == 0, count <= max_count,
+ * max_count % 32 == 0) holds the partial row on entry and the sum on return; every rank adds in rank order, so all
+ * ranks get identical bits.  Waits on peers are bounded (default one second, tuning key "allreduce_timeout_ms"):
+ * when one runs out the call's result is void and kuiper_allreduce_status (synchronous) returns 5. ---- */
+KUIPER_API size_t kuiper_allreduce_buffer_bytes(int world, int64_t max_count);
+KUIPER_API int kuiper_allreduce_oneshot_f32(float* data, int64_t count, int rank, int world,
+                                            void* const* rank_buffers, int64_t max_count, uint32_t* state,
+                                            kuiper_stream_t stream);
+KUIPER_API int kuiper_allreduce_status(const uint32_t* state);
+
 /* ---- BF16 GEMV (lm_head): W bf16 [N, K], y[M,N] = x[M,K] . W^T ---- */
 KUIPER_API int kuiper_bf16_gemv_f32(const float* x, const uint16_t* W, float* y, int M, int K, int N,
                          kuiper_stream_t stream);

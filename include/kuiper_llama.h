@@ -52,6 +52,10 @@ KUIPER_LLAMA_API int kuiper_model_load_globals(kuiper_model* model, const void* 
 /* tensor parallelism: rank 0 makes a 128-byte id, every rank passes it to init_tp */
 KUIPER_LLAMA_API int kuiper_tp_unique_id(void* out128);
 KUIPER_LLAMA_API int kuiper_model_init_tp(kuiper_model* model, const void* unique_id128);
+/* 1 if decode rows are summed by the one-shot exchange over peer memory, 0 if everything goes through NCCL */
+KUIPER_LLAMA_API int kuiper_model_tp_one_shot(kuiper_model* model);
+/* synchronous health check of that exchange: 5 if a bounded wait on a peer ever ran out */
+KUIPER_LLAMA_API int kuiper_model_tp_status(kuiper_model* model);
 
 /* one pass over M host rows; next (M ids) and logits (M x vocab, may be NULL) come back to the host */
 KUIPER_LLAMA_API int kuiper_model_predict(kuiper_model* model, const int32_t* tokens, const int32_t* pos,

@@ -47,6 +47,9 @@ KERNEL_API = {
     "kuiper_awq_gemm_workspace_bytes": (_sz, [_i32, _i32]),
     "kuiper_awq_gemm_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "kuiper_awq_gemm_status": (_i32, []),
+    "kuiper_allreduce_buffer_bytes": (_sz, [_i32, _i64]),
+    "kuiper_allreduce_oneshot_f32": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _vp]),
+    "kuiper_allreduce_status": (_i32, [_vp]),
     "kuiper_bf16_gemv_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_rmsnorm_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _vp]),
     "kuiper_qknorm_rope_kvwrite": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _i32,
@@ -110,6 +113,8 @@ HOST_API = {
     "kuiper_model_load_globals": (_i32, [_vp, _vp, _vp, _vp, _i32]),
     "kuiper_tp_unique_id": (_i32, [_vp]),
     "kuiper_model_init_tp": (_i32, [_vp, _vp]),
+    "kuiper_model_tp_one_shot": (_i32, [_vp]),
+    "kuiper_model_tp_status": (_i32, [_vp]),
     "kuiper_model_predict": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp]),
     "kuiper_model_prefill": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "kuiper_model_decode_begin": (_i32, [_vp, _vp, _vp, _vp, _i32]),

@@ -207,6 +207,24 @@ def rope_flash_decode(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, seq_len, slot,
     return out
 
 
+def allreduce_buffer(world, max_count, device="cuda"):
+    n = kernels().kuiper_allreduce_buffer_bytes(world, max_count)
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def allreduce_oneshot(data, rank, world, rank_buffers, max_count, state):
+    """In-place sum of `data` over the ranks whose exchange buffers are listed in rank_buffers (tensors or raw pointers)."""
+    import ctypes
+    _dev(data, state)
+    ptrs = (ctypes.c_void_p * world)(*[b if isinstance(b, int) else b.data_ptr() for b in rank_buffers])
+    check(kernels().kuiper_allreduce_oneshot_f32(_ptr(data), data.numel(), rank, world, ptrs, max_count, _ptr(state), _stream()))
+    return data
+
+
+def allreduce_status(state) -> None:
+    check(kernels().kuiper_allreduce_status(_ptr(state)))
+
+
 def swiglu(gate_up, out=None, clear_input=False):
     _dev(gate_up, out)
     M, I2 = gate_up.shape

@@ -51,6 +51,11 @@ protected:
     base::DeviceType device_type_ = base::DeviceType::DeviceUnknown;
     std::shared_ptr<kernel::CudaConfig> cuda_config_;
     std::unique_ptr<parallel::Communicator> communicator_;
+
+public:
+    const parallel::Communicator* communicator() const { return communicator_.get(); }
+
+protected:
     std::map<ModelBufferType, tensor::Tensor> buffers_;
 };
 

@@ -28,8 +28,16 @@ public:
     static base::Status make_unique_id(void* out);
 
     base::Status init(const void* unique_id, int32_t rank, int32_t world_size);
-    // in-place sum over all ranks of `count` fp32 values, enqueued on `stream`
+    // Optional: exchange buffers for the one-shot all-reduce of small rows (<= max_count floats) over peer memory.
+    // Each rank allocates its buffer, the CUDA IPC handles travel through an NCCL all-gather, and every rank maps
+    // its peers' buffers.  If any rank cannot, all ranks keep using NCCL (the outcome is agreed with an all-reduce).
+    base::Status enable_one_shot(size_t max_count);
+    bool one_shot_enabled() const { return one_shot_; }
+    // in-place sum over all ranks of `count` fp32 values, enqueued on `stream`; rows that fit the one-shot
+    // exchange go through it, everything else through ncclAllReduce
     base::Status all_reduce_sum(float* data, size_t count, cudaStream_t stream) const;
+    // synchronous health check of the one-shot path: error if a bounded wait on a peer ever ran out
+    base::Status one_shot_status() const;
 
     int32_t rank() const { return rank_; }
     int32_t world_size() const { return world_size_; }
@@ -39,6 +47,12 @@ private:
     void* comm_ = nullptr;  // ncclComm_t
     int32_t rank_ = 0;
     int32_t world_size_ = 1;
+    // one-shot exchange
+    bool one_shot_ = false;
+    size_t one_shot_max_count_ = 0;
+    void* exchange_ = nullptr;          // this rank's exchange buffer (cudaMalloc)
+    uint32_t* state_ = nullptr;         // sequence number + error word
+    void* rank_buffers_[8] = {};        // every rank's exchange buffer as mapped here
 };
 
 }  // namespace parallel

@@ -84,6 +84,18 @@ int kuiper_model_init_tp(kuiper_model* model, const void* unique_id128) {
     return done(as_model(model)->init_tensor_parallel(unique_id128));
 }
 
+int kuiper_model_tp_one_shot(kuiper_model* model) {
+    if (!model) return 0;
+    const parallel::Communicator* c = as_model(model)->communicator();
+    return c && c->one_shot_enabled() ? 1 : 0;
+}
+
+int kuiper_model_tp_status(kuiper_model* model) {
+    if (!model) return fail(base::error::invalid_argument("null model"));
+    const parallel::Communicator* c = as_model(model)->communicator();
+    return done(c ? c->one_shot_status() : base::error::success());
+}
+
 int kuiper_model_predict(kuiper_model* model, const int32_t* tokens, const int32_t* pos, const int32_t* slot, int M,
                          int32_t* next, float* logits) {
     if (!model) return fail(base::error::invalid_argument("null model"));

@@ -1,6 +1,8 @@
 // Model base: buffer table and tensor-parallel set-up.
 #include "model/model.h"
 
+#include <cstdlib>
+
 namespace model {
 
 Model::Model(base::ModelType model_type, const ModelConfig& config) : model_type_(model_type), config_(config) {}
@@ -35,6 +37,13 @@ base::Status Model::init_tensor_parallel(const void* unique_id) {
         return st;
     }
     cuda_config_->set_communicator(communicator_.get());
+    // decode rows (up to 8 of them) can be summed by the one-shot exchange over peer memory: KUIPER_TP_ONESHOT=1
+    // switches it on, otherwise everything goes through ncclAllReduce
+    const char* env = std::getenv("KUIPER_TP_ONESHOT");
+    if (env && env[0] == '1') {
+        const int32_t rows = config_.max_batch < 8 ? config_.max_batch : 8;
+        st = communicator_->enable_one_shot(size_t(rows) * size_t(config_.dim));
+    }
     return st;
 }
 

@@ -5,6 +5,10 @@
 
 #include <cstring>
 #include <mutex>
+#include <vector>
+
+#include "base/log.h"
+#include "kuiper_b200.h"
 
 namespace parallel {
 namespace {
@@ -18,6 +22,7 @@ struct NcclApi {
     int (*GetUniqueId)(void* id) = nullptr;
     int (*CommInitRank)(void** comm, int nranks, IdByValue id, int rank) = nullptr;
     int (*AllReduce)(const void* send, void* recv, size_t count, int dtype, int op, void* comm, cudaStream_t s) = nullptr;
+    int (*AllGather)(const void* send, void* recv, size_t sendcount, int dtype, void* comm, cudaStream_t s) = nullptr;
     int (*CommDestroy)(void* comm) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
     bool ok = false;
@@ -25,6 +30,8 @@ struct NcclApi {
 
 constexpr int kNcclFloat32 = 7;  // ncclFloat32 in nccl.h
 constexpr int kNcclSum = 0;      // ncclSum
+constexpr int kNcclMin = 3;      // ncclMin
+constexpr int kNcclInt8 = 0;     // ncclInt8 / ncclChar
 
 NcclApi& api() {
     static NcclApi a;
@@ -36,6 +43,7 @@ NcclApi& api() {
         a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
         a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
         a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(h, "ncclAllReduce"));
+        a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
         a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
         a.GetErrorString = reinterpret_cast<decltype(a.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
         a.ok = a.GetUniqueId && a.CommInitRank && a.AllReduce && a.CommDestroy && a.GetErrorString;
@@ -51,6 +59,10 @@ base::Status nccl_status(int rc, const char* what) {
 }  // namespace
 
 Communicator::~Communicator() {
+    for (int r = 0; r < world_size_ && r < 8; r++)
+        if (rank_buffers_[r] && r != rank_) cudaIpcCloseMemHandle(rank_buffers_[r]);
+    if (exchange_) cudaFree(exchange_);
+    if (state_) cudaFree(state_);
     if (comm_ && api().ok) api().CommDestroy(comm_);
 }
 
@@ -76,8 +88,73 @@ base::Status Communicator::init(const void* unique_id, int32_t rank, int32_t wor
     return st;
 }
 
+base::Status Communicator::enable_one_shot(size_t max_count) {
+    if (!comm_) return base::error::internal_error("communicator is not initialised");
+    if (one_shot_) return base::error::success();
+    if (world_size_ > 8 || !api().AllGather) return base::error::success();  // stays on NCCL
+    max_count = (max_count + 31) / 32 * 32;
+    const size_t bytes = kuiper_allreduce_buffer_bytes(world_size_, int64_t(max_count));
+    // every step below is attempted on every rank; `good` is agreed at the end so that all ranks take the same path
+    float good = 1.f;
+    cudaIpcMemHandle_t mine;
+    std::memset(&mine, 0, sizeof(mine));
+    char* d_handles = nullptr;
+    if (bytes == 0 || cudaMalloc(&exchange_, bytes) != cudaSuccess || cudaMemset(exchange_, 0, bytes) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&state_), 2 * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(state_, 0, 2 * sizeof(uint32_t)) != cudaSuccess || cudaIpcGetMemHandle(&mine, exchange_) != cudaSuccess)
+        good = 0.f;
+    const size_t hb = sizeof(cudaIpcMemHandle_t);
+    std::vector<cudaIpcMemHandle_t> all(static_cast<size_t>(world_size_));
+    if (cudaMalloc(reinterpret_cast<void**>(&d_handles), hb * size_t(world_size_ + 1)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return base::error::internal_error("cannot allocate the handle exchange buffer");
+    }
+    cudaMemcpy(d_handles + hb * size_t(world_size_), &mine, hb, cudaMemcpyHostToDevice);
+    base::Status st = nccl_status(api().AllGather(d_handles + hb * size_t(world_size_), d_handles, hb, kNcclInt8, comm_, nullptr),
+                                  "ncclAllGather");
+    if (st) {
+        cudaDeviceSynchronize();
+        cudaMemcpy(all.data(), d_handles, hb * size_t(world_size_), cudaMemcpyDeviceToHost);
+        for (int r = 0; r < world_size_ && good > 0.f; r++) {
+            if (r == rank_) {
+                rank_buffers_[r] = exchange_;
+            } else if (cudaIpcOpenMemHandle(&rank_buffers_[r], all[size_t(r)], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                rank_buffers_[r] = nullptr;
+                good = 0.f;
+            }
+        }
+        (void)cudaGetLastError();
+        // agree: one rank without peer mappings keeps everybody on NCCL
+        float* d_good = reinterpret_cast<float*>(d_handles);
+        cudaMemcpy(d_good, &good, sizeof(float), cudaMemcpyHostToDevice);
+        st = nccl_status(api().AllReduce(d_good, d_good, 1, kNcclFloat32, kNcclMin, comm_, nullptr), "ncclAllReduce");
+        if (st) {
+            cudaDeviceSynchronize();
+            cudaMemcpy(&good, d_good, sizeof(float), cudaMemcpyDeviceToHost);
+        }
+    }
+    cudaFree(d_handles);
+    if (!st) return st;
+    one_shot_ = good > 0.f;
+    one_shot_max_count_ = max_count;
+    if (!one_shot_) LOG(WARNING) << "one-shot all-reduce unavailable (no peer mapping on some rank): using NCCL";
+    return base::error::success();
+}
+
+base::Status Communicator::one_shot_status() const {
+    if (!one_shot_) return base::error::success();
+    if (kuiper_allreduce_status(state_) != 0) return base::error::internal_error(kuiper_last_error());
+    return base::error::success();
+}
+
 base::Status Communicator::all_reduce_sum(float* data, size_t count, cudaStream_t stream) const {
     if (!comm_) return base::error::internal_error("communicator is not initialised");
+    if (one_shot_ && count <= one_shot_max_count_ && count % 4 == 0) {
+        if (kuiper_allreduce_oneshot_f32(data, int64_t(count), rank_, world_size_, rank_buffers_, int64_t(one_shot_max_count_),
+                                         state_, reinterpret_cast<kuiper_stream_t>(stream)) != 0)
+            return base::error::internal_error(kuiper_last_error());
+        return base::error::success();
+    }
     return nccl_status(api().AllReduce(data, data, count, kNcclFloat32, kNcclSum, comm_, stream), "ncclAllReduce");
 }
 

@@ -88,6 +88,14 @@ class Qwen3Engine:
     def init_tp(self, unique_id: bytes) -> None:
         check_host(host().kuiper_model_init_tp(self._h, C.c_char_p(unique_id)))
 
+    def tp_one_shot(self) -> bool:
+        """True if decode rows are all-reduced by the one-shot exchange over peer memory (else NCCL)."""
+        return bool(host().kuiper_model_tp_one_shot(self._h))
+
+    def tp_status(self) -> None:
+        """Raises if a bounded wait of the one-shot all-reduce ever ran out."""
+        check_host(host().kuiper_model_tp_status(self._h))
+
     # ---- passes
     def predict(self, tokens, pos, slot=None, want_logits=False):
         tokens, pos = _i32(tokens), _i32(pos)

@@ -266,6 +266,52 @@ def test_awq_gemm_rejects_bad_arguments(cuda):
     assert e.value.code == 7
 
 
+# ----------------------------------------------------------------------------- one-shot all-reduce (single-GPU checks)
+def test_allreduce_oneshot_two_ranks_emulated_on_one_gpu(cuda, oracle):
+    # Both "ranks" live on this GPU and their kernels are issued one after the other on one stream, so the first one
+    # cannot see the second one's flag: pre-load rank 1's slot and flag by hand instead, then run rank 0 only.
+    rng = np.random.default_rng(41)
+    world, count, max_count = 2, 4096, 8192
+    bufs = [cuda.allreduce_buffer(world, max_count) for _ in range(world)]
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    a = rng.standard_normal(count).astype(np.float32)
+    b = rng.standard_normal(count).astype(np.float32)
+    # sequence number 1 -> parity 1; slot (parity 1, src 1) of rank 0's buffer, flag (parity 1, src 1)
+    slot = (1 * world + 1) * max_count
+    bufs[0].view(torch.float32)[slot:slot + count] = dev(b)
+    flags = bufs[0][2 * world * max_count * 4:].view(torch.int32)
+    flags[(1 * world + 1) * 32] = 1
+    data = dev(a)
+    cuda.allreduce_oneshot(data, 0, world, bufs, max_count, state)
+    torch.cuda.synchronize()
+    assert np.array_equal(data.cpu().numpy(), a + b)  # rank order: a first, then b
+    assert state.cpu().tolist() == [1, 0]
+    # rank 0 also delivered its row and flag to "rank 1"
+    assert np.array_equal(bufs[1].view(torch.float32)[(1 * world + 0) * max_count:(1 * world + 0) * max_count + count].cpu().numpy(), a)
+    cuda.allreduce_status(state)
+
+
+def test_allreduce_oneshot_wait_is_bounded(cuda):
+    # a peer that never raises its flag: the kernel gives up after the time limit, reports which rank, and the
+    # context stays usable
+    from mykuiperllama_b200._lib import KuiperError
+    world, count, max_count = 2, 1024, 1024
+    bufs = [cuda.allreduce_buffer(world, max_count) for _ in range(world)]
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    data = torch.ones(count, device="cuda")
+    cuda.set_tuning("allreduce_timeout_ms", 50)
+    try:
+        cuda.allreduce_oneshot(data, 0, world, bufs, max_count, state)
+        torch.cuda.synchronize()
+    finally:
+        cuda.set_tuning("allreduce_timeout_ms", 1000)
+    with pytest.raises(KuiperError) as e:
+        cuda.allreduce_status(state)
+    assert e.value.code == 5 and "rank 1" in str(e.value)
+    assert state.cpu().tolist()[0] == 1  # the sequence number still advanced
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
+
+
 # ----------------------------------------------------------------------------- BF16 GEMV
 @pytest.mark.parametrize("M,K,N", [(1, 1024, 5000), (1, 2560, 1001), (3, 4096, 2048), (4, 1024, 777), (7, 520, 64)])
 def test_bf16_gemv(cuda, oracle, M, K, N):

@@ -46,8 +46,9 @@ def main():
         got = int(eng.decode_read(1)[0])
         assert got == nx[0], (rank, i, got, nx[0])
         tok = got
+    eng.tp_status()
     dist.barrier()
-    sys.stdout.write("tp-rank%d-ok\n" % rank)
+    sys.stdout.write("tp-rank%d-ok one-shot=%d\n" % (rank, int(eng.tp_one_shot())))
     eng.close()
     dist.destroy_process_group()
 
