@@ -311,6 +311,9 @@ base::Status Qwen3Model::load_layer(int32_t layer, const RawLayerWeights& w, boo
     RETURN_IF_ERROR(copy_rows(*L.o, w.o_qw, w.o_qz, w.o_s, H, r * Hq * D, Hq * D));
     RETURN_IF_ERROR(copy_rows(*L.down, w.down_qw, w.down_qz, w.down_s, H, r * I, I));
     (void)tp;
+    // device-to-device copies may return before they are done, and the engine's stream does not wait for the
+    // default stream they ran on
+    if (on_device) CUDA_OK(cudaDeviceSynchronize());
     layer_loaded_[size_t(layer)] = true;
     return base::error::success();
 }
@@ -322,6 +325,7 @@ base::Status Qwen3Model::load_globals(const void* embed, const void* final_norm,
     CUDA_OK(cudaMemcpy(embedding_->get_weight(0).ptr<void>(), embed, table, kind));
     CUDA_OK(cudaMemcpy(final_norm_->get_weight(0).ptr<void>(), final_norm, size_t(config_.dim) * 2, kind));
     CUDA_OK(cudaMemcpy(lm_head_->get_weight(0).ptr<void>(), lm_head, table, kind));
+    if (on_device) CUDA_OK(cudaDeviceSynchronize());
     globals_loaded_ = true;
     return base::error::success();
 }
