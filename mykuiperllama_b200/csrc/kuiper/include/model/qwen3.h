@@ -91,6 +91,10 @@ private:
     // pinned staging for the host <-> device token traffic
     int32_t* host_stage_ = nullptr;
     std::map<int32_t, cudaGraphExec_t> graphs_;  // decode graph per batch size
+    // the same step captured kGraphUnroll times in one graph: a run of decode steps then pays the gap between two
+    // graph launches once per kGraphUnroll tokens
+    std::map<int32_t, cudaGraphExec_t> graphs_unrolled_;
+    static constexpr int32_t kGraphUnroll = 4;
     int32_t decode_batch_ = 0;
     int32_t kernels_per_step_ = 0;
     int32_t logit_rows_ = 0;  // rows (counted from the end of a pass) that get logits and a sampled id

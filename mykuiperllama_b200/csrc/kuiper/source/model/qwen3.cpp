@@ -61,6 +61,7 @@ Qwen3Model::Qwen3Model(const ModelConfig& config) : Model(base::ModelType::Model
 Qwen3Model::~Qwen3Model() {
     if (cuda_config_ && cuda_config_->stream()) cudaStreamSynchronize(cuda_config_->stream());
     for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second);
+    for (auto& kv : graphs_unrolled_) cudaGraphExecDestroy(kv.second);
     if (host_stage_) cudaFreeHost(host_stage_);
 }
 
@@ -521,38 +522,50 @@ base::Status Qwen3Model::ensure_graph(int32_t B) {
     RETURN_IF_ERROR(run_pass(B, true));
     CUDA_OK(cudaStreamSynchronize(s));
 
-    cudaGraph_t graph = nullptr;
-    CUDA_OK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-    base::Status st = run_pass(B, true);
-    if (st) {
-        const int rc = kuiper_decode_advance(get_buffer(ModelBufferType::InputTokens).ptr<int32_t>(),
-                                             get_buffer(ModelBufferType::NextTokens).ptr<int32_t>(),
-                                             get_buffer(ModelBufferType::InputPos).ptr<int32_t>(),
-                                             get_buffer(ModelBufferType::SeqLen).ptr<int32_t>(), B, config_.max_seq_len,
-                                             reinterpret_cast<kuiper_stream_t>(s));
-        if (rc != 0) st = base::error::internal_error(kuiper_last_error());
-    }
-    cudaError_t end = cudaStreamEndCapture(s, &graph);
-    if (!st) {
-        if (graph) cudaGraphDestroy(graph);
-        return st;
-    }
-    CUDA_OK(end);
-    size_t n_nodes = 0;
-    CUDA_OK(cudaGraphGetNodes(graph, nullptr, &n_nodes));
-    std::vector<cudaGraphNode_t> nodes(n_nodes);
-    CUDA_OK(cudaGraphGetNodes(graph, nodes.data(), &n_nodes));
-    int32_t kernels = 0;
-    for (cudaGraphNode_t node : nodes) {
-        cudaGraphNodeType type;
-        if (cudaGraphNodeGetType(node, &type) == cudaSuccess && type == cudaGraphNodeTypeKernel) kernels++;
-    }
-    kernels_per_step_ = kernels;
-    cudaGraphExec_t exec = nullptr;
-    cudaError_t inst = cudaGraphInstantiate(&exec, graph, 0);
-    cudaGraphDestroy(graph);
-    CUDA_OK(inst);
-    graphs_[B] = exec;
+    // capture `steps` consecutive decode steps (pass + advance) into one executable graph
+    auto capture = [&](int32_t steps, cudaGraphExec_t* out, int32_t* kernel_nodes) -> base::Status {
+        cudaGraph_t graph = nullptr;
+        CUDA_OK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        base::Status st = base::error::success();
+        for (int32_t i = 0; i < steps && st; i++) {
+            st = run_pass(B, true);
+            if (st) {
+                const int rc = kuiper_decode_advance(get_buffer(ModelBufferType::InputTokens).ptr<int32_t>(),
+                                                     get_buffer(ModelBufferType::NextTokens).ptr<int32_t>(),
+                                                     get_buffer(ModelBufferType::InputPos).ptr<int32_t>(),
+                                                     get_buffer(ModelBufferType::SeqLen).ptr<int32_t>(), B,
+                                                     config_.max_seq_len, reinterpret_cast<kuiper_stream_t>(s));
+                if (rc != 0) st = base::error::internal_error(kuiper_last_error());
+            }
+        }
+        cudaError_t end = cudaStreamEndCapture(s, &graph);
+        if (!st) {
+            if (graph) cudaGraphDestroy(graph);
+            return st;
+        }
+        CUDA_OK(end);
+        if (kernel_nodes) {
+            size_t n_nodes = 0;
+            CUDA_OK(cudaGraphGetNodes(graph, nullptr, &n_nodes));
+            std::vector<cudaGraphNode_t> nodes(n_nodes);
+            CUDA_OK(cudaGraphGetNodes(graph, nodes.data(), &n_nodes));
+            int32_t kernels = 0;
+            for (cudaGraphNode_t node : nodes) {
+                cudaGraphNodeType type;
+                if (cudaGraphNodeGetType(node, &type) == cudaSuccess && type == cudaGraphNodeTypeKernel) kernels++;
+            }
+            *kernel_nodes = kernels;
+        }
+        cudaError_t inst = cudaGraphInstantiate(out, graph, 0);
+        cudaGraphDestroy(graph);
+        CUDA_OK(inst);
+        return base::error::success();
+    };
+    cudaGraphExec_t single = nullptr, unrolled = nullptr;
+    RETURN_IF_ERROR(capture(1, &single, &kernels_per_step_));
+    graphs_[B] = single;
+    RETURN_IF_ERROR(capture(kGraphUnroll, &unrolled, nullptr));
+    graphs_unrolled_[B] = unrolled;
     return base::error::success();
 }
 
@@ -568,8 +581,10 @@ base::Status Qwen3Model::decode_begin(const int32_t* tokens, const int32_t* pos,
 
 base::Status Qwen3Model::decode_step(int32_t n_steps) {
     if (decode_batch_ <= 0) return base::error::internal_error("decode_begin() has not been called");
-    cudaGraphExec_t exec = graphs_[decode_batch_];
-    for (int32_t i = 0; i < n_steps; i++) CUDA_OK(cudaGraphLaunch(exec, stream()));
+    cudaGraphExec_t exec = graphs_[decode_batch_], exec_unrolled = graphs_unrolled_[decode_batch_];
+    int32_t i = 0;
+    for (; i + kGraphUnroll <= n_steps; i += kGraphUnroll) CUDA_OK(cudaGraphLaunch(exec_unrolled, stream()));
+    for (; i < n_steps; i++) CUDA_OK(cudaGraphLaunch(exec, stream()));
     return base::error::success();
 }
 
