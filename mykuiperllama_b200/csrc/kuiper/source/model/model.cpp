@@ -37,10 +37,10 @@ base::Status Model::init_tensor_parallel(const void* unique_id) {
         return st;
     }
     cuda_config_->set_communicator(communicator_.get());
-    // decode rows (up to 8 of them) can be summed by the one-shot exchange over peer memory: KUIPER_TP_ONESHOT=1
-    // switches it on, otherwise everything goes through ncclAllReduce
+    // decode rows (up to 8 of them) are summed by the one-shot exchange over peer memory (it falls back to NCCL
+    // by agreement of all ranks when peer mapping is unavailable); KUIPER_TP_ONESHOT=0 keeps everything on ncclAllReduce
     const char* env = std::getenv("KUIPER_TP_ONESHOT");
-    if (env && env[0] == '1') {
+    if (!(env && env[0] == '0')) {
         const int32_t rows = config_.max_batch < 8 ? config_.max_batch : 8;
         st = communicator_->enable_one_shot(size_t(rows) * size_t(config_.dim));
     }
