@@ -435,6 +435,9 @@ def run_gemv_micro(args):
         args.gemv_impl = 2
     if args.gemv_impl in (0, 1):
         capi.set_tuning("gemv_impl", args.gemv_impl)
+    if args.gemv_impl == 4:  # the fp16 mma.sync kernel (used for 2..4 token rows) on one row, accumulate mode
+        capi.set_tuning("gemv_int8", 0)
+        args.gemv_impl = 2
     if args.gemv_impl == 3:  # the first-generation persistent kernel (SIMT products), accumulate mode
         capi.set_tuning("gemv_impl", 2)
         args.gemv_impl = 2
@@ -617,13 +620,20 @@ def main():
     ap.add_argument("--gemm-impl", type=int, default=2, help="2 pipelined 128x256 kernel (default), 1 first-generation kernel")
     ap.add_argument("--mats", type=int, default=0, help="distinct weight matrices in the gemv microbenchmark (0 = 512 MiB worth)")
     ap.add_argument("--gemv-impl", type=int, default=None, help="2 accumulate mode of the tensor-core GEMV (engine path, default), 0 its ordered combine, "
-                         "1 register-staged kernel, 3 first-generation persistent SIMT kernel (accumulate)")
+                         "1 register-staged kernel, 3 first-generation persistent SIMT kernel (accumulate), 4 fp16 mma.sync kernel (accumulate)")
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (config 4 of the workload list uses 16)")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for a profiler run with profile-from-start off)")
     ap.add_argument("--prompt", type=int, default=None, help="override the workload's prompt length (profiling aid)")
+    ap.add_argument("--tuning", action="append", default=[], metavar="KEY=VALUE",
+                    help="kernel tuning switch applied before the run (profiling aid), e.g. gemv_int8=0")
     args = ap.parse_args()
+    if args.tuning and args.impl == "engine":
+        from mykuiperllama_b200 import capi
+        for kv in args.tuning:
+            key, _, value = kv.partition("=")
+            capi.set_tuning(key, int(value))
     if args.warmup < 3 and args.impl == "engine":
         args.warmup = 3
     if args.workload == "gemv":

@@ -114,6 +114,37 @@ KUIPER_API int kuiper_swiglu_awq_gemv_accum_f32(const float* gate_up, const int3
                                                 kuiper_stream_t stream);
 /* health check (synchronises): 5 if a bounded wait inside the pipelined GEMV ever ran out on this device */
 KUIPER_API int kuiper_awq_gemv_status(void);
+/*
+ * A chain of one-row accumulate-mode projections in ONE launch (no counterpart in the reference, whose decode
+ * step launches each projection by itself): y_i += op_i(x_i) . W_i for i = 0 .. n_ops-1 in order, where x_{i+1}
+ * may be any buffer projection i (or an earlier one) accumulated into - all CTAs meet at a grid barrier between
+ * two projections while the weight stream of the next one is already running.  op_i: identity, RMSNorm(x; norm_w,
+ * eps) when norm_w is not null, or SwiGLU of a gate|up row [2K] when swiglu != 0.  Every y_i must hold its addend.
+ * `sync`: kuiper_awq_gemv_chain_sync_bytes() bytes of device memory, zeroed once by the caller; every launch
+ * leaves them at zero.  Waits are bounded; kuiper_awq_gemv_status() reports a wait that ran out.
+ */
+typedef struct kuiper_gemv_chain_op {
+    const float* x;          /* [K], or [2K] with swiglu */
+    const int32_t* qweight;  /* [K, N/8] */
+    const int32_t* qzeros;   /* [K/128, N/8] */
+    const uint16_t* scales;  /* fp16 [K/128, N] */
+    float* y;                /* [N] */
+    const uint16_t* norm_w;  /* bf16 [K] or NULL */
+    float eps;
+    int32_t swiglu;
+    int32_t K, N;
+} kuiper_gemv_chain_op;
+KUIPER_API size_t kuiper_awq_gemv_chain_sync_bytes(void);
+KUIPER_API int kuiper_awq_gemv_chain_f32(const kuiper_gemv_chain_op* ops, int n_ops, int group, void* sync,
+                                         kuiper_stream_t stream);
+
+/* Pipeline trace of the one-row GEMV (no counterpart in the reference).  After kuiper_set_tuning("gemv_trace", 1)
+ * every accumulate-mode one-row launch (single or chained) records, per CTA, 24 clock readings: [0] global timer (ns)
+ * at kernel entry, then SM clock cycles at [1] entry and, for projection i of the launch, [2+4i] operand may be
+ * read (dependency wait or grid barrier passed), [3+4i] first weight unit ready, [4+4i] last weight unit ready,
+ * [5+4i] sums issued, [18+i] first activation fragments written.  Copies up to max_values readings ([CTA][24]) of
+ * the last such launch to the host array `out` (synchronises); returns how many, or -1. */
+KUIPER_API int kuiper_gemv_trace_read(int64_t* out, int max_values);
 
 /*
  * The INT4 GEMV once more, for callers that must not allocate: no counterpart in the reference (its

@@ -571,6 +571,19 @@ extern "C" int kuiper_swiglu_awq_gemv_accum_f32(const float* gate_up, const int3
     return awq_gemv_accum_common(gate_up, nullptr, 0.f, true, qweight, qzeros, scales, y, M, K, N, group, stream);
 }
 
+namespace kuiper {
+int awq_gemv_trace_read(long long* out, int max_values);
+}
+extern "C" int kuiper_gemv_trace_read(int64_t* out, int max_values) {
+    KUIPER_REQUIRE(out != nullptr && max_values > 0, "gemv_trace_read: empty destination");
+    const int n = kuiper::awq_gemv_trace_read(reinterpret_cast<long long*>(out), max_values);
+    if (n < 0) {
+        set_error("gemv_trace_read: cannot read the trace buffer");
+        return -1;
+    }
+    return n;
+}
+
 extern "C" int kuiper_awq_gemv_status(void) {
     int v = awq_gemv_tma_status();
     if (v == 0) v = awq_gemv_mma_status();

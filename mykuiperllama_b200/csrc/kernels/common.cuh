@@ -100,6 +100,11 @@ __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
 // Programmatic dependent launch: let the next grid start its prologue, and wait for
 // the previous grid's writes before touching anything it produced.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 }  // namespace kuiper

@@ -260,3 +260,11 @@ def test_tensor_parallel_sharding_two_gloo_ranks(tmp_path, oracle):
                          capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     assert "rank0-ok" in res.stdout and "rank1-ok" in res.stdout
+
+
+def test_python_front_ends_import_without_a_gpu():
+    # the torch-tensor front end of the kernel ABI and the engine wrapper are importable on a CPU-only host
+    # (they only fail, loudly, when a kernel is called)
+    import importlib
+    for name in ("mykuiperllama_b200.capi", "mykuiperllama_b200.engine"):
+        importlib.import_module(name)

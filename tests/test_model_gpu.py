@@ -66,7 +66,11 @@ def test_tiny_model_logits_and_tokens(oracle, engine_mod, act_mode):
     assert rel_err(lg_again, lg_plain) <= 1e-2
 
 
-def test_prefill_and_graph_decode_match_oracle_greedy(oracle, engine_mod):
+@pytest.mark.parametrize("chained", ["0", "1"])
+def test_prefill_and_graph_decode_match_oracle_greedy(oracle, engine_mod, monkeypatch, chained):
+    # chained = "1": O, gate|up, down and the next layer's QKV of the decode step run as one launch per layer
+    # (integer tensor-core kernel with grid barriers); the switch is read when the model is created
+    monkeypatch.setenv("KUIPER_CHAIN_DECODE", chained)
     ref, eng, _ = _pair(oracle, engine_mod, TINY, seed=3)
     rng = np.random.default_rng(4)
     prompt = rng.integers(0, 1000, 19).astype(np.int32)  # 19 = two full chunks of 8 + a ragged one
@@ -87,6 +91,9 @@ def test_prefill_and_graph_decode_match_oracle_greedy(oracle, engine_mod):
         got.append(int(eng.decode_read(1)[0]))
     assert got == want
     assert eng.kernels_per_step > 0
+    if chained == "1":
+        # embedding, first QKV, per layer attention + chain, final norm, lm_head, argmax, advance
+        assert eng.kernels_per_step == 2 + 2 * TINY["n_layers"] + 4
 
 
 def test_decode_predict_end_to_end_path(oracle, engine_mod):
