@@ -238,6 +238,9 @@ KUIPER_API int kuiper_qknorm_rope_kvwrite(float* qkv, const uint16_t* q_norm_w, 
  * seq_len[m] - F were final before the previous kernel on the stream started (that kernel appended
  * at most the newest F rows of a sequence and produced q).  The kernel then fetches those rows
  * under programmatic dependent launch while the previous kernel is still finishing.
+ * Two kernels sit behind the call: by default the contractions run on the tensor cores (mma.sync bf16: cache
+ * rows as exact operands, q and the probabilities as bf16 high + low parts; agrees with the fp32 oracle to
+ * ~1e-5; fresh_rows is accepted and ignored), kuiper_set_tuning("flash_mma", 0) selects the SIMT kernel.
  */
 KUIPER_API size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq);
 KUIPER_API int kuiper_flash_decode(const float* q, const uint16_t* kcache, const uint16_t* vcache,
@@ -252,7 +255,9 @@ KUIPER_API int kuiper_flash_decode(const float* q, const uint16_t* kcache, const
  * row to the caches and uses it.  With clear_input != 0 the last CTA of a (row, kv head) zeroes the
  * slices of qkv it read; clear_extra / clear_extra_count as in kuiper_qknorm_rope_kvwrite.  fresh_rows
  * as in kuiper_flash_decode (the newest row is never fetched early: it does not exist yet).
- * Results are bit-identical to kuiper_qknorm_rope_kvwrite followed by kuiper_flash_decode.
+ * Results are bit-identical to kuiper_qknorm_rope_kvwrite followed by kuiper_flash_decode with its SIMT kernel
+ * (kuiper_set_tuning("flash_mma", 0); by default kuiper_flash_decode runs its contractions on the tensor cores,
+ * which agrees to ~1e-5).
  */
 KUIPER_API int kuiper_rope_flash_decode(float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
                                         const float* cos_t, const float* sin_t, const int32_t* pos,

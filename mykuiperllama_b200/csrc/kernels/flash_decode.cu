@@ -26,6 +26,7 @@ constexpr int kRowsPerStep = 8;  // row slots per half warp per step
 
 int g_force_splits = 0;
 int g_flash_early = 1;  // 0: ignore fresh_rows, touch nothing before the dependent-launch wait
+int g_flash_mma = 1;    // the stand-alone attention call runs its contractions on the tensor cores (0: SIMT kernel)
 
 struct FlashParams {
     const float* q;       // [M, Nq, 128]
@@ -438,6 +439,285 @@ flash_decode_kernel(const FlashParams p) {
     clear_raw();
 }
 
+// ---------------------------------------------------------------- the same attention on the tensor cores
+//
+// For long caches the kernel above is bound by instruction issue (~2 000 SIMT instructions per 16 cache rows and
+// kv head), not by the memory system.  This variant keeps its grid, slices, workspace and combine, and moves the
+// two contractions of a 16-row step to mma.sync.m16n8k16 (bf16 x bf16 -> fp32), transposed so that the cache rows
+// fill the 16-wide dimension and the (up to 8) query heads of the kv head the 8-wide one:
+//
+//   S^T[row][head] = K[row][dim] . Q^T[dim][head]      A = K as it lies in the cache (row-major), B = q
+//   O^T[dim][head] += V^T[dim][row] . P^T[row][head]   A = V^T and B = P^T by movmatrix (8x8 transposes in registers)
+//
+// K and V are bf16 in the cache, so they are exact operands; q and the probabilities are split into a bf16 high and
+// low part (two mma each), which keeps 16 significant bits.  A lane loads 16 contiguous bytes of a row as in the
+// kernel above; which head dimension sits at which contraction / fragment index is a fixed permutation that q's
+// fragments and the final store follow.
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+// (x, y) as bf16 high parts in one register (x in the low half) and what is left of them as bf16 low parts
+__device__ __forceinline__ void split_bf16x2(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const uint32_t xh = float_to_bf16_bits(x), yh = float_to_bf16_bits(y);
+    hi = xh | (yh << 16);
+    const float xr = x - bf16_bits_to_float(uint16_t(xh)), yr = y - bf16_bits_to_float(uint16_t(yh));
+    lo = uint32_t(float_to_bf16_bits(xr)) | (uint32_t(float_to_bf16_bits(yr)) << 16);
+}
+
+template <int R>
+__global__ void __launch_bounds__(kWarps * 32)
+flash_decode_mma_kernel(const FlashParams p) {
+    __shared__ float s_o[kWarps][R][kD];
+    __shared__ float s_ml[kWarps][R][2];
+    __shared__ int s_last;
+
+    const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;  // fragment row / column group and thread in group
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    int L = __ldcg(p.seq_len + m), sl = __ldcg(p.slot + m);
+    L = L < 0 ? 0 : (L > p.max_seq ? p.max_seq : L);
+    sl = sl < 0 ? 0 : (sl >= p.n_slots ? p.n_slots - 1 : sl);
+    const int blocks = max((L + 63) / 64, 1);
+    const int per = (blocks + p.S - 1) / p.S;
+    const int n_active = (blocks + per - 1) / per;
+    if (split >= n_active) return;
+    const int begin = split * per * 64;
+    const int end = min(L, begin + per * 64);
+    const size_t head_off = (size_t(sl) * p.Nkv + kvh) * p.max_seq * kD;
+    const uint16_t* kb = p.kc + head_off;
+    const uint16_t* vb = p.vc + head_off;
+
+    // q as B fragments.  Contraction step (i, h2), i = 32-dimension chunk, h2 = half of the lane's 16 bytes:
+    // index 2t, 2t+1 <-> dimensions 32 i + 8 t + 4 h2 + {0, 1}, index 2t+8, 2t+9 <-> ... + {2, 3}; column g = head g.
+    uint32_t qh[4][2][2], ql[4][2][2];
+    {
+        const float* qp = p.q + (size_t(m) * p.Nq + kvh * R + (g < R ? g : 0)) * kD;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(qp + 32 * i + 8 * t));
+            const float4 b = __ldcg(reinterpret_cast<const float4*>(qp + 32 * i + 8 * t + 4));
+            const bool live = g < R;
+            split_bf16x2(live ? a.x : 0.f, live ? a.y : 0.f, qh[i][0][0], ql[i][0][0]);
+            split_bf16x2(live ? a.z : 0.f, live ? a.w : 0.f, qh[i][0][1], ql[i][0][1]);
+            split_bf16x2(live ? b.x : 0.f, live ? b.y : 0.f, qh[i][1][0], ql[i][1][0]);
+            split_bf16x2(live ? b.z : 0.f, live ? b.w : 0.f, qh[i][1][1], ql[i][1][1]);
+        }
+    }
+
+    const float scale = 0.08838834764831845f;  // 1/sqrt(128)
+    // this lane's two heads (2t, 2t+1): running maximum, sum over its own rows (rows g and g+8 of every step)
+    float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f};
+    // O^T: block (i, jp) holds dimension rows g -> dim(i, 2jp, g) and g+8 -> dim(i, 2jp+1, g), where
+    // dim(i, j, c) = 32 i + 8 (c >> 1) + 2 j + (c & 1); columns 2t, 2t+1 = heads
+    float oacc[8][4];
+#pragma unroll
+    for (int b = 0; b < 8; b++) { oacc[b][0] = oacc[b][1] = oacc[b][2] = oacc[b][3] = 0.f; }
+
+    // warp w takes rows begin + w*16 + step*64 .. +15: fragment rows g and g+8
+    for (int base = begin + warp * 16; base < end; base += kWarps * 16) {
+        const int r0 = base + g, r1 = base + g + 8;
+        const bool ok0 = r0 < end, ok1 = r1 < end;
+        uint4 k0[4], k1[4], v0[4], v1[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            k0[i] = ok0 ? ld_stream_u4(kb + size_t(r0) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+            k1[i] = ok1 ? ld_stream_u4(kb + size_t(r1) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            v0[i] = ok0 ? ld_stream_u4(vb + size_t(r0) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+            v1[i] = ok1 ? ld_stream_u4(vb + size_t(r1) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+        }
+        // scores S^T[rows g, g+8][heads 2t, 2t+1]
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            mma_bf16(s, k0[i].x, k1[i].x, k0[i].y, k1[i].y, qh[i][0][0], qh[i][0][1]);
+            mma_bf16(s, k0[i].x, k1[i].x, k0[i].y, k1[i].y, ql[i][0][0], ql[i][0][1]);
+            mma_bf16(s, k0[i].z, k1[i].z, k0[i].w, k1[i].w, qh[i][1][0], qh[i][1][1]);
+            mma_bf16(s, k0[i].z, k1[i].z, k0[i].w, k1[i].w, ql[i][1][0], ql[i][1][1]);
+        }
+        s[0] = ok0 ? s[0] * scale : -INFINITY;
+        s[1] = ok0 ? s[1] * scale : -INFINITY;
+        s[2] = ok1 ? s[2] * scale : -INFINITY;
+        s[3] = ok1 ? s[3] * scale : -INFINITY;
+        // online softmax per head: maximum over the 16 rows of the step (the 8 lanes with this t)
+        float pr[4];
+        float corr[2];
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            float bm = fmaxf(s[e], s[2 + e]);
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
+            const float nm = fmaxf(mx[e], bm);  // base < end: the step has at least one valid row, so nm is finite
+            corr[e] = (mx[e] == -INFINITY) ? 0.f : __expf(mx[e] - nm);
+            mx[e] = nm;
+            pr[e] = (s[e] == -INFINITY) ? 0.f : __expf(s[e] - nm);
+            pr[2 + e] = (s[2 + e] == -INFINITY) ? 0.f : __expf(s[2 + e] - nm);
+            sum[e] = sum[e] * corr[e] + pr[e] + pr[2 + e];
+        }
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            oacc[b][0] *= corr[0]; oacc[b][1] *= corr[1]; oacc[b][2] *= corr[0]; oacc[b][3] *= corr[1];
+        }
+        // P^T as B fragments: (rows 2t, 2t+1 | rows 2t+8, 2t+9) of head g, by transposing the two 8x8 halves
+        uint32_t ph0, pl0, ph1, pl1;
+        split_bf16x2(pr[0], pr[1], ph0, pl0);
+        split_bf16x2(pr[2], pr[3], ph1, pl1);
+        const uint32_t bh0 = movmatrix_trans(ph0), bh1 = movmatrix_trans(ph1);
+        const uint32_t bl0 = movmatrix_trans(pl0), bl1 = movmatrix_trans(pl1);
+        // V^T as A fragments: the register that holds dimensions (8t + 2j, +1) of row g, transposed, holds rows
+        // (2t, 2t+1) of dimension dim(i, j, g)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            {
+                const uint32_t a0 = movmatrix_trans(v0[i].x), a1 = movmatrix_trans(v0[i].y);
+                const uint32_t a2 = movmatrix_trans(v1[i].x), a3 = movmatrix_trans(v1[i].y);
+                mma_bf16(oacc[2 * i], a0, a1, a2, a3, bh0, bh1);
+                mma_bf16(oacc[2 * i], a0, a1, a2, a3, bl0, bl1);
+            }
+            {
+                const uint32_t a0 = movmatrix_trans(v0[i].z), a1 = movmatrix_trans(v0[i].w);
+                const uint32_t a2 = movmatrix_trans(v1[i].z), a3 = movmatrix_trans(v1[i].w);
+                mma_bf16(oacc[2 * i + 1], a0, a1, a2, a3, bh0, bh1);
+                mma_bf16(oacc[2 * i + 1], a0, a1, a2, a3, bl0, bl1);
+            }
+        }
+    }
+
+    // sums over all rows of the warp: the 8 lanes with this t hold different rows
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+        sum[e] += __shfl_xor_sync(0xffffffffu, sum[e], 4);
+        sum[e] += __shfl_xor_sync(0xffffffffu, sum[e], 8);
+        sum[e] += __shfl_xor_sync(0xffffffffu, sum[e], 16);
+    }
+    // a warp without rows keeps max = -inf and zeros
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+        const int h = 2 * t + e;
+        if (h < R) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+#pragma unroll
+                for (int jp = 0; jp < 2; jp++) {
+                    const int d_lo = 32 * i + 8 * (g >> 1) + 2 * (2 * jp) + (g & 1);
+                    const int d_hi = 32 * i + 8 * (g >> 1) + 2 * (2 * jp + 1) + (g & 1);
+                    s_o[warp][h][d_lo] = oacc[2 * i + jp][e];
+                    s_o[warp][h][d_hi] = oacc[2 * i + jp][2 + e];
+                }
+            }
+            if (g == 0) { s_ml[warp][h][0] = mx[e]; s_ml[warp][h][1] = sum[e]; }
+        }
+    }
+    __syncthreads();
+
+    // merge the warps: thread t owns element t of every head
+    const int tx = threadIdx.x;
+    float fo[R], fm[R], fs[R];
+#pragma unroll
+    for (int h = 0; h < R; h++) {
+        float nm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) nm = fmaxf(nm, s_ml[w][h][0]);
+        float acc = 0.f, ssum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) {
+            const float wm = s_ml[w][h][0];
+            const float c = (wm == -INFINITY) ? 0.f : __expf(wm - nm);
+            acc += s_o[w][h][tx] * c;
+            ssum += s_ml[w][h][1] * c;
+        }
+        fo[h] = acc; fm[h] = nm; fs[h] = ssum;
+    }
+
+    if (n_active == 1) {
+#pragma unroll
+        for (int h = 0; h < R; h++)
+            p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + tx] = fs[h] > 0.f ? fo[h] / fs[h] : 0.f;
+        return;
+    }
+
+    const size_t pbase = (size_t(m) * p.Nkv + kvh) * p.S;
+#pragma unroll
+    for (int h = 0; h < R; h++) {
+        p.part_o[((pbase + split) * R + h) * kD + tx] = fo[h];
+        if (tx == 0) {
+            p.part_ml[((pbase + split) * R + h) * 2] = fm[h];
+            p.part_ml[((pbase + split) * R + h) * 2 + 1] = fs[h];
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tx == 0) {
+        const int prev = atomicAdd(p.counters + m * p.Nkv + kvh, 1);
+        s_last = (prev == n_active - 1);
+        if (s_last) p.counters[m * p.Nkv + kvh] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // ---- final combine by the last CTA.  Weights first: warp w takes heads w, w + 4, ...; lane l holds the
+    // (max, sum) of slices l and l + 32, so the maximum and the denominator are two warp reductions.
+    __shared__ float s_w[64 * R];   // weight of slice sp for head h at [sp * R + h]
+    __shared__ float s_den[R];
+    for (int h = warp; h < R; h += kWarps) {
+        float2 ml0 = make_float2(-INFINITY, 0.f), ml1 = ml0;
+        if (lane < n_active) ml0 = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((pbase + lane) * R + h) * 2));
+        if (lane + 32 < n_active) ml1 = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((pbase + lane + 32) * R + h) * 2));
+        const float nm = warp_max(fmaxf(ml0.x, ml1.x));
+        const float w0 = (ml0.x == -INFINITY) ? 0.f : __expf(ml0.x - nm);
+        const float w1 = (ml1.x == -INFINITY) ? 0.f : __expf(ml1.x - nm);
+        const float den = warp_sum(ml0.y * w0 + ml1.y * w1);
+        s_w[lane * R + h] = w0;
+        s_w[(lane + 32) * R + h] = w1;
+        if (lane == 0) s_den[h] = den;
+    }
+    __syncthreads();
+    // then the partial outputs in slice order, eight slices of every head in flight per thread
+    float acc[R];
+#pragma unroll
+    for (int h = 0; h < R; h++) acc[h] = 0.f;
+    const float* po = p.part_o + pbase * R * kD + tx;
+    int sp = 0;
+    for (; sp + 8 <= n_active; sp += 8) {
+        float a[8][R];
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+#pragma unroll
+            for (int h = 0; h < R; h++) a[q][h] = __ldcg(po + (size_t(sp + q) * R + h) * kD);
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+#pragma unroll
+            for (int h = 0; h < R; h++) acc[h] = fmaf(a[q][h], s_w[(sp + q) * R + h], acc[h]);
+    }
+    for (; sp < n_active; sp++) {
+        float a[R];
+#pragma unroll
+        for (int h = 0; h < R; h++) a[h] = __ldcg(po + (size_t(sp) * R + h) * kD);
+#pragma unroll
+        for (int h = 0; h < R; h++) acc[h] = fmaf(a[h], s_w[sp * R + h], acc[h]);
+    }
+#pragma unroll
+    for (int h = 0; h < R; h++) {
+        const float den = s_den[h];
+        p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + tx] = den > 0.f ? acc[h] / den : 0.f;
+    }
+}
+
+
 int pick_splits(int M, int Nkv, int max_seq) {
     if (g_force_splits > 0) return g_force_splits;
     const int by_len = (max_seq + 63) / 64;  // a slice is at least one 64-row step of the CTA
@@ -455,6 +735,7 @@ size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 void flash_decode_set_tuning(const char* key, int value) {
     if (!strcmp(key, "flash_splits")) g_force_splits = value;
     if (!strcmp(key, "flash_early")) g_flash_early = value;
+    if (!strcmp(key, "flash_mma")) g_flash_mma = value;
 }
 
 }  // namespace kuiper
@@ -510,6 +791,13 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
             case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<2, true>, p); break;
             case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<4, true>, p); break;
             default: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<8, true>, p); break;
+        }
+    } else if (g_flash_mma) {
+        switch (R) {
+            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<1>, p); break;
+            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<2>, p); break;
+            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<4>, p); break;
+            default: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<8>, p); break;
         }
     } else {
         switch (R) {

@@ -542,12 +542,18 @@ def test_qknorm_rope_kvwrite(cuda, oracle):
 
 
 # ----------------------------------------------------------------------------- flash decoding
+FLASH_MMA_DEFAULT = 1  # what the library starts with (kuiper_set_tuning key flash_mma)
+
+
 @pytest.mark.parametrize("B,Nq,Nkv,lens", [
     (1, 32, 8, [1024]), (2, 32, 8, [4096, 777]), (1, 16, 8, [192]), (3, 8, 8, [1, 64, 65]),
     (4, 32, 8, [0, 63, 2048, 300]), (1, 32, 8, [16384]),
 ])
 @pytest.mark.parametrize("splits", [0, 1, 7])
-def test_flash_decode(cuda, oracle, B, Nq, Nkv, lens, splits):
+@pytest.mark.parametrize("tensor_cores", [0, 1])
+def test_flash_decode(cuda, oracle, B, Nq, Nkv, lens, splits, tensor_cores):
+    # tensor_cores = 1: the contractions run on mma.sync (bf16 cache rows as exact operands, q and the
+    # probabilities as bf16 high + low parts); same grid, slices and combine
     rng = np.random.default_rng(sum(lens) + Nq + splits)
     D = 128
     max_seq = max(64, max(lens))
@@ -558,6 +564,7 @@ def test_flash_decode(cuda, oracle, B, Nq, Nkv, lens, splits):
     slot = np.arange(B, dtype=np.int32)[::-1].copy()  # rows read sequences in reverse order
     ref = oracle.attention(q, kc, vc, seq, slot)
     cuda.set_tuning("flash_splits", splits)
+    cuda.set_tuning("flash_mma", tensor_cores)
     try:
         ws = cuda.flash_decode_workspace(B, Nq, D, max_seq)
         args = (dev(q), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), dev(seq), dev(slot))
@@ -565,9 +572,11 @@ def test_flash_decode(cuda, oracle, B, Nq, Nkv, lens, splits):
         out2 = cuda.flash_decode(*args, workspace=ws).cpu().numpy()
     finally:
         cuda.set_tuning("flash_splits", 0)
+        cuda.set_tuning("flash_mma", FLASH_MMA_DEFAULT)
     assert np.array_equal(out1, out2)
     err = rel_err(out1, ref)
-    assert err <= SPEC_TOL and err <= 1e-5
+    # 16 significant bits in q and in the probabilities on the tensor-core path
+    assert err <= SPEC_TOL and err <= (5e-5 if tensor_cores else 1e-5)
 
 
 def test_flash_decode_early_fetch_matches_conservative_path(cuda, oracle):
@@ -581,11 +590,16 @@ def test_flash_decode_early_fetch_matches_conservative_path(cuda, oracle):
     seq = dev(np.array([2084, 1, 700], np.int32))
     slot = dev(np.arange(B, dtype=np.int32))
     ws = cuda.flash_decode_workspace(B, Nq, D, Lmax)
-    ref = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws)
-    for fresh in (0, 1, 3, 5000):
-        got = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws, fresh_rows=fresh)
-        torch.cuda.synchronize()
-        assert torch.equal(got, ref), fresh
+    for mma in (0, 1):  # the SIMT kernel fetches ahead of the wait, the tensor-core kernel ignores the promise
+        cuda.set_tuning("flash_mma", mma)
+        try:
+            ref = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws)
+            for fresh in (0, 1, 3, 5000):
+                got = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws, fresh_rows=fresh)
+                torch.cuda.synchronize()
+                assert torch.equal(got, ref), fresh
+        finally:
+            cuda.set_tuning("flash_mma", FLASH_MMA_DEFAULT)
 
 
 @pytest.mark.parametrize("Nq,Nkv,lens", [(32, 8, [2084, 1, 700]), (16, 8, [65, 64]), (8, 8, [130])])
@@ -606,7 +620,13 @@ def test_rope_fused_into_flash_decode_is_bit_identical(cuda, oracle, Nq, Nkv, le
     slot = dev(np.arange(B, dtype=np.int32))
     ws = cuda.flash_decode_workspace(B, Nq, D, Lmax)
     q = cuda.qknorm_rope_kvwrite(qkv.clone(), qn, kn, cos_t, sin_t, pos, slot, Nq, Nkv, D, 1e-6, kc, vc)
-    ref = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws)
+    cuda.set_tuning("flash_mma", 0)  # the fused kernel shares its arithmetic with the SIMT attention kernel
+    try:
+        ref = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws)
+    finally:
+        cuda.set_tuning("flash_mma", FLASH_MMA_DEFAULT)
+    ref_mma = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws)
+    assert rel_err(ref_mma.cpu().numpy(), ref.cpu().numpy()) <= 5e-5
     for fresh in (-1, 1):
         raw = qkv.clone()
         side = torch.ones((B, 512), device="cuda")
