@@ -471,8 +471,9 @@ __device__ __forceinline__ void split_bf16x2(float x, float y, uint32_t& hi, uin
     lo = uint32_t(float_to_bf16_bits(xr)) | (uint32_t(float_to_bf16_bits(yr)) << 16);
 }
 
+// five CTAs per SM (96 registers): the kernel is bound by memory latency, so resident warps matter more than a few spilled values
 template <int R>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, 5)
 flash_decode_mma_kernel(const FlashParams p) {
     __shared__ float s_o[kWarps][R][kD];
     __shared__ float s_ml[kWarps][R][2];
