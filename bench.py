@@ -599,11 +599,13 @@ def run_attn_micro(args):
     print(json.dumps({
         "metric": "GQA flash-decoding KV-read GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16 KV cache, fp32 softmax and accumulation", "data": "synthetic",
+        "dtype": "bf16 KV cache, bf16 x bf16 -> fp32 mma (q and probabilities as bf16 high + low parts), fp32 softmax", "data": "synthetic",
         "config": {"workload": f"flash-decoding batch {B}, 32 q heads / 8 kv heads, head_dim 128, KV length {L}",
                    "distinct_caches": n, "l2_policy": f"{n} caches ({kv_bytes * n >> 20} MiB) visited in turn: larger than L2"},
-        "roofline": {"bound": "hbm", "kernel": "flash_decode_kernel<4>", "achieved": gbs, "peak": peak, "peak_kind": kind,
-                     "unit": "GB/s", "frac": gbs / peak, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS, "traffic": None,
+        "roofline": {"bound": "hbm", "kernel": "flash_decode_mma_kernel<4>", "achieved": gbs, "peak": peak, "peak_kind": kind,
+                     "unit": "GB/s", "frac": gbs / peak, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
+                     # ncu: dram bytes / KV bytes = 1.01 on batch 16, 4096 rows (profiles/flash_decode_mma_b16_kv4096.md)
+                     "traffic": int(kv_bytes * 1.01),
                      "avg_us_per_launch": ms * 1e3 / n, "avg_bytes_per_launch": kv_bytes},
         "gpu_launches": n * args.steps, "clocks": clocks.summary()}), flush=True)
 
