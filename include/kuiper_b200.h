@@ -255,9 +255,10 @@ KUIPER_API int kuiper_flash_decode(const float* q, const uint16_t* kcache, const
  * row to the caches and uses it.  With clear_input != 0 the last CTA of a (row, kv head) zeroes the
  * slices of qkv it read; clear_extra / clear_extra_count as in kuiper_qknorm_rope_kvwrite.  fresh_rows
  * as in kuiper_flash_decode (the newest row is never fetched early: it does not exist yet).
- * Results are bit-identical to kuiper_qknorm_rope_kvwrite followed by kuiper_flash_decode with its SIMT kernel
- * (kuiper_set_tuning("flash_mma", 0); by default kuiper_flash_decode runs its contractions on the tensor cores,
- * which agrees to ~1e-5).
+ * Like kuiper_flash_decode the call runs its contractions on the tensor cores by default; with
+ * kuiper_set_tuning("flash_mma_fused", 0) it uses the SIMT arithmetic and is then bit-identical to
+ * kuiper_qknorm_rope_kvwrite followed by kuiper_flash_decode with its SIMT kernel ("flash_mma" = 0).  The two
+ * arithmetic paths agree to ~1e-5; the appended cache rows are identical.
  */
 KUIPER_API int kuiper_rope_flash_decode(float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
                                         const float* cos_t, const float* sin_t, const int32_t* pos,

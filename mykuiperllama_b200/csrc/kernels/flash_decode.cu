@@ -26,6 +26,7 @@ constexpr int kRowsPerStep = 8;  // row slots per half warp per step
 
 int g_force_splits = 0;
 int g_flash_early = 1;  // 0: ignore fresh_rows, touch nothing before the dependent-launch wait
+int g_flash_mma_fused = 1;  // the fused decode kernel (rotary + append + attention) also uses the tensor cores (0: SIMT)
 int g_flash_mma = 1;    // the stand-alone attention call runs its contractions on the tensor cores (0: SIMT kernel)
 
 struct FlashParams {
@@ -471,11 +472,13 @@ __device__ __forceinline__ void split_bf16x2(float x, float y, uint32_t& hi, uin
     lo = uint32_t(float_to_bf16_bits(xr)) | (uint32_t(float_to_bf16_bits(yr)) << 16);
 }
 
-// five CTAs per SM (96 registers): the kernel is bound by memory latency, so resident warps matter more than a few spilled values
-template <int R>
-__global__ void __launch_bounds__(kWarps * 32, 5)
+// stand-alone: five CTAs per SM (96 registers) - the kernel is bound by memory latency, so resident warps matter more
+// than a few spilled values; fused: the rows fetched ahead of the wait stay in registers across the prologue, three CTAs
+template <int R, bool FUSED>
+__global__ void __launch_bounds__(kWarps * 32, FUSED ? 3 : 5)
 flash_decode_mma_kernel(const FlashParams p) {
     __shared__ float s_o[kWarps][R][kD];
+    __shared__ float s_q[FUSED ? R : 1][kD];
     __shared__ float s_ml[kWarps][R][2];
     __shared__ int s_last;
 
@@ -484,30 +487,134 @@ flash_decode_mma_kernel(const FlashParams p) {
     const int g = lane >> 2, t = lane & 3;  // fragment row / column group and thread in group
 
     pdl_launch_dependents();
-    pdl_wait();
+    // fused: rows older than this pass are fetched ahead of the dependency wait, exactly as in the SIMT kernel
+    // (fresh_rows, re-check of seq_len / slot after the wait); the stand-alone call waits first
+    bool waited = !FUSED || p.fresh_rows < 0;
+    if (waited) pdl_wait();
 
-    int L = __ldcg(p.seq_len + m), sl = __ldcg(p.slot + m);
-    L = L < 0 ? 0 : (L > p.max_seq ? p.max_seq : L);
-    sl = sl < 0 ? 0 : (sl >= p.n_slots ? p.n_slots - 1 : sl);
-    const int blocks = max((L + 63) / 64, 1);
-    const int per = (blocks + p.S - 1) / p.S;
-    const int n_active = (blocks + per - 1) / per;
+    int L, sl, n_active, begin, end, base0, fetched_end;
+    const uint16_t *kb, *vb;
+    // first step of this warp: rows base0 + g and base0 + g + 8, 16 bytes of every 32-dimension chunk per lane
+    uint4 k0[4], k1[4], v0[4], v1[4];
+    while (true) {
+        L = __ldcg(p.seq_len + m);
+        sl = __ldcg(p.slot + m);
+        const int L_seen = L, sl_seen = sl;
+        L = L < 0 ? 0 : (L > p.max_seq ? p.max_seq : L);
+        sl = sl < 0 ? 0 : (sl >= p.n_slots ? p.n_slots - 1 : sl);
+        const int blocks = max((L + 63) / 64, 1);
+        const int per = (blocks + p.S - 1) / p.S;
+        n_active = (blocks + per - 1) / per;
+        begin = split * per * 64;
+        end = min(L, begin + per * 64);
+        const size_t head_off = (size_t(sl) * p.Nkv + kvh) * p.max_seq * kD;
+        kb = p.kc + head_off;
+        vb = p.vc + head_off;
+        base0 = begin + warp * 16;
+        const bool has_rows = split < n_active;
+        const int safe_end = waited ? (FUSED ? min(end, L - 1) : end) : min(end, L - max(p.fresh_rows, 1));
+        fetched_end = safe_end;
+        const bool f0 = FUSED && has_rows && base0 + g < safe_end, f1 = FUSED && has_rows && base0 + g + 8 < safe_end;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            k0[i] = f0 ? ld_stream_u4(kb + size_t(base0 + g) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+            k1[i] = f1 ? ld_stream_u4(kb + size_t(base0 + g + 8) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            v0[i] = f0 ? ld_stream_u4(vb + size_t(base0 + g) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+            v1[i] = f1 ? ld_stream_u4(vb + size_t(base0 + g + 8) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+        }
+        if (waited) break;
+        pdl_wait();
+        waited = true;
+        if (__ldcg(p.seq_len + m) != L_seen || __ldcg(p.slot + m) != sl_seen) continue;
+        break;
+    }
+    if (FUSED) {
+        // side job: zero the buffer the caller named (nothing uses it at this point of a layer)
+        const int ctas = gridDim.x * gridDim.y * gridDim.z;
+        const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        for (int i = cta * (kWarps * 32) + threadIdx.x; i < p.clear_extra_vec4; i += ctas * kWarps * 32)
+            p.clear_extra[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     if (split >= n_active) return;
-    const int begin = split * per * 64;
-    const int end = min(L, begin + per * 64);
-    const size_t head_off = (size_t(sl) * p.Nkv + kvh) * p.max_seq * kD;
-    const uint16_t* kb = p.kc + head_off;
-    const uint16_t* vb = p.vc + head_off;
+
+    const int heads = p.Nq + 2 * p.Nkv;
+    const int newest = L - 1;  // the row appended by this pass (fused) / by the previous kernel
+    if (FUSED) {
+        int pp = p.pos[m];
+        pp = pp < 0 ? 0 : (pp >= p.max_seq ? p.max_seq - 1 : pp);
+        const float* cos_row = p.cos_t + size_t(pp) * 64;
+        const float* sin_row = p.sin_t + size_t(pp) * 64;
+        // q heads of this kv head: one warp per head
+        for (int h = warp; h < R; h += kWarps) {
+            const float* src = p.qkv + (size_t(m) * heads + kvh * R + h) * kD;
+            float r4[4];
+            head_norm_rope(__ldcg(src + lane), __ldcg(src + lane + 32), __ldcg(src + lane + 64), __ldcg(src + lane + 96),
+                           p.q_norm_w, cos_row, sin_row, p.eps, lane, r4);
+            s_q[h][lane] = r4[0]; s_q[h][lane + 32] = r4[1]; s_q[h][lane + 64] = r4[2]; s_q[h][lane + 96] = r4[3];
+        }
+        // the CTA whose slice holds the newest row appends it: K through norm + rotary, V as it is, both as bf16
+        if (newest >= begin && newest < end) {
+            const size_t row_off = ((size_t(sl) * p.Nkv + kvh) * p.max_seq + pp) * kD;
+            if (warp == kWarps - 1) {
+                const float* src = p.qkv + (size_t(m) * heads + p.Nq + kvh) * kD;
+                float r4[4];
+                head_norm_rope(__ldcg(src + lane), __ldcg(src + lane + 32), __ldcg(src + lane + 64), __ldcg(src + lane + 96),
+                               p.k_norm_w, cos_row, sin_row, p.eps, lane, r4);
+                uint16_t* dst = p.kc_w + row_off;
+                dst[lane] = float_to_bf16_bits(r4[0]);
+                dst[lane + 32] = float_to_bf16_bits(r4[1]);
+                dst[lane + 64] = float_to_bf16_bits(r4[2]);
+                dst[lane + 96] = float_to_bf16_bits(r4[3]);
+            } else if (warp == kWarps - 2) {
+                const float* src = p.qkv + (size_t(m) * heads + p.Nq + p.Nkv + kvh) * kD;
+                uint16_t* dst = p.vc_w + row_off;
+                dst[lane] = float_to_bf16_bits(__ldcg(src + lane));
+                dst[lane + 32] = float_to_bf16_bits(__ldcg(src + lane + 32));
+                dst[lane + 64] = float_to_bf16_bits(__ldcg(src + lane + 64));
+                dst[lane + 96] = float_to_bf16_bits(__ldcg(src + lane + 96));
+            }
+        }
+        __syncthreads();  // s_q is complete; the appended row is visible to the whole CTA
+    }
+    // rows of the first step that were not fetched ahead of the wait (the stand-alone call loads inside the loop)
+    if (FUSED) {
+        const int r0 = base0 + g, r1 = base0 + g + 8;
+        if (r0 >= fetched_end && r0 < end) {
+            const bool coherent = FUSED && r0 >= newest;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                k0[i] = ld_row(kb + size_t(r0) * kD + 32 * i + 8 * t, coherent);
+                v0[i] = ld_row(vb + size_t(r0) * kD + 32 * i + 8 * t, coherent);
+            }
+        }
+        if (r1 >= fetched_end && r1 < end) {
+            const bool coherent = FUSED && r1 >= newest;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                k1[i] = ld_row(kb + size_t(r1) * kD + 32 * i + 8 * t, coherent);
+                v1[i] = ld_row(vb + size_t(r1) * kD + 32 * i + 8 * t, coherent);
+            }
+        }
+    }
 
     // q as B fragments.  Contraction step (i, h2), i = 32-dimension chunk, h2 = half of the lane's 16 bytes:
     // index 2t, 2t+1 <-> dimensions 32 i + 8 t + 4 h2 + {0, 1}, index 2t+8, 2t+9 <-> ... + {2, 3}; column g = head g.
     uint32_t qh[4][2][2], ql[4][2][2];
     {
-        const float* qp = p.q + (size_t(m) * p.Nq + kvh * R + (g < R ? g : 0)) * kD;
+        const float* qp = FUSED ? &s_q[g < R ? g : 0][0] : p.q + (size_t(m) * p.Nq + kvh * R + (g < R ? g : 0)) * kD;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const float4 a = __ldcg(reinterpret_cast<const float4*>(qp + 32 * i + 8 * t));
-            const float4 b = __ldcg(reinterpret_cast<const float4*>(qp + 32 * i + 8 * t + 4));
+            float4 a, b;
+            if (FUSED) {
+                a = *reinterpret_cast<const float4*>(qp + 32 * i + 8 * t);
+                b = *reinterpret_cast<const float4*>(qp + 32 * i + 8 * t + 4);
+            } else {
+                a = __ldcg(reinterpret_cast<const float4*>(qp + 32 * i + 8 * t));
+                b = __ldcg(reinterpret_cast<const float4*>(qp + 32 * i + 8 * t + 4));
+            }
             const bool live = g < R;
             split_bf16x2(live ? a.x : 0.f, live ? a.y : 0.f, qh[i][0][0], ql[i][0][0]);
             split_bf16x2(live ? a.z : 0.f, live ? a.w : 0.f, qh[i][0][1], ql[i][0][1]);
@@ -526,19 +633,20 @@ flash_decode_mma_kernel(const FlashParams p) {
     for (int b = 0; b < 8; b++) { oacc[b][0] = oacc[b][1] = oacc[b][2] = oacc[b][3] = 0.f; }
 
     // warp w takes rows begin + w*16 + step*64 .. +15: fragment rows g and g+8
-    for (int base = begin + warp * 16; base < end; base += kWarps * 16) {
+    for (int base = base0; base < end; base += kWarps * 16) {
         const int r0 = base + g, r1 = base + g + 8;
         const bool ok0 = r0 < end, ok1 = r1 < end;
-        uint4 k0[4], k1[4], v0[4], v1[4];
+        if (!FUSED || base != base0) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            k0[i] = ok0 ? ld_stream_u4(kb + size_t(r0) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
-            k1[i] = ok1 ? ld_stream_u4(kb + size_t(r1) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
-        }
+            for (int i = 0; i < 4; i++) {
+                k0[i] = ok0 ? ld_row(kb + size_t(r0) * kD + 32 * i + 8 * t, FUSED && r0 >= newest) : make_uint4(0, 0, 0, 0);
+                k1[i] = ok1 ? ld_row(kb + size_t(r1) * kD + 32 * i + 8 * t, FUSED && r1 >= newest) : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            v0[i] = ok0 ? ld_stream_u4(vb + size_t(r0) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
-            v1[i] = ok1 ? ld_stream_u4(vb + size_t(r1) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < 4; i++) {
+                v0[i] = ok0 ? ld_row(vb + size_t(r0) * kD + 32 * i + 8 * t, FUSED && r0 >= newest) : make_uint4(0, 0, 0, 0);
+                v1[i] = ok1 ? ld_row(vb + size_t(r1) * kD + 32 * i + 8 * t, FUSED && r1 >= newest) : make_uint4(0, 0, 0, 0);
+            }
         }
         // scores S^T[rows g, g+8][heads 2t, 2t+1]
         float s[4] = {0.f, 0.f, 0.f, 0.f};
@@ -644,10 +752,22 @@ flash_decode_mma_kernel(const FlashParams p) {
         fo[h] = acc; fm[h] = nm; fs[h] = ssum;
     }
 
+    // fused: once every CTA of this (row, kv head) is past its prologue, the raw q / k / v slices can be zeroed for
+    // the next projection that accumulates into the buffer
+    auto clear_raw = [&]() {
+        if (FUSED && p.clear_qkv) {
+            float* row = p.qkv + size_t(m) * heads * kD;
+#pragma unroll
+            for (int h = 0; h < R; h++) row[(kvh * R + h) * kD + tx] = 0.f;
+            row[(p.Nq + kvh) * kD + tx] = 0.f;
+            row[(p.Nq + p.Nkv + kvh) * kD + tx] = 0.f;
+        }
+    };
     if (n_active == 1) {
 #pragma unroll
         for (int h = 0; h < R; h++)
             p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + tx] = fs[h] > 0.f ? fo[h] / fs[h] : 0.f;
+        clear_raw();
         return;
     }
 
@@ -716,6 +836,7 @@ flash_decode_mma_kernel(const FlashParams p) {
         const float den = s_den[h];
         p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + tx] = den > 0.f ? acc[h] / den : 0.f;
     }
+    clear_raw();
 }
 
 
@@ -737,6 +858,7 @@ void flash_decode_set_tuning(const char* key, int value) {
     if (!strcmp(key, "flash_splits")) g_force_splits = value;
     if (!strcmp(key, "flash_early")) g_flash_early = value;
     if (!strcmp(key, "flash_mma")) g_flash_mma = value;
+    if (!strcmp(key, "flash_mma_fused")) g_flash_mma_fused = value;
 }
 
 }  // namespace kuiper
@@ -786,7 +908,14 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
     cfg.attrs = attr;
     cfg.numAttrs = g_pdl_enabled ? 1 : 0;
     cudaError_t err;
-    if (fused) {
+    if (fused && g_flash_mma_fused) {
+        switch (R) {
+            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<1, true>, p); break;
+            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<2, true>, p); break;
+            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<4, true>, p); break;
+            default: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<8, true>, p); break;
+        }
+    } else if (fused) {
         switch (R) {
             case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<1, true>, p); break;
             case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_kernel<2, true>, p); break;
@@ -795,10 +924,10 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
         }
     } else if (g_flash_mma) {
         switch (R) {
-            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<1>, p); break;
-            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<2>, p); break;
-            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<4>, p); break;
-            default: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<8>, p); break;
+            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<1, false>, p); break;
+            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<2, false>, p); break;
+            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<4, false>, p); break;
+            default: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<8, false>, p); break;
         }
     } else {
         switch (R) {

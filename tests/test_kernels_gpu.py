@@ -542,6 +542,7 @@ def test_qknorm_rope_kvwrite(cuda, oracle):
 
 
 # ----------------------------------------------------------------------------- flash decoding
+FLASH_MMA_FUSED_DEFAULT = 1  # same for the fused rotary + attention kernel (key flash_mma_fused)
 FLASH_MMA_DEFAULT = 1  # what the library starts with (kuiper_set_tuning key flash_mma)
 
 
@@ -627,16 +628,35 @@ def test_rope_fused_into_flash_decode_is_bit_identical(cuda, oracle, Nq, Nkv, le
         cuda.set_tuning("flash_mma", FLASH_MMA_DEFAULT)
     ref_mma = cuda.flash_decode(q, kc, vc, seq, slot, workspace=ws)
     assert rel_err(ref_mma.cpu().numpy(), ref.cpu().numpy()) <= 5e-5
-    for fresh in (-1, 1):
-        raw = qkv.clone()
-        side = torch.ones((B, 512), device="cuda")
-        k_f, v_f = kc2.clone(), vc2.clone()
-        got = cuda.rope_flash_decode(raw, qn, kn, cos_t, sin_t, pos, seq, slot, Nq, Nkv, D, 1e-6, k_f, v_f, workspace=ws,
-                                     fresh_rows=fresh, clear_input=True, clear_extra=side)
-        torch.cuda.synchronize()
-        assert torch.equal(got, ref), fresh
-        assert torch.equal(k_f.view(torch.int16), kc.view(torch.int16)) and torch.equal(v_f.view(torch.int16), vc.view(torch.int16))
-        assert float(raw.abs().max()) == 0.0 and float(side.abs().max()) == 0.0
+    cuda.set_tuning("flash_mma_fused", 0)  # SIMT arithmetic in the fused kernel: bit-identical to the two SIMT kernels
+    try:
+        for fresh in (-1, 1):
+            raw = qkv.clone()
+            side = torch.ones((B, 512), device="cuda")
+            k_f, v_f = kc2.clone(), vc2.clone()
+            got = cuda.rope_flash_decode(raw, qn, kn, cos_t, sin_t, pos, seq, slot, Nq, Nkv, D, 1e-6, k_f, v_f, workspace=ws,
+                                         fresh_rows=fresh, clear_input=True, clear_extra=side)
+            torch.cuda.synchronize()
+            assert torch.equal(got, ref), fresh
+            assert torch.equal(k_f.view(torch.int16), kc.view(torch.int16)) and torch.equal(v_f.view(torch.int16), vc.view(torch.int16))
+            assert float(raw.abs().max()) == 0.0 and float(side.abs().max()) == 0.0
+    finally:
+        cuda.set_tuning("flash_mma_fused", FLASH_MMA_FUSED_DEFAULT)
+    # the same fused kernel with its contractions on the tensor cores: same caches and clearing, output to ~1e-5
+    cuda.set_tuning("flash_mma_fused", 1)
+    try:
+        for fresh in (-1, 1):
+            raw = qkv.clone()
+            side = torch.ones((B, 512), device="cuda")
+            k_f, v_f = kc2.clone(), vc2.clone()
+            got = cuda.rope_flash_decode(raw, qn, kn, cos_t, sin_t, pos, seq, slot, Nq, Nkv, D, 1e-6, k_f, v_f, workspace=ws,
+                                         fresh_rows=fresh, clear_input=True, clear_extra=side)
+            torch.cuda.synchronize()
+            assert rel_err(got.cpu().numpy(), ref.cpu().numpy()) <= 5e-5, fresh
+            assert torch.equal(k_f.view(torch.int16), kc.view(torch.int16)) and torch.equal(v_f.view(torch.int16), vc.view(torch.int16))
+            assert float(raw.abs().max()) == 0.0 and float(side.abs().max()) == 0.0
+    finally:
+        cuda.set_tuning("flash_mma_fused", FLASH_MMA_FUSED_DEFAULT)
 
 
 def test_flash_decode_shared_cache_is_causal_prefill(cuda, oracle):
