@@ -191,6 +191,9 @@ def cpu_decode_sample(cfg, n_layers_sample, steps, warmup, seed=0):
     truncated to n_layers_sample layers and extrapolates to the full depth.  Returns tokens/s."""
     from oracle import cpu_oracle as orc
     orc.build()
+    # the launcher may have exported OMP_NUM_THREADS=1 (torch.distributed.run does): the CPU arm takes every core it
+    # is allowed to run on regardless
+    orc.set_num_threads(host_cores())
     ocfg = orc.ModelConfig(**{**cfg, "n_layers": n_layers_sample}, max_seq=max(64, steps + warmup + 8), max_batch=1,
                            act_round=orc.ROUND_FP16)
     weights = make_cpu_weights(orc, ocfg, seed=seed)
@@ -278,6 +281,37 @@ def gemv_roofline(cfg, tp, layers_kept, iters=3):
     return total_bytes / launches, best * 1e-3 / launches, launches
 
 
+def tp1_stream_check(cfg, ecfg, prompt, ids, device):
+    """Rank 0 of a tensor-parallel run: the same weights (same seed) on a single-GPU engine, the same prompt, and
+    the number of leading greedy tokens on which the two engines agree.  At the first disagreement the single-GPU
+    engine's top-1 / top-2 logit margin is reported (a near-tie that the different summation order flipped)."""
+    import torch
+    from mykuiperllama_b200 import engine as eng_mod
+    one = eng_mod.Qwen3Engine(eng_mod.EngineConfig(**{**ecfg.__dict__, "tp_rank": 0, "tp_size": 1, "max_batch": 1}))
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1234)
+    for l in range(cfg["n_layers"]):
+        one.load_layer(l, make_layer_torch(cfg, gen, device))
+    one.load_globals(*make_globals_torch(cfg, gen, device))
+    tok = one.prefill(prompt, slot=0)
+    matching, margin, one_margin = 0, None, None
+    for i, want in enumerate(ids):
+        if tok != want:
+            margin = one_margin
+            break
+        matching += 1
+        if i + 1 == len(ids):
+            break
+        lg, nx = one.predict([tok], [len(prompt) + i], want_logits=True)
+        top2 = np.partition(lg[0], -2)[-2:]
+        one_margin = float(top2[1] - top2[0])
+        tok = int(nx[0])
+    one.close()
+    del one
+    torch.cuda.empty_cache()
+    return {"tokens_compared": len(ids), "matching_leading": matching, "tp1_margin_at_first_mismatch": margin}
+
+
 def run_engine(args, cfg, prompt_len, desc, rank, world):
     import torch
     import torch.distributed as dist
@@ -291,7 +325,8 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
 
     B = max(1, args.batch)
     steps_total = args.warmup + args.steps
-    max_seq = prompt_len + 2 * steps_total + 16
+    n_ids = 32  # greedy ids printed with the line (the first tokens after the prompt, read back step by step)
+    max_seq = prompt_len + n_ids + 2 * steps_total + 16
     ecfg = eng_mod.EngineConfig(**cfg, max_seq=max_seq, max_batch=B, max_rows=max(128, B), tp_rank=rank, tp_size=world)
     eng = eng_mod.Qwen3Engine(ecfg)
 
@@ -328,6 +363,22 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # ---- the first n_ids greedy tokens of sequence 0, read back one step at a time: every N prints them, and for
+    #      N > 1 rank 0 also runs the single-GPU engine on the same weights and counts the leading tokens that agree
+    eng.decode_begin(firsts, [prompt_len] * B, list(range(B)))
+    ids = [int(firsts[0])]
+    for _ in range(n_ids - 1):
+        eng.decode_step(1)
+        ids.append(int(eng.decode_read(B)[0]))
+    eng.decode_step(1)
+    firsts = [int(t) for t in eng.decode_read(B)]
+    prompt_tokens = prompt_len
+    prompt_len += n_ids
+    tp_parity = None
+    if world > 1:
+        tp_parity = tp1_stream_check(cfg, ecfg, prompt, ids, device) if rank == 0 else None
+        barrier()
+
     # ---- device-resident loop: value
     eng.decode_begin(firsts, [prompt_len] * B, list(range(B)))
     eng.decode_step(args.warmup)
@@ -344,6 +395,8 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         if args.profile_range:
             torch.cuda.profiler.stop()
         barrier()
+    if world > 1:
+        eng.tp_status()  # raises if a bounded wait of the peer exchange ran out during the timed loop
     ms = e0.elapsed_time(e1)
     t = torch.tensor([ms], device=device)
     if world > 1:
@@ -364,6 +417,8 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         tok = eng.decode_predict(tok)
     barrier()
     e2e_s = time.perf_counter() - t0
+    if world > 1:
+        eng.tp_status()
     t = torch.tensor([e2e_s], device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -386,9 +441,9 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights (AWQ g128), fp16 x operand, fp32 accumulate",
         "data": "synthetic",
-        "config": {"workload": desc if B == 1 else desc.replace("batch 1", f"batch {B}"), "batch": B, "prompt_tokens": prompt_len, "context_during_timing": ctx_mid,
+        "config": {"workload": desc if B == 1 else desc.replace("batch 1", f"batch {B}"), "batch": B, "prompt_tokens": prompt_tokens, "context_during_timing": ctx_mid,
                    "parallelism": f"tp{world}", "l2_policy": "inputs larger than L2 (weights streamed once per token)",
-                   "prefill_s": round(prefill_s, 3)},
+                   "prefill_s": round(prefill_s, 3), "greedy_ids_first32": ids, "tp1_stream_check": tp_parity},
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
         "gpu_launches": eng.kernels_per_step * args.steps,
         "clocks": clocks.summary(),
@@ -435,9 +490,6 @@ def run_gemv_micro(args):
         args.gemv_impl = 2
     if args.gemv_impl in (0, 1):
         capi.set_tuning("gemv_impl", args.gemv_impl)
-    if args.gemv_impl == 4:  # the fp16 mma.sync kernel (used for 2..4 token rows) on one row, accumulate mode
-        capi.set_tuning("gemv_int8", 0)
-        args.gemv_impl = 2
     if args.gemv_impl == 3:  # the first-generation persistent kernel (SIMT products), accumulate mode
         capi.set_tuning("gemv_impl", 2)
         args.gemv_impl = 2
@@ -509,7 +561,7 @@ def run_gemm_micro(args):
     sc = [(torch.rand((K // 128, N), device="cuda", generator=gen) * 0.018 + 0.002).half() for _ in range(n)]
     x = torch.randn((M, K), device="cuda", generator=gen)
     y = torch.zeros((M, N), device="cuda")
-    ws = None if args.gemm_impl == 1 else capi.awq_gemm_workspace(M, K)  # None: first-generation kernel
+    ws = capi.awq_gemm_workspace(M, K)
 
     def sweep():
         for i in range(n):
@@ -619,17 +671,16 @@ def main():
     ap.add_argument("--kv-len", type=int, default=4096, help="KV length of the attn microbenchmark")
     ap.add_argument("--shape", default="2048x2048", help="KxN of the gemv microbenchmark")
     ap.add_argument("--rows", type=int, default=2048, help="token rows M of the gemm microbenchmark")
-    ap.add_argument("--gemm-impl", type=int, default=2, help="2 pipelined 128x256 kernel (default), 1 first-generation kernel")
     ap.add_argument("--mats", type=int, default=0, help="distinct weight matrices in the gemv microbenchmark (0 = 512 MiB worth)")
     ap.add_argument("--gemv-impl", type=int, default=None, help="2 accumulate mode of the tensor-core GEMV (engine path, default), 0 its ordered combine, "
-                         "1 register-staged kernel, 3 first-generation persistent SIMT kernel (accumulate), 4 fp16 mma.sync kernel (accumulate)")
+                         "1 register-staged kernel, 3 first-generation persistent SIMT kernel (accumulate)")
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (config 4 of the workload list uses 16)")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for a profiler run with profile-from-start off)")
     ap.add_argument("--prompt", type=int, default=None, help="override the workload's prompt length (profiling aid)")
     ap.add_argument("--tuning", action="append", default=[], metavar="KEY=VALUE",
-                    help="kernel tuning switch applied before the run (profiling aid), e.g. gemv_int8=0")
+                    help="kernel tuning switch applied before the run (profiling aid), e.g. flash_mma_fused=0")
     args = ap.parse_args()
     if args.tuning and args.impl == "engine":
         from mykuiperllama_b200 import capi

@@ -115,45 +115,16 @@ KUIPER_API int kuiper_swiglu_awq_gemv_accum_f32(const float* gate_up, const int3
 /* health check (synchronises): 5 if a bounded wait inside the pipelined GEMV ever ran out on this device */
 KUIPER_API int kuiper_awq_gemv_status(void);
 /*
- * A chain of one-row accumulate-mode projections in ONE launch (no counterpart in the reference, whose decode
- * step launches each projection by itself): y_i += op_i(x_i) . W_i for i = 0 .. n_ops-1 in order, where x_{i+1}
- * may be any buffer projection i (or an earlier one) accumulated into - all CTAs meet at a grid barrier between
- * two projections while the weight stream of the next one is already running.  op_i: identity, RMSNorm(x; norm_w,
- * eps) when norm_w is not null, or SwiGLU of a gate|up row [2K] when swiglu != 0.  Every y_i must hold its addend.
- * `sync`: kuiper_awq_gemv_chain_sync_bytes() bytes of device memory, zeroed once by the caller; every launch
- * leaves them at zero.  Waits are bounded; kuiper_awq_gemv_status() reports a wait that ran out.
- */
-typedef struct kuiper_gemv_chain_op {
-    const float* x;          /* [K], or [2K] with swiglu */
-    const int32_t* qweight;  /* [K, N/8] */
-    const int32_t* qzeros;   /* [K/128, N/8] */
-    const uint16_t* scales;  /* fp16 [K/128, N] */
-    float* y;                /* [N] */
-    const uint16_t* norm_w;  /* bf16 [K] or NULL */
-    float eps;
-    int32_t swiglu;
-    int32_t K, N;
-} kuiper_gemv_chain_op;
-KUIPER_API size_t kuiper_awq_gemv_chain_sync_bytes(void);
-KUIPER_API int kuiper_awq_gemv_chain_f32(const kuiper_gemv_chain_op* ops, int n_ops, int group, void* sync,
-                                         kuiper_stream_t stream);
-
-/* Pipeline trace of the one-row GEMV (no counterpart in the reference).  After kuiper_set_tuning("gemv_trace", 1)
- * every accumulate-mode one-row launch (single or chained) records, per CTA, 24 clock readings: [0] global timer (ns)
- * at kernel entry, then SM clock cycles at [1] entry and, for projection i of the launch, [2+4i] operand may be
- * read (dependency wait or grid barrier passed), [3+4i] first weight unit ready, [4+4i] last weight unit ready,
- * [5+4i] sums issued, [18+i] first activation fragments written.  Copies up to max_values readings ([CTA][24]) of
- * the last such launch to the host array `out` (synchronises); returns how many, or -1. */
-KUIPER_API int kuiper_gemv_trace_read(int64_t* out, int max_values);
-
-/*
  * The INT4 GEMV once more, for callers that must not allocate: no counterpart in the reference (its
  * kernels take caller-owned tensors only and it has no split-K scratch at all).  Meant for code that
  * runs after the application has committed all device memory to its own pool, or inside a loop where
  * cudaMalloc and the synchronisation it implies are ruled out.  The scratch of the ordered combine
  * lives in a fixed array inside the library image (kuiper_awq_gemv_noalloc_scratch_bytes(), about
- * 2.1 MiB held per GPU for the life of the process); the call itself allocates nothing, on the host
- * or on the device.  Limits: N <= 32768, N % 32 == 0, K % 128 == 0, group 128, M <= 8; other sizes
+ * 2.1 MiB held per GPU for the life of the process); the call allocates no device or pinned memory.
+ * Its first call on a device does one-time set-up on the host (it asks the runtime for the array's address
+ * and for the driver's tensor-map encoder, sets the kernel's shared-memory attribute) and an error path may
+ * format a message into a thread-local string; later calls only build a tensor map on the stack and launch.
+ * Limits: N <= 32768, N % 32 == 0, K % 128 == 0, group 128, M <= 8; other sizes
  * return 7.  Same result as kuiper_awq_gemv_f32 up to fp32 summation order.  The first call on a
  * device resolves the array's device address: issue it before any stream capture.  All calls on a
  * device share the array, so calls that may overlap on the GPU race; its counters are cleared at the
@@ -172,8 +143,7 @@ KUIPER_API int kuiper_awq_gemv_f32_noalloc(const float* x, const int32_t* qweigh
  *   accumulate != 0                   : y += x . W              (summation order fixed: deterministic)
  * Any M > 0 is accepted (rows are padded to 128 inside the kernel); K % 128 == 0, N % 8 == 0.
  * workspace: kuiper_awq_gemm_workspace_bytes(M, K) bytes (16-byte aligned) for the fp16 copy of x that the
- * pipelined kernel reads (128 x 256 tiles, three stages); with NULL / too small a workspace the call
- * falls back to the first-generation kernel, which converts x tile by tile.
+ * pipelined kernel reads (128 x 256 tiles); required.
  * kuiper_awq_gemm_status() synchronously reads the kernel's bounded-wait error word. ---- */
 KUIPER_API size_t kuiper_awq_gemm_workspace_bytes(int M, int K);
 KUIPER_API int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
@@ -190,7 +160,7 @@ KUIPER_API int kuiper_awq_gemm_status(void);
  * zero-initialised uint32 on the device (sequence number, error word), private to the rank.  All ranks must issue
  * the same sequence of calls with the same count.  data (16-byte aligned, count % 4 == 0, count <= max_count,
  * max_count % 32 == 0) holds the partial row on entry and the sum on return; every rank adds in rank order, so all
- * ranks get identical bits.  Waits on peers are bounded (default one second, tuning key "allreduce_timeout_ms"):
+ * ranks get identical bits.  Waits on peers are bounded (default five seconds, tuning key "allreduce_timeout_ms"):
  * when one runs out the call's result is void and kuiper_allreduce_status (synchronous) returns 5. ---- */
 KUIPER_API size_t kuiper_allreduce_buffer_bytes(int world, int64_t max_count);
 KUIPER_API int kuiper_allreduce_oneshot_f32(float* data, int64_t count, int rank, int world,

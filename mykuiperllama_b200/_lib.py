@@ -42,9 +42,6 @@ KERNEL_API = {
     "kuiper_rmsnorm_awq_gemv_accum_f32": (_i32, [_vp, _vp, _f32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_swiglu_awq_gemv_accum_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_awq_gemv_status": (_i32, []),
-    "kuiper_gemv_trace_read": (_i32, [_vp, _i32]),
-    "kuiper_awq_gemv_chain_sync_bytes": (_sz, []),
-    "kuiper_awq_gemv_chain_f32": (_i32, [_vp, _i32, _i32, _vp, _vp]),
     "kuiper_awq_gemv_noalloc_scratch_bytes": (_sz, []),
     "kuiper_awq_gemv_f32_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_awq_gemm_workspace_bytes": (_sz, [_i32, _i32]),

@@ -108,30 +108,6 @@ def swiglu_awq_gemv_accum(gate_up, qweight, qzeros, scales, y, group=128):
     return y
 
 
-class _ChainOp(ctypes.Structure):
-    _fields_ = [("x", ctypes.c_void_p), ("qweight", ctypes.c_void_p), ("qzeros", ctypes.c_void_p), ("scales", ctypes.c_void_p),
-                ("y", ctypes.c_void_p), ("norm_w", ctypes.c_void_p), ("eps", ctypes.c_float), ("swiglu", ctypes.c_int32),
-                ("K", ctypes.c_int32), ("N", ctypes.c_int32)]
-
-
-def awq_gemv_chain_sync(device="cuda"):
-    """Barrier counters of awq_gemv_chain: zeroed once, left at zero by every launch."""
-    return torch.zeros(max(kernels().kuiper_awq_gemv_chain_sync_bytes(), 16), dtype=torch.uint8, device=device)
-
-
-def awq_gemv_chain(ops, sync, group=128):
-    """One launch for a chain of one-row projections y_i += op_i(x_i) . W_i (see kuiper_awq_gemv_chain_f32).
-    ops: dicts with x, qweight, qzeros, scales, y and optionally norm_w (bf16 weight as int16/uint16 tensor), eps, swiglu."""
-    arr = (_ChainOp * len(ops))()
-    for i, o in enumerate(ops):
-        _dev(o["x"], o["qweight"], o["qzeros"], o["scales"], o["y"], o.get("norm_w"))
-        swiglu = bool(o.get("swiglu", False))
-        K = o["x"].numel() // (2 if swiglu else 1)
-        arr[i] = _ChainOp(_ptr(o["x"]), _ptr(o["qweight"]), _ptr(o["qzeros"]), _ptr(o["scales"]), _ptr(o["y"]), _ptr(o.get("norm_w")),
-                          float(o.get("eps", 0.0)), int(swiglu), K, o["qweight"].shape[1] * 8)
-    check(kernels().kuiper_awq_gemv_chain_f32(ctypes.addressof(arr), len(ops), group, _ptr(sync), _stream()))
-
-
 def awq_gemm_workspace(M, K, device="cuda"):
     n = kernels().kuiper_awq_gemm_workspace_bytes(M, K)
     return torch.empty(max(n, 16), dtype=torch.uint8, device=device)
@@ -139,8 +115,7 @@ def awq_gemm_workspace(M, K, device="cuda"):
 
 def awq_gemm(x, qweight, qzeros, scales, y=None, residual=None, accumulate=False, group=128, workspace="auto"):
     """Tensor-core INT4 GEMM for M >= 16 rows: y = x . W (+ residual), or y += x . W.
-    workspace: "auto" allocates the fp16 activation copy of the pipelined kernel, None selects the first-generation
-    kernel, a tensor is used as it is."""
+    workspace: "auto" allocates the fp16 activation copy the kernel reads; a tensor is used as it is."""
     _dev(x, qweight, qzeros, scales)
     M, K = x.shape
     N = qweight.shape[1] * 8
@@ -161,16 +136,6 @@ def awq_gemm_status() -> None:
 
 def awq_gemv_status() -> None:
     check(kernels().kuiper_awq_gemv_status())
-
-
-def gemv_trace_read():
-    """Clock readings of the last traced one-row GEMV launch as an int64 array [CTAs, 24] (see kuiper_gemv_trace_read)."""
-    import numpy as np
-    out = np.zeros((296, 24), dtype=np.int64)
-    n = kernels().kuiper_gemv_trace_read(out.ctypes.data, out.size)
-    if n < 0:
-        check(5)
-    return out
 
 
 def bf16_gemv(x, W, out=None):

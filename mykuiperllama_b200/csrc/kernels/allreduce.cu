@@ -27,7 +27,7 @@ constexpr int kArMaxWorld = 8;
 constexpr int kArThreads = 1024;
 constexpr int kFlagStride = 32;  // uint32 per flag: 128 bytes apart
 
-long long g_ar_timeout_ns = 1000000000ll;  // one second
+long long g_ar_timeout_ns = 5000000000ll;  // five seconds: ranks may be this far apart after start-up work (graph capture)
 
 struct ArParams {
     float* data;              // [count] partial row in, sum out

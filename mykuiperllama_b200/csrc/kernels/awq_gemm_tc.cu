@@ -4,19 +4,17 @@
 //
 // y[M,N] (+)= x[M,K] . dequant(qweight)[K,N]
 //
-// One CTA owns a 128 x 128 output tile; its fp32 accumulator lives in tensor memory
-// (128 lanes x 128 columns).  The K loop advances 64 rows at a time through two shared-memory
-// stages.  Warps 0-3 convert the activation tile to fp16 (the same operand rounding as the GEMV);
-// warps 4-7 dequantise the packed weights: eight rows of one packed word column are loaded per
-// thread, the nibble pairs come out of the LOP3 / 0x6400 trick exactly as in the GEMV, the fp16
-// group scale is applied, and 2 x 2 register transposes (PRMT) turn "two columns of one row" into
-// "two rows of one column", so that each column's eight K values are one 16-byte shared-memory
-// store.  Both operands are stored K-major with the 128-byte swizzle: a tile row is the 64 K values
-// (128 bytes) of one token row / weight column, eight rows form a 1024-byte atom, and the 16-byte
-// chunk c of row r sits at chunk position c ^ (r % 8) - the eight lanes that write one row's eight
-// chunks hit eight different bank groups.  One thread issues four tcgen05.mma (K = 16 each) per stage
-// and a tcgen05.commit onto the stage's mbarrier; the other stage is refilled meanwhile.  The
-// epilogue reads the accumulator with tcgen05.ld (one TMEM lane = one output row per thread).
+// One CTA owns a 128 x 256 output tile; its fp32 accumulator lives in tensor memory (128 lanes x 256
+// columns), two CTAs share an SM.  The activations are converted to fp16 once per call (the same operand
+// rounding as the GEMV) and reach shared memory with cp.async; every thread dequantises one packed word
+// column and one K octet of the weight tile: the nibble pairs come out of the LOP3 / 0x6400 trick exactly
+// as in the GEMV, the fp16 group scale is applied, and register transposes (PRMT) turn "two columns of one
+// row" into "two rows of one column", so that each column's eight K values are one 16-byte shared-memory
+// store.  Both operands are stored K-major with the 128-byte swizzle: a tile row is the 64 K values (128
+// bytes) of one token row / weight column, eight rows form a 1024-byte atom, and the 16-byte chunk c of row
+// r sits at chunk position c ^ (r % 8).  One thread issues four tcgen05.mma (K = 16 each) per stage and a
+// tcgen05.commit onto the stage's mbarrier; a stage is refilled only after that commit.  The epilogue reads
+// the accumulator with tcgen05.ld (one TMEM lane = one output row per thread).
 //
 // Every mbarrier wait is bounded; on a timeout the CTA records an error word, stops issuing work,
 // still frees its tensor memory and returns.
@@ -27,10 +25,8 @@
 namespace kuiper {
 namespace {
 
-constexpr int kBM = 128, kBN = 128, kBK = 64;
+constexpr int kBM = 128, kBK = 64;
 constexpr int kGemmThreads = 256;
-constexpr int kStageA = kBM * kBK * 2;  // 16 KB
-constexpr int kStageB = kBN * kBK * 2;  // 16 KB
 constexpr uint32_t kMagicTc = 0x64006400u;
 constexpr uint32_t kSpinLimitTc = 1u << 22;
 
@@ -83,200 +79,6 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
     return d;
 }
 
-// eight dequantised fp16 values of one packed word (logical column order), scale applied
-__device__ __forceinline__ void dequant_word_scaled(uint32_t w, uint32_t zw, const uint4& sraw, uint32_t (&out)[4]) {
-    const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
-    const __half2 neg_sixteenth = __floats2half2_rn(-0.0625f, -0.0625f);
-    const uint32_t w8 = w >> 8, z8 = zw >> 8;
-    const __half2 d0 = __hsub2(tc_u2h2((w & 0x000f000fu) | kMagicTc), tc_u2h2((zw & 0x000f000fu) | kMagicTc));
-    const __half2 d1 = __hfma2(tc_u2h2((w & 0x00f000f0u) | kMagicTc), sixteenth,
-                               __hmul2(tc_u2h2((zw & 0x00f000f0u) | kMagicTc), neg_sixteenth));
-    const __half2 d2 = __hsub2(tc_u2h2((w8 & 0x000f000fu) | kMagicTc), tc_u2h2((z8 & 0x000f000fu) | kMagicTc));
-    const __half2 d3 = __hfma2(tc_u2h2((w8 & 0x00f000f0u) | kMagicTc), sixteenth,
-                               __hmul2(tc_u2h2((z8 & 0x00f000f0u) | kMagicTc), neg_sixteenth));
-    out[0] = tc_h22u(__hmul2(d0, tc_u2h2(sraw.x)));  // columns 0,1
-    out[1] = tc_h22u(__hmul2(d1, tc_u2h2(sraw.y)));  // columns 2,3
-    out[2] = tc_h22u(__hmul2(d2, tc_u2h2(sraw.z)));  // columns 4,5
-    out[3] = tc_h22u(__hmul2(d3, tc_u2h2(sraw.w)));  // columns 6,7
-}
-
-__global__ void __launch_bounds__(kGemmThreads, 1) awq_gemm_tc_kernel(const GemmParams p) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
-    unsigned char* sA = smem;                      // 2 stages x 16 KB
-    unsigned char* sB = smem + 2 * kStageA;        // 2 stages x 16 KB
-    __shared__ uint64_t mma_bar[2];
-    __shared__ uint32_t s_tmem;
-    __shared__ int s_dead;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
-    const int NW = p.N >> 3;
-
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&mma_bar[0])));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&mma_bar[1])));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        s_dead = 0;
-    }
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&s_tmem)), "r"(uint32_t(kBN))
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = s_tmem;
-
-    pdl_launch_dependents();
-    pdl_wait();
-
-    // instruction descriptor: D fp32, A and B fp16, both K-major, N = 128, M = 128
-    const uint32_t idesc = (1u << 4) | (uint32_t(kBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
-    const int nk = p.K / kBK;
-    bool dead = false;
-
-    for (int it = 0; it < nk; it++) {
-        const int s = it & 1;
-        const int k0 = it * kBK;
-        if (it >= 2 && !dead) {
-            // the MMAs that read this stage two iterations ago must have finished
-            if (!tc_mbar_wait(&mma_bar[s], uint32_t((it >> 1) - 1) & 1u)) {
-                atomicExch(&g_gemm_wait_error, 1);
-                s_dead = 1;
-                dead = true;
-            }
-        }
-        if (warp < 4) {
-            // ---- activation tile: 128 rows x 64 K values, fp32 -> fp16, one 16-byte store per (row, K octet)
-            unsigned char* dst = sA + s * kStageA;
-#pragma unroll
-            for (int q = 0; q < 8; q++) {
-                const int item = q * 128 + tid;
-                const int koct = item & 7, m = item >> 3;
-                uint4 o = make_uint4(0, 0, 0, 0);
-                if (m0 + m < p.M) {
-                    const float4* xp = reinterpret_cast<const float4*>(p.x + size_t(m0 + m) * p.K + k0 + koct * 8);
-                    const float4 a = __ldcg(xp), b = __ldcg(xp + 1);
-                    o.x = tc_h22u(__floats2half2_rn(a.x, a.y));
-                    o.y = tc_h22u(__floats2half2_rn(a.z, a.w));
-                    o.z = tc_h22u(__floats2half2_rn(b.x, b.y));
-                    o.w = tc_h22u(__floats2half2_rn(b.z, b.w));
-                }
-                *reinterpret_cast<uint4*>(dst + (m >> 3) * 1024 + (m & 7) * 128 + ((koct ^ (m & 7)) << 4)) = o;
-            }
-        } else {
-            // ---- weight tile: 128 columns x 64 K values; this thread: packed word column j, K octet koct
-            const int t = tid - 128;
-            const int koct = t & 7, j = t >> 3;
-            const int wcol = (n0 >> 3) + j;
-            const bool col_ok = wcol < NW;
-            const int g = k0 >> 7;
-            uint32_t w[8];
-#pragma unroll
-            for (int r = 0; r < 8; r++) w[r] = col_ok ? __ldg(p.qw + size_t(k0 + koct * 8 + r) * NW + wcol) : 0u;
-            const uint32_t zw = col_ok ? __ldg(p.qz + size_t(g) * NW + wcol) : 0u;
-            const uint4 sraw = col_ok ? __ldg(reinterpret_cast<const uint4*>(p.scales + size_t(g) * p.N + n0 + j * 8))
-                                      : make_uint4(0, 0, 0, 0);
-            uint32_t d[8][4];  // [row][column pair]
-#pragma unroll
-            for (int r = 0; r < 8; r++) dequant_word_scaled(w[r], zw, sraw, d[r]);
-            unsigned char* dst = sB + s * kStageB + j * 1024;
-#pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const int pr = c >> 1;
-                const uint32_t sel = (c & 1) ? 0x7632u : 0x5410u;
-                uint4 o;  // rows (0,1) (2,3) (4,5) (6,7) of column c
-                o.x = __byte_perm(d[0][pr], d[1][pr], sel);
-                o.y = __byte_perm(d[2][pr], d[3][pr], sel);
-                o.z = __byte_perm(d[4][pr], d[5][pr], sel);
-                o.w = __byte_perm(d[6][pr], d[7][pr], sel);
-                *reinterpret_cast<uint4*>(dst + c * 128 + ((koct ^ c) << 4)) = o;
-            }
-        }
-        // make the generic-proxy stores visible to the tensor core (async proxy), then hand over
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        dead = dead || (s_dead != 0);
-        if (tid == 0 && !dead) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_base = smem_addr(sA + s * kStageA), b_base = smem_addr(sB + s * kStageB);
-#pragma unroll
-            for (int kk = 0; kk < kBK / 16; kk++) {
-                // inside a swizzle atom the K offset is added to the start address (16 fp16 = 32 bytes)
-                const uint64_t adesc = make_desc(a_base + kk * 32);
-                const uint64_t bdesc = make_desc(b_base + kk * 32);
-                const uint32_t accumulate = (it > 0 || kk > 0) ? 1u : 0u;
-                asm volatile(
-                    "{\n\t.reg .pred p;\n\t"
-                    "setp.ne.b32 p, %4, 0;\n\t"
-                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                    ::"r"(tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-                    : "memory");
-            }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(&mma_bar[s]))
-                         : "memory");
-        }
-    }
-
-    // ---- all MMAs done?  (they complete in order: the last commit covers everything)
-    if (!dead) {
-        const int last = nk - 1;
-        if (!tc_mbar_wait(&mma_bar[last & 1], uint32_t(last >> 1) & 1u)) {
-            atomicExch(&g_gemm_wait_error, 2);
-            dead = true;
-        }
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-    if (!dead) {
-        // ---- epilogue: warp w reads TMEM lanes 32*(w&3).., columns 64*(w>>2)..; one output row per thread
-        const int row = m0 + (warp & 3) * 32 + lane;
-        const int cbase = (warp >> 2) * 64;
-#pragma unroll
-        for (int ch = 0; ch < 2; ch++) {
-            uint32_t r[32];
-            const uint32_t taddr = tmem + (uint32_t((warp & 3) * 32) << 16) + uint32_t(cbase + ch * 32);
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-                  "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                : "r"(taddr)
-                : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (row < p.M) {
-                const int col0 = n0 + cbase + ch * 32;
-                float* yp = p.y + size_t(row) * p.N + col0;
-                const float* rp = p.mode == 1 ? p.residual + size_t(row) * p.N + col0 : (p.mode == 2 ? yp : nullptr);
-#pragma unroll
-                for (int v = 0; v < 8; v++) {
-                    if (col0 + v * 4 < p.N) {
-                        float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                               __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                        if (rp) {
-                            const float4 a = __ldcg(reinterpret_cast<const float4*>(rp) + v);
-                            o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
-                        }
-                        reinterpret_cast<float4*>(yp)[v] = o;
-                    }
-                }
-            }
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kBN)) : "memory");
-    }
-}
-
-// zero-point and scale pairs of one (group, packed column): computed once per tile, used for its eight rows
 struct TileConsts {
     __half2 z0, z1, z2, z3;  // (1024 + z) pairs for the low nibbles, -(64 + z) pairs for the high nibbles
     __half2 s0, s1, s2, s3;  // fp16 scales of column pairs (0,1) (2,3) (4,5) (6,7)
@@ -575,40 +377,27 @@ extern "C" int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const
     p.residual = residual;
     p.M = M; p.K = K; p.N = N;
     p.mode = accumulate ? 2 : (residual ? 1 : 0);
-    if (workspace != nullptr && workspace_bytes >= kuiper_awq_gemm_workspace_bytes(M, K) &&
-        (reinterpret_cast<uintptr_t>(workspace) & 15) == 0) {
-        // second-generation kernel: activations converted to fp16 once, 128 x 256 tiles
-        const int64_t n4 = int64_t(M) * K / 4;
-        int blocks = int((n4 + 255) / 256);
-        if (blocks > 148 * 8) blocks = 148 * 8;
-        int rc = pdl_status(launch_pdl(convert_f16_kernel, dim3(blocks), dim3(256), 0, as_stream(stream),
-                                       reinterpret_cast<const float4*>(x), reinterpret_cast<uint2*>(workspace), n4),
-                            "awq_gemm convert");
-        if (rc != KUIPER_OK) return rc;
-        GemmParams2 p2;
-        p2.g = p;
-        p2.x16 = reinterpret_cast<const __half*>(workspace);
-        const size_t smem2 = 1024 + size_t(kStages2) * (kStageA2 + kStageB2);
-        static bool configured2 = false;
-        if (!configured2) {
-            if (cudaFuncSetAttribute(awq_gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem2)) != cudaSuccess) {
-                set_error("awq_gemm: cannot reserve %zu bytes of shared memory", smem2);
-                return KUIPER_INTERNAL_ERROR;
-            }
-            configured2 = true;
-        }
-        const dim3 grid2((N + kBN2 - 1) / kBN2, (M + kBM - 1) / kBM, 1);
-        return pdl_status(launch_pdl(awq_gemm_tc2_kernel, grid2, dim3(kGemmThreads), smem2, as_stream(stream), p2), "awq_gemm");
+    KUIPER_REQUIRE(workspace != nullptr && workspace_bytes >= kuiper_awq_gemm_workspace_bytes(M, K) &&
+                       (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+                   "awq_gemm: needs a 16-byte aligned workspace of kuiper_awq_gemm_workspace_bytes(M, K) bytes (got %zu)",
+                   workspace_bytes);
+    // activations converted to fp16 once, then 128 x 256 output tiles
+    const int64_t n4 = int64_t(M) * K / 4;
+    int blocks = int((n4 + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    int rc = pdl_status(launch_pdl(convert_f16_kernel, dim3(blocks), dim3(256), 0, as_stream(stream),
+                                   reinterpret_cast<const float4*>(x), reinterpret_cast<uint2*>(workspace), n4),
+                        "awq_gemm convert");
+    if (rc != KUIPER_OK) return rc;
+    GemmParams2 p2;
+    p2.g = p;
+    p2.x16 = reinterpret_cast<const __half*>(workspace);
+    const size_t smem2 = 1024 + size_t(kStages2) * (kStageA2 + kStageB2);
+    static size_t configured[kMaxDevices] = {};
+    if (!ensure_dynamic_smem(awq_gemm_tc2_kernel, smem2, configured)) {
+        set_error("awq_gemm: cannot reserve %zu bytes of shared memory", smem2);
+        return KUIPER_INTERNAL_ERROR;
     }
-    const size_t smem = 1024 + 2 * kStageA + 2 * kStageB;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(awq_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-            set_error("awq_gemm: cannot reserve %zu bytes of shared memory", smem);
-            return KUIPER_INTERNAL_ERROR;
-        }
-        configured = true;
-    }
-    const dim3 grid((N + kBN - 1) / kBN, (M + kBM - 1) / kBM, 1);
-    return pdl_status(launch_pdl(awq_gemm_tc_kernel, grid, dim3(kGemmThreads), smem, as_stream(stream), p), "awq_gemm");
+    const dim3 grid2((N + kBN2 - 1) / kBN2, (M + kBM - 1) / kBM, 1);
+    return pdl_status(launch_pdl(awq_gemm_tc2_kernel, grid2, dim3(kGemmThreads), smem2, as_stream(stream), p2), "awq_gemm");
 }

@@ -353,10 +353,10 @@ template <int MODE, int MT, int ROWS>
 int launch(const GemvParams& p, cudaStream_t stream) {
     auto kern = awq_gemv_kernel<MODE, MT, ROWS>;
     const size_t smem = size_t(kWarps) * MT * 256 * sizeof(float4);
-    static bool configured = false;  // per instantiation
-    if (!configured) {
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        configured = true;
+    static size_t configured[kMaxDevices] = {};  // per instantiation and device
+    if (!ensure_dynamic_smem(kern, smem, configured)) {
+        set_error("awq_gemv: cannot reserve %zu bytes of shared memory", smem);
+        return KUIPER_INTERNAL_ERROR;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((p.N + kTileCols - 1) / kTileCols, p.S, 1);
@@ -569,19 +569,6 @@ extern "C" int kuiper_swiglu_awq_gemv_accum_f32(const float* gate_up, const int3
                                                 const uint16_t* scales, float* y, int M, int K, int N, int group,
                                                 kuiper_stream_t stream) {
     return awq_gemv_accum_common(gate_up, nullptr, 0.f, true, qweight, qzeros, scales, y, M, K, N, group, stream);
-}
-
-namespace kuiper {
-int awq_gemv_trace_read(long long* out, int max_values);
-}
-extern "C" int kuiper_gemv_trace_read(int64_t* out, int max_values) {
-    KUIPER_REQUIRE(out != nullptr && max_values > 0, "gemv_trace_read: empty destination");
-    const int n = kuiper::awq_gemv_trace_read(reinterpret_cast<long long*>(out), max_values);
-    if (n < 0) {
-        set_error("gemv_trace_read: cannot read the trace buffer");
-        return -1;
-    }
-    return n;
 }
 
 extern "C" int kuiper_awq_gemv_status(void) {

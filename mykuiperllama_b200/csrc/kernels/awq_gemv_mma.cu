@@ -120,8 +120,6 @@ __device__ __forceinline__ void tma_box(void* dst, const CUtensorMap* map, int c
 __device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumersC) : "memory"); }
 // consumers + the activation warp (the fused norm's 1/rms is handed over through shared memory)
 __device__ __forceinline__ void norm_sync() { asm volatile("bar.sync 2, %0;" ::"n"(kConsumersC + 32) : "memory"); }
-// the activation warp tells the consumers that the operand of a chained projection may be read
-__device__ __forceinline__ void operand_sync() { asm volatile("bar.sync 3, %0;" ::"n"(kConsumersC + 32) : "memory"); }
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -138,12 +136,6 @@ template <int IMM>
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
     uint2 v;
     asm volatile("ld.shared.v2.b32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(IMM));
-    return v;
-}
-// w >> 8 as a multiply-high: runs on the FMA pipe and leaves the half-rate integer pipe to the masks
-__device__ __forceinline__ uint32_t shr8(uint32_t w) {
-    uint32_t v;
-    asm("mul.hi.u32 %0, %1, 16777216;" : "=r"(v) : "r"(w));
     return v;
 }
 __device__ __forceinline__ bool bar_try(uint32_t addr, uint32_t parity) {
@@ -170,7 +162,7 @@ __device__ __forceinline__ float2 halves_to_floats(uint32_t u) { return __half22
 // MT token rows (1..4).  ACCUM: y += x.W with vector float reductions, the caller guarantees that y holds the
 // addend.  Otherwise y = x.W (+ residual) through workspace slots and arrival counters, summed in CTA order.
 // NORM: the operand is RMSNorm(x) = (x * rstd) * norm_w, formed by the activation warp.
-template <int MT, int STAGES, bool ACCUM, bool NORM, int PROBE = 0>
+template <int MT, int STAGES, bool ACCUM, bool NORM>
 __global__ void __launch_bounds__(kThreadsMma, kCtasPerSmMma)
 awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParams p) {
     // B-fragment rows of the 2*MT live column slots, one row of zeros for the other lanes, per-token sums
@@ -218,12 +210,6 @@ awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParam
                     atomicExch(&g_gemv_mma_wait_error, 1);
                     ok = false;
                     break;
-                }
-                if (PROBE == 2) {  // measurement aid: no weight traffic at all, the consumers run on stale shared memory
-                    bar_arrive(&full_bar[s]);
-                    if (++kb == p.upt) { kb = 0; t++; }
-                    if (++s == STAGES) { s = 0; parity ^= 1u; }
-                    continue;
                 }
                 bar_expect_tx(&full_bar[s], kStageBytesM);
 #pragma unroll
@@ -416,13 +402,6 @@ awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParam
         uint32_t w0[2][2], w1[2][2];
         uint2 xb[2];
         auto math = [&]() {
-            if (PROBE == 1) {  // measurement aid: keep the loads alive, skip the arithmetic
-                uint32_t v = 0;
-#pragma unroll
-                for (int rb = 0; rb < 2; rb++) v ^= w0[0][rb] ^ w1[0][rb] ^ w0[1][rb] ^ w1[1][rb] ^ xb[rb].x ^ xb[rb].y;
-                acc_g[0][0][0] += __uint_as_float(v & 0x3fffffffu);
-                return;
-            }
 #pragma unroll
             for (int rb = 0; rb < 2; rb++) {
 #pragma unroll
@@ -592,589 +571,7 @@ awq_gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const MmaGemvParam
     }
 }
 
-// ---------------------------------------------------------------- one token row on the integer tensor path
-//
-// Same ring, same units and the same shared-memory layout as the kernel above, other arithmetic: the nibbles are
-// used as unsigned bytes and the activations as four signed bytes, so a packed word costs two integer
-// instructions and one quarter of an mma.sync.m16n8k32 (s8 x u8 -> s32):
-//
-//   * (w & 0x0f0f0f0f) holds nibbles 0,2,4,6 of a word as bytes q, (w & 0xf0f0f0f0) holds nibbles 1,3,5,7 as
-//     bytes 16 q: both are B operands as they are (contraction index = (weight row, byte position), fragment
-//     column = word column), no shift;
-//   * the activations of a 128-row group (or of the part of it that this CTA walks) are scaled by a power of
-//     two so that the largest is below 2^30, rounded to integers and cut into four signed bytes
-//     (x_int = d3 2^24 + d2 2^16 + d1 2^8 + d0, exact).  A-fragment row (digit, byte position c) carries digit d
-//     of x[row] at contraction index (row, c) and zeros at the other three positions, which separates the
-//     four nibbles of a B byte quadruple into four result rows.  16 fragment rows = 4 digits x 4 positions;
-//   * all sums are exact 32-bit integers until the group ends; there the four digit sums are recombined in
-//     fp32, the zero point is taken out (sum (q - z) x = sum q x - z sum x) and the fp16 group scale and the
-//     power-of-two activation scale are applied.
-//
-// The activations keep 24+ significant bits relative to the largest of their group (the fp16 B operand of the
-// kernel above keeps 11 per element).
-//
-// Chains.  One launch can run up to kMaxChain projections one after the other, each reading what the one before
-// it accumulated (O -> gate|up -> down -> next layer's QKV in the decode step).  Between two projections all
-// CTAs meet at a grid barrier (an arrival counter in global memory; every wait on it is bounded).  The weight
-// producer does not take part in the barrier: the weights do not depend on the activations, so the ring keeps
-// filling with the next projection's units while the consumers drain, meet and fetch their new activations -
-// the weight stream does not stop at a projection boundary the way it does between two kernels.  All CTAs of
-// the grid are resident at once (2 per SM), which the barrier relies on.
-__device__ __forceinline__ void mma_s8u8(int (&d)[4], const uint4& a, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
 
-constexpr int kXStageI = 4 * 512 + 16;  // four 8-row steps of ready-made A fragments (16 bytes per lane), sum, scale
-constexpr int kMaxChain = 4;
-constexpr int kChainSyncInts = 8;       // arrival counters of the barriers + exit counter
-constexpr uint32_t kGridSpinLimit = 1u << 21;
-
-struct ChainOp {
-    const float* x;          // [K] ([2K] gate|up row with swiglu)
-    float* y;                // [N]
-    const uint32_t* qz;      // [K/128][N/8]
-    const __half* scales;    // [K/128][N]
-    const uint16_t* norm_w;  // bf16 [K] or null: the operand is RMSNorm(x)
-    float eps;
-    int swiglu;              // != 0: the operand is silu(gate) * up
-    int K, N, upt, U;        // upt = units per column tile = K / 32, U = total units
-};
-struct ChainParams {
-    CUtensorMap tmap[kMaxChain];
-    ChainOp op[kMaxChain];
-    const float* residual;   // ordered mode (single projection): [N] or null
-    float* partial;          // ordered mode: [slots][1024]
-    int* counters;           // ordered mode: [tiles]
-    int* sync;               // chains: kChainSyncInts zero-initialised ints, left at zero by every launch
-    int n_ops;
-    int probe;               // measurement aid: 1 = plain stores instead of the reductions (wrong sums), 2 = neither
-};
-
-// TRACE: per-CTA clock readings at the milestones of every projection go to g_gemv_trace (kuiper_gemv_trace_read)
-constexpr int kTraceSlots = 24;  // 0 global timer, 1 entry, 2 + 4 op + {0 operand may be read, 1 first unit ready, 2 last unit ready, 3 sums issued}, 18 + op first fragments written
-__device__ long long g_gemv_trace[2 * 148 * kTraceSlots];
-template <bool TRACE>
-__device__ __forceinline__ void trace(int slot) {
-    if (TRACE && blockIdx.x < 2 * 148) g_gemv_trace[blockIdx.x * kTraceSlots + slot] = slot == 0 ? (long long)globaltimer_ns() : clock64();
-}
-
-// bounded wait until all CTAs of the grid have arrived at barrier `k`
-__device__ __noinline__ bool grid_wait(const int* counter, int ctas) {
-    for (uint32_t spin = 0; spin < kGridSpinLimit; spin++) {
-        int v;
-        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-        if (v >= ctas) return true;
-        __nanosleep(32);
-    }
-    atomicExch(&g_gemv_mma_wait_error, 4);
-    return false;
-}
-
-template <int STAGES, bool ACCUM, bool TRACE = false>
-__global__ void __launch_bounds__(kThreadsMma, kCtasPerSmMma)
-awq_gemv_imma_kernel(const __grid_constant__ ChainParams p) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = smem_raw + ((1024u - (sm_u32(smem_raw) & 1023u)) & 1023u);
-    unsigned char* stages = smem;                                   // STAGES x 16 KB, 1024-byte aligned for the swizzle
-    unsigned char* xstages = smem + STAGES * kStageBytesM;          // STAGES x kXStageI
-    // accumulate mode: 128 floats per consumer warp (transpose before the vector reductions);
-    // ordered mode: the 1024 columns of the tile
-    float* red = reinterpret_cast<float*>(xstages + STAGES * kXStageI);
-    __shared__ uint64_t full_bar[STAGES];
-    __shared__ uint64_t empty_bar[STAGES];
-    __shared__ float s_rstd;
-    __shared__ float s_part[kWarpsC];
-    __shared__ int s_last;
-
-    const int tid = threadIdx.x;
-    const int warp = tid >> 5, lane = tid & 31;
-    const int C = gridDim.x;
-    // fragment coordinates: g = fragment row / column, t = thread in group; as an A row, g = (digit pair, byte position)
-    const int g = lane >> 2, t = lane & 3;
-    const int c = g & 3, plo = g >> 2;
-
-    if (tid == 0) {
-#pragma unroll
-        for (int s = 0; s < STAGES; s++) {
-            bar_init(&full_bar[s], 2);          // TMA warp (with the byte count) + activation warp
-            bar_init(&empty_bar[s], kWarpsC);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        trace<TRACE>(0);
-        trace<TRACE>(1);
-    }
-    __syncthreads();
-    pdl_launch_dependents();
-
-    if (warp == kWarpsC) {
-        // ------------------------------------------------------------ weight producer (one thread)
-        if (lane == 0) {
-            int s = 0;
-            uint32_t parity = 0;
-            bool ok = true;
-            for (int op = 0; op < p.n_ops && ok; op++) {
-                const ChainOp& o = p.op[op];
-                const int u0 = int((long long)blockIdx.x * o.U / C), u1 = int((long long)(blockIdx.x + 1) * o.U / C);
-                int tl = u0 / o.upt, kb = u0 - tl * o.upt;
-                for (int u = u0; u < u1; u++) {
-                    if (!bar_wait_relaxed(&empty_bar[s], parity ^ 1u)) {
-                        atomicExch(&g_gemv_mma_wait_error, 1);
-                        ok = false;
-                        break;
-                    }
-                    bar_expect_tx(&full_bar[s], kStageBytesM);
-#pragma unroll
-                    for (int b = 0; b < 4; b++)
-                        tma_box(stages + s * kStageBytesM + b * kBoxBytes, &p.tmap[op], tl * kTileWordsM + b * kBoxWords,
-                                kb * kUnitRowsM, &full_bar[s]);
-                    if (++kb == o.upt) { kb = 0; tl++; }
-                    if (++s == STAGES) { s = 0; parity ^= 1u; }
-                }
-            }
-            if (!ok) {
-                // give copies already issued a bounded chance to land before the CTA goes away
-                for (int q = 0; q < STAGES; q++) bar_wait(&full_bar[q], 0);
-            }
-        }
-        return;
-    }
-
-    if (warp == kWarpsC + 1) {
-        // ------------------------------------------------------------ activation producer (one warp, lane = row of the unit)
-        pdl_wait();  // x belongs to the previous kernel until here
-        // byte selectors that put digit plo (plo + 2) of a word at byte position c and zeros elsewhere
-        const uint32_t sel_keep = 0x4444u & ~(0xfu << (4 * c));
-        const uint32_t sel_lo = sel_keep | (uint32_t(plo) << (4 * c));
-        const uint32_t sel_hi = sel_keep | (uint32_t(plo + 2) << (4 * c));
-        int s = 0;
-        uint32_t parity = 0;
-        bool alive = true;  // false once a wait ran out: keep walking without waiting so that nobody hangs, the result is void
-        for (int op = 0; op < p.n_ops; op++) {
-            const ChainOp& o = p.op[op];
-            const int u0 = int((long long)blockIdx.x * o.U / C), u1 = int((long long)(blockIdx.x + 1) * o.U / C);
-            const bool norm = o.norm_w != nullptr;
-            if (op > 0 && alive) {
-                // the operand is what all CTAs accumulated in the projection before
-                int ok = 1;
-                if (lane == 0) ok = grid_wait(p.sync + (op - 1), C) ? 1 : 0;
-                alive = __shfl_sync(0xffffffffu, ok, 0) != 0;
-            }
-            if (op > 0 && norm) operand_sync();  // lets the consumers start the sum of squares
-            if (TRACE && lane == 0 && !norm) trace<TRACE>(2 + 4 * op);
-            float rstd = 1.f;
-            int kb = u0 % o.upt;
-            // Rows are requested a segment ahead and only loaded here: the arithmetic on them (SwiGLU, norm weight)
-            // happens when the segment becomes current, so that the warp does not stall on the loads it has just issued.
-            // a = x (or gate), b = up (SwiGLU) or the bf16 norm weight's bits
-            auto fetch = [&](int kblock, float& a, uint32_t& b) {
-                const float* xp = o.x + kblock * kUnitRowsM + lane;
-                a = __ldcg(xp);
-                b = 0u;
-                if (o.swiglu) b = __float_as_uint(__ldcg(xp + o.K));
-                else if (norm) b = uint32_t(__ldg(o.norm_w + kblock * kUnitRowsM + lane));
-            };
-            // a segment = the units of one 128-row group that lie in this CTA's run; they share one activation scale
-            auto seg_len = [&](int u, int kblock) {
-                const int n = 4 - (kblock & 3);
-                return n < u1 - u ? n : u1 - u;
-            };
-            float cur[4], nxt[4];
-            uint32_t cur_b[4], nxt_b[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) { cur[i] = nxt[i] = 0.f; cur_b[i] = nxt_b[i] = 0u; }
-            int u = u0;
-            int n_cur = u0 < u1 ? seg_len(u0, kb) : 0;
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-                if (i < n_cur) fetch(kb + i, cur[i], cur_b[i]);
-            if (norm) {
-                // the consumers' sum of squares; the first rows were requested before waiting for it
-                norm_sync();
-                rstd = s_rstd;
-            }
-            while (u < u1) {
-                const int u_next = u + n_cur;
-                int kb_next = kb + n_cur;
-                if (kb_next == o.upt) kb_next = 0;
-                const int n_next = u_next < u1 ? seg_len(u_next, kb_next) : 0;
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    if (i < n_next) fetch(kb_next + i, nxt[i], nxt_b[i]);
-                float amax = 0.f;
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    if (i < n_cur) {
-                        if (o.swiglu) cur[i] = (cur[i] / (1.0f + expf(-cur[i]))) * __uint_as_float(cur_b[i]);
-                        else if (norm) cur[i] = (cur[i] * rstd) * __uint_as_float(cur_b[i] << 16);
-                        amax = fmaxf(amax, fabsf(cur[i]));
-                    }
-                }
-                // amax < 2^(eb - 126): scaling by 2^(156 - eb) puts every value of the segment below 2^30
-                uint32_t eb = __reduce_max_sync(0xffffffffu, __float_as_uint(amax)) >> 23;
-                eb = eb < 30u ? 30u : eb;
-                const float to_int = __uint_as_float((283u - eb) << 23);
-                const float from_int = __uint_as_float((eb - 29u) << 23);
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    if (i < n_cur) {
-                        if (alive && !bar_wait_relaxed(&empty_bar[s], parity ^ 1u)) {
-                            atomicExch(&g_gemv_mma_wait_error, 3);
-                            alive = false;
-                        }
-                        {
-                            const int xi = __float2int_rn(cur[i] * to_int);
-                            // bytes of `digits` read as signed: d0, d1, d2, d3 with xi = d3 2^24 + d2 2^16 + d1 2^8 + d0
-                            const uint32_t digits = (uint32_t(xi) + 0x00808080u) ^ 0x00808080u;
-                            // sum of the unit's integers, exact: low and high halves are reduced separately
-                            const int sum_lo = __reduce_add_sync(0xffffffffu, xi & 0xffff);
-                            const int sum_hi = __reduce_add_sync(0xffffffffu, xi >> 16);
-                            const float sum = fmaf(__int2float_rn(sum_hi), 65536.f, __int2float_rn(sum_lo));
-                            unsigned char* xs = xstages + s * kXStageI;
-#pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                // fragment of rows 8j .. 8j+7: contraction slots (t, first half) / (t, second half) = rows 8j+2t / 8j+2t+1
-                                const uint32_t d0 = __shfl_sync(0xffffffffu, digits, 8 * j + 2 * t);
-                                const uint32_t d1 = __shfl_sync(0xffffffffu, digits, 8 * j + 2 * t + 1);
-                                uint4 frag;
-                                frag.x = __byte_perm(d0, 0u, sel_lo);   // fragment row g,     first half
-                                frag.y = __byte_perm(d0, 0u, sel_hi);   // fragment row g + 8, first half
-                                frag.z = __byte_perm(d1, 0u, sel_lo);   // fragment row g,     second half
-                                frag.w = __byte_perm(d1, 0u, sel_hi);   // fragment row g + 8, second half
-                                *reinterpret_cast<uint4*>(xs + j * 512 + lane * 16) = frag;
-                            }
-                            if (lane == 0) *reinterpret_cast<float2*>(xs + 2048) = make_float2(sum, from_int);
-                            __syncwarp();
-                            if (lane == 0) bar_arrive(&full_bar[s]);
-                            if (TRACE && lane == 0 && u == u0 && i == 0) trace<TRACE>(18 + op);
-                            if (++s == STAGES) { s = 0; parity ^= 1u; }
-                        }
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 4; i++) { cur[i] = nxt[i]; cur_b[i] = nxt_b[i]; }
-                kb = kb_next;
-                u = u_next;
-                n_cur = n_next;
-            }
-        }
-        return;
-    }
-
-    // ---------------------------------------------------------------- consumers
-    pdl_wait();  // y, the workspace and (for the norm) x belong to the previous kernel until here
-
-    // this warp: word columns 16*warp .. 16*warp+15 of the tile = two blocks of 8 (cb = 2*warp, 2*warp+1), which lie
-    // in TMA box warp>>1 at block position cbl = 2*(warp&1) + {0,1}.  Lane (g, t) reads word g of the block in
-    // rows 2t and 2t+1 of each 8-row step (the two halves of its B fragment); with the 128-byte swizzle the
-    // 16-byte chunk index is XORed with (row & 7), which spreads the 32 lanes over all 32 banks.
-    uint32_t off0[2], off1[2];
-#pragma unroll
-    for (int cbi = 0; cbi < 2; cbi++) {
-        const int cbl = 2 * (warp & 1) + cbi;
-        const int chunk = 2 * cbl + (g >> 2);
-        off0[cbi] = uint32_t((warp >> 1) * kBoxBytes + (2 * t) * 128 + ((chunk ^ (2 * t)) << 4) + (g & 3) * 4);
-        off1[cbi] = uint32_t((warp >> 1) * kBoxBytes + (2 * t + 1) * 128 + ((chunk ^ (2 * t + 1)) << 4) + (g & 3) * 4);
-    }
-    const float digit_lo = plo ? 256.f : 1.f, digit_hi = digit_lo * 65536.f;   // weights of this lane's two digits
-    const int zshift = 8 * c, sshift = 16 * (c >> 1);
-    // column of this lane's results inside a word: [0,4,1,5][c] for the low nibbles, two further for the high ones
-    const int col_in_word = ((c & 1) << 2) + (c >> 1) + 2 * plo;
-
-    // 32-bit shared-memory addresses that walk the ring with the stage index
-    const uint32_t stage0 = sm_u32(stages), xstage0 = sm_u32(xstages) + uint32_t(lane) * 16u;
-    const uint32_t full0 = sm_u32(&full_bar[0]), empty0 = sm_u32(&empty_bar[0]);
-    const uint32_t sum_rel = 2048u - uint32_t(lane) * 16u;
-    uint32_t sbase = stage0, xbase = xstage0, fbar = full0, ebar = empty0;
-    int s = 0;
-    uint32_t parity = 0;
-    bool dead = false;  // a wait ran out: keep walking so that nobody hangs, the result is void
-
-    for (int op = 0; op < p.n_ops; op++) {
-        const ChainOp& o = p.op[op];
-        const int u0 = int((long long)blockIdx.x * o.U / C), u1 = int((long long)(blockIdx.x + 1) * o.U / C);
-        const int groups = o.K >> 7;
-        const int NW = o.N >> 3;
-        const bool last_op = op + 1 == p.n_ops;
-
-        // This lane's results: fragment rows g and g + 8 (digits plo and plo + 2 at byte position c), fragment columns
-        // 2t and 2t + 1 = word columns 2t + ni of each block.  Byte position c of the low-nibble operand is nibble 2c =
-        // column [0,4,1,5][c] of the word; the high-nibble operand is two columns further.  The group constants it
-        // needs: the zero word of its four word columns and, of each one's eight fp16 scales, the 8-byte half that
-        // holds those two columns (.x -> low-nibble column, .y -> high-nibble column, 16-bit lane c >> 1).
-        auto load_consts = [&](int tile, int grp, uint32_t (&zw)[2][2], uint2 (&sc)[2][2]) {
-#pragma unroll
-            for (int cbi = 0; cbi < 2; cbi++) {
-#pragma unroll
-                for (int ni = 0; ni < 2; ni++) {
-                    const int wcol = tile * kTileWordsM + (2 * warp + cbi) * 8 + 2 * t + ni;
-                    if (wcol < NW) {
-                        zw[cbi][ni] = __ldg(o.qz + size_t(grp) * NW + wcol);
-                        sc[cbi][ni] = __ldg(reinterpret_cast<const uint2*>(o.scales + size_t(grp) * o.N + size_t(wcol) * 8 + 4 * (c & 1)));
-                    } else {
-                        zw[cbi][ni] = 0u;
-                        sc[cbi][ni] = make_uint2(0u, 0u);
-                    }
-                }
-            }
-        };
-
-        int tl = u0 / o.upt, kb = u0 - tl * o.upt;
-        // constants of the current group and of the one after it (fetched a whole group ahead); they belong to
-        // the weights, so they are requested before the barrier
-        uint32_t z_cur[2][2], z_next[2][2];
-        uint2 s_cur[2][2], s_next[2][2];
-        load_consts(tl, kb >> 2, z_cur, s_cur);
-        int nt = tl, ng = (kb >> 2) + 1;  // the group after the current one on this CTA's path
-        if (ng == groups) { ng = 0; nt++; }
-        load_consts(nt, ng, z_next, s_next);
-
-        // The consumers do not wait at the grid barrier themselves: they only ever see the new operand through the
-        // fragments of the activation warp, which does (a poll with acquire semantics has to wait for the loads
-        // above, which go to DRAM).  Only the norm's sum of squares reads the operand directly.
-        if (o.norm_w != nullptr) {
-            if (op > 0) operand_sync();  // the activation warp has passed the barrier
-            if (TRACE && tid == 0) trace<TRACE>(2 + 4 * op);
-            // sum of squares of the whole input row, by all consumer threads, 4 x 16-byte loads in flight each
-            const float4* hp = reinterpret_cast<const float4*>(o.x);
-            const int n4 = o.K >> 2;
-            float ss = 0.f;
-            for (int i = tid; i < n4; i += 4 * kConsumersC) {
-                float4 v[4];
-#pragma unroll
-                for (int q = 0; q < 4; q++)
-                    v[q] = (i + q * kConsumersC < n4) ? __ldcg(hp + i + q * kConsumersC) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    ss = fmaf(v[q].x, v[q].x, ss); ss = fmaf(v[q].y, v[q].y, ss);
-                    ss = fmaf(v[q].z, v[q].z, ss); ss = fmaf(v[q].w, v[q].w, ss);
-                }
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) s_part[warp] = ss;
-            consumers_sync();
-            if (tid == 0) {
-                float tot = 0.f;
-#pragma unroll
-                for (int q = 0; q < kWarpsC; q++) tot += s_part[q];
-                s_rstd = 1.0f / sqrtf(tot / float(o.K) + o.eps);
-            }
-            norm_sync();
-        }
-
-        int acc_lo[2][4], acc_hi[2][4];  // [block][fragment]: integer sums of the current group, low / high nibbles (x 16)
-        float acc_t[2][2][2];            // [block][low / high nibble][ni]: this lane's share of the current tile
-        float gsum = 0.f;                // sum of the integer activations over the rows of the current group seen so far
-        float from_int = 0.f;            // what one integer step of the current group's activations is worth
-#pragma unroll
-        for (int cbi = 0; cbi < 2; cbi++) {
-#pragma unroll
-            for (int i = 0; i < 4; i++) { acc_lo[cbi][i] = 0; acc_hi[cbi][i] = 0; }
-            acc_t[cbi][0][0] = acc_t[cbi][0][1] = acc_t[cbi][1][0] = acc_t[cbi][1][1] = 0.f;
-        }
-
-        for (int u = u0; u < u1; u++) {
-            if (!dead && !bar_try(fbar, parity) && !bar_wait_addr(fbar, parity)) {
-                atomicExch(&g_gemv_mma_wait_error, 2);
-                dead = true;
-            }
-            if (TRACE && tid == 0) {
-                if (u == u0) trace<TRACE>(3 + 4 * op);
-                if (u + 1 == u1) trace<TRACE>(4 + 4 * op);
-            }
-            // the unit is taken in two halves of 16 rows so that only half of it is live in registers at a time;
-            // the stage is released after the second half has been read
-            const uint32_t a00 = sbase + off0[0], a10 = sbase + off1[0], a01 = sbase + off0[1], a11 = sbase + off1[1];
-            uint32_t w0[2][2], w1[2][2];
-            uint4 xa[2];
-            auto math = [&]() {
-#pragma unroll
-                for (int rb = 0; rb < 2; rb++) {
-#pragma unroll
-                    for (int cbi = 0; cbi < 2; cbi++) {
-                        const uint32_t a = w0[cbi][rb], b = w1[cbi][rb];
-                        mma_s8u8(acc_lo[cbi], xa[rb], a & 0x0f0f0f0fu, b & 0x0f0f0f0fu);
-                        mma_s8u8(acc_hi[cbi], xa[rb], a & 0xf0f0f0f0u, b & 0xf0f0f0f0u);
-                    }
-                }
-            };
-            w0[0][0] = lds32<0>(a00);    w1[0][0] = lds32<0>(a10);    w0[1][0] = lds32<0>(a01);    w1[1][0] = lds32<0>(a11);
-            w0[0][1] = lds32<1024>(a00); w1[0][1] = lds32<1024>(a10); w0[1][1] = lds32<1024>(a01); w1[1][1] = lds32<1024>(a11);
-            xa[0] = lds128(xbase);
-            xa[1] = lds128(xbase + 512u);
-            {
-                const uint2 sv = lds64<0>(xbase + sum_rel);
-                gsum += __uint_as_float(sv.x);
-                from_int = __uint_as_float(sv.y);
-            }
-            math();
-            w0[0][0] = lds32<2048>(a00); w1[0][0] = lds32<2048>(a10); w0[1][0] = lds32<2048>(a01); w1[1][0] = lds32<2048>(a11);
-            w0[0][1] = lds32<3072>(a00); w1[0][1] = lds32<3072>(a10); w0[1][1] = lds32<3072>(a01); w1[1][1] = lds32<3072>(a11);
-            xa[0] = lds128(xbase + 1024u);
-            xa[1] = lds128(xbase + 1536u);
-            __syncwarp();
-            if (lane == 0) bar_arrive_addr(ebar);  // the stage is in registers now
-            if (++s == STAGES) {
-                s = 0; parity ^= 1u; sbase = stage0; xbase = xstage0; fbar = full0; ebar = empty0;
-            } else {
-                sbase += kStageBytesM; xbase += kXStageI; fbar += 8; ebar += 8;
-            }
-            kb++;
-            math();
-            const bool tile_end = kb == o.upt;
-            const bool run_end = u + 1 == u1;
-            if ((kb & 3) != 0 && !run_end) continue;
-
-            // ---- group done (or the run ends inside it): recombine the digits, take the zero point out, apply the scales
-            {
-                const float zsum = plo ? 0.f : gsum;  // the zero point is subtracted once, by the lane with digits 0 and 2
-#pragma unroll
-                for (int cbi = 0; cbi < 2; cbi++) {
-#pragma unroll
-                    for (int ni = 0; ni < 2; ni++) {
-                        const uint32_t zw = z_cur[cbi][ni] >> zshift;
-                        const float z_lo = float(zw & 15u), z_hi = float(zw & 0xf0u);  // the high nibble keeps its factor 16
-                        const float s_lo = __half2float(__ushort_as_half((unsigned short)(s_cur[cbi][ni].x >> sshift)));
-                        const float s_hi = __half2float(__ushort_as_half((unsigned short)(s_cur[cbi][ni].y >> sshift)));
-                        const float v_lo = fmaf(__int2float_rn(acc_lo[cbi][2 + ni]), digit_hi, __int2float_rn(acc_lo[cbi][ni]) * digit_lo);
-                        const float v_hi = fmaf(__int2float_rn(acc_hi[cbi][2 + ni]), digit_hi, __int2float_rn(acc_hi[cbi][ni]) * digit_lo);
-                        acc_t[cbi][0][ni] = fmaf(fmaf(-z_lo, zsum, v_lo), s_lo * from_int, acc_t[cbi][0][ni]);
-                        acc_t[cbi][1][ni] = fmaf(fmaf(-z_hi, zsum, v_hi), s_hi * (from_int * 0.0625f), acc_t[cbi][1][ni]);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; i++) { acc_lo[cbi][i] = 0; acc_hi[cbi][i] = 0; }
-                }
-            }
-            gsum = 0.f;
-            if (!run_end) {
-#pragma unroll
-                for (int cbi = 0; cbi < 2; cbi++)
-#pragma unroll
-                    for (int ni = 0; ni < 2; ni++) { z_cur[cbi][ni] = z_next[cbi][ni]; s_cur[cbi][ni] = s_next[cbi][ni]; }
-                if (++ng == groups) { ng = 0; nt++; }
-                load_consts(nt, ng, z_next, s_next);  // clamped to zeros past the last tile
-            }
-            if (!tile_end && !run_end) continue;
-
-            // ---- this CTA's contribution to column tile tl is complete: add the two digit halves (lanes g and g ^ 4),
-            //      then lanes with plo = 0 place the low-nibble columns and lanes with plo = 1 the high-nibble columns
-            float mine[2][2];  // [block][ni]
-#pragma unroll
-            for (int cbi = 0; cbi < 2; cbi++) {
-#pragma unroll
-                for (int ni = 0; ni < 2; ni++) {
-                    const float lo = acc_t[cbi][0][ni] + __shfl_xor_sync(0xffffffffu, acc_t[cbi][0][ni], 16);
-                    const float hi = acc_t[cbi][1][ni] + __shfl_xor_sync(0xffffffffu, acc_t[cbi][1][ni], 16);
-                    mine[cbi][ni] = plo ? hi : lo;
-                    acc_t[cbi][0][ni] = 0.f;
-                    acc_t[cbi][1][ni] = 0.f;
-                }
-            }
-            if (ACCUM) {
-                float* wred = red + warp * 128;
-                __syncwarp();
-#pragma unroll
-                for (int cbi = 0; cbi < 2; cbi++)
-#pragma unroll
-                    for (int ni = 0; ni < 2; ni++) wred[(cbi * 8 + 2 * t + ni) * 8 + col_in_word] = mine[cbi][ni];
-                __syncwarp();
-                const float4 v = *reinterpret_cast<const float4*>(wred + lane * 4);
-                const int col = (tl * kTileWordsM + warp * 16) * 8 + lane * 4;
-                if (col < o.N) {
-                    if (p.probe == 0)
-                        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o.y + col), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
-                                     : "memory");
-                    else if (p.probe == 1)
-                        *reinterpret_cast<float4*>(o.y + col) = v;
-                }
-            } else {
-#pragma unroll
-                for (int cbi = 0; cbi < 2; cbi++)
-#pragma unroll
-                    for (int ni = 0; ni < 2; ni++) red[((2 * warp + cbi) * 8 + 2 * t + ni) * 8 + col_in_word] = mine[cbi][ni];
-                consumers_sync();
-                // thread f owns float4 f of the tile (columns 4f .. 4f+3)
-                const int f = tid;
-                const int col = tl * kTileColsM + f * 4;
-                float4 v = *reinterpret_cast<const float4*>(red + f * 4);
-                // contributors of this tile: CTAs owning its first and last unit
-                const long long first_u = (long long)tl * o.upt, last_u = first_u + o.upt - 1;
-                const int c_first = int(((first_u + 1) * C - 1) / o.U);
-                const int c_last = int(((last_u + 1) * C - 1) / o.U);
-                const int n_contrib = c_last - c_first + 1;
-                bool finish = true;  // whether this CTA writes y for the tile
-                if (n_contrib > 1) {
-                    *reinterpret_cast<float4*>(p.partial + size_t(blockIdx.x + tl) * kTileColsM + f * 4) = v;
-                    __threadfence();
-                    consumers_sync();
-                    if (tid == 0) {
-                        const int prev = atomicAdd(p.counters + tl, 1);
-                        s_last = (prev == n_contrib - 1);
-                        if (s_last) p.counters[tl] = 0;
-                    }
-                    consumers_sync();
-                    finish = s_last != 0;
-                    if (finish) {
-                        __threadfence();
-                        // slots are added in CTA order (deterministic); loads are issued eight at a time
-                        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-                        const float* base = p.partial + size_t(tl) * kTileColsM + f * 4;
-                        int cc = c_first;
-                        for (; cc + 8 <= c_last + 1; cc += 8) {
-                            float4 a[8];
-#pragma unroll
-                            for (int q = 0; q < 8; q++) a[q] = __ldcg(reinterpret_cast<const float4*>(base + size_t(cc + q) * kTileColsM));
-#pragma unroll
-                            for (int q = 0; q < 8; q++) { sum.x += a[q].x; sum.y += a[q].y; sum.z += a[q].z; sum.w += a[q].w; }
-                        }
-                        for (; cc <= c_last; cc++) {
-                            const float4 a = __ldcg(reinterpret_cast<const float4*>(base + size_t(cc) * kTileColsM));
-                            sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
-                        }
-                        v = sum;
-                    }
-                }
-                if (finish && col < o.N) {
-                    if (p.residual) {
-                        const float4 r = __ldcg(reinterpret_cast<const float4*>(p.residual + col));
-                        v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
-                    }
-                    *reinterpret_cast<float4*>(o.y + col) = v;
-                }
-                consumers_sync();  // red is reused by the next tile
-            }
-            kb = 0;
-            tl++;
-        }
-
-        if (TRACE && tid == 0) trace<TRACE>(5 + 4 * op);
-        if (!last_op) {
-            // arrive at the grid barrier once this CTA's sums are visible to the whole device
-            __threadfence();
-            consumers_sync();
-            if (tid == 0) {
-                __threadfence();
-                asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.sync + op) : "memory");
-            }
-        }
-    }
-    if (tid == 0) {
-        if (p.n_ops > 1) {
-            // the last CTA to leave puts the counters back to zero for the next launch
-            const int prev = atomicAdd(p.sync + (kChainSyncInts - 1), 1);
-            if (prev == C - 1) {
-#pragma unroll
-                for (int i = 0; i < kChainSyncInts; i++) p.sync[i] = 0;
-            }
-        }
-    }
-}
 
 // ---------------------------------------------------------------- host side
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1217,6 +614,8 @@ struct MapKeyMHash {
     }
 };
 
+// a tensor map depends on the address and shape only (device pointers of different devices are distinct under
+// unified addressing), so one process-wide cache serves every device
 bool get_map_mma(const int32_t* qweight, int K, int N, CUtensorMap* out) {
     static std::mutex mu;
     static std::unordered_map<MapKeyM, CUtensorMap, MapKeyMHash> cache;
@@ -1235,36 +634,16 @@ bool get_map_mma(const int32_t* qweight, int K, int N, CUtensorMap* out) {
     return true;
 }
 
-int sm_count_mma() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
-    }
-    return n;
-}
-
-int g_mma_nomath = 0;
-int g_mma_stages = 0;
-int g_mma_trace = 0;
-int g_chain_stages = 0;
-int g_mma_int8 = 0;  // 1: one-row launches take the integer kernel (measured slower inside the decode step; chains always use it)
-
-template <int MT, int STAGES, bool ACCUM, bool NORM, int PROBE = 0>
+template <int MT, int STAGES, bool ACCUM, bool NORM>
 int launch_mma(const CUtensorMap& map, const MmaGemvParams& p, int ctas, cudaStream_t stream) {
-    auto kern = awq_gemv_mma_kernel<MT, STAGES, ACCUM, NORM, PROBE>;
+    auto kern = awq_gemv_mma_kernel<MT, STAGES, ACCUM, NORM>;
     constexpr int kXStage = (2 * MT + 1) * kXRowStride + 16 * MT;
     const size_t smem = 1024 + size_t(STAGES) * kStageBytesM + ((size_t(STAGES) * kXStage + 15) & ~size_t(15)) +
                         (ACCUM ? 0 : size_t(MT) * kTileColsM * sizeof(float));
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-            set_error("awq_gemv_mma: cannot reserve %zu bytes of shared memory", smem);
-            return KUIPER_INTERNAL_ERROR;
-        }
-        configured = true;
+    static size_t configured[kMaxDevices] = {};  // per instantiation and device
+    if (!ensure_dynamic_smem(kern, smem, configured)) {
+        set_error("awq_gemv_mma: cannot reserve %zu bytes of shared memory", smem);
+        return KUIPER_INTERNAL_ERROR;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas, 1, 1);
@@ -1284,55 +663,6 @@ int launch_mma(const CUtensorMap& map, const MmaGemvParams& p, int ctas, cudaStr
     return KUIPER_OK;
 }
 
-template <int STAGES, bool ACCUM, bool TRACE = false>
-int launch_imma(const ChainParams& p, int ctas, cudaStream_t stream) {
-    auto kern = awq_gemv_imma_kernel<STAGES, ACCUM, TRACE>;
-    const size_t smem = 1024 + size_t(STAGES) * (kStageBytesM + kXStageI) + size_t(kTileColsM) * sizeof(float);
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-            set_error("awq_gemv_imma: cannot reserve %zu bytes of shared memory", smem);
-            return KUIPER_INTERNAL_ERROR;
-        }
-        configured = true;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ctas, 1, 1);
-    cfg.blockDim = dim3(kThreadsMma, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = g_pdl_enabled ? 1 : 0;
-    cudaError_t err = cudaLaunchKernelEx(&cfg, kern, p);
-    if (err != cudaSuccess) {
-        set_error("awq_gemv_imma launch failed: %s", cudaGetErrorString(err));
-        return KUIPER_INTERNAL_ERROR;
-    }
-    return KUIPER_OK;
-}
-
-// one projection of a chain (or the only one of a plain launch)
-bool fill_chain_op(ChainParams& cp, int i, const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
-                   float* y, int K, int N, const uint16_t* norm_w, float eps, bool swiglu) {
-    if (!get_map_mma(qweight, K, N, &cp.tmap[i])) return false;
-    ChainOp& o = cp.op[i];
-    o.x = x;
-    o.y = y;
-    o.qz = reinterpret_cast<const uint32_t*>(qzeros);
-    o.scales = reinterpret_cast<const __half*>(scales);
-    o.norm_w = norm_w;
-    o.eps = eps;
-    o.swiglu = swiglu ? 1 : 0;
-    o.K = K;
-    o.N = N;
-    o.upt = K / kUnitRowsM;
-    o.U = ((N + kTileColsM - 1) / kTileColsM) * o.upt;
-    return true;
-}
-
 template <bool ACCUM, bool NORM>
 int launch_mma_rows(int rows, const CUtensorMap& map, const MmaGemvParams& p, int ctas, cudaStream_t stream) {
     switch (rows) {
@@ -1346,23 +676,14 @@ int launch_mma_rows(int rows, const CUtensorMap& map, const MmaGemvParams& p, in
 }  // namespace
 
 void awq_gemv_mma_set_tuning(const char* key, int value) {
-    if (!strcmp(key, "gemv_nomath")) g_mma_nomath = value;
-    if (!strcmp(key, "gemv_stages")) g_mma_stages = value;
-    if (!strcmp(key, "gemv_int8")) g_mma_int8 = value;
-    if (!strcmp(key, "gemv_trace")) g_mma_trace = value;
-    if (!strcmp(key, "gemv_chain_stages")) g_chain_stages = value;
+    (void)key;
+    (void)value;
 }
 
 int awq_gemv_mma_status() {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_gemv_mma_wait_error, sizeof(int)) != cudaSuccess) return -1;
     return v;
-}
-
-// copies the clock readings of the last traced launch: [CTA][8] (slot 0: global timer in ns, slots 1..: SM clock)
-int awq_gemv_trace_read(long long* out, int max_values) {
-    const int n = max_values < 2 * 148 * kTraceSlots ? max_values : 2 * 148 * kTraceSlots;
-    return cudaMemcpyFromSymbol(out, g_gemv_trace, size_t(n) * sizeof(long long)) == cudaSuccess ? n : -1;
 }
 
 bool awq_gemv_mma_supported(int K, int N) { return N % 32 == 0 && K % 128 == 0 && encode_fn_mma() != nullptr; }
@@ -1406,96 +727,16 @@ int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* q
     }
     p.counters = reinterpret_cast<int*>(workspace);
     p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + head);
-    long long ctas = (long long)sm_count_mma() * kCtasPerSmMma;
+    long long ctas = (long long)device_sm_count() * kCtasPerSmMma;
     if (ctas > p.U) ctas = p.U;
     if ((norm_w || swiglu) && !accumulate) {
         set_error("awq_gemv_mma: the fused input norm / SwiGLU exist in accumulate mode only");
         return KUIPER_INVALID_ARGUMENT;
     }
-    if (rows == 1 && g_mma_int8 && g_mma_nomath == 0 && g_mma_stages == 0) {
-        ChainParams cp;
-        memset(&cp, 0, sizeof(cp));
-        if (!fill_chain_op(cp, 0, x, qweight, qzeros, scales, y, K, N, norm_w, eps, swiglu)) {
-            set_error("awq_gemv_mma: tensor map encoding failed");
-            return KUIPER_INTERNAL_ERROR;
-        }
-        cp.n_ops = 1;
-        cp.residual = residual;
-        cp.partial = p.partial;
-        cp.counters = p.counters;
-        if (accumulate && g_mma_trace) return launch_imma<kStagesM, true, true>(cp, int(ctas), stream);
-        if (accumulate) return launch_imma<kStagesM, true>(cp, int(ctas), stream);
-        return launch_imma<kStagesM, false>(cp, int(ctas), stream);
-    }
     if (accumulate && norm_w) return launch_mma_rows<true, true>(rows, map, p, int(ctas), stream);
-    if (accumulate && g_mma_nomath == 1 && rows == 1) return launch_mma<1, kStagesM, true, false, 1>(map, p, int(ctas), stream);
-    if (accumulate && g_mma_nomath == 2 && rows == 1) return launch_mma<1, kStagesM, true, false, 2>(map, p, int(ctas), stream);
-    if (accumulate && !norm_w && rows == 1 && g_mma_stages == 5) return launch_mma<1, 5, true, false>(map, p, int(ctas), stream);
-    if (accumulate && !norm_w && rows == 1 && g_mma_stages == 4) return launch_mma<1, 4, true, false>(map, p, int(ctas), stream);
-    if (accumulate && !norm_w && rows == 1 && g_mma_stages == 6) return launch_mma<1, 6, true, false>(map, p, int(ctas), stream);
     if (accumulate) return launch_mma_rows<true, false>(rows, map, p, int(ctas), stream);
     if (rows == 2) return launch_mma<2, kStagesM, false, false>(map, p, int(ctas), stream);
     return launch_mma<1, kStagesM, false, false>(map, p, int(ctas), stream);
 }
 
-
-// A chain of one-row projections in one launch: operand i + 1 is read after every CTA's sums of projection i have
-// landed (grid barrier).  `sync`: kChainSyncInts zero-initialised ints that every launch leaves at zero.
-int awq_gemv_chain_max_ops() { return kMaxChain; }
-size_t awq_gemv_chain_sync_bytes() { return kChainSyncInts * sizeof(int); }
-int awq_gemv_chain_launch(const kuiper_gemv_chain_op* ops, int n_ops, int* sync, cudaStream_t stream) {
-    if (n_ops < 1 || n_ops > kMaxChain) {
-        set_error("awq_gemv_chain: %d projections in one chain (1..%d)", n_ops, kMaxChain);
-        return KUIPER_INVALID_ARGUMENT;
-    }
-    if (n_ops > 1 && sync == nullptr) {
-        set_error("awq_gemv_chain: a chain needs the barrier counters");
-        return KUIPER_INVALID_ARGUMENT;
-    }
-    ChainParams cp;
-    memset(&cp, 0, sizeof(cp));
-    for (int i = 0; i < n_ops; i++) {
-        const kuiper_gemv_chain_op& o = ops[i];
-        if (!fill_chain_op(cp, i, o.x, o.qweight, o.qzeros, o.scales, o.y, o.K, o.N, o.norm_w, o.eps, o.swiglu != 0)) {
-            set_error("awq_gemv_chain: tensor map encoding failed");
-            return KUIPER_INTERNAL_ERROR;
-        }
-    }
-    cp.n_ops = n_ops;
-    cp.sync = sync;
-    cp.probe = g_mma_nomath;
-    // every CTA takes part in the barriers, also those without units in one of the projections
-    const int ctas = sm_count_mma() * kCtasPerSmMma;
-    if (g_mma_trace) return launch_imma<5, true, true>(cp, ctas, stream);
-    if (g_chain_stages == 3) return launch_imma<3, true>(cp, ctas, stream);
-    if (g_chain_stages == 4) return launch_imma<4, true>(cp, ctas, stream);
-    return launch_imma<5, true>(cp, ctas, stream);
-}
-
 }  // namespace kuiper
-
-using namespace kuiper;
-
-extern "C" size_t kuiper_awq_gemv_chain_sync_bytes(void) { return awq_gemv_chain_sync_bytes(); }
-
-extern "C" int kuiper_awq_gemv_chain_f32(const kuiper_gemv_chain_op* ops, int n_ops, int group, void* sync, kuiper_stream_t stream) {
-    KUIPER_REQUIRE(ops != nullptr, "awq_gemv_chain: null projection list");
-    KUIPER_REQUIRE(group == 128, "awq_gemv_chain: group size %d is not supported (128 only)", group);
-    KUIPER_REQUIRE(n_ops >= 1 && n_ops <= awq_gemv_chain_max_ops(), "awq_gemv_chain: %d projections in one chain (1..%d)", n_ops,
-                   awq_gemv_chain_max_ops());
-    for (int i = 0; i < n_ops; i++) {
-        const kuiper_gemv_chain_op& o = ops[i];
-        KUIPER_REQUIRE(o.x && o.qweight && o.qzeros && o.scales && o.y, "awq_gemv_chain: null tensor pointer in projection %d", i);
-        KUIPER_REQUIRE(o.K > 0 && o.N > 0 && o.K % 128 == 0 && o.N % 32 == 0,
-                       "awq_gemv_chain: projection %d needs K %% 128 == 0 and N %% 32 == 0 (K=%d N=%d)", i, o.K, o.N);
-        KUIPER_REQUIRE(((reinterpret_cast<uintptr_t>(o.qweight) | reinterpret_cast<uintptr_t>(o.qzeros) |
-                         reinterpret_cast<uintptr_t>(o.scales) | reinterpret_cast<uintptr_t>(o.y) | reinterpret_cast<uintptr_t>(o.x) |
-                         reinterpret_cast<uintptr_t>(o.norm_w)) & 15) == 0,
-                       "awq_gemv_chain: tensors of projection %d must be 16-byte aligned", i);
-        KUIPER_REQUIRE(!(o.norm_w && o.swiglu), "awq_gemv_chain: projection %d asks for both the fused norm and the fused SwiGLU", i);
-    }
-    KUIPER_REQUIRE(n_ops == 1 || (sync != nullptr && (reinterpret_cast<uintptr_t>(sync) & 15) == 0),
-                   "awq_gemv_chain: a chain needs 16-byte aligned barrier counters");
-    KUIPER_REQUIRE(awq_gemv_mma_supported(128, 32), "awq_gemv_chain: tensor-map support is unavailable");
-    return awq_gemv_chain_launch(ops, n_ops, static_cast<int*>(sync), as_stream(stream));
-}

@@ -150,7 +150,7 @@ __device__ __forceinline__ void word_fma(uint32_t w, const ZeroPairs& z, const u
 // ACCUM: y += x.W with vector float reductions (no cross-CTA ordering, no tail); the caller guarantees
 // that y holds the addend (residual stream or zeros).  Otherwise y = x.W (+ residual) with the
 // deterministic slot / arrival-counter combine.
-template <int MT, int STAGES, bool ACCUM, bool NOMATH = false, bool NORM = false>
+template <int MT, int STAGES, bool ACCUM, bool NORM = false>
 __global__ void __launch_bounds__(kThreadsTma, (MT == 1 ? kCtasPerSm : 1))
 awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParams p) {
     extern __shared__ unsigned char smem_raw[];
@@ -345,10 +345,6 @@ awq_gemv_tma_kernel(const __grid_constant__ CUtensorMap tmap, const TmaGemvParam
                 // activations of the next unit this thread will see (same tile or the start of the next one)
                 kb++;
                 if (j + 1 < gu || more) load_x(kb == p.upt ? 0 : kb, xr);
-                if (NOMATH) {  // measurement aid: keep the loads alive, skip the arithmetic
-                    acc_g[0][0] += __uint_as_float((w[0].x ^ w[1].x ^ w[2].x ^ w[3].x ^ w[4].y ^ w[5].y ^ w[6].y ^ w[7].y ^ x16[0][0] ^ x16[7][0]) & 0x3fffffffu);
-                    continue;
-                }
 #pragma unroll
                 for (int i = 0; i < 8; i++) {
                     word_fma<MT>(w[i].x, z0, x16[i], acc_g, 0);
@@ -528,30 +524,16 @@ bool get_tensor_map(const int32_t* qweight, int K, int N, CUtensorMap* out) {
     return true;
 }
 
-int g_sm_count = 0;
-int sm_count() {
-    if (g_sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-        if (g_sm_count <= 0) g_sm_count = 148;
-    }
-    return g_sm_count;
-}
+int sm_count() { return device_sm_count(); }
 
-int g_tma_nomath = 0;
-
-template <int MT, int STAGES, bool ACCUM, bool NOMATH = false, bool NORM = false>
+template <int MT, int STAGES, bool ACCUM, bool NORM = false>
 int launch_tma(const CUtensorMap& map, const TmaGemvParams& p, int ctas, cudaStream_t stream) {
-    auto kern = awq_gemv_tma_kernel<MT, STAGES, ACCUM, NOMATH, NORM>;
+    auto kern = awq_gemv_tma_kernel<MT, STAGES, ACCUM, NORM>;
     const size_t smem = 128 + size_t(STAGES) * kStageBytes + size_t(kRowGroups) * MT * 1024 * 4;
-    static size_t configured = 0;
-    if (configured < smem) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-            set_error("awq_gemv_tma: cannot reserve %zu bytes of shared memory", smem);
-            return KUIPER_INTERNAL_ERROR;
-        }
-        configured = smem;
+    static size_t configured[kMaxDevices] = {};  // per instantiation and device
+    if (!ensure_dynamic_smem(kern, smem, configured)) {
+        set_error("awq_gemv_tma: cannot reserve %zu bytes of shared memory", smem);
+        return KUIPER_INTERNAL_ERROR;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas, 1, 1);
@@ -581,7 +563,8 @@ int awq_gemv_tma_status() {
 }
 
 void awq_gemv_tma_set_tuning(const char* key, int value) {
-    if (!strcmp(key, "gemv_nomath")) g_tma_nomath = value;
+    (void)key;
+    (void)value;
 }
 
 // Workspace layout of the TMA kernel: [counters: tiles ints][error word][partial slots].
@@ -628,8 +611,8 @@ int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* q
     long long ctas = (long long)sm_count() * (rows == 1 ? kCtasPerSm : 1);
     if (ctas > p.U) ctas = p.U;
     if (accumulate && norm_w) {
-        if (rows == 2) return launch_tma<2, 4, true, false, true>(map, p, int(ctas), stream);
-        return launch_tma<1, 5, true, false, true>(map, p, int(ctas), stream);
+        if (rows == 2) return launch_tma<2, 4, true, true>(map, p, int(ctas), stream);
+        return launch_tma<1, 5, true, true>(map, p, int(ctas), stream);
     }
     if (norm_w) {
         set_error("awq_gemv_tma: the fused input norm exists in accumulate mode only");
@@ -637,7 +620,6 @@ int awq_gemv_tma_launch(const float* x, const int32_t* qweight, const int32_t* q
     }
     if (accumulate) {
         if (rows == 2) return launch_tma<2, 4, true>(map, p, int(ctas), stream);
-        if (g_tma_nomath) return launch_tma<1, 5, true, true>(map, p, int(ctas), stream);
         return launch_tma<1, 5, true>(map, p, int(ctas), stream);
     }
     if (rows == 2) return launch_tma<2, 4, false>(map, p, int(ctas), stream);
@@ -662,7 +644,6 @@ constexpr size_t kNoAllocScratchBytes =
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
-constexpr int kMaxDevices = 64;
 void* g_noalloc_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
 std::mutex g_noalloc_mu;
 

@@ -65,6 +65,36 @@ inline int pdl_status(cudaError_t err, const char* what) {
 
 inline cudaStream_t as_stream(kuiper_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// Per-device facts and one-time settings.  cudaFuncSetAttribute and the SM count belong to a device, not to the
+// process, so both are tracked per device ordinal (a process may drive several GPUs).  Races between host threads
+// are benign: every writer stores the same value, and setting a function attribute twice is harmless.
+constexpr int kMaxDevices = 64;
+inline int current_device() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) d = 0;
+    return d;
+}
+inline int device_sm_count() {
+    static int count[kMaxDevices] = {};
+    const int d = current_device();
+    if (count[d] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) n = 148;
+        count[d] = n;
+    }
+    return count[d];
+}
+// raises the dynamic shared-memory limit of `kernel` on the current device the first time it is launched there;
+// `done` is the caller's per-instantiation table
+template <typename Kernel>
+inline bool ensure_dynamic_smem(Kernel kernel, size_t bytes, size_t (&done)[kMaxDevices]) {
+    const int d = current_device();
+    if (done[d] >= bytes && done[d] != 0) return true;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)) != cudaSuccess) return false;
+    done[d] = bytes;
+    return true;
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }
 // low / high bf16 of a packed 32-bit word
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }

@@ -51,7 +51,6 @@ enum class ModelBufferType {
     MatmulWorkspace = 36,
     MHAWorkspace = 37,
     GemmWorkspace = 38,  // fp16 copy of the activation rows for the tensor-core matmul
-    ChainSync = 39,      // arrival counters of the chained one-row matmul launch
 };
 }  // namespace model
 

@@ -72,6 +72,7 @@ private:
     base::Status upload_rows(const int32_t* tokens, const int32_t* pos, const int32_t* slot, int32_t M);
     base::Status ensure_graph(int32_t B);
     base::Status check_loaded() const;
+    base::Status check_exchange() const;
 
     int32_t local_heads() const { return config_.head_num / config_.tp_size; }
     int32_t local_kv_heads() const { return config_.kv_head_num / config_.tp_size; }
@@ -95,7 +96,6 @@ private:
     // graph launches once per kGraphUnroll tokens
     std::map<int32_t, cudaGraphExec_t> graphs_unrolled_;
     static constexpr int32_t kGraphUnroll = 4;
-    bool chain_decode_ = false;  // KUIPER_CHAIN_DECODE=1: O, gate|up, down and the next QKV of the one-row decode pass share one launch
     int32_t decode_batch_ = 0;
     int32_t kernels_per_step_ = 0;
     int32_t logit_rows_ = 0;  // rows (counted from the end of a pass) that get logits and a sampled id

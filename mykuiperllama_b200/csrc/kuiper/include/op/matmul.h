@@ -47,16 +47,10 @@ public:
     // scratch of the split-K kernel: kernel::matmul_quant_workspace_bytes(M, K, N) bytes, zero-initialised once
     void set_workspace(const tensor::Tensor& workspace);
     // scratch of the tensor-core path: kernel::matmul_quant_gemm_workspace_bytes(max rows, dim1) bytes, no
-    // initialisation needed; without it the first-generation GEMM kernel is used
+    // initialisation needed
     void set_gemm_workspace(const tensor::Tensor& workspace) { gemm_workspace_ = workspace; }
     // how the INT4 kernel rounds x: 1 = fp16 operand (default), 0 = fp32 operand
     void set_act_mode(int32_t act_mode) { act_mode_ = act_mode; }
-
-    // Several one-row accumulate-mode layers in one launch: layers[i] runs on inputs[i] -> outputs[i] in order, a
-    // later input may be an earlier output (decode: O -> gate|up -> down -> next layer's QKV).  Every layer keeps
-    // its own fused norm / SwiGLU setting.  `sync`: kernel::matmul_chain_sync_bytes() bytes, zeroed once.
-    static base::Status forward_chain(MatmulLayer* const* layers, const tensor::Tensor* inputs, const tensor::Tensor* outputs,
-                                      int32_t count, const tensor::Tensor& sync);
 
     int32_t out_features() const { return dim0_; }
     int32_t in_features() const { return dim1_; }

@@ -36,8 +36,9 @@ public:
     // in-place sum over all ranks of `count` fp32 values, enqueued on `stream`; rows that fit the one-shot
     // exchange go through it, everything else through ncclAllReduce
     base::Status all_reduce_sum(float* data, size_t count, cudaStream_t stream) const;
-    // synchronous health check of the one-shot path: error if a bounded wait on a peer ever ran out
-    base::Status one_shot_status() const;
+    // synchronous health check of the one-shot path: error if a bounded wait on a peer ever ran out (the result of
+    // that exchange, and of everything computed from it, is void); clear = true resets the error word once reported
+    base::Status one_shot_status(bool clear = false) const;
 
     int32_t rank() const { return rank_; }
     int32_t world_size() const { return world_size_; }

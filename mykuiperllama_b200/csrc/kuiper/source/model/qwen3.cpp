@@ -142,11 +142,6 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::MatmulWorkspace, dev(DataType::DataTypeInt8, {int32_t(ws_mm)})));
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::MHAWorkspace, dev(DataType::DataTypeInt8, {int32_t(ws_mha)})));
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::GemmWorkspace, dev(DataType::DataTypeInt8, {int32_t(ws_gemm)})));
-    {
-        const size_t sync_bytes = std::max<size_t>(kernel::matmul_chain_sync_bytes(), 16);
-        RETURN_IF_ERROR(insert_buffer(ModelBufferType::ChainSync, dev(DataType::DataTypeInt8, {int32_t(sync_bytes)})));
-        CUDA_OK(cudaMemset(const_cast<void*>(get_buffer(ModelBufferType::ChainSync).ptr<void>()), 0, sync_bytes));
-    }
     CUDA_OK(cudaMemset(get_buffer(ModelBufferType::MatmulWorkspace).ptr<void>(), 0, ws_mm));
     CUDA_OK(cudaMemset(get_buffer(ModelBufferType::MHAWorkspace).ptr<void>(), 0, ws_mha));
     // accumulating projections need their output buffers zero before the first pass
@@ -201,12 +196,6 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     // accumulate with their pre-norms fused in.
     accumulate_cols_ = c.act_mode == 1 && QKV % 32 == 0 && H % 32 == 0 && (2 * I) % 32 == 0;
     accumulate_ = accumulate_cols_ && c.tp_size == 1;
-    {
-        // opt-in: as measured, the grid barrier between two chained projections costs what a kernel boundary costs
-        const char* env = std::getenv("KUIPER_CHAIN_DECODE");
-        chain_decode_ = env && env[0] == '1';
-    }
-
     layers_.resize(size_t(c.layer_num));
     layer_loaded_.assign(size_t(c.layer_num), false);
     for (Qwen3Layer& L : layers_) {
@@ -430,25 +419,7 @@ base::Status Qwen3Model::run_pass(int32_t M, bool inputs_settled) {
     };
 
     RETURN_IF_ERROR(embedding_->forward(tokens, h));
-    // One-row decode pass: O -> gate|up -> down -> the next layer's QKV run as one chained launch per layer (the
-    // weight stream keeps running across the projection boundaries), with the attention kernel in between.
-    const bool chained = chain_decode_ && M == 1 && accumulate_ && inputs_settled && slots_distinct_;
-    if (chained) {
-        const Tensor& sync = get_buffer(ModelBufferType::ChainSync);
-        RETURN_IF_ERROR(layers_[0].qkv->forward(h, qkv));
-        for (size_t li = 0; li < layers_.size(); li++) {
-            Qwen3Layer& L = layers_[li];
-            RETURN_IF_ERROR(L.rope->forward_with_attention(qkv, pos, slot, cos_t, sin_t, seq_len, att, 1));
-            op::MatmulLayer* chain[4] = {L.o.get(), L.gate_up.get(), L.down.get(), nullptr};
-            const Tensor ins[4] = {att, h, gu, h};
-            const Tensor outs[4] = {h, gu, h, qkv};
-            int32_t count = 3;
-            if (li + 1 < layers_.size()) chain[count++] = layers_[li + 1].qkv.get();
-            RETURN_IF_ERROR(op::MatmulLayer::forward_chain(chain, ins, outs, count, sync));
-        }
-    }
     for (Qwen3Layer& L : layers_) {
-        if (chained) break;
         if (accumulate_cols_) {
             RETURN_IF_ERROR(L.qkv->forward(h, qkv));  // RMSNorm fused into the projection
         } else {
@@ -496,6 +467,13 @@ base::Status Qwen3Model::run_pass(int32_t M, bool inputs_settled) {
     return base::error::success();
 }
 
+// Called after a stream synchronisation: a tensor-parallel exchange whose bounded wait ran out leaves this rank
+// with a partial sum, so everything read back after it is void and the caller must hear about it.
+base::Status Qwen3Model::check_exchange() const {
+    if (config_.tp_size > 1 && communicator_) return communicator_->one_shot_status(true);
+    return base::error::success();
+}
+
 base::Status Qwen3Model::forward(const int32_t* tokens, const int32_t* pos, const int32_t* slot, int32_t M) {
     RETURN_IF_ERROR(check_loaded());
     if (!tokens || !pos || !slot) return base::error::invalid_argument("null input pointer");
@@ -512,6 +490,7 @@ base::Status Qwen3Model::predict(const int32_t* tokens, const int32_t* pos, cons
     CUDA_OK(cudaMemcpyAsync(st, get_buffer(ModelBufferType::NextTokens).ptr<void>(), size_t(M) * 4,
                             cudaMemcpyDeviceToHost, stream()));
     CUDA_OK(cudaStreamSynchronize(stream()));
+    RETURN_IF_ERROR(check_exchange());
     std::memcpy(next, st, size_t(M) * 4);
     return base::error::success();
 }
@@ -538,7 +517,7 @@ base::Status Qwen3Model::prefill(const int32_t* tokens, int32_t n, int32_t slot,
         }
     }
     CUDA_OK(cudaStreamSynchronize(stream()));
-    return base::error::success();
+    return check_exchange();
 }
 
 // ------------------------------------------------------------------ graph decode loop
@@ -622,6 +601,7 @@ base::Status Qwen3Model::decode_read(int32_t* tokens, int32_t B) {
     CUDA_OK(cudaMemcpyAsync(host_stage_, get_buffer(ModelBufferType::NextTokens).ptr<void>(), size_t(B) * 4,
                             cudaMemcpyDeviceToHost, stream()));
     CUDA_OK(cudaStreamSynchronize(stream()));
+    RETURN_IF_ERROR(check_exchange());
     std::memcpy(tokens, host_stage_, size_t(B) * 4);
     return base::error::success();
 }
@@ -640,6 +620,7 @@ base::Status Qwen3Model::decode_predict(const int32_t* tokens, int32_t B, int32_
     CUDA_OK(cudaMemcpyAsync(host_stage_ + R, get_buffer(ModelBufferType::NextTokens).ptr<void>(), size_t(B) * 4,
                             cudaMemcpyDeviceToHost, s));
     CUDA_OK(cudaStreamSynchronize(s));
+    RETURN_IF_ERROR(check_exchange());
     std::memcpy(next, host_stage_ + R, size_t(B) * 4);
     return base::error::success();
 }

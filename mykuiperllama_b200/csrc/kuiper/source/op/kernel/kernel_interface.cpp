@@ -256,45 +256,9 @@ MatmulKernel get_matmul_kernel(base::DeviceType d) { return pick<MatmulKernel>(d
 MatmulKernelQuant get_matmul_kernel_quant(base::DeviceType d) {
     return pick<MatmulKernelQuant>(d, matmul_kernel_quant_cu, "quantised matmul");
 }
-void matmul_chain_kernel_cu(const MatmulChainItem* items, int32_t count, int32_t group_size, const Tensor& sync, void* stream) {
-    CHECK(items != nullptr);
-    CHECK(count >= 1 && count <= matmul_chain_max_items());
-    require_cuda(sync, "matmul chain barrier counters");
-    CHECK(sync.byte_size() >= matmul_chain_sync_bytes());
-    kuiper_gemv_chain_op ops[4];
-    for (int32_t i = 0; i < count; i++) {
-        const MatmulChainItem& it = items[i];
-        CHECK(it.input && it.qweight && it.qzeros && it.scales && it.output);
-        require_cuda(*it.input, "matmul chain input");
-        require_cuda(*it.qweight, "matmul chain qweight");
-        require_cuda(*it.output, "matmul chain output");
-        CHECK_EQ(it.qweight->dims_size(), 2);
-        const int32_t K = it.qweight->get_dim(0), N = it.qweight->get_dim(1) * 8;
-        CHECK_EQ(it.input->size(), size_t(K) * (it.input_swiglu ? 2 : 1));
-        CHECK_EQ(it.output->size(), size_t(N));
-        if (it.input_norm_weight) CHECK_EQ(it.input_norm_weight->size(), size_t(K));
-        ops[i].x = it.input->ptr<float>();
-        ops[i].qweight = it.qweight->ptr<int32_t>();
-        ops[i].qzeros = it.qzeros->ptr<int32_t>();
-        ops[i].scales = it.scales->ptr<uint16_t>();
-        ops[i].y = out_ptr<float>(*it.output);
-        ops[i].norm_w = it.input_norm_weight ? it.input_norm_weight->ptr<uint16_t>() : nullptr;
-        ops[i].eps = it.eps;
-        ops[i].swiglu = it.input_swiglu ? 1 : 0;
-        ops[i].K = K;
-        ops[i].N = N;
-    }
-    KERNEL_OK(kuiper_awq_gemv_chain_f32(ops, count, group_size, const_cast<void*>(sync.ptr<void>()), as_stream(stream)));
-}
-
 MatmulKernelQuantAccum get_matmul_kernel_quant_accum(base::DeviceType d) {
     return pick<MatmulKernelQuantAccum>(d, matmul_kernel_quant_accum_cu, "accumulating quantised matmul");
 }
-MatmulChainKernel get_matmul_chain_kernel(base::DeviceType d) {
-    return pick<MatmulChainKernel>(d, matmul_chain_kernel_cu, "chained quantised matmul");
-}
-int32_t matmul_chain_max_items() { return 4; }
-size_t matmul_chain_sync_bytes() { return kuiper_awq_gemv_chain_sync_bytes(); }
 MatmulKernelQuantGemm get_matmul_kernel_quant_gemm(base::DeviceType d) {
     return pick<MatmulKernelQuantGemm>(d, matmul_kernel_quant_gemm_cu, "tensor-core quantised matmul");
 }

@@ -38,22 +38,6 @@ using MatmulKernelQuantAccum = void (*)(const tensor::Tensor& input, const tenso
                                         const tensor::Tensor* input_norm_weight, float eps, bool input_swiglu,
                                         void* stream);
 
-// Several one-row accumulating projections in one launch: output_i += op_i(input_i) . dequant(...) in order, where
-// a later input may be an earlier output (the kernel puts a grid barrier between two projections and keeps the
-// weight stream running across it).  `sync`: matmul_chain_sync_bytes() bytes, zeroed once.
-struct MatmulChainItem {
-    const tensor::Tensor* input = nullptr;
-    const tensor::Tensor* qweight = nullptr;
-    const tensor::Tensor* qzeros = nullptr;
-    const tensor::Tensor* scales = nullptr;
-    const tensor::Tensor* output = nullptr;
-    const tensor::Tensor* input_norm_weight = nullptr;  // bf16 [K] or null
-    float eps = 0.f;
-    bool input_swiglu = false;
-};
-using MatmulChainKernel = void (*)(const MatmulChainItem* items, int32_t count, int32_t group_size,
-                                   const tensor::Tensor& sync, void* stream);
-
 // Tensor-core path for M >= 16 rows: output = input . dequant(...) (+ residual), or output += ... when accumulate.
 using MatmulKernelQuantGemm = void (*)(const tensor::Tensor& input, const tensor::Tensor& qweight,
                                        const tensor::Tensor& qzeros, const tensor::Tensor& scales,
@@ -93,9 +77,6 @@ AddKernel get_add_kernel(base::DeviceType device_type);
 MatmulKernel get_matmul_kernel(base::DeviceType device_type);
 MatmulKernelQuant get_matmul_kernel_quant(base::DeviceType device_type);
 MatmulKernelQuantAccum get_matmul_kernel_quant_accum(base::DeviceType device_type);
-MatmulChainKernel get_matmul_chain_kernel(base::DeviceType device_type);
-int32_t matmul_chain_max_items();
-size_t matmul_chain_sync_bytes();
 MatmulKernelQuantGemm get_matmul_kernel_quant_gemm(base::DeviceType device_type);
 RMSNormKernel get_rmsnorm_kernel(base::DeviceType device_type);
 RoPEKernel get_rope_kernel(base::DeviceType device_type);

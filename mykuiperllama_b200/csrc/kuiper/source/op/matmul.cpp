@@ -107,34 +107,4 @@ base::Status MatmulLayer::forward() {
     return base::error::success();
 }
 
-base::Status MatmulLayer::forward_chain(MatmulLayer* const* layers, const tensor::Tensor* inputs, const tensor::Tensor* outputs,
-                                        int32_t count, const tensor::Tensor& sync) {
-    if (!layers || !inputs || !outputs || count < 1 || count > kernel::matmul_chain_max_items())
-        return base::error::invalid_argument("a matmul chain takes 1.." + std::to_string(kernel::matmul_chain_max_items()) + " layers");
-    kernel::MatmulChainItem items[4];
-    for (int32_t i = 0; i < count; i++) {
-        MatmulLayer* l = layers[i];
-        if (!l) return base::error::invalid_argument("null layer in a matmul chain");
-        l->set_input(0, inputs[i]);
-        l->set_output(0, outputs[i]);
-        base::Status status = l->check();
-        if (!status) return status;
-        if (!(l->is_quant_layer_ && l->accumulate_) || l->has_residual_ || l->group_size_ != layers[0]->group_size_ ||
-            l->device_type_ != layers[0]->device_type_)
-            return base::error::invalid_argument("a matmul chain takes quantised accumulate-mode layers of one group size");
-        const size_t in_row = size_t(l->dim1_) * (l->input_swiglu_ ? 2 : 1);
-        if (inputs[i].size() != in_row) return base::error::invalid_argument("a matmul chain takes one token row");
-        items[i].input = &l->get_input(0);
-        items[i].qweight = &l->get_weight(0);
-        items[i].qzeros = &l->get_weight(1);
-        items[i].scales = &l->scales_;
-        items[i].output = &l->get_output(0);
-        items[i].input_norm_weight = l->input_norm_.is_empty() ? nullptr : &l->input_norm_;
-        items[i].eps = l->input_norm_eps_;
-        items[i].input_swiglu = l->input_swiglu_;
-    }
-    kernel::get_matmul_chain_kernel(layers[0]->device_type_)(items, count, layers[0]->group_size_, sync, layers[0]->stream());
-    return base::error::success();
-}
-
 }  // namespace op

@@ -141,9 +141,14 @@ base::Status Communicator::enable_one_shot(size_t max_count) {
     return base::error::success();
 }
 
-base::Status Communicator::one_shot_status() const {
+base::Status Communicator::one_shot_status(bool clear) const {
     if (!one_shot_) return base::error::success();
-    if (kuiper_allreduce_status(state_) != 0) return base::error::internal_error(kuiper_last_error());
+    if (kuiper_allreduce_status(state_) != 0) {
+        const std::string msg = kuiper_last_error();
+        // the error word is sticky on the device; once reported it is cleared so that the next call starts clean
+        if (clear) cudaMemset(reinterpret_cast<char*>(state_) + sizeof(uint32_t), 0, sizeof(uint32_t));
+        return base::error::internal_error(msg);
+    }
     return base::error::success();
 }
 

@@ -50,6 +50,11 @@ def lib() -> C.CDLL:
     return _lib
 
 
+def set_num_threads(n: int) -> int:
+    """OpenMP threads of the oracle's loops (n <= 0 only queries); returns the number in effect."""
+    return int(lib().orc_set_num_threads(int(n)))
+
+
 def _p(a: np.ndarray):
     assert a.flags["C_CONTIGUOUS"], "oracle wants C-contiguous arrays"
     return a.ctypes.data_as(C.c_void_p)

@@ -86,6 +86,20 @@ void orc_f32_to_f16_n(const float* in, uint16_t* out, int64_t n) {
 void orc_bf16_to_f32_n(const uint16_t* in, float* out, int64_t n) {
     for (int64_t i = 0; i < n; i++) out[i] = orc_bf16_to_f32(in[i]);
 }
+/* number of OpenMP threads the oracle's loops use from now on (the timed CPU baseline sets this itself, because a
+ * launcher may have exported OMP_NUM_THREADS=1); returns the value in effect */
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+int orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
 static inline float round_act(float v, int mode) {
     if (mode == ORC_ROUND_FP16) return orc_f16_to_f32(orc_f32_to_f16(v));
     if (mode == ORC_ROUND_BF16) return orc_bf16_to_f32(orc_f32_to_bf16(v));

@@ -30,6 +30,9 @@ extern "C" {
 /* how an activation vector is rounded before it enters a matmul */
 enum { ORC_ROUND_NONE = 0, ORC_ROUND_FP16 = 1, ORC_ROUND_BF16 = 2 };
 
+/* OpenMP threads used by the loops below from now on (n <= 0: only query); returns the value in effect */
+int orc_set_num_threads(int n);
+
 /* scalar conversions (round to nearest even) */
 uint16_t orc_f32_to_f16(float f);
 float orc_f16_to_f32(uint16_t h);

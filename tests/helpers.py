@@ -43,3 +43,54 @@ def make_model_weights(oracle, cfg, seed=0, norm_jitter=0.02):
             lw[f"{name}_qw"], lw[f"{name}_qz"], lw[f"{name}_s"] = qw, qz, s
         weights["layers"].append(lw)
     return weights
+
+
+def make_model_weights_fast(oracle, cfg, seed=0, norm_jitter=0.02):
+    """Same distributions as make_model_weights for the large shapes (hidden 2560 / 4096, full vocabulary): the
+    random draws, the 4-bit quantisation (per group and column min-max, the oracle quantiser's rule) and the AWQ
+    packing run in torch on the GPU; the result comes back as numpy arrays that the oracle and the engine both load."""
+    import torch
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    H, D, I, g = cfg.hidden, cfg.head_dim, cfg.inter, cfg.group
+    QKV = (cfg.n_q_heads + 2 * cfg.n_kv_heads) * D
+    order = (0, 2, 4, 6, 1, 3, 5, 7)
+
+    def pack(v):  # [rows, N] integers 0..15 -> int32 [rows, N/8] in the AWQ nibble order
+        rows, N = v.shape
+        v = v.view(rows, N // 8, 8).to(torch.int64)
+        w = torch.zeros((rows, N // 8), dtype=torch.int64, device=dev)
+        for i, o in enumerate(order):
+            w |= v[:, :, o] << (4 * i)
+        return ((w + 2 ** 31) % 2 ** 32 - 2 ** 31).to(torch.int32).cpu().numpy()
+
+    def quant(K, N):
+        W = torch.randn((K, N), generator=gen, device=dev) * 0.02
+        Wg = W.view(K // g, g, N)
+        mn, mx = Wg.amin(1), Wg.amax(1)
+        s16 = ((mx - mn) / 15.0).clamp_min(1e-8).half()
+        s = s16.float()
+        z = torch.round(-mn / s).clamp_(0, 15)
+        q = (torch.round(Wg / s[:, None, :]) + z[:, None, :]).clamp_(0, 15).view(K, N)
+        return pack(q), pack(z), s16.view(torch.int16).cpu().numpy().view(np.uint16)
+
+    def bf16(t):
+        return t.bfloat16().view(torch.int16).cpu().numpy().view(np.uint16)
+
+    def norm(n):
+        return bf16(1.0 + norm_jitter * torch.randn(n, generator=gen, device=dev))
+
+    weights = {
+        "embed": bf16(torch.randn((cfg.vocab, H), generator=gen, device=dev) * 0.02),
+        "final_norm": norm(H),
+        "lm_head": bf16(torch.randn((cfg.vocab, H), generator=gen, device=dev) * 0.02),
+        "layers": [],
+    }
+    for _ in range(cfg.n_layers):
+        lw = {"input_norm": norm(H), "post_norm": norm(H), "q_norm": norm(D), "k_norm": norm(D)}
+        for name, (K, N) in {"qkv": (H, QKV), "o": (cfg.n_q_heads * D, H), "gu": (H, 2 * I), "down": (I, H)}.items():
+            lw[f"{name}_qw"], lw[f"{name}_qz"], lw[f"{name}_s"] = quant(K, N)
+        weights["layers"].append(lw)
+    torch.cuda.empty_cache()
+    return weights

@@ -99,36 +99,6 @@ def test_awq_gemv_fp16_mode_matches_mirrored_oracle(cuda, oracle):
         assert rel_err(y, ref16) <= 2e-6
 
 
-@pytest.fixture
-def int8_kernel(cuda):
-    """One-row launches go through the integer tensor-core kernel (opt-in)."""
-    cuda.set_tuning("gemv_int8", 1)
-    yield
-    cuda.set_tuning("gemv_int8", 0)
-
-
-@pytest.mark.parametrize("scale", [1.0, 1e-6, 3e4])
-def test_awq_gemv_one_row_integer_kernel_keeps_fp32_activations(cuda, oracle, int8_kernel, scale):
-    # one token row goes through the integer tensor path: activations are block-scaled 30-bit integers, all sums
-    # exact until the group ends - the result matches the oracle on the unrounded fp32 activations, also when the
-    # activations are tiny, large, or dominated by a few outliers
-    rng = np.random.default_rng(11)
-    K, N = 4096, 1024
-    q, z, s = awq_random(rng, K, N)
-    qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
-    x = (rng.standard_normal((1, K)) * scale).astype(np.float32)
-    x[0, ::97] *= 300.0  # outliers inside many groups
-    ref = oracle.awq_gemv(x, qw, qz, su, acc_double=True)
-    ws = cuda.awq_gemv_workspace(1, K, N)
-    y = cuda.awq_gemv(dev(x), dev(qw), dev(qz), dev(su, torch.float16), workspace=ws, act_mode=1)
-    ya = torch.zeros((1, N), device="cuda")
-    cuda.awq_gemv_accum(dev(x), dev(qw), dev(qz), dev(su, torch.float16), ya)
-    torch.cuda.synchronize()
-    assert rel_err(y.cpu().numpy(), ref) <= 2e-6
-    assert rel_err(ya.cpu().numpy(), ref) <= 2e-6
-    cuda.awq_gemv_status()  # raises if a bounded pipeline wait ran out
-
-
 @pytest.mark.parametrize("M,K,N", [(1, 1024, 4096), (1, 4096, 6144), (1, 2560, 2560), (2, 1024, 3072), (3, 3072, 1024),
                                    (5, 512, 2048), (8, 256, 1056), (1, 128, 32), (1, 12288, 4096)])
 @pytest.mark.parametrize("rows", [0, 4, 8, 16])
@@ -196,9 +166,11 @@ def test_swiglu_fused_into_accumulating_gemv(cuda, oracle, M, K, N):
     cuda.awq_gemv_status()
 
 
-@pytest.mark.parametrize("K,N", [(4096, 4096), (12288, 4096), (2560, 1056), (128, 32)])
-def test_integer_kernel_accumulate_norm_and_swiglu_variants(cuda, oracle, int8_kernel, K, N):
-    rng = np.random.default_rng(K + 3 * N)
+@pytest.mark.parametrize("K,N", [(4096, 24576), (2560, 19456), (9728, 2560), (2560, 6144)])
+def test_awq_gemv_layer_shapes_of_the_4b_and_8b_models_match_oracle(cuda, oracle, K, N):
+    # the widest projection of the 8B shape and the three distinct 4B shapes, against the oracle (not a property test):
+    # accumulate entry, fused-RMSNorm entry and - with K as the SwiGLU width - the fused-SwiGLU entry
+    rng = np.random.default_rng(K * 7 + N)
     q, z, s = awq_random(rng, K, N)
     qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
     W = (dev(qw), dev(qz), dev(su, torch.float16))
@@ -206,81 +178,29 @@ def test_integer_kernel_accumulate_norm_and_swiglu_variants(cuda, oracle, int8_k
     x = rng.standard_normal((1, K)).astype(np.float32)
     y = dev(addend)
     cuda.awq_gemv_accum(dev(x), *W, y)
-    assert rel_err(y.cpu().numpy(), oracle.awq_gemv(x, qw, qz, su).astype(np.float64) + addend) <= 2e-6
+    ref = oracle.awq_gemv(x, qw, qz, su, acc_double=True)
+    err = rel_err(y.cpu().numpy(), ref.astype(np.float64) + addend)
+    assert err <= SPEC_TOL and err <= 1e-3                      # against the un-rounded oracle: the workload's bound
+    ref16 = oracle.awq_gemv(x, qw, qz, su, acc_double=True, act_round=oracle.ROUND_FP16)
+    assert rel_err(y.cpu().numpy(), ref16.astype(np.float64) + addend) <= 2e-6   # mirrored operand rounding
+    # ordered-combine entry (deterministic summation order) on the same matrix
+    yo = cuda.awq_gemv(dev(x), *W, residual=dev(addend))
+    assert rel_err(yo.cpu().numpy(), ref16.astype(np.float64) + addend) <= 2e-6
     nw = oracle.f32_to_bf16((1 + 0.1 * rng.standard_normal(K)).astype(np.float32))
+    h = (x * 2.5).astype(np.float32)
     y = dev(addend)
-    cuda.rmsnorm_awq_gemv_accum(dev(x * 2.5), dev(nw), 1e-6, *W, y)
-    assert rel_err(y.cpu().numpy(), oracle.awq_gemv(oracle.rmsnorm(x * 2.5, nw, 1e-6), qw, qz, su).astype(np.float64) + addend) <= 1e-5
+    cuda.rmsnorm_awq_gemv_accum(dev(h), dev(nw), 1e-6, *W, y)
+    ref = oracle.awq_gemv(oracle.rmsnorm(h, nw, 1e-6), qw, qz, su, acc_double=True).astype(np.float64) + addend
+    err = rel_err(y.cpu().numpy(), ref)
+    assert err <= SPEC_TOL and err <= 1e-3
     gu = rng.standard_normal((1, 2 * K)).astype(np.float32)
     y = dev(addend)
     cuda.swiglu_awq_gemv_accum(dev(gu), *W, y)
     act = oracle.swiglu(gu[0, :K], gu[0, K:])[None, :]
-    assert rel_err(y.cpu().numpy(), oracle.awq_gemv(act, qw, qz, su).astype(np.float64) + addend) <= 1e-5
+    ref = oracle.awq_gemv(act, qw, qz, su, acc_double=True, act_round=oracle.ROUND_FP16).astype(np.float64) + addend
+    err = rel_err(y.cpu().numpy(), ref)
+    assert err <= SPEC_TOL and err <= 1e-5
     cuda.awq_gemv_status()
-
-
-@pytest.mark.parametrize("H,I,QKV,n_ops", [(1024, 3072, 2048, 4), (4096, 12288, 6144, 4), (256, 512, 384, 4), (1024, 3072, 2048, 2)])
-def test_awq_gemv_chain_runs_a_decode_layer_in_one_launch(cuda, oracle, int8_kernel, H, I, QKV, n_ops):
-    # O -> gate|up (fused norm) -> down (fused SwiGLU) -> next QKV (fused norm) in one launch with grid barriers
-    # between the projections; checked against the oracle's chain and against four separate launches
-    rng = np.random.default_rng(H + I + n_ops)
-
-    def weights(K, N):
-        q, z, s = awq_random(rng, K, N)
-        return oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
-
-    Wo, Wgu, Wd, Wqkv = weights(H, H), weights(H, 2 * I), weights(I, H), weights(H, QKV)
-    att = rng.standard_normal((1, H)).astype(np.float32)
-    h0 = rng.standard_normal((1, H)).astype(np.float32)
-    nw1 = oracle.f32_to_bf16((1 + 0.1 * rng.standard_normal(H)).astype(np.float32))
-    nw2 = oracle.f32_to_bf16((1 + 0.1 * rng.standard_normal(H)).astype(np.float32))
-    # oracle chain (scales are small, so keep everything in float64 until the comparison)
-    h1 = h0.astype(np.float64) + oracle.awq_gemv(att, *Wo)
-    gu = oracle.awq_gemv(oracle.rmsnorm(h1.astype(np.float32), nw1, 1e-6), *Wgu)
-    act = oracle.swiglu(gu[0, :I], gu[0, I:])[None, :]
-    h2 = h1 + oracle.awq_gemv(act, *Wd)
-    qkv = oracle.awq_gemv(oracle.rmsnorm(h2.astype(np.float32), nw2, 1e-6), *Wqkv)
-
-    def dw(W):
-        return dev(W[0]), dev(W[1]), dev(W[2], torch.float16)
-
-    dWo, dWgu, dWd, dWqkv = dw(Wo), dw(Wgu), dw(Wd), dw(Wqkv)
-    d_att, d_nw1, d_nw2 = dev(att), dev(nw1), dev(nw2)
-    sync = cuda.awq_gemv_chain_sync()
-
-    def run_chain():
-        t_h, t_gu, t_qkv = dev(h0), torch.zeros((1, 2 * I), device="cuda"), torch.zeros((1, QKV), device="cuda")
-        ops = [dict(x=d_att, qweight=dWo[0], qzeros=dWo[1], scales=dWo[2], y=t_h),
-               dict(x=t_h, qweight=dWgu[0], qzeros=dWgu[1], scales=dWgu[2], y=t_gu, norm_w=d_nw1, eps=1e-6),
-               dict(x=t_gu, qweight=dWd[0], qzeros=dWd[1], scales=dWd[2], y=t_h, swiglu=True),
-               dict(x=t_h, qweight=dWqkv[0], qzeros=dWqkv[1], scales=dWqkv[2], y=t_qkv, norm_w=d_nw2, eps=1e-6)]
-        cuda.awq_gemv_chain(ops[:n_ops], sync)
-        torch.cuda.synchronize()
-        return t_h.cpu().numpy(), t_gu.cpu().numpy(), t_qkv.cpu().numpy()
-
-    got_h, got_gu, got_qkv = run_chain()
-    cuda.awq_gemv_status()
-    assert not sync.any(), "the barrier counters must be back at zero after the launch"
-    if n_ops == 4:
-        assert rel_err(got_h, h2) <= 1e-5
-        assert rel_err(got_qkv, qkv) <= 1e-5
-    else:
-        assert rel_err(got_h, h1) <= 1e-5
-    assert rel_err(got_gu, gu) <= 1e-5
-    # a second launch on the same counters
-    again_h, again_gu, again_qkv = run_chain()
-    assert rel_err(again_h, got_h) <= 1e-5 and rel_err(again_qkv, got_qkv if n_ops == 4 else again_qkv) <= 1e-5
-    # the same projections as separate launches
-    t_h, t_gu, t_qkv = dev(h0), torch.zeros((1, 2 * I), device="cuda"), torch.zeros((1, QKV), device="cuda")
-    cuda.awq_gemv_accum(d_att, *dWo, t_h)
-    cuda.rmsnorm_awq_gemv_accum(t_h, d_nw1, 1e-6, *dWgu, t_gu)
-    if n_ops == 4:
-        cuda.swiglu_awq_gemv_accum(t_gu, *dWd, t_h)
-        cuda.rmsnorm_awq_gemv_accum(t_h, d_nw2, 1e-6, *dWqkv, t_qkv)
-    torch.cuda.synchronize()
-    assert rel_err(got_h, t_h.cpu().numpy()) <= 1e-5
-    assert rel_err(got_gu, t_gu.cpu().numpy()) <= 1e-5
-    assert rel_err(got_qkv, t_qkv.cpu().numpy()) <= 1e-5 or n_ops != 4
 
 
 def test_awq_gemv_ragged_width_uses_generic_kernel(cuda, oracle):
@@ -328,10 +248,9 @@ def test_awq_gemv_rejects_bad_arguments(cuda):
 
 
 # ----------------------------------------------------------------------------- INT4 GEMM (tcgen05), M >= 16
-@pytest.mark.parametrize("gen", [2, 1])
 @pytest.mark.parametrize("M,K,N", [(16, 128, 128), (16, 256, 136), (100, 1024, 384), (128, 4096, 1024), (129, 512, 256),
                                    (300, 1024, 4104), (16, 4096, 6144), (64, 3072, 1024)])
-def test_awq_gemm_tensor_core(cuda, oracle, M, K, N, gen):
+def test_awq_gemm_tensor_core(cuda, oracle, M, K, N):
     rng = np.random.default_rng(M + K + N)
     q, z, s = awq_random(rng, K, N)
     qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
@@ -339,7 +258,7 @@ def test_awq_gemm_tensor_core(cuda, oracle, M, K, N, gen):
     res = rng.standard_normal((M, N)).astype(np.float32)
     ref = oracle.awq_gemv(x, qw, qz, su, act_round=oracle.ROUND_FP16).astype(np.float64)
     tx, tqw, tqz, ts = dev(x), dev(qw), dev(qz), dev(su, torch.float16)
-    ws = cuda.awq_gemm_workspace(M, K) if gen == 2 else None  # None: first-generation kernel (converts x per tile)
+    ws = cuda.awq_gemm_workspace(M, K)
     y = cuda.awq_gemm(tx, tqw, tqz, ts, workspace=ws)
     y_res = cuda.awq_gemm(tx, tqw, tqz, ts, residual=dev(res), workspace=ws)
     y_acc = dev(res)
@@ -422,7 +341,7 @@ def test_allreduce_oneshot_wait_is_bounded(cuda):
         cuda.allreduce_oneshot(data, 0, world, bufs, max_count, state)
         torch.cuda.synchronize()
     finally:
-        cuda.set_tuning("allreduce_timeout_ms", 1000)
+        cuda.set_tuning("allreduce_timeout_ms", 5000)
     with pytest.raises(KuiperError) as e:
         cuda.allreduce_status(state)
     assert e.value.code == 5 and "rank 1" in str(e.value)
@@ -577,6 +496,46 @@ def test_flash_decode(cuda, oracle, B, Nq, Nkv, lens, splits, tensor_cores):
     assert np.array_equal(out1, out2)
     err = rel_err(out1, ref)
     # 16 significant bits in q and in the probabilities on the tensor-core path
+    assert err <= SPEC_TOL and err <= (5e-5 if tensor_cores else 1e-5)
+
+
+_C3_CACHE = {}
+
+
+def _c3_case(oracle, name):
+    """Attention-workload extremes: batch 16 with mixed lengths (one at 32 768) and batch 1 at 32 768.  The caches are
+    drawn on the GPU (N(0,1) rounded to bf16) and copied to the host for the oracle; the oracle's answer is kept for
+    the second kernel."""
+    if name in _C3_CACHE:
+        return _C3_CACHE[name]
+    lens = {"b16": [32768, 1, 64, 65, 4096, 777, 2048, 16384, 300, 1024, 5000, 63, 192, 8191, 12000, 31], "b1": [32768]}[name]
+    B, Nq, Nkv, D, max_seq = len(lens), 32, 8, 128, 32768
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(321 + B)
+    kc = torch.randn((B, Nkv, max_seq, D), device="cuda", generator=gen).bfloat16()
+    vc = torch.randn((B, Nkv, max_seq, D), device="cuda", generator=gen).bfloat16()
+    q = torch.randn((B, Nq, D), device="cuda", generator=gen)
+    seq = np.array(lens, np.int32)
+    slot = np.arange(B, dtype=np.int32)[::-1].copy()
+    ref = oracle.attention(q.cpu().numpy(), kc.view(torch.int16).cpu().numpy().view(np.uint16),
+                           vc.view(torch.int16).cpu().numpy().view(np.uint16), seq, slot)
+    _C3_CACHE.clear()  # one case (up to 2 GB of cache) alive at a time
+    _C3_CACHE[name] = (q, kc, vc, seq, slot, ref)
+    return _C3_CACHE[name]
+
+
+@pytest.mark.parametrize("name", ["b16", "b1"])
+@pytest.mark.parametrize("tensor_cores", [1, 0])
+def test_flash_decode_batch16_and_32k(cuda, oracle, name, tensor_cores):
+    q, kc, vc, seq, slot, ref = _c3_case(oracle, name)
+    B, Nq, D = q.shape
+    cuda.set_tuning("flash_mma", tensor_cores)
+    try:
+        ws = cuda.flash_decode_workspace(B, Nq, D, kc.shape[2])
+        out = cuda.flash_decode(q, kc, vc, dev(seq), dev(slot), workspace=ws).cpu().numpy()
+    finally:
+        cuda.set_tuning("flash_mma", FLASH_MMA_DEFAULT)
+    err = rel_err(out, ref)
     assert err <= SPEC_TOL and err <= (5e-5 if tensor_cores else 1e-5)
 
 

@@ -20,7 +20,8 @@ def _dev(a, dtype=None):
     return t if dtype is None else t.view(dtype)
 
 
-@pytest.mark.parametrize("M,K,N,residual", [(1, 4096, 4096, True), (3, 1024, 3072, False), (1, 256, 1056, True)])
+@pytest.mark.parametrize("M,K,N,residual", [(1, 4096, 4096, True), (3, 1024, 3072, False), (1, 256, 1056, True),
+                                            (8, 256, 32768, False)])  # last: both limits at once (8 rows, widest N)
 def test_noalloc_entry_matches_workspace_entry(cuda, oracle, M, K, N, residual):
     from mykuiperllama_b200._lib import check, kernels
     lib = kernels()
@@ -32,17 +33,31 @@ def test_noalloc_entry_matches_workspace_entry(cuda, oracle, M, K, N, residual):
     x = _dev(rng.standard_normal((M, K)).astype(np.float32))
     res = _dev(rng.standard_normal((M, N)).astype(np.float32)) if residual else None
     want = cuda.awq_gemv(x, qw, qz, sc, residual=res).cpu().numpy()  # existing entry point, caller workspace
+    # the checker's answer for the same inputs (activation rounded to fp16 as the kernel does)
+    ref = oracle.awq_gemv(x.cpu().numpy(), oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16), acc_double=True,
+                          act_round=oracle.ROUND_FP16).astype(np.float64)
+    if residual:
+        ref = ref + res.cpu().numpy()
     stream = torch.cuda.current_stream().cuda_stream
     outs = []
-    for _ in range(2):  # the second call finds the scratch as the first one left it
-        y = torch.full((M, N), float("nan"), device="cuda")
+    ys = [torch.full((M, N), float("nan"), device="cuda") for _ in range(2)]
+    free_before = None
+    for i in range(2):  # the second call finds the scratch as the first one left it
+        y = ys[i]
+        if i == 1:
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
         check(lib.kuiper_awq_gemv_f32_noalloc(x.data_ptr(), qw.data_ptr(), qz.data_ptr(), sc.data_ptr(), y.data_ptr(),
                                               res.data_ptr() if residual else None, M, K, N, 128, stream))
         torch.cuda.synchronize()
+        if i == 1:
+            # the defining property: the device's free memory is the same before and after the call
+            assert torch.cuda.mem_get_info()[0] == free_before
         outs.append(y.cpu().numpy())
     for y in outs:
         # same kernel, possibly a different grid: only the order of the fp32 partial sums may differ
         assert rel_err(y, want) <= 2e-6
+        assert rel_err(y, ref) <= 2e-6
     assert np.array_equal(outs[0], outs[1])
 
 

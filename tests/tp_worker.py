@@ -20,7 +20,8 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dist.init_process_group("gloo")  # host plumbing only; the engine talks NCCL itself
-    cfg = dict(n_layers=2, hidden=256, n_q_heads=4, n_kv_heads=2, head_dim=128, inter=512, vocab=1000, max_seq=64,
+    # 8 kv heads and an intermediate width of 8 groups: shards evenly over 2, 4 and 8 ranks
+    cfg = dict(n_layers=2, hidden=512, n_q_heads=16, n_kv_heads=8, head_dim=128, inter=1024, vocab=1000, max_seq=64,
                max_batch=1)
     ocfg = orc.ModelConfig(**cfg, act_round=orc.ROUND_FP16)
     weights = make_model_weights(orc, ocfg, seed=21)
