@@ -397,6 +397,12 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         barrier()
     if world > 1:
         eng.tp_status()  # raises if a bounded wait of the peer exchange ran out during the timed loop
+    if args.flash_trace:
+        # measurement build (KUIPER_TRACE=1): per-CTA clock readings of the step's last attention launch
+        from mykuiperllama_b200._lib import kernels
+        trace = np.zeros((1024, 10), np.int64)
+        got = kernels().kuiper_flash_trace_read(trace.ctypes.data, trace.size)
+        np.save(args.flash_trace, trace[: max(got, 0) // 10])
     ms = e0.elapsed_time(e1)
     t = torch.tensor([ms], device=device)
     if world > 1:
@@ -678,6 +684,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (config 4 of the workload list uses 16)")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for a profiler run with profile-from-start off)")
+    ap.add_argument("--flash-trace", default=None, metavar="FILE.npy",
+                    help="with the KUIPER_TRACE=1 build: save the per-CTA clock readings of the last attention launch")
     ap.add_argument("--prompt", type=int, default=None, help="override the workload's prompt length (profiling aid)")
     ap.add_argument("--tuning", action="append", default=[], metavar="KEY=VALUE",
                     help="kernel tuning switch applied before the run (profiling aid), e.g. flash_mma_fused=0")

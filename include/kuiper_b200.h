@@ -238,6 +238,14 @@ KUIPER_API int kuiper_rope_flash_decode(float* qkv, const uint16_t* q_norm_w, co
                                         float* clear_extra, int64_t clear_extra_count, void* workspace,
                                         size_t workspace_bytes, kuiper_stream_t stream);
 
+#ifdef KUIPER_TRACE
+/* Measurement builds only (compiled with -DKUIPER_TRACE; absent from the shipped library): per-CTA clock readings of
+ * the last launch of the tensor-core attention kernel, [CTA][10] int64 (slot 0 global timer in ns at entry, then SM
+ * clock at 1 entry, 2 early fetches issued, 3 dependency wait passed, 4 q ready, 5 cache rows processed, 6 partial
+ * stored, 7 arrival counter answered, 8 slices combined, 9 output stored).  Synchronises; returns the number of values copied or -1. */
+KUIPER_API int kuiper_flash_trace_read(int64_t* out, int max_values);
+#endif
+
 /* ---- SwiGLU: placeholder kuiper/include/op/swiglu.h:1-10 ---- */
 /* out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]; gate_up is [M, 2I]; clear_input != 0 zeroes gate_up afterwards */
 KUIPER_API int kuiper_swiglu_f32(float* gate_up, float* out, int M, int I, int clear_input, kuiper_stream_t stream);

@@ -20,7 +20,10 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 OBJ_DIR = os.path.join(PKG, "lib", "obj")
 
-KERNEL_LIB = os.path.join(LIB_DIR, "libkuiper_b200.so")
+# KUIPER_TRACE=1 in the environment selects a second kernel library built with -DKUIPER_TRACE (per-CTA clock
+# readings inside the kernels, read back with kuiper_*_trace_read); the shipped library has none of it
+TRACE = os.environ.get("KUIPER_TRACE", "0") == "1"
+KERNEL_LIB = os.path.join(LIB_DIR, "libkuiper_b200_trace.so" if TRACE else "libkuiper_b200.so")
 HOST_LIB = os.path.join(LIB_DIR, "libkuiper_llama.so")
 
 NVCC_FLAGS = [
@@ -58,9 +61,9 @@ def build_kernels(force: bool = False, verbose: bool = False, ptxas_info: bool =
     srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")))
     hdrs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cuh"))) + [os.path.join(ROOT, "include", "kuiper_b200.h")]
     objs = []
-    flags = NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else [])
+    flags = NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + (["-DKUIPER_TRACE=1"] if TRACE else [])
     for src in srcs:
-        obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+        obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ("_trace.o" if TRACE else ".o"))
         objs.append(obj)
         if force or ptxas_info or _stale(obj, [src] + hdrs):
             _run([_nvcc(), *flags, "-I", os.path.join(ROOT, "include"), "-I", os.path.join(CSRC, "kernels"),

@@ -81,6 +81,8 @@ def kernels() -> C.CDLL:
             _build.build_kernels()
         lib = C.CDLL(path, mode=C.RTLD_GLOBAL)
         _bind(lib, KERNEL_API)
+        if _build.TRACE:  # measurement build only
+            _bind(lib, {"kuiper_flash_trace_read": (_i32, [_vp, _i32])})
         _kernels = lib
     return _kernels
 

@@ -28,6 +28,25 @@ int g_force_splits = 0;
 int g_flash_early = 1;  // 0: ignore fresh_rows, touch nothing before the dependent-launch wait
 int g_flash_mma_fused = 1;  // the fused decode kernel (rotary + append + attention) also uses the tensor cores (0: SIMT)
 int g_flash_mma = 1;    // the stand-alone attention call runs its contractions on the tensor cores (0: SIMT kernel)
+int g_flash_wide = 1;   // fused tensor-core kernel: eight-warp CTAs when the whole grid is one wave of them (0: always four warps)
+
+// Build flag KUIPER_TRACE (off in the shipped library): every CTA of the tensor-core attention kernel stores clock
+// readings at its milestones; kuiper_flash_trace_read() copies those of the last launch to the host.
+// slot 0: global timer (ns) at entry; then SM clock at 1 entry, 2 early fetches issued, 3 dependency wait passed,
+// 4 q / appended row ready, 5 cache rows processed, 6 partial stored and fenced, 7 arrival counter answered,
+// 8 slices combined, 9 output stored (last CTA of a kv head only)
+#ifdef KUIPER_TRACE
+constexpr int kFlashTraceCtas = 1024, kFlashTraceSlots = 10;
+__device__ long long g_flash_trace[kFlashTraceCtas * kFlashTraceSlots];
+__device__ __forceinline__ void flash_trace(int slot) {
+    if (threadIdx.x == 0) {
+        const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        if (cta < kFlashTraceCtas) g_flash_trace[cta * kFlashTraceSlots + slot] = slot == 0 ? (long long)globaltimer_ns() : clock64();
+    }
+}
+#else
+__device__ __forceinline__ void flash_trace(int) {}
+#endif
 
 struct FlashParams {
     const float* q;       // [M, Nq, 128]
@@ -472,20 +491,49 @@ __device__ __forceinline__ void split_bf16x2(float x, float y, uint32_t& hi, uin
     lo = uint32_t(float_to_bf16_bits(xr)) | (uint32_t(float_to_bf16_bits(yr)) << 16);
 }
 
-// stand-alone: five CTAs per SM (96 registers) - the kernel is bound by memory latency, so resident warps matter more
-// than a few spilled values; fused: the rows fetched ahead of the wait stay in registers across the prologue, three CTAs
-template <int R, bool FUSED>
-__global__ void __launch_bounds__(kWarps * 32, FUSED ? 3 : 5)
+// q/k RMSNorm over the head + half-split rotary with the norm weights and the rotary row already in registers
+// (w: elements lane, lane+32, lane+64, lane+96 of the bf16 weight; cs: cos[lane], cos[lane+32], sin[lane], sin[lane+32]).
+// Same arithmetic, in the same order, as head_norm_rope.
+__device__ __forceinline__ void head_norm_rope_regs(float a0, float a1, float b0, float b1, const float (&w)[4],
+                                                    const float (&cs)[4], float eps, float (&out)[4]) {
+    float ss = a0 * a0;
+    ss = fmaf(a1, a1, ss);
+    ss = fmaf(b0, b0, ss);
+    ss = fmaf(b1, b1, ss);
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss / float(128) + eps);
+    const float x0 = (a0 * rstd) * w[0];
+    const float x1 = (a1 * rstd) * w[1];
+    const float y0 = (b0 * rstd) * w[2];
+    const float y1 = (b1 * rstd) * w[3];
+    out[0] = __fsub_rn(__fmul_rn(x0, cs[0]), __fmul_rn(y0, cs[2]));
+    out[1] = __fsub_rn(__fmul_rn(x1, cs[1]), __fmul_rn(y1, cs[3]));
+    out[2] = __fadd_rn(__fmul_rn(y0, cs[0]), __fmul_rn(x0, cs[2]));
+    out[3] = __fadd_rn(__fmul_rn(y1, cs[1]), __fmul_rn(x1, cs[3]));
+}
+
+// Launch shapes.  Stand-alone: four warps, five CTAs per SM (96 registers) - long caches are bound by memory latency, so
+// resident warps matter more than a few spilled values.  Fused, four warps: the rows fetched ahead of the wait stay in
+// registers across the prologue, three CTAs per SM.  Fused, eight warps: one CTA per SM and one 128-row step per CTA -
+// the shape for a single sequence at a context of a few thousand rows, where the kernel is a chain of latencies and the
+// number of slices the last CTA has to combine is what counts.
+template <int R, bool FUSED, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, FUSED ? (WARPS == 8 ? 1 : 3) : 5)
 flash_decode_mma_kernel(const FlashParams p) {
-    __shared__ float s_o[kWarps][R][kD];
+    constexpr int kBlk = WARPS * 16;  // cache rows per CTA step
+    constexpr int kThreads = WARPS * 32;
+    __shared__ float s_o[WARPS][R][kD];
     __shared__ float s_q[FUSED ? R : 1][kD];
-    __shared__ float s_ml[kWarps][R][2];
+    __shared__ float s_ml[WARPS][R][2];
+    __shared__ __align__(16) uint16_t s_new[FUSED ? 2 : 1][kD];  // fused: the K / V row appended by this CTA
     __shared__ int s_last;
 
     const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;  // fragment row / column group and thread in group
 
+    flash_trace(0);
+    flash_trace(1);
     pdl_launch_dependents();
     // fused: rows older than this pass are fetched ahead of the dependency wait, exactly as in the SIMT kernel
     // (fresh_rows, re-check of seq_len / slot after the wait); the stand-alone call waits first
@@ -496,17 +544,21 @@ flash_decode_mma_kernel(const FlashParams p) {
     const uint16_t *kb, *vb;
     // first step of this warp: rows base0 + g and base0 + g + 8, 16 bytes of every 32-dimension chunk per lane
     uint4 k0[4], k1[4], v0[4], v1[4];
+    // fused: norm weight of the head this warp prepares (q heads: warps 0..R-1 and so on; k: the last warp) and the
+    // rotary row of position seq_len - 1, also fetched ahead of the wait (they do not depend on the previous kernel
+    // beyond seq_len, which is re-checked)
+    float nw[4] = {1.f, 1.f, 1.f, 1.f}, nwk[4] = {1.f, 1.f, 1.f, 1.f}, cs[4] = {1.f, 1.f, 0.f, 0.f};
     while (true) {
         L = __ldcg(p.seq_len + m);
         sl = __ldcg(p.slot + m);
         const int L_seen = L, sl_seen = sl;
         L = L < 0 ? 0 : (L > p.max_seq ? p.max_seq : L);
         sl = sl < 0 ? 0 : (sl >= p.n_slots ? p.n_slots - 1 : sl);
-        const int blocks = max((L + 63) / 64, 1);
+        const int blocks = max((L + kBlk - 1) / kBlk, 1);
         const int per = (blocks + p.S - 1) / p.S;
         n_active = (blocks + per - 1) / per;
-        begin = split * per * 64;
-        end = min(L, begin + per * 64);
+        begin = split * per * kBlk;
+        end = min(L, begin + per * kBlk);
         const size_t head_off = (size_t(sl) * p.Nkv + kvh) * p.max_seq * kD;
         kb = p.kc + head_off;
         vb = p.vc + head_off;
@@ -525,8 +577,25 @@ flash_decode_mma_kernel(const FlashParams p) {
             v0[i] = f0 ? ld_stream_u4(vb + size_t(base0 + g) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
             v1[i] = f1 ? ld_stream_u4(vb + size_t(base0 + g + 8) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
         }
+        if (FUSED && has_rows) {
+            // the position of a decode row is seq_len - 1 (the caller's contract for the fused call)
+            int pp = L - 1;
+            pp = pp < 0 ? 0 : pp;
+            const float* cos_row = p.cos_t + size_t(pp) * 64;
+            const float* sin_row = p.sin_t + size_t(pp) * 64;
+            cs[0] = __ldg(cos_row + lane); cs[1] = __ldg(cos_row + lane + 32);
+            cs[2] = __ldg(sin_row + lane); cs[3] = __ldg(sin_row + lane + 32);
+#pragma unroll
+            for (int j = 0; j < 4; j++) nw[j] = bf16_bits_to_float(__ldg(p.q_norm_w + lane + 32 * j));
+            if (warp == WARPS - 1) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) nwk[j] = bf16_bits_to_float(__ldg(p.k_norm_w + lane + 32 * j));
+            }
+        }
         if (waited) break;
+        flash_trace(2);
         pdl_wait();
+        flash_trace(3);
         waited = true;
         if (__ldcg(p.seq_len + m) != L_seen || __ldcg(p.slot + m) != sl_seen) continue;
         break;
@@ -535,67 +604,87 @@ flash_decode_mma_kernel(const FlashParams p) {
         // side job: zero the buffer the caller named (nothing uses it at this point of a layer)
         const int ctas = gridDim.x * gridDim.y * gridDim.z;
         const int cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-        for (int i = cta * (kWarps * 32) + threadIdx.x; i < p.clear_extra_vec4; i += ctas * kWarps * 32)
+        for (int i = cta * kThreads + threadIdx.x; i < p.clear_extra_vec4; i += ctas * kThreads)
             p.clear_extra[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (split >= n_active) return;
 
     const int heads = p.Nq + 2 * p.Nkv;
     const int newest = L - 1;  // the row appended by this pass (fused) / by the previous kernel
+    const bool appends = FUSED && newest >= begin && newest < end;  // this CTA's slice holds the row this pass adds
     if (FUSED) {
-        int pp = p.pos[m];
-        pp = pp < 0 ? 0 : (pp >= p.max_seq ? p.max_seq - 1 : pp);
-        const float* cos_row = p.cos_t + size_t(pp) * 64;
-        const float* sin_row = p.sin_t + size_t(pp) * 64;
-        // q heads of this kv head: one warp per head
-        for (int h = warp; h < R; h += kWarps) {
+        // q heads of this kv head: one warp per head; the norm weights and the rotary row are in registers already
+        for (int h = warp; h < R; h += WARPS) {
             const float* src = p.qkv + (size_t(m) * heads + kvh * R + h) * kD;
             float r4[4];
-            head_norm_rope(__ldcg(src + lane), __ldcg(src + lane + 32), __ldcg(src + lane + 64), __ldcg(src + lane + 96),
-                           p.q_norm_w, cos_row, sin_row, p.eps, lane, r4);
+            head_norm_rope_regs(__ldcg(src + lane), __ldcg(src + lane + 32), __ldcg(src + lane + 64), __ldcg(src + lane + 96),
+                                nw, cs, p.eps, r4);
             s_q[h][lane] = r4[0]; s_q[h][lane + 32] = r4[1]; s_q[h][lane + 64] = r4[2]; s_q[h][lane + 96] = r4[3];
         }
-        // the CTA whose slice holds the newest row appends it: K through norm + rotary, V as it is, both as bf16
-        if (newest >= begin && newest < end) {
+        // the CTA whose slice holds the newest row appends it: K through norm + rotary, V as it is, both as bf16;
+        // the row also stays in shared memory for the warp that attends to it
+        if (appends) {
+            const int pp = newest < 0 ? 0 : newest;
             const size_t row_off = ((size_t(sl) * p.Nkv + kvh) * p.max_seq + pp) * kD;
-            if (warp == kWarps - 1) {
+            if (warp == WARPS - 1) {
                 const float* src = p.qkv + (size_t(m) * heads + p.Nq + kvh) * kD;
                 float r4[4];
-                head_norm_rope(__ldcg(src + lane), __ldcg(src + lane + 32), __ldcg(src + lane + 64), __ldcg(src + lane + 96),
-                               p.k_norm_w, cos_row, sin_row, p.eps, lane, r4);
+                head_norm_rope_regs(__ldcg(src + lane), __ldcg(src + lane + 32), __ldcg(src + lane + 64), __ldcg(src + lane + 96),
+                                    nwk, cs, p.eps, r4);
                 uint16_t* dst = p.kc_w + row_off;
-                dst[lane] = float_to_bf16_bits(r4[0]);
-                dst[lane + 32] = float_to_bf16_bits(r4[1]);
-                dst[lane + 64] = float_to_bf16_bits(r4[2]);
-                dst[lane + 96] = float_to_bf16_bits(r4[3]);
-            } else if (warp == kWarps - 2) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint16_t b = float_to_bf16_bits(r4[j]);
+                    dst[lane + 32 * j] = b;
+                    s_new[0][lane + 32 * j] = b;
+                }
+            } else if (warp == WARPS - 2) {
                 const float* src = p.qkv + (size_t(m) * heads + p.Nq + p.Nkv + kvh) * kD;
                 uint16_t* dst = p.vc_w + row_off;
-                dst[lane] = float_to_bf16_bits(__ldcg(src + lane));
-                dst[lane + 32] = float_to_bf16_bits(__ldcg(src + lane + 32));
-                dst[lane + 64] = float_to_bf16_bits(__ldcg(src + lane + 64));
-                dst[lane + 96] = float_to_bf16_bits(__ldcg(src + lane + 96));
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint16_t b = float_to_bf16_bits(__ldcg(src + lane + 32 * j));
+                    dst[lane + 32 * j] = b;
+                    s_new[FUSED ? 1 : 0][lane + 32 * j] = b;
+                }
             }
         }
-        __syncthreads();  // s_q is complete; the appended row is visible to the whole CTA
+        __syncthreads();  // s_q and the appended row are complete
+        flash_trace(4);
     }
     // rows of the first step that were not fetched ahead of the wait (the stand-alone call loads inside the loop)
     if (FUSED) {
         const int r0 = base0 + g, r1 = base0 + g + 8;
         if (r0 >= fetched_end && r0 < end) {
-            const bool coherent = FUSED && r0 >= newest;
+            if (appends && r0 == newest) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                k0[i] = ld_row(kb + size_t(r0) * kD + 32 * i + 8 * t, coherent);
-                v0[i] = ld_row(vb + size_t(r0) * kD + 32 * i + 8 * t, coherent);
+                for (int i = 0; i < 4; i++) {
+                    k0[i] = *reinterpret_cast<const uint4*>(&s_new[0][32 * i + 8 * t]);
+                    v0[i] = *reinterpret_cast<const uint4*>(&s_new[FUSED ? 1 : 0][32 * i + 8 * t]);
+                }
+            } else {
+                const bool coherent = r0 >= newest;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    k0[i] = ld_row(kb + size_t(r0) * kD + 32 * i + 8 * t, coherent);
+                    v0[i] = ld_row(vb + size_t(r0) * kD + 32 * i + 8 * t, coherent);
+                }
             }
         }
         if (r1 >= fetched_end && r1 < end) {
-            const bool coherent = FUSED && r1 >= newest;
+            if (appends && r1 == newest) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                k1[i] = ld_row(kb + size_t(r1) * kD + 32 * i + 8 * t, coherent);
-                v1[i] = ld_row(vb + size_t(r1) * kD + 32 * i + 8 * t, coherent);
+                for (int i = 0; i < 4; i++) {
+                    k1[i] = *reinterpret_cast<const uint4*>(&s_new[0][32 * i + 8 * t]);
+                    v1[i] = *reinterpret_cast<const uint4*>(&s_new[FUSED ? 1 : 0][32 * i + 8 * t]);
+                }
+            } else {
+                const bool coherent = r1 >= newest;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    k1[i] = ld_row(kb + size_t(r1) * kD + 32 * i + 8 * t, coherent);
+                    v1[i] = ld_row(vb + size_t(r1) * kD + 32 * i + 8 * t, coherent);
+                }
             }
         }
     }
@@ -632,8 +721,8 @@ flash_decode_mma_kernel(const FlashParams p) {
 #pragma unroll
     for (int b = 0; b < 8; b++) { oacc[b][0] = oacc[b][1] = oacc[b][2] = oacc[b][3] = 0.f; }
 
-    // warp w takes rows begin + w*16 + step*64 .. +15: fragment rows g and g+8
-    for (int base = base0; base < end; base += kWarps * 16) {
+    // warp w takes rows begin + w*16 + step*kBlk .. +15: fragment rows g and g+8
+    for (int base = base0; base < end; base += kBlk) {
         const int r0 = base + g, r1 = base + g + 8;
         const bool ok0 = r0 < end, ok1 = r1 < end;
         if (!FUSED || base != base0) {
@@ -706,6 +795,7 @@ flash_decode_mma_kernel(const FlashParams p) {
         }
     }
 
+    flash_trace(5);
     // sums over all rows of the warp: the 8 lanes with this t hold different rows
 #pragma unroll
     for (int e = 0; e < 2; e++) {
@@ -733,23 +823,29 @@ flash_decode_mma_kernel(const FlashParams p) {
     }
     __syncthreads();
 
-    // merge the warps: thread t owns element t of every head
-    const int tx = threadIdx.x;
-    float fo[R], fm[R], fs[R];
+    // merge the warps: thread (hh, d) owns dimension d of heads hh, hh + HS, ... (HS = threads / 128)
+    constexpr int HS = kThreads / kD;            // 1 or 2 head strides
+    constexpr int HP = (R + HS - 1) / HS;        // heads per thread
+    const int d = threadIdx.x & (kD - 1), hh = threadIdx.x >> 7;
+    float fo[HP], fm[HP], fs[HP];
 #pragma unroll
-    for (int h = 0; h < R; h++) {
-        float nm = -INFINITY;
+    for (int j = 0; j < HP; j++) {
+        const int h = hh + j * HS;
+        fo[j] = 0.f; fm[j] = -INFINITY; fs[j] = 0.f;
+        if (h < R) {
+            float nm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kWarps; w++) nm = fmaxf(nm, s_ml[w][h][0]);
-        float acc = 0.f, ssum = 0.f;
+            for (int w = 0; w < WARPS; w++) nm = fmaxf(nm, s_ml[w][h][0]);
+            float acc = 0.f, ssum = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarps; w++) {
-            const float wm = s_ml[w][h][0];
-            const float c = (wm == -INFINITY) ? 0.f : __expf(wm - nm);
-            acc += s_o[w][h][tx] * c;
-            ssum += s_ml[w][h][1] * c;
+            for (int w = 0; w < WARPS; w++) {
+                const float wm = s_ml[w][h][0];
+                const float c = (wm == -INFINITY) ? 0.f : __expf(wm - nm);
+                acc += s_o[w][h][d] * c;
+                ssum += s_ml[w][h][1] * c;
+            }
+            fo[j] = acc; fm[j] = nm; fs[j] = ssum;
         }
-        fo[h] = acc; fm[h] = nm; fs[h] = ssum;
     }
 
     // fused: once every CTA of this (row, kv head) is past its prologue, the raw q / k / v slices can be zeroed for
@@ -758,92 +854,102 @@ flash_decode_mma_kernel(const FlashParams p) {
         if (FUSED && p.clear_qkv) {
             float* row = p.qkv + size_t(m) * heads * kD;
 #pragma unroll
-            for (int h = 0; h < R; h++) row[(kvh * R + h) * kD + tx] = 0.f;
-            row[(p.Nq + kvh) * kD + tx] = 0.f;
-            row[(p.Nq + p.Nkv + kvh) * kD + tx] = 0.f;
+            for (int j = 0; j < HP; j++)
+                if (hh + j * HS < R) row[(kvh * R + hh + j * HS) * kD + d] = 0.f;
+            if (hh == 0) {
+                row[(p.Nq + kvh) * kD + d] = 0.f;
+                row[(p.Nq + p.Nkv + kvh) * kD + d] = 0.f;
+            }
         }
     };
     if (n_active == 1) {
 #pragma unroll
-        for (int h = 0; h < R; h++)
-            p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + tx] = fs[h] > 0.f ? fo[h] / fs[h] : 0.f;
+        for (int j = 0; j < HP; j++)
+            if (hh + j * HS < R)
+                p.out[(size_t(m) * p.Nq + kvh * R + hh + j * HS) * kD + d] = fs[j] > 0.f ? fo[j] / fs[j] : 0.f;
         clear_raw();
         return;
     }
 
     const size_t pbase = (size_t(m) * p.Nkv + kvh) * p.S;
 #pragma unroll
-    for (int h = 0; h < R; h++) {
-        p.part_o[((pbase + split) * R + h) * kD + tx] = fo[h];
-        if (tx == 0) {
-            p.part_ml[((pbase + split) * R + h) * 2] = fm[h];
-            p.part_ml[((pbase + split) * R + h) * 2 + 1] = fs[h];
+    for (int j = 0; j < HP; j++) {
+        const int h = hh + j * HS;
+        if (h < R) {
+            p.part_o[((pbase + split) * R + h) * kD + d] = fo[j];
+            if (d == 0) *reinterpret_cast<float2*>(p.part_ml + ((pbase + split) * R + h) * 2) = make_float2(fm[j], fs[j]);
         }
     }
-    __threadfence();
+    // Arrival: the barrier orders every thread's partial stores before thread 0's release, and thread 0's acquire
+    // before every thread's loads after the second barrier (release / acquire are cumulative over a CTA barrier), so
+    // one acq_rel atomic by one thread stands in for a fence by every thread on either side of it.
     __syncthreads();
-    if (tx == 0) {
-        const int prev = atomicAdd(p.counters + m * p.Nkv + kvh, 1);
+    flash_trace(6);
+    if (threadIdx.x == 0) {
+        int prev;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(prev) : "l"(p.counters + m * p.Nkv + kvh) : "memory");
         s_last = (prev == n_active - 1);
         if (s_last) p.counters[m * p.Nkv + kvh] = 0;
     }
     __syncthreads();
+    flash_trace(7);
     if (!s_last) return;
-    __threadfence();
-    // ---- final combine by the last CTA.  Weights first: warp w takes heads w, w + 4, ...; lane l holds the
-    // (max, sum) of slices l and l + 32, so the maximum and the denominator are two warp reductions.
-    __shared__ float s_w[64 * R];   // weight of slice sp for head h at [sp * R + h]
-    __shared__ float s_den[R];
-    for (int h = warp; h < R; h += kWarps) {
-        float2 ml0 = make_float2(-INFINITY, 0.f), ml1 = ml0;
-        if (lane < n_active) ml0 = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((pbase + lane) * R + h) * 2));
-        if (lane + 32 < n_active) ml1 = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((pbase + lane + 32) * R + h) * 2));
-        const float nm = warp_max(fmaxf(ml0.x, ml1.x));
-        const float w0 = (ml0.x == -INFINITY) ? 0.f : __expf(ml0.x - nm);
-        const float w1 = (ml1.x == -INFINITY) ? 0.f : __expf(ml1.x - nm);
-        const float den = warp_sum(ml0.y * w0 + ml1.y * w1);
-        s_w[lane * R + h] = w0;
-        s_w[(lane + 32) * R + h] = w1;
-        if (lane == 0) s_den[h] = den;
+    // ---- final combine by the last CTA, in slice order.  Every load is independent of every other (the slice weights
+    // come from the (max, sum) pairs, the sums from the partial outputs), so they are all issued before the first use:
+    // one trip to the L2 for up to kInFlight slices (20 for the eight-warp CTAs of a 4:1 head ratio).
+    constexpr int kInFlight = HP <= 2 ? 20 : (HP == 4 ? 12 : 6);
+    float acc[HP], den[HP], gmax[HP];
+#pragma unroll
+    for (int j = 0; j < HP; j++) { acc[j] = 0.f; den[j] = 0.f; gmax[j] = -INFINITY; }
+    const float* po = p.part_o + pbase * R * kD + d;
+    const float* pml = p.part_ml + pbase * R * 2;
+    // global maximum per head first (cheap: one float2 per slice and head, the same address for all threads of a head)
+    for (int sp0 = 0; sp0 < n_active; sp0 += kInFlight) {
+        float2 ml[kInFlight][HP];
+        float a[kInFlight][HP];
+#pragma unroll
+        for (int q = 0; q < kInFlight; q++)
+#pragma unroll
+            for (int j = 0; j < HP; j++) {
+                const int h = hh + j * HS;
+                const bool ok = sp0 + q < n_active && h < R;
+                ml[q][j] = ok ? __ldcg(reinterpret_cast<const float2*>(pml + (size_t(sp0 + q) * R + h) * 2)) : make_float2(-INFINITY, 0.f);
+                a[q][j] = ok ? __ldcg(po + (size_t(sp0 + q) * R + h) * kD) : 0.f;
+            }
+#pragma unroll
+        for (int j = 0; j < HP; j++) {
+            float bm = gmax[j];
+#pragma unroll
+            for (int q = 0; q < kInFlight; q++) bm = fmaxf(bm, ml[q][j].x);
+            // rescale what was accumulated under the previous maximum (slice order is kept: a fixed summation order)
+            const float c = (gmax[j] == -INFINITY) ? 0.f : __expf(gmax[j] - bm);
+            acc[j] *= c;
+            den[j] *= c;
+            gmax[j] = bm;
+#pragma unroll
+            for (int q = 0; q < kInFlight; q++) {
+                const float w = (ml[q][j].x == -INFINITY) ? 0.f : __expf(ml[q][j].x - bm);
+                acc[j] = fmaf(a[q][j], w, acc[j]);
+                den[j] = fmaf(ml[q][j].y, w, den[j]);
+            }
+        }
     }
-    __syncthreads();
-    // then the partial outputs in slice order, eight slices of every head in flight per thread
-    float acc[R];
+    flash_trace(8);
 #pragma unroll
-    for (int h = 0; h < R; h++) acc[h] = 0.f;
-    const float* po = p.part_o + pbase * R * kD + tx;
-    int sp = 0;
-    for (; sp + 8 <= n_active; sp += 8) {
-        float a[8][R];
-#pragma unroll
-        for (int q = 0; q < 8; q++)
-#pragma unroll
-            for (int h = 0; h < R; h++) a[q][h] = __ldcg(po + (size_t(sp + q) * R + h) * kD);
-#pragma unroll
-        for (int q = 0; q < 8; q++)
-#pragma unroll
-            for (int h = 0; h < R; h++) acc[h] = fmaf(a[q][h], s_w[(sp + q) * R + h], acc[h]);
-    }
-    for (; sp < n_active; sp++) {
-        float a[R];
-#pragma unroll
-        for (int h = 0; h < R; h++) a[h] = __ldcg(po + (size_t(sp) * R + h) * kD);
-#pragma unroll
-        for (int h = 0; h < R; h++) acc[h] = fmaf(a[h], s_w[sp * R + h], acc[h]);
-    }
-#pragma unroll
-    for (int h = 0; h < R; h++) {
-        const float den = s_den[h];
-        p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + tx] = den > 0.f ? acc[h] / den : 0.f;
+    for (int j = 0; j < HP; j++) {
+        const int h = hh + j * HS;
+        if (h < R) p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + d] = den[j] > 0.f ? acc[j] / den[j] : 0.f;
     }
     clear_raw();
+    flash_trace(9);
 }
 
 
-int pick_splits(int M, int Nkv, int max_seq) {
+// rows per CTA step: 64 (four warps) or 128 (eight warps)
+int pick_splits(int M, int Nkv, int max_seq, int rows_per_step) {
     if (g_force_splits > 0) return g_force_splits;
-    const int by_len = (max_seq + 63) / 64;  // a slice is at least one 64-row step of the CTA
-    int want = (148 * 4 + M * Nkv - 1) / (M * Nkv);
+    const int by_len = (max_seq + rows_per_step - 1) / rows_per_step;  // a slice is at least one step of the CTA
+    int want = (device_sm_count() * 4 + M * Nkv - 1) / (M * Nkv);
     int s = want < by_len ? want : by_len;
     if (s < 1) s = 1;
     if (s > 64) s = 64;
@@ -859,11 +965,24 @@ void flash_decode_set_tuning(const char* key, int value) {
     if (!strcmp(key, "flash_early")) g_flash_early = value;
     if (!strcmp(key, "flash_mma")) g_flash_mma = value;
     if (!strcmp(key, "flash_mma_fused")) g_flash_mma_fused = value;
+    if (!strcmp(key, "flash_wide")) g_flash_wide = value;
 }
 
 }  // namespace kuiper
 
 using namespace kuiper;
+
+#ifdef KUIPER_TRACE
+extern "C" KUIPER_API int kuiper_flash_trace_read(int64_t* out, int max_values) {
+    KUIPER_REQUIRE(out != nullptr && max_values > 0, "flash_trace_read: empty destination");
+    const int n = max_values < kFlashTraceCtas * kFlashTraceSlots ? max_values : kFlashTraceCtas * kFlashTraceSlots;
+    if (cudaMemcpyFromSymbol(out, g_flash_trace, size_t(n) * sizeof(long long)) != cudaSuccess) {
+        set_error("flash_trace_read: cannot read the trace buffer");
+        return -1;
+    }
+    return n;
+}
+#endif
 
 extern "C" size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq) {
     if (M <= 0 || Nq <= 0 || D <= 0 || max_seq <= 0) return 0;
@@ -883,7 +1002,11 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
     KUIPER_REQUIRE(R == 1 || R == 2 || R == 4 || R == 8, "flash_decode: group size %d is not supported", R);
     p.M = M; p.Nq = Nq; p.Nkv = Nkv; p.max_seq = max_seq; p.n_slots = n_slots;
     p.fresh_rows = g_flash_early ? fresh_rows : -1;
-    p.S = pick_splits(M, Nkv, max_seq);
+    // one sequence (or a few) at a context of a few thousand rows: eight-warp CTAs, one 128-row step each, so that the
+    // last CTA of a kv head combines half as many slices; anything larger keeps the four-warp CTAs (more of them per SM)
+    const bool wide = fused && g_flash_mma_fused && g_flash_wide &&
+                      (long long)M * Nkv * ((max_seq + 127) / 128) <= 2ll * device_sm_count();
+    p.S = pick_splits(M, Nkv, max_seq, wide ? 128 : 64);
     if (p.S > 1) {
         KUIPER_REQUIRE(workspace != nullptr, "flash_decode: split KV needs a workspace");
         KUIPER_REQUIRE(workspace_bytes >= kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq),
@@ -900,7 +1023,7 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.S, Nkv, M);
-    cfg.blockDim = dim3(kWarps * 32, 1, 1);
+    cfg.blockDim = dim3((wide ? 8 : kWarps) * 32, 1, 1);
     cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -908,12 +1031,19 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
     cfg.attrs = attr;
     cfg.numAttrs = g_pdl_enabled ? 1 : 0;
     cudaError_t err;
-    if (fused && g_flash_mma_fused) {
+    if (wide) {
         switch (R) {
-            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<1, true>, p); break;
-            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<2, true>, p); break;
-            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<4, true>, p); break;
-            default: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<8, true>, p); break;
+            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<1, true, 8>, p); break;
+            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<2, true, 8>, p); break;
+            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<4, true, 8>, p); break;
+            default: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<8, true, 8>, p); break;
+        }
+    } else if (fused && g_flash_mma_fused) {
+        switch (R) {
+            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<1, true, 4>, p); break;
+            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<2, true, 4>, p); break;
+            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<4, true, 4>, p); break;
+            default: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<8, true, 4>, p); break;
         }
     } else if (fused) {
         switch (R) {
@@ -924,10 +1054,10 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
         }
     } else if (g_flash_mma) {
         switch (R) {
-            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<1, false>, p); break;
-            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<2, false>, p); break;
-            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<4, false>, p); break;
-            default: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<8, false>, p); break;
+            case 1: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<1, false, 4>, p); break;
+            case 2: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<2, false, 4>, p); break;
+            case 4: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<4, false, 4>, p); break;
+            default: err = cudaLaunchKernelEx(&cfg, flash_decode_mma_kernel<8, false, 4>, p); break;
         }
     } else {
         switch (R) {

@@ -562,7 +562,8 @@ def test_flash_decode_early_fetch_matches_conservative_path(cuda, oracle):
             cuda.set_tuning("flash_mma", FLASH_MMA_DEFAULT)
 
 
-@pytest.mark.parametrize("Nq,Nkv,lens", [(32, 8, [2084, 1, 700]), (16, 8, [65, 64]), (8, 8, [130])])
+@pytest.mark.parametrize("Nq,Nkv,lens", [(32, 8, [2084, 1, 700]), (16, 8, [65, 64]), (8, 8, [130]), (32, 8, [2084]), (32, 8, [2048, 129]),
+                                         (64, 8, [1000])])
 def test_rope_fused_into_flash_decode_is_bit_identical(cuda, oracle, Nq, Nkv, lens):
     # decode batch: one row per slot, seq_len = pos + 1; the fused kernel must reproduce the two-kernel path bit for bit,
     # caches included, and may clear the raw projection rows and a side buffer
