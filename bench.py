@@ -247,20 +247,22 @@ def run_reference(args, cfg, desc, rank, world):
 
 # --------------------------------------------------------------------------- GPU arm
 def gemv_roofline(cfg, tp, layers_kept, iters=3):
-    """INT4-AWQ GEMV launches of one token (4 shapes x n_layers), over distinct weights, timed alone."""
+    """INT4-AWQ GEMV launches of one token (4 shapes x n_layers), over distinct weights, timed alone.  Every launch
+    has its own balance counters, as every layer object of the engine has."""
     import torch
     from mykuiperllama_b200 import capi
     shapes = layer_shapes(cfg, tp)
     x = {n: torch.randn((1, K), device="cuda") for n, (K, N) in shapes.items()}
     y = {n: torch.zeros((1, N), device="cuda") for n, (K, N) in shapes.items()}
-    ws = capi.awq_gemv_workspace(1, max(K for K, _ in shapes.values()), max(N for _, N in shapes.values()))
     L = cfg["n_layers"]
+    tickets = [[capi.awq_gemv_tickets() for _ in range(4)] for _ in range(L)]
 
     def one_token():
         for l in range(L):
             lw = layers_kept[l % len(layers_kept)]
-            for n in ("qkv", "o", "gu", "down"):
-                capi.awq_gemv_accum(x[n], lw[f"{n}_qw"], lw[f"{n}_qz"], lw[f"{n}_s"], y[n])  # the engine's path
+            for j, n in enumerate(("qkv", "o", "gu", "down")):
+                capi.awq_gemv_accum_balanced(x[n], lw[f"{n}_qw"], lw[f"{n}_qz"], lw[f"{n}_s"], y[n], tickets[l][j],
+                                             act_mode=capi.ACT_INT16_BLOCK)  # the engine's path
 
     one_token()
     torch.cuda.synchronize()
@@ -279,6 +281,55 @@ def gemv_roofline(cfg, tp, layers_kept, iters=3):
     launches = 4 * L
     total_bytes = L * sum(int4_bytes(K, N) + 4 * K + 4 * N for K, N in shapes.values())
     return total_bytes / launches, best * 1e-3 / launches, launches
+
+
+def gemv_set(K, N, n, grouped, iters=5, seed=0):
+    """One INT4 GEMV shape over n distinct weight sets (more than L2 in total), visited in turn: as n balanced launches
+    inside a CUDA graph, or as ONE grouped launch.  Returns (bytes per matrix, seconds per matrix)."""
+    import torch
+    from mykuiperllama_b200 import capi
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    qw = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), dtype=torch.int32, device="cuda", generator=gen) for _ in range(n)]
+    qz = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 128, N // 8), dtype=torch.int32, device="cuda", generator=gen) for _ in range(n)]
+    sc = [(torch.rand((K // 128, N), device="cuda", generator=gen) * 0.018 + 0.002).half() for _ in range(n)]
+    x = torch.randn((1, K), device="cuda", generator=gen)
+    ys = [torch.zeros((1, N), device="cuda") for _ in range(n)]
+    if grouped:
+        grp = capi.GemvGroup([dict(x=x, qweight=qw[i], qzeros=qz[i], scales=sc[i], y=ys[i]) for i in range(n)])
+        run = grp.run
+    else:
+        tk = [capi.awq_gemv_tickets() for _ in range(n)]
+
+        def run():
+            for i in range(n):
+                capi.awq_gemv_accum_balanced(x, qw[i], qz[i], sc[i], ys[i], tk[i], act_mode=capi.ACT_INT16_BLOCK)
+    run()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        run()
+    g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    per = int4_bytes(K, N) + 4 * K + 4 * N
+    return per, float(np.median(times)) * 1e-3 / n
+
+
+def gemv_sub_record(K, N, n, grouped, peak):
+    per, sec = gemv_set(K, N, n, grouped)
+    gbs = per / sec / 1e9
+    return {"shape": f"{K}x{N}", "achieved": gbs, "unit": "GB/s", "frac": gbs / peak, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
+            "matrices_visited": n, "us_per_matrix": sec * 1e6, "bytes_per_matrix": per,
+            "launch": "one grouped persistent launch over all matrices" if grouped else "one launch per matrix inside a CUDA graph",
+            "l2_policy": f"{n} distinct weight sets ({per * n >> 20} MiB) visited in turn: larger than L2"}
 
 
 def tp1_stream_check(cfg, ecfg, prompt, ids, device):
@@ -327,7 +378,8 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
     steps_total = args.warmup + args.steps
     n_ids = 32  # greedy ids printed with the line (the first tokens after the prompt, read back step by step)
     max_seq = prompt_len + n_ids + 2 * steps_total + 16
-    ecfg = eng_mod.EngineConfig(**cfg, max_seq=max_seq, max_batch=B, max_rows=max(128, B), tp_rank=rank, tp_size=world)
+    ecfg = eng_mod.EngineConfig(**cfg, max_seq=max_seq, max_batch=B, max_rows=max(128, B), tp_rank=rank, tp_size=world,
+                                act_mode=args.act_mode)
     eng = eng_mod.Qwen3Engine(ecfg)
 
     gen = torch.Generator(device=device)
@@ -445,7 +497,9 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
     line = {
         "metric": "Qwen3 INT4 decode tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "int4 weights (AWQ g128), fp16 x operand, fp32 accumulate",
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": ("int4 weights (AWQ g128), 16-bit block-scaled integer x operand for one-row passes (u8 x s8 mma, exact sums per 32 rows), "
+                  "fp16 x operand otherwise, fp32 accumulate") if args.act_mode == 2 else "int4 weights (AWQ g128), fp16 x operand, fp32 accumulate",
         "data": "synthetic",
         "config": {"workload": desc if B == 1 else desc.replace("batch 1", f"batch {B}"), "batch": B, "prompt_tokens": prompt_tokens, "context_during_timing": ctx_mid,
                    "parallelism": f"tp{world}", "l2_policy": "inputs larger than L2 (weights streamed once per token)",
@@ -463,7 +517,7 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         # DRAM traffic per launch: ncu measured 52.44 MB read + 0.07 MB written for 52.41 MB of algorithmic bytes on the
         # largest shape (profiles/awq_gemv_mma_accumulate_4096x24576.md); traffic grows with the matrix, so the ratio
         # is applied to the average launch of the four shapes timed here
-        line["roofline"] = {"bound": "hbm", "kernel": "awq_gemv_mma_kernel<1,3,accumulate>", "achieved": achieved, "peak": peak,
+        line["roofline"] = {"bound": "hbm", "kernel": "awq_gemv_mma_kernel<1 row, 3 stages, accumulate, integer operand>", "achieved": achieved, "peak": peak,
                             "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                             "traffic": int(per_launch_bytes * NCU_TRAFFIC_RATIO),
@@ -471,6 +525,13 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
                             "launches_per_token": launches, "avg_bytes_per_launch": int(per_launch_bytes),
                             "avg_us_per_launch": per_launch_s * 1e6}
         del keep
+        torch.cuda.empty_cache()
+        # the single-GEMV half of the metric: the 2048 x 2048 workload over 128 weight sets (one grouped launch), and the
+        # widest projection of this model over 6 weight sets
+        line["gemv_c1"] = gemv_sub_record(2048, 2048, 128, True, peak)
+        torch.cuda.empty_cache()
+        Kl, Nl = max(layer_shapes(cfg).values(), key=lambda kn: kn[0] * kn[1])
+        line["gemv_largest"] = gemv_sub_record(Kl, Nl, 6, False, peak)
         torch.cuda.empty_cache()
         n_sample = 2 if cfg["hidden"] >= 2560 else 4
         tps_cpu, _ = cpu_decode_sample(cfg, n_sample, steps=3, warmup=1)
@@ -509,11 +570,19 @@ def run_gemv_micro(args):
     x = torch.randn((1, K), device="cuda", generator=gen)
     y = torch.zeros((1, N), device="cuda")
     ws = capi.awq_gemv_workspace(1, K, N)
+    tk = [capi.awq_gemv_tickets() for _ in range(n)]
+    grp = capi.GemvGroup([dict(x=x, qweight=qw[i], qzeros=qz[i], scales=sc[i], y=y) for i in range(n)], act_mode=args.act_mode,
+                         balanced=args.group_tickets) if args.gemv_impl == 5 else None
 
     def sweep():
+        if args.gemv_impl == 5:
+            grp.run()
+            return
         for i in range(n):
             if args.gemv_impl == 2:
-                capi.awq_gemv_accum(x, qw[i], qz[i], sc[i], y)
+                capi.awq_gemv_accum_balanced(x, qw[i], qz[i], sc[i], y, tk[i], act_mode=args.act_mode)
+            elif args.gemv_impl == 6:
+                capi.awq_gemv_accum_balanced(x, qw[i], qz[i], sc[i], y, None, act_mode=args.act_mode)
             else:
                 capi.awq_gemv(x, qw[i], qz[i], sc[i], workspace=ws, out=y)
 
@@ -534,6 +603,12 @@ def run_gemv_micro(args):
             e1.record()
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1))
+    if args.gemv_trace:
+        # measurement build (KUIPER_TRACE=1): per-CTA clock readings of the sweep's last launch
+        from mykuiperllama_b200._lib import kernels
+        trace = np.zeros((304, 10), np.int64)
+        kernels().kuiper_gemv_trace_read(trace.ctypes.data, trace.size)
+        np.save(args.gemv_trace, trace)
     ms = float(np.median(times))
     gbs = per * n / (ms * 1e-3) / 1e9
     peak, kind = measured_peak_gbs()
@@ -545,7 +620,7 @@ def run_gemv_micro(args):
                    "l2_policy": f"{n} matrices ({per * n >> 20} MiB) visited in turn: larger than L2"},
         "roofline": {"bound": "hbm", "kernel": "awq_gemv", "achieved": gbs, "peak": peak, "peak_kind": kind, "unit": "GB/s",
                      "frac": gbs / peak, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
-                     "traffic": int(per * NCU_TRAFFIC_RATIO) if args.gemv_impl == 2 else None,
+                     "traffic": int(per * NCU_TRAFFIC_RATIO) if args.gemv_impl in (2, 5, 6) else None,
                      "avg_us_per_launch": ms * 1e3 / n, "avg_bytes_per_launch": per},
         "gpu_launches": n * args.steps, "clocks": clocks.summary()}), flush=True)
 
@@ -678,12 +753,18 @@ def main():
     ap.add_argument("--shape", default="2048x2048", help="KxN of the gemv microbenchmark")
     ap.add_argument("--rows", type=int, default=2048, help="token rows M of the gemm microbenchmark")
     ap.add_argument("--mats", type=int, default=0, help="distinct weight matrices in the gemv microbenchmark (0 = 512 MiB worth)")
-    ap.add_argument("--gemv-impl", type=int, default=None, help="2 accumulate mode of the tensor-core GEMV (engine path, default), 0 its ordered combine, "
+    ap.add_argument("--gemv-impl", type=int, default=None, help="2 accumulate mode of the tensor-core GEMV with ticket balancing (engine path, default), 6 the same dealt statically, "
+                         "5 all matrices in one grouped launch, 0 the ordered combine, "
                          "1 register-staged kernel, 3 first-generation persistent SIMT kernel (accumulate)")
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded together (config 4 of the workload list uses 16)")
     ap.add_argument("--profile-range", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for a profiler run with profile-from-start off)")
+    ap.add_argument("--act-mode", type=int, default=2, help="INT4 matmul operand: 2 block-scaled 16-bit integers for one-row passes "
+                    "(integer tensor-core kernel; fp16 for passes of several rows), 1 fp16 everywhere")
+    ap.add_argument("--group-tickets", action="store_true", help="gemv-impl 5: hand the tail of the grouped launch out by ticket")
+    ap.add_argument("--gemv-trace", default=None, metavar="FILE.npy",
+                    help="gemv workload with the KUIPER_TRACE=1 build: save the per-CTA clock readings of the last GEMV launch")
     ap.add_argument("--flash-trace", default=None, metavar="FILE.npy",
                     help="with the KUIPER_TRACE=1 build: save the per-CTA clock readings of the last attention launch")
     ap.add_argument("--prompt", type=int, default=None, help="override the workload's prompt length (profiling aid)")

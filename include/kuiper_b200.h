@@ -47,6 +47,10 @@ enum {
 enum {
     KUIPER_ACT_FP16 = 1, /* x rounded to fp16, exact products, fp32 accumulation */
     KUIPER_ACT_FP32 = 0, /* x kept in fp32 */
+    /* single-row calls of the tensor-core GEMV: per 32 consecutive rows of K, x' = rint(x * 2^e) * 2^-e with e the largest
+     * exponent that keeps |x * 2^e| < 2^14 (16-bit block floating point); integer products, exact sums inside a block,
+     * fp32 accumulation across blocks.  Calls with more rows round to fp16 as KUIPER_ACT_FP16 does. */
+    KUIPER_ACT_INT16_BLOCK = 2,
 };
 
 KUIPER_API const char* kuiper_version(void);
@@ -80,7 +84,7 @@ KUIPER_API int kuiper_workspace_init(void* workspace, size_t bytes, kuiper_strea
  * y[M,N] = x[M,K] . dequant(qweight) (+ residual[M,N] if residual != NULL; y may alias
  * residual).  group must be 128, K % 128 == 0, N % 8 == 0.  M <= 8 runs the SIMT
  * dequant-fused GEMV; larger M is processed in row blocks.
- * act_mode: KUIPER_ACT_FP16 or KUIPER_ACT_FP32.
+ * act_mode: KUIPER_ACT_FP16, KUIPER_ACT_FP32, or KUIPER_ACT_INT16_BLOCK (N % 32 == 0; applies to M == 1, more rows round to fp16).
  */
 KUIPER_API int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
                         const uint16_t* scales, float* y, const float* residual,
@@ -112,6 +116,43 @@ KUIPER_API int kuiper_rmsnorm_awq_gemv_accum_f32(const float* h, const uint16_t*
 KUIPER_API int kuiper_swiglu_awq_gemv_accum_f32(const float* gate_up, const int32_t* qweight, const int32_t* qzeros,
                                                 const uint16_t* scales, float* y, int M, int K, int N, int group,
                                                 kuiper_stream_t stream);
+/*
+ * The three accumulating calls above in one (the engine's entry): norm_w != NULL selects the fused RMSNorm, swiglu != 0
+ * the fused SwiGLU (not both); act_mode KUIPER_ACT_FP16 or KUIPER_ACT_INT16_BLOCK (the faster kernel for M == 1).  tickets: kuiper_awq_gemv_ticket_bytes() bytes of device memory owned by the call site,
+ * zeroed once (kuiper_workspace_init) and left at zero by every call; with it the kernel deals only three quarters of
+ * the weight stream out statically and hands the rest to whichever CTA is free (an atomic ticket counter), so that
+ * all CTAs finish together.  NULL: a fully static deal, as in the calls above.  Launches that may overlap on the
+ * GPU (consecutive launches of a stream do, under programmatic dependent launch) must not share tickets; the engine
+ * gives every layer object its own.  No counterpart in the reference.
+ */
+KUIPER_API size_t kuiper_awq_gemv_ticket_bytes(void);
+KUIPER_API int kuiper_awq_gemv_accum_balanced_f32(const float* x, const uint16_t* norm_w, float eps, int swiglu,
+                                                  const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
+                                                  float* y, int M, int K, int N, int group, int act_mode, void* tickets,
+                                                  kuiper_stream_t stream);
+/*
+ * A list of independent one-row projections in ONE persistent launch: y_i += x_i . dequant(W_i) for every item, in no
+ * particular order (no item may read another's output).  The units of all matrices form one stream, so a list of small
+ * matrices (the 2048 x 2048 single-GEMV workload visited over many weight sets) runs at streaming speed instead of
+ * paying a launch per 2 MB.  Three steps: kuiper_awq_gemv_group_plan() fills a HOST buffer of
+ * kuiper_awq_gemv_group_table_bytes(n) bytes with the table the kernel reads and returns the number of work units in
+ * *units; the caller copies the table to 64-byte aligned device memory (it stays valid while the item pointers do);
+ * kuiper_awq_gemv_group_f32() launches (act_mode KUIPER_ACT_FP16 or KUIPER_ACT_INT16_BLOCK).  Every item: K % 128 == 0, N % 32 == 0, 16-byte aligned tensors, y holds
+ * the addend.  tickets as above (may be NULL).  No counterpart in the reference.
+ */
+typedef struct kuiper_gemv_item {
+    const float* x;          /* [K] */
+    const int32_t* qweight;  /* [K, N/8] */
+    const int32_t* qzeros;   /* [K/128, N/8] */
+    const uint16_t* scales;  /* fp16 [K/128, N] */
+    float* y;                /* [N] */
+    int32_t K, N;
+} kuiper_gemv_item;
+KUIPER_API size_t kuiper_awq_gemv_group_table_bytes(int n_items);
+KUIPER_API int kuiper_awq_gemv_group_plan(const kuiper_gemv_item* items, int n_items, int group, void* host_table,
+                                          int64_t* units);
+KUIPER_API int kuiper_awq_gemv_group_f32(const void* device_table, int n_items, int64_t units, int act_mode, void* tickets,
+                                         kuiper_stream_t stream);
 /* health check (synchronises): 5 if a bounded wait inside the pipelined GEMV ever ran out on this device */
 KUIPER_API int kuiper_awq_gemv_status(void);
 /*
@@ -244,6 +285,10 @@ KUIPER_API int kuiper_rope_flash_decode(float* qkv, const uint16_t* q_norm_w, co
  * clock at 1 entry, 2 early fetches issued, 3 dependency wait passed, 4 q ready, 5 cache rows processed, 6 partial
  * stored, 7 arrival counter answered, 8 slices combined, 9 output stored).  Synchronises; returns the number of values copied or -1. */
 KUIPER_API int kuiper_flash_trace_read(int64_t* out, int max_values);
+/* The same for the last launch of the tensor-core INT4 GEMV: [CTA][10] (0 global timer at entry, then SM clock at 1 entry,
+ * 2 consumers past the dependency wait, 3 first unit ready, 4 last unit consumed, 5 consumer exit, 6 activation warp saw
+ * its first descriptor, 7 first fragments written, 8 first weight copy issued, 9 last weight copy issued). */
+KUIPER_API int kuiper_gemv_trace_read(int64_t* out, int max_values);
 #endif
 
 /* ---- SwiGLU: placeholder kuiper/include/op/swiglu.h:1-10 ---- */

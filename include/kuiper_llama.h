@@ -26,7 +26,8 @@ typedef struct {
     int32_t max_seq, max_batch, max_rows;
     float eps;
     double rope_theta;
-    int32_t act_mode; /* 1: INT4 matmul rounds x to fp16 (default), 0: keeps fp32 */
+    int32_t act_mode; /* INT4 matmul operand: 1 rounds x to fp16, 0 keeps fp32, 2 block-scaled 16-bit integers for one-row
+                         passes (decode steps of one sequence: the fastest kernel) and fp16 for passes of several rows */
     int32_t tp_rank, tp_size;
 } kuiper_model_config;
 

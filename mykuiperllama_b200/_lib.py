@@ -41,6 +41,11 @@ KERNEL_API = {
     "kuiper_awq_gemv_accum_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_rmsnorm_awq_gemv_accum_f32": (_i32, [_vp, _vp, _f32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_swiglu_awq_gemv_accum_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "kuiper_awq_gemv_ticket_bytes": (_sz, []),
+    "kuiper_awq_gemv_accum_balanced_f32": (_i32, [_vp, _vp, _f32, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "kuiper_awq_gemv_group_table_bytes": (_sz, [_i32]),
+    "kuiper_awq_gemv_group_plan": (_i32, [_vp, _i32, _i32, _vp, _vp]),
+    "kuiper_awq_gemv_group_f32": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp]),
     "kuiper_awq_gemv_status": (_i32, []),
     "kuiper_awq_gemv_noalloc_scratch_bytes": (_sz, []),
     "kuiper_awq_gemv_f32_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
@@ -82,7 +87,7 @@ def kernels() -> C.CDLL:
         lib = C.CDLL(path, mode=C.RTLD_GLOBAL)
         _bind(lib, KERNEL_API)
         if _build.TRACE:  # measurement build only
-            _bind(lib, {"kuiper_flash_trace_read": (_i32, [_vp, _i32])})
+            _bind(lib, {"kuiper_flash_trace_read": (_i32, [_vp, _i32]), "kuiper_gemv_trace_read": (_i32, [_vp, _i32])})
         _kernels = lib
     return _kernels
 

@@ -14,7 +14,7 @@ import torch
 
 from ._lib import check, kernels
 
-ACT_FP32, ACT_FP16 = 0, 1
+ACT_FP32, ACT_FP16, ACT_INT16_BLOCK = 0, 1, 2
 
 
 def _ptr(t):
@@ -106,6 +106,52 @@ def swiglu_awq_gemv_accum(gate_up, qweight, qzeros, scales, y, group=128):
     check(kernels().kuiper_swiglu_awq_gemv_accum_f32(_ptr(gate_up), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(y), M, K, N,
                                                      group, _stream()))
     return y
+
+
+def awq_gemv_tickets(device="cuda"):
+    """Balance counters of one call site (zeroed once; every launch leaves them at zero)."""
+    return torch.zeros(max(kernels().kuiper_awq_gemv_ticket_bytes(), 16), dtype=torch.uint8, device=device)
+
+
+def awq_gemv_accum_balanced(x, qweight, qzeros, scales, y, tickets=None, norm_w=None, eps=1e-6, swiglu=False, group=128,
+                            act_mode=ACT_FP16):
+    """y += op(x) . W with the tail of the weight stream handed out by ticket (see kuiper_awq_gemv_accum_balanced_f32)."""
+    _dev(x, qweight, qzeros, scales, y, tickets, norm_w)
+    M = x.shape[0]
+    K = x.shape[1] // (2 if swiglu else 1)
+    N = qweight.shape[1] * 8
+    check(kernels().kuiper_awq_gemv_accum_balanced_f32(_ptr(x), _ptr(norm_w), eps, int(bool(swiglu)), _ptr(qweight), _ptr(qzeros),
+                                                       _ptr(scales), _ptr(y), M, K, N, group, act_mode, _ptr(tickets), _stream()))
+    return y
+
+
+class _GemvItem(ctypes.Structure):
+    _fields_ = [("x", ctypes.c_void_p), ("qweight", ctypes.c_void_p), ("qzeros", ctypes.c_void_p), ("scales", ctypes.c_void_p),
+                ("y", ctypes.c_void_p), ("K", ctypes.c_int32), ("N", ctypes.c_int32)]
+
+
+class GemvGroup:
+    """A list of independent one-row projections y_i += x_i . W_i that runs as one persistent launch.
+    items: dicts with x [K] or [1, K], qweight, qzeros, scales, y.  The tensors must stay alive while the group is used."""
+
+    def __init__(self, items, group=128, balanced=False, act_mode=ACT_INT16_BLOCK):
+        import numpy as np
+        n = len(items)
+        arr = (_GemvItem * n)()
+        for i, o in enumerate(items):
+            _dev(o["x"], o["qweight"], o["qzeros"], o["scales"], o["y"])
+            arr[i] = _GemvItem(_ptr(o["x"]), _ptr(o["qweight"]), _ptr(o["qzeros"]), _ptr(o["scales"]), _ptr(o["y"]),
+                               o["qweight"].shape[0], o["qweight"].shape[1] * 8)
+        host = np.zeros(kernels().kuiper_awq_gemv_group_table_bytes(n), np.uint8)
+        units = ctypes.c_int64(0)
+        check(kernels().kuiper_awq_gemv_group_plan(ctypes.addressof(arr), n, group, host.ctypes.data, ctypes.byref(units)))
+        self.keep = items
+        self.n, self.units, self.act_mode = n, units.value, act_mode
+        self.table = torch.from_numpy(host).cuda()  # torch allocations are 256-byte aligned
+        self.tickets = awq_gemv_tickets() if balanced else None
+
+    def run(self):
+        check(kernels().kuiper_awq_gemv_group_f32(_ptr(self.table), self.n, self.units, self.act_mode, _ptr(self.tickets), _stream()))
 
 
 def awq_gemm_workspace(M, K, device="cuda"):

@@ -422,7 +422,11 @@ int awq_gemv_mma_status();
 int awq_gemv_mma_max_rows(bool accumulate);
 int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales, float* y,
                         const float* residual, int rows, int K, int N, void* workspace, bool accumulate,
-                        const uint16_t* norm_w, float eps, bool swiglu, cudaStream_t stream);
+                        const uint16_t* norm_w, float eps, bool swiglu, int* tickets, bool int_operand, cudaStream_t stream);
+size_t awq_gemv_group_table_bytes(int n_items);
+long long awq_gemv_group_fill(const kuiper_gemv_item* items, int n_items, void* host_table);
+int awq_gemv_group_launch(const void* device_table, int n_items, long long units, int* tickets, bool int_operand,
+                          cudaStream_t stream);
 
 }  // namespace kuiper
 
@@ -448,7 +452,8 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
     KUIPER_REQUIRE(group == 128, "awq_gemv: group size %d is not supported (128 only)", group);
     KUIPER_REQUIRE(K % 128 == 0, "awq_gemv: K=%d is not a multiple of the group size", K);
     KUIPER_REQUIRE(N % 8 == 0, "awq_gemv: N=%d is not a multiple of 8", N);
-    KUIPER_REQUIRE(act_mode == KUIPER_ACT_FP16 || act_mode == KUIPER_ACT_FP32, "awq_gemv: unknown act_mode %d", act_mode);
+    KUIPER_REQUIRE(act_mode == KUIPER_ACT_FP16 || act_mode == KUIPER_ACT_FP32 || act_mode == KUIPER_ACT_INT16_BLOCK,
+                   "awq_gemv: unknown act_mode %d", act_mode);
     cudaStream_t st = as_stream(stream);
 
     if (N % 32 != 0) {
@@ -465,7 +470,10 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
                        (reinterpret_cast<uintptr_t>(scales) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(x) & 3) == 0 && (!residual || (reinterpret_cast<uintptr_t>(residual) & 15) == 0),
                    "awq_gemv: tensors must be 16-byte aligned");
-    const bool want_tma = (g_force_impl == 0 || g_force_impl == 2) && g_force_math < 0 && act_mode == KUIPER_ACT_FP16 &&
+    const bool int_operand = act_mode == KUIPER_ACT_INT16_BLOCK && M == 1;  // more rows round to fp16
+    KUIPER_REQUIRE(!int_operand || (g_force_impl == 0 && g_force_math < 0 && awq_gemv_mma_supported(K, N)),
+                   "awq_gemv: the integer operand needs the tensor-core kernel (N %% 32 == 0, K %% 128 == 0)");
+    const bool want_tma = (g_force_impl == 0 || g_force_impl == 2) && g_force_math < 0 && act_mode != KUIPER_ACT_FP32 &&
                           awq_gemv_tma_supported(K, N);
     if (want_tma) {
         const bool mma = g_force_impl == 0 && awq_gemv_mma_supported(K, N);
@@ -477,7 +485,8 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
             const float* xm = x + size_t(m0) * K;
             float* ym = y + size_t(m0) * N;
             const float* rm = residual ? residual + size_t(m0) * N : nullptr;
-            int rc = mma ? awq_gemv_mma_launch(xm, qweight, qzeros, scales, ym, rm, mt, K, N, workspace, false, nullptr, 0.f, false, st)
+            int rc = mma ? awq_gemv_mma_launch(xm, qweight, qzeros, scales, ym, rm, mt, K, N, workspace, false, nullptr, 0.f, false, nullptr,
+                                               int_operand, st)
                          : awq_gemv_tma_launch(xm, qweight, qzeros, scales, ym, rm, mt, K, N, workspace, false, nullptr, 0.f, st);
             if (rc != KUIPER_OK) return rc;
             m0 += mt;
@@ -526,7 +535,8 @@ extern "C" int kuiper_awq_gemv_f32(const float* x, const int32_t* qweight, const
 
 static int awq_gemv_accum_common(const float* x, const uint16_t* norm_w, float eps, bool swiglu, const int32_t* qweight,
                                  const int32_t* qzeros, const uint16_t* scales, float* y, int M, int K, int N, int group,
-                                 kuiper_stream_t stream) {
+                                 void* tickets, int act_mode, kuiper_stream_t stream) {
+    KUIPER_REQUIRE(act_mode == KUIPER_ACT_FP16 || act_mode == KUIPER_ACT_INT16_BLOCK, "awq_gemv_accum: unknown act_mode %d", act_mode);
     KUIPER_REQUIRE(x && qweight && qzeros && scales && y, "awq_gemv_accum: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && K > 0 && N > 0, "awq_gemv_accum: empty shape M=%d K=%d N=%d", M, K, N);
     KUIPER_REQUIRE(group == 128, "awq_gemv_accum: group size %d is not supported (128 only)", group);
@@ -538,12 +548,18 @@ static int awq_gemv_accum_common(const float* x, const uint16_t* norm_w, float e
     cudaStream_t st = as_stream(stream);
     const bool mma = g_force_impl != 2 && awq_gemv_mma_supported(K, N);
     KUIPER_REQUIRE(mma || !swiglu, "awq_gemv_accum: the fused SwiGLU needs the tensor-core kernel");
+    KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(tickets) & 7) == 0, "awq_gemv_accum: tickets must be 8-byte aligned");
+    // (more rows than one launch takes: the row blocks are consecutive launches that may overlap, so they cannot
+    // share the counters and are dealt out statically)
+    // the integer operand is a one-row kernel: it serves single-row calls, everything else rounds to fp16
+    const bool int_operand = act_mode == KUIPER_ACT_INT16_BLOCK && M == 1 && mma;
     const int max_rows = mma ? awq_gemv_mma_max_rows(true) : 2;
     for (int m0 = 0; m0 < M;) {
         const int mt = (M - m0 >= max_rows) ? max_rows : (M - m0);
         const float* xm = x + size_t(m0) * K * (swiglu ? 2 : 1);
         float* ym = y + size_t(m0) * N;
-        int rc = mma ? awq_gemv_mma_launch(xm, qweight, qzeros, scales, ym, nullptr, mt, K, N, nullptr, true, norm_w, eps, swiglu, st)
+        int rc = mma ? awq_gemv_mma_launch(xm, qweight, qzeros, scales, ym, nullptr, mt, K, N, nullptr, true, norm_w, eps, swiglu,
+                                         M <= max_rows ? static_cast<int*>(tickets) : nullptr, int_operand, st)
                      : awq_gemv_tma_launch(xm, qweight, qzeros, scales, ym, nullptr, mt, K, N, nullptr, true, norm_w, eps, st);
         if (rc != KUIPER_OK) return rc;
         m0 += mt;
@@ -554,7 +570,7 @@ static int awq_gemv_accum_common(const float* x, const uint16_t* norm_w, float e
 extern "C" int kuiper_awq_gemv_accum_f32(const float* x, const int32_t* qweight, const int32_t* qzeros,
                                          const uint16_t* scales, float* y, int M, int K, int N, int group,
                                          kuiper_stream_t stream) {
-    return awq_gemv_accum_common(x, nullptr, 0.f, false, qweight, qzeros, scales, y, M, K, N, group, stream);
+    return awq_gemv_accum_common(x, nullptr, 0.f, false, qweight, qzeros, scales, y, M, K, N, group, nullptr, KUIPER_ACT_FP16, stream);
 }
 
 extern "C" int kuiper_rmsnorm_awq_gemv_accum_f32(const float* h, const uint16_t* norm_w, float eps, const int32_t* qweight,
@@ -562,13 +578,71 @@ extern "C" int kuiper_rmsnorm_awq_gemv_accum_f32(const float* h, const uint16_t*
                                                  int N, int group, kuiper_stream_t stream) {
     KUIPER_REQUIRE(norm_w != nullptr, "rmsnorm_awq_gemv_accum: null norm weight");
     KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(norm_w) & 15) == 0, "rmsnorm_awq_gemv_accum: norm weight must be 16-byte aligned");
-    return awq_gemv_accum_common(h, norm_w, eps, false, qweight, qzeros, scales, y, M, K, N, group, stream);
+    return awq_gemv_accum_common(h, norm_w, eps, false, qweight, qzeros, scales, y, M, K, N, group, nullptr, KUIPER_ACT_FP16, stream);
 }
 
 extern "C" int kuiper_swiglu_awq_gemv_accum_f32(const float* gate_up, const int32_t* qweight, const int32_t* qzeros,
                                                 const uint16_t* scales, float* y, int M, int K, int N, int group,
                                                 kuiper_stream_t stream) {
-    return awq_gemv_accum_common(gate_up, nullptr, 0.f, true, qweight, qzeros, scales, y, M, K, N, group, stream);
+    return awq_gemv_accum_common(gate_up, nullptr, 0.f, true, qweight, qzeros, scales, y, M, K, N, group, nullptr, KUIPER_ACT_FP16, stream);
+}
+
+#ifdef KUIPER_TRACE
+namespace kuiper {
+int awq_gemv_trace_read(long long* out, int max_values);
+}
+extern "C" KUIPER_API int kuiper_gemv_trace_read(int64_t* out, int max_values) {
+    KUIPER_REQUIRE(out != nullptr && max_values > 0, "gemv_trace_read: empty destination");
+    return kuiper::awq_gemv_trace_read(reinterpret_cast<long long*>(out), max_values);
+}
+#endif
+
+extern "C" size_t kuiper_awq_gemv_ticket_bytes(void) { return 2 * sizeof(int); }
+
+extern "C" int kuiper_awq_gemv_accum_balanced_f32(const float* x, const uint16_t* norm_w, float eps, int swiglu,
+                                                  const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
+                                                  float* y, int M, int K, int N, int group, int act_mode, void* tickets,
+                                                  kuiper_stream_t stream) {
+    KUIPER_REQUIRE(!(norm_w && swiglu), "awq_gemv_accum_balanced: the fused norm and the fused SwiGLU exclude each other");
+    KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(norm_w) & 15) == 0, "awq_gemv_accum_balanced: norm weight must be 16-byte aligned");
+    return awq_gemv_accum_common(x, norm_w, eps, swiglu != 0, qweight, qzeros, scales, y, M, K, N, group, tickets, act_mode, stream);
+}
+
+extern "C" size_t kuiper_awq_gemv_group_table_bytes(int n_items) { return awq_gemv_group_table_bytes(n_items); }
+
+extern "C" int kuiper_awq_gemv_group_plan(const kuiper_gemv_item* items, int n_items, int group, void* host_table,
+                                          int64_t* units) {
+    KUIPER_REQUIRE(items && host_table && units, "awq_gemv_group_plan: null pointer");
+    KUIPER_REQUIRE(n_items > 0 && n_items <= 65536, "awq_gemv_group_plan: %d items", n_items);
+    KUIPER_REQUIRE(group == 128, "awq_gemv_group_plan: group size %d is not supported (128 only)", group);
+    KUIPER_REQUIRE(awq_gemv_mma_supported(128, 32), "awq_gemv_group_plan: tensor-map support is unavailable");
+    for (int i = 0; i < n_items; i++) {
+        const kuiper_gemv_item& o = items[i];
+        KUIPER_REQUIRE(o.x && o.qweight && o.qzeros && o.scales && o.y, "awq_gemv_group_plan: null tensor pointer in item %d", i);
+        KUIPER_REQUIRE(o.K > 0 && o.N > 0 && o.K % 128 == 0 && o.N % 32 == 0,
+                       "awq_gemv_group_plan: item %d needs K %% 128 == 0 and N %% 32 == 0 (K=%d N=%d)", i, o.K, o.N);
+        KUIPER_REQUIRE(((reinterpret_cast<uintptr_t>(o.qweight) | reinterpret_cast<uintptr_t>(o.qzeros) |
+                         reinterpret_cast<uintptr_t>(o.scales) | reinterpret_cast<uintptr_t>(o.y) | reinterpret_cast<uintptr_t>(o.x)) & 15) == 0,
+                       "awq_gemv_group_plan: tensors of item %d must be 16-byte aligned", i);
+    }
+    const long long u = awq_gemv_group_fill(items, n_items, host_table);
+    if (u <= 0) {
+        set_error("awq_gemv_group_plan: tensor map encoding failed or the list is too long");
+        return KUIPER_INTERNAL_ERROR;
+    }
+    *units = u;
+    return KUIPER_OK;
+}
+
+extern "C" int kuiper_awq_gemv_group_f32(const void* device_table, int n_items, int64_t units, int act_mode, void* tickets,
+                                         kuiper_stream_t stream) {
+    KUIPER_REQUIRE(act_mode == KUIPER_ACT_FP16 || act_mode == KUIPER_ACT_INT16_BLOCK, "awq_gemv_group: unknown act_mode %d", act_mode);
+    KUIPER_REQUIRE(device_table && (reinterpret_cast<uintptr_t>(device_table) & 63) == 0,
+                   "awq_gemv_group: the item table must be 64-byte aligned device memory");
+    KUIPER_REQUIRE(n_items > 0 && units > 0 && units <= 0x3fffffff, "awq_gemv_group: empty call");
+    KUIPER_REQUIRE((reinterpret_cast<uintptr_t>(tickets) & 7) == 0, "awq_gemv_group: tickets must be 8-byte aligned");
+    return awq_gemv_group_launch(device_table, n_items, units, static_cast<int*>(tickets), act_mode == KUIPER_ACT_INT16_BLOCK,
+                                 as_stream(stream));
 }
 
 extern "C" int kuiper_awq_gemv_status(void) {

@@ -49,7 +49,11 @@ public:
     // scratch of the tensor-core path: kernel::matmul_quant_gemm_workspace_bytes(max rows, dim1) bytes, no
     // initialisation needed
     void set_gemm_workspace(const tensor::Tensor& workspace) { gemm_workspace_ = workspace; }
-    // how the INT4 kernel rounds x: 1 = fp16 operand (default), 0 = fp32 operand
+    // accumulate mode: kernel::matmul_quant_ticket_bytes() zeroed bytes owned by this layer (its balance counters);
+    // without them the kernel deals its work out statically
+    void set_tickets(const tensor::Tensor& tickets) { tickets_ = tickets; }
+    // how the INT4 kernel rounds x: 1 = fp16 operand (default), 0 = fp32 operand, 2 = block-scaled 16-bit integers for
+    // single-row passes (the fastest decode kernel) and fp16 for passes of several rows
     void set_act_mode(int32_t act_mode) { act_mode_ = act_mode; }
 
     int32_t out_features() const { return dim0_; }
@@ -70,6 +74,7 @@ private:
     tensor::Tensor workspace_;
     tensor::Tensor gemm_workspace_;
     tensor::Tensor norm_scratch_;
+    tensor::Tensor tickets_;
     int32_t gemm_min_rows_ = 64;
 };
 }  // namespace op

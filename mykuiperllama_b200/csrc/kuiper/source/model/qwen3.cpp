@@ -116,6 +116,7 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     total += round256(size_t(R) * c.vocab_size * 4);
     total += 2 * round256(size_t(c.max_seq_len) * (D / 2) * 4);
     total += round256(ws_mm) + round256(ws_mha) + round256(ws_gemm) + (1u << 20);
+    total += size_t(c.layer_num) * 4 * 256;  // balance counters of the four projections of a layer
     auto arena = std::make_shared<base::CUDAArenaAllocator>(total);
     weight_alloc_ = arena;
 
@@ -176,6 +177,13 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         l->set_residual(residual);
         l->set_workspace(get_buffer(ModelBufferType::MatmulWorkspace));
         l->set_gemm_workspace(get_buffer(ModelBufferType::GemmWorkspace));
+        {
+            // balance counters of this layer object alone: launches that overlap under programmatic dependent
+            // launch are always different layer objects
+            Tensor tk = dev(DataType::DataTypeInt32, {int32_t(kernel::matmul_quant_ticket_bytes() / 4)});
+            cudaMemset(tk.ptr<void>(), 0, tk.byte_size());
+            l->set_tickets(tk);
+        }
         STATUS_CHECK(l->set_weight(0, dev(DataType::DataTypeInt32, {s.K, s.N / 8})));
         STATUS_CHECK(l->set_weight(1, dev(DataType::DataTypeInt32, {s.K / g, s.N / 8})));
         l->set_scales(dev(DataType::DataTypeFp16, {s.K / g, s.N}));
@@ -194,7 +202,7 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     // Under tensor parallelism the row-split projections (O, down) keep the ordered combine - their output is a
     // partial sum that goes through the all-reduce - while QKV and gate|up, whose outputs stay on the rank, still
     // accumulate with their pre-norms fused in.
-    accumulate_cols_ = c.act_mode == 1 && QKV % 32 == 0 && H % 32 == 0 && (2 * I) % 32 == 0;
+    accumulate_cols_ = c.act_mode != 0 && QKV % 32 == 0 && H % 32 == 0 && (2 * I) % 32 == 0;
     accumulate_ = accumulate_cols_ && c.tp_size == 1;
     layers_.resize(size_t(c.layer_num));
     layer_loaded_.assign(size_t(c.layer_num), false);

@@ -78,7 +78,7 @@ void matmul_kernel_quant_cu(const Tensor& input, const Tensor& qweight, const Te
 
 void matmul_kernel_quant_accum_cu(const Tensor& input, const Tensor& qweight, const Tensor& qzeros, const Tensor& scales,
                                   const Tensor& output, int32_t group_size, const Tensor* input_norm_weight, float eps,
-                                  bool input_swiglu, void* stream) {
+                                  bool input_swiglu, int32_t act_mode, const Tensor* tickets, void* stream) {
     require_cuda(input, "matmul input");
     require_cuda(qweight, "matmul qweight");
     require_cuda(qzeros, "matmul qzeros");
@@ -90,24 +90,21 @@ void matmul_kernel_quant_accum_cu(const Tensor& input, const Tensor& qweight, co
     CHECK_EQ(input.size() % in_row, size_t(0));
     const int32_t M = int32_t(input.size() / in_row);
     CHECK_EQ(output.size(), size_t(M) * size_t(N));
-    if (input_swiglu) {
-        CHECK(input_norm_weight == nullptr);
-        KERNEL_OK(kuiper_swiglu_awq_gemv_accum_f32(input.ptr<float>(), qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(),
-                                                   scales.ptr<uint16_t>(), out_ptr<float>(output), M, K, N, group_size,
-                                                   as_stream(stream)));
-        return;
-    }
+    CHECK(!(input_swiglu && input_norm_weight != nullptr));
     if (input_norm_weight) {
         require_cuda(*input_norm_weight, "matmul input norm weight");
         CHECK_EQ(input_norm_weight->size(), size_t(K));
-        KERNEL_OK(kuiper_rmsnorm_awq_gemv_accum_f32(input.ptr<float>(), input_norm_weight->ptr<uint16_t>(), eps,
-                                                    qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(), scales.ptr<uint16_t>(),
-                                                    out_ptr<float>(output), M, K, N, group_size, as_stream(stream)));
-        return;
     }
-    KERNEL_OK(kuiper_awq_gemv_accum_f32(input.ptr<float>(), qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(),
-                                        scales.ptr<uint16_t>(), out_ptr<float>(output), M, K, N, group_size,
-                                        as_stream(stream)));
+    void* tk = nullptr;
+    if (tickets && !tickets->is_empty()) {
+        require_cuda(*tickets, "matmul balance counters");
+        CHECK_GE(tickets->byte_size(), kuiper_awq_gemv_ticket_bytes());
+        tk = out_ptr<void>(*tickets);
+    }
+    KERNEL_OK(kuiper_awq_gemv_accum_balanced_f32(input.ptr<float>(), input_norm_weight ? input_norm_weight->ptr<uint16_t>() : nullptr,
+                                                 eps, input_swiglu ? 1 : 0, qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(),
+                                                 scales.ptr<uint16_t>(), out_ptr<float>(output), M, K, N, group_size, act_mode, tk,
+                                                 as_stream(stream)));
 }
 
 void matmul_kernel_quant_gemm_cu(const Tensor& input, const Tensor& qweight, const Tensor& qzeros, const Tensor& scales,
@@ -271,6 +268,7 @@ EmbeddingKernel get_emb_kernel(base::DeviceType d) { return pick<EmbeddingKernel
 ArgmaxKernel get_argmax_kernel(base::DeviceType d) { return pick<ArgmaxKernel>(d, argmax_kernel_cu, "argmax"); }
 
 size_t matmul_quant_workspace_bytes(int32_t M, int32_t K, int32_t N) { return kuiper_awq_gemv_workspace_bytes(M, K, N); }
+size_t matmul_quant_ticket_bytes() { return kuiper_awq_gemv_ticket_bytes(); }
 size_t matmul_quant_gemm_workspace_bytes(int32_t M, int32_t K) { return kuiper_awq_gemm_workspace_bytes(M, K); }
 size_t mha_workspace_bytes(int32_t M, int32_t head_num, int32_t head_size, int32_t max_seq) {
     return kuiper_flash_decode_workspace_bytes(M, head_num, head_size, max_seq);

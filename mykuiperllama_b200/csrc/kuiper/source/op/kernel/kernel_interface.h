@@ -32,11 +32,14 @@ using MatmulKernelQuant = void (*)(const tensor::Tensor& input, const tensor::Te
 // output[M,N] += input[M,K] . dequant(...): the output already holds the addend (residual stream or zeros).
 // With input_norm_weight (bf16 [K]) the operand is RMSNorm(input) formed inside the kernel.
 // With input_swiglu the input is a gate|up row [M, 2K] and the operand is silu(gate) * up (no norm then).
+// act_mode: 1 fp16 operand, 2 block-scaled 16-bit integer operand for single-row calls (fp16 otherwise).
+// tickets (may be null): matmul_quant_ticket_bytes() zeroed bytes owned by the calling layer; with them the kernel
+// hands the tail of the weight stream to whichever CTA is free, so that all CTAs finish together.
 using MatmulKernelQuantAccum = void (*)(const tensor::Tensor& input, const tensor::Tensor& qweight,
                                         const tensor::Tensor& qzeros, const tensor::Tensor& scales,
                                         const tensor::Tensor& output, int32_t group_size,
                                         const tensor::Tensor* input_norm_weight, float eps, bool input_swiglu,
-                                        void* stream);
+                                        int32_t act_mode, const tensor::Tensor* tickets, void* stream);
 
 // Tensor-core path for M >= 16 rows: output = input . dequant(...) (+ residual), or output += ... when accumulate.
 using MatmulKernelQuantGemm = void (*)(const tensor::Tensor& input, const tensor::Tensor& qweight,
@@ -88,6 +91,7 @@ ArgmaxKernel get_argmax_kernel(base::DeviceType device_type);
 
 // scratch sizes of the two kernels that need a workspace
 size_t matmul_quant_workspace_bytes(int32_t M, int32_t K, int32_t N);
+size_t matmul_quant_ticket_bytes();  // balance counters of one accumulate-mode layer
 size_t matmul_quant_gemm_workspace_bytes(int32_t M, int32_t K);  // fp16 activation copy of the tensor-core path
 size_t mha_workspace_bytes(int32_t M, int32_t head_num, int32_t head_size, int32_t max_seq);
 

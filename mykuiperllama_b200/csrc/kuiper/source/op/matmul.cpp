@@ -71,7 +71,7 @@ base::Status MatmulLayer::forward() {
     const int32_t M = int32_t(get_input(0).size() / (size_t(dim1_) * (input_swiglu_ ? 2 : 1)));
     if (input_swiglu_ && !(is_quant_layer_ && accumulate_ && input_norm_.is_empty()))
         return base::error::invalid_argument("the fused SwiGLU input needs a quantised layer in accumulate mode without a norm");
-    if (is_quant_layer_ && act_mode_ == 1 && gemm_min_rows_ > 0 && M >= gemm_min_rows_) {
+    if (is_quant_layer_ && act_mode_ != 0 && gemm_min_rows_ > 0 && M >= gemm_min_rows_) {
         // enough rows for the tensor cores: x and the dequantised weight go through tcgen05 as fp16
         if (accumulate_ && has_residual_) return base::error::invalid_argument("accumulate mode takes no residual input");
         const tensor::Tensor* x = &get_input(0);
@@ -95,7 +95,7 @@ base::Status MatmulLayer::forward() {
         if (has_residual_) return base::error::invalid_argument("accumulate mode takes no residual input");
         kernel::get_matmul_kernel_quant_accum(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),
                                                             group_size_, input_norm_.is_empty() ? nullptr : &input_norm_,
-                                                            input_norm_eps_, input_swiglu_, stream());
+                                                            input_norm_eps_, input_swiglu_, act_mode_ == 2 ? 2 : 1, &tickets_, stream());
     } else if (is_quant_layer_) {
         kernel::get_matmul_kernel_quant(device_type_)(get_input(0), get_weight(0), get_weight(1), scales_, get_output(0),
                                                       has_residual_ ? &get_input(1) : nullptr, group_size_, act_mode_,

@@ -21,7 +21,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 
-ROUND_NONE, ROUND_FP16, ROUND_BF16 = 0, 1, 2
+ROUND_NONE, ROUND_FP16, ROUND_BF16, ROUND_I16_BLOCK32, ROUND_ENGINE = 0, 1, 2, 3, 4
 AWQ_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)
 
 

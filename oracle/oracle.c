@@ -106,6 +106,41 @@ static inline float round_act(float v, int mode) {
     return v;
 }
 
+/* Rounds the M rows of an operand [M, K] the way the matmul named by `mode` does.  ORC_ROUND_I16_BLOCK32 is a block
+ * floating point: per 32 consecutive elements of a row, e is the largest exponent with |x * 2^e| < 2^14 for the
+ * largest magnitude of the block (e <= 126; a zero block takes 126) and x' = rint(x * 2^e) * 2^-e, ties to even.
+ * ORC_ROUND_ENGINE mirrors an engine created with act_mode 2: block floating point for a one-row pass, fp16 else. */
+static int engine_mode(int mode, int M) {
+    if (mode == ORC_ROUND_ENGINE) return M == 1 ? ORC_ROUND_I16_BLOCK32 : ORC_ROUND_FP16;
+    return mode;
+}
+static void round_rows(const float* x, float* out, int M, int K, int mode) {
+    mode = engine_mode(mode, M);
+    if (mode != ORC_ROUND_I16_BLOCK32) {
+        for (int64_t i = 0; i < (int64_t)M * K; i++) out[i] = round_act(x[i], mode);
+        return;
+    }
+    for (int m = 0; m < M; m++) {
+        for (int k0 = 0; k0 < K; k0 += 32) {
+            const int n = K - k0 < 32 ? K - k0 : 32;
+            const float* xb = x + (int64_t)m * K + k0;
+            float* ob = out + (int64_t)m * K + k0;
+            float amax = 0.0f;
+            for (int i = 0; i < n; i++) {
+                float a = fabsf(xb[i]);
+                if (a > amax) amax = a;
+            }
+            uint32_t bits;
+            memcpy(&bits, &amax, sizeof(bits));
+            int ea = (int)((bits >> 23) & 0xffu) - 127; /* floor(log2 amax); -127 for zero and subnormals */
+            int e = 13 - ea;
+            if (e > 126) e = 126;
+            const float scale = ldexpf(1.0f, e), inv = ldexpf(1.0f, -e);
+            for (int i = 0; i < n; i++) ob[i] = rintf(xb[i] * scale) * inv;
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ */
 /* add                                                                 */
 /* ------------------------------------------------------------------ */
@@ -211,7 +246,7 @@ void orc_gemv_f32(const float* x, const float* W, float* y, int M, int K, int N,
     ORC_CHECK(x && W && y && M > 0 && K > 0 && N > 0);
     float* xr = (float*)malloc((size_t)M * K * sizeof(float));
     ORC_CHECK(xr);
-    for (int64_t i = 0; i < (int64_t)M * K; i++) xr[i] = round_act(x[i], act_round);
+    round_rows(x, xr, M, K, act_round);
     /* column-blocked so W streams once per row of x and the accumulators stay in cache */
     enum { NB = 512 };
 #pragma omp parallel for schedule(static)
@@ -250,7 +285,7 @@ void orc_awq_gemv(const float* x, const int32_t* qweight, const int32_t* qzeros,
     int NW = N / 8;
     float* xr = (float*)malloc((size_t)M * K * sizeof(float));
     ORC_CHECK(xr);
-    for (int64_t i = 0; i < (int64_t)M * K; i++) xr[i] = round_act(x[i], act_round);
+    round_rows(x, xr, M, K, act_round);
     /* one task per packed word column: 8 outputs; each weight is dequantised once and
        applied to all M rows */
 #pragma omp parallel for schedule(static)

@@ -28,7 +28,15 @@ extern "C" {
 #endif
 
 /* how an activation vector is rounded before it enters a matmul */
-enum { ORC_ROUND_NONE = 0, ORC_ROUND_FP16 = 1, ORC_ROUND_BF16 = 2 };
+enum {
+    ORC_ROUND_NONE = 0,
+    ORC_ROUND_FP16 = 1,
+    ORC_ROUND_BF16 = 2,
+    /* 16-bit block floating point per 32 consecutive elements: x' = rint(x * 2^e) * 2^-e, |x * 2^e| < 2^14 */
+    ORC_ROUND_I16_BLOCK32 = 3,
+    /* what an engine with act_mode 2 does: I16_BLOCK32 for a one-row operand, FP16 for several rows */
+    ORC_ROUND_ENGINE = 4
+};
 
 /* OpenMP threads used by the loops below from now on (n <= 0: only query); returns the value in effect */
 int orc_set_num_threads(int n);

@@ -203,6 +203,111 @@ def test_awq_gemv_layer_shapes_of_the_4b_and_8b_models_match_oracle(cuda, oracle
     cuda.awq_gemv_status()
 
 
+@pytest.mark.parametrize("M,K,N,kind", [(1, 4096, 6144, "norm"), (1, 12288, 4096, "swiglu"), (1, 4096, 24576, "plain"), (2, 1024, 3072, "plain"),
+                                        (4, 2560, 1056, "norm"), (1, 128, 32, "plain"), (1, 4096, 4096, "plain")])
+@pytest.mark.parametrize("pct,chunk", [(25, 0), (90, 1), (50, 3)])
+@pytest.mark.parametrize("act_mode", [1, 2])
+def test_awq_gemv_balanced_by_tickets_matches_oracle(cuda, oracle, M, K, N, kind, pct, chunk, act_mode):
+    # the engine's entry: a share of the weight stream is handed out through an atomic ticket counter; whatever CTA
+    # takes which unit, the sum is the oracle's, and the counters are back at zero after every launch
+    rng = np.random.default_rng(M + K + N + pct)
+    q, z, s = awq_random(rng, K, N)
+    qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
+    W = (dev(qw), dev(qz), dev(su, torch.float16))
+    addend = rng.standard_normal((M, N)).astype(np.float32)
+    tickets = cuda.awq_gemv_tickets()
+    cuda.set_tuning("gemv_dyn_pct", pct)
+    cuda.set_tuning("gemv_dyn_chunk", chunk)
+    # act_mode 2: a one-row call rounds its operand to 16-bit block floating point (integer tensor-core kernel), calls
+    # with more rows to fp16 - the oracle's ROUND_ENGINE does the same
+    mirror = oracle.ROUND_ENGINE if act_mode == 2 else oracle.ROUND_FP16
+    try:
+        for rep in range(3):  # the second and third launch find the counters as the one before left them
+            y = dev(addend)
+            if kind == "norm":
+                h = (rng.standard_normal((M, K)) * 2.5).astype(np.float32)
+                nw = oracle.f32_to_bf16((1 + 0.1 * rng.standard_normal(K)).astype(np.float32))
+                cuda.awq_gemv_accum_balanced(dev(h), *W, y, tickets, norm_w=dev(nw), eps=1e-6, act_mode=act_mode)
+                ref, tol = oracle.awq_gemv(oracle.rmsnorm(h, nw, 1e-6), qw, qz, su).astype(np.float64) + addend, 1e-3
+            elif kind == "swiglu":
+                gu = rng.standard_normal((M, 2 * K)).astype(np.float32)
+                cuda.awq_gemv_accum_balanced(dev(gu), *W, y, tickets, swiglu=True, act_mode=act_mode)
+                act = np.stack([oracle.swiglu(gu[m, :K], gu[m, K:]) for m in range(M)])
+                ref, tol = oracle.awq_gemv(act, qw, qz, su, act_round=mirror).astype(np.float64) + addend, 1e-5
+            else:
+                x = rng.standard_normal((M, K)).astype(np.float32)
+                cuda.awq_gemv_accum_balanced(dev(x), *W, y, tickets, act_mode=act_mode)
+                ref, tol = oracle.awq_gemv(x, qw, qz, su, act_round=mirror).astype(np.float64) + addend, 2e-6
+            torch.cuda.synchronize()
+            err = rel_err(y.cpu().numpy(), ref)
+            assert err <= SPEC_TOL and err <= tol, (rep, err)
+            assert not tickets.any(), "the ticket and exit counters must be back at zero after the launch"
+    finally:
+        cuda.set_tuning("gemv_dyn_pct", -1)
+        cuda.set_tuning("gemv_dyn_chunk", -1)
+    cuda.awq_gemv_status()
+
+
+@pytest.mark.parametrize("shapes", [[(2048, 2048)] * 9, [(256, 1056), (4096, 4096), (128, 32), (1024, 3072), (2560, 2560)],
+                                    [(128, 32)] * 3, [(2048, 2048)] * 70])
+@pytest.mark.parametrize("balanced,act_mode", [(True, 1), (False, 1), (False, 2), (True, 2)])
+def test_awq_gemv_grouped_launch_matches_oracle(cuda, oracle, shapes, balanced, act_mode):
+    # a list of independent projections as ONE persistent launch (the single-GEMV workload visited over many weight
+    # sets): every item against the oracle, twice on the same table and counters
+    rng = np.random.default_rng(len(shapes) * 13 + shapes[0][0])
+    items, refs = [], []
+    distinct = {}
+    for i, (K, N) in enumerate(shapes):
+        key = (K, N, i % 5)  # a handful of distinct weight sets per shape keeps the oracle's share of the test short
+        if key not in distinct:
+            q, z, s = awq_random(rng, K, N)
+            distinct[key] = (oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16))
+        qw, qz, su = distinct[key]
+        x = rng.standard_normal((1, K)).astype(np.float32)
+        addend = rng.standard_normal((1, N)).astype(np.float32)
+        items.append(dict(x=dev(x), qweight=dev(qw), qzeros=dev(qz), scales=dev(su, torch.float16), y=dev(addend)))
+        refs.append((oracle.awq_gemv(x, qw, qz, su, act_round=oracle.ROUND_FP16 if act_mode == 1 else oracle.ROUND_I16_BLOCK32).astype(np.float64),
+                     addend))
+    grp = cuda.GemvGroup(items, balanced=balanced, act_mode=act_mode)
+    for rep in (1, 2):
+        grp.run()
+        torch.cuda.synchronize()
+        for it, (ref, addend) in zip(items, refs):
+            assert rel_err(it["y"].cpu().numpy(), rep * ref + addend) <= 4e-6
+        if balanced:
+            assert not grp.tickets.any()
+    cuda.awq_gemv_status()
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (2048, 2048), (256, 1056), (128, 32), (12288, 4096)])
+@pytest.mark.parametrize("scale", [1.0, 1e-6, 3e4])
+def test_awq_gemv_integer_operand_kernel(cuda, oracle, K, N, scale):
+    # one token row on the integer tensor path (act_mode 2): the operand is 16-bit block floating point per 32 rows, every
+    # product and every sum inside a block is an exact integer.  Against the oracle with the same operand rounding only
+    # the fp32 summation across blocks differs; against the un-rounded oracle the workload's 1e-2 holds with a wide
+    # margin also when the activations are tiny, large, or carry outliers
+    rng = np.random.default_rng(K + N)
+    q, z, s = awq_random(rng, K, N)
+    qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
+    W = (dev(qw), dev(qz), dev(su, torch.float16))
+    x = (rng.standard_normal((1, K)) * scale).astype(np.float32)
+    x[0, ::97] *= 300.0  # outliers inside many blocks
+    res = (rng.standard_normal((1, N)) * scale).astype(np.float32)
+    ref_mirror = oracle.awq_gemv(x, qw, qz, su, acc_double=True, act_round=oracle.ROUND_I16_BLOCK32).astype(np.float64) + res
+    ref_plain = oracle.awq_gemv(x, qw, qz, su, acc_double=True).astype(np.float64) + res
+    y = cuda.awq_gemv(dev(x), *W, residual=dev(res), act_mode=2)          # ordered combine: deterministic
+    y2 = cuda.awq_gemv(dev(x), *W, residual=dev(res), act_mode=2)
+    ya = dev(res)
+    cuda.awq_gemv_accum_balanced(dev(x), *W, ya, act_mode=2)               # accumulate mode
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2)
+    for got in (y.cpu().numpy(), ya.cpu().numpy()):
+        assert rel_err(got, ref_mirror) <= 2e-6
+        err = rel_err(got, ref_plain)
+        assert err <= SPEC_TOL and err <= 1e-3
+    cuda.awq_gemv_status()
+
+
 def test_awq_gemv_ragged_width_uses_generic_kernel(cuda, oracle):
     err, *_ = _gemv_case(cuda, oracle, np.random.default_rng(5), 2, 256, 40, 1, residual=True)
     assert err <= 2e-6

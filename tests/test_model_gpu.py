@@ -15,8 +15,13 @@ def engine_mod(cuda):
     return engine
 
 
+def _mirror(oracle, act_mode):
+    """The oracle's operand rounding that mirrors an engine created with this act_mode."""
+    return {0: oracle.ROUND_NONE, 1: oracle.ROUND_FP16, 2: oracle.ROUND_ENGINE}[act_mode]
+
+
 def _pair(oracle, engine_mod, cfg_kwargs, seed, act_mode=1):
-    ocfg = oracle.ModelConfig(**cfg_kwargs, act_round=oracle.ROUND_FP16 if act_mode == 1 else oracle.ROUND_NONE)
+    ocfg = oracle.ModelConfig(**cfg_kwargs, act_round=_mirror(oracle, act_mode))
     weights = make_model_weights(oracle, ocfg, seed=seed)
     ref = oracle.OracleModel(ocfg, weights)
     ecfg = engine_mod.EngineConfig(**cfg_kwargs, max_rows=8, act_mode=act_mode)
@@ -35,7 +40,7 @@ def test_selftest_with_cuda(cuda):
     assert failed == 0, buf.value.decode()
 
 
-@pytest.mark.parametrize("act_mode", [1, 0])
+@pytest.mark.parametrize("act_mode", [2, 1, 0])
 def test_tiny_model_logits_and_tokens(oracle, engine_mod, act_mode):
     ref, eng, _ = _pair(oracle, engine_mod, TINY, seed=1, act_mode=act_mode)
     rng = np.random.default_rng(2)
@@ -66,8 +71,9 @@ def test_tiny_model_logits_and_tokens(oracle, engine_mod, act_mode):
     assert rel_err(lg_again, lg_plain) <= 1e-2
 
 
-def test_prefill_and_graph_decode_match_oracle_greedy(oracle, engine_mod):
-    ref, eng, _ = _pair(oracle, engine_mod, TINY, seed=3)
+@pytest.mark.parametrize("act_mode", [2, 1])
+def test_prefill_and_graph_decode_match_oracle_greedy(oracle, engine_mod, act_mode):
+    ref, eng, _ = _pair(oracle, engine_mod, TINY, seed=3, act_mode=act_mode)
     rng = np.random.default_rng(4)
     prompt = rng.integers(0, 1000, 19).astype(np.int32)  # 19 = two full chunks of 8 + a ragged one
     _, nx_ref = ref.forward(prompt, np.arange(19, dtype=np.int32))
@@ -90,7 +96,7 @@ def test_prefill_and_graph_decode_match_oracle_greedy(oracle, engine_mod):
 
 
 def test_decode_predict_end_to_end_path(oracle, engine_mod):
-    ref, eng, _ = _pair(oracle, engine_mod, TINY, seed=5)
+    ref, eng, _ = _pair(oracle, engine_mod, TINY, seed=5, act_mode=2)
     prompt = np.array([3, 1, 4, 1, 5, 9, 2, 6], np.int32)
     _, nx_ref = ref.forward(prompt, np.arange(8, dtype=np.int32))
     first = eng.prefill(prompt)
@@ -164,12 +170,13 @@ def test_passes_of_64_rows_or_more_use_the_tensor_core_gemm(oracle, engine_mod):
     capi.awq_gemm_status()
 
 
-def test_qwen3_0p6b_shape_greedy_identity_32_tokens(oracle, engine_mod):
+@pytest.mark.parametrize("act_mode", [2, 1])
+def test_qwen3_0p6b_shape_greedy_identity_32_tokens(oracle, engine_mod, act_mode):
     """Config 2 of the workload: Qwen3-0.6B shape, random init, 64-token prompt, greedy tokens identical
     to the oracle's for the first 32 decode steps."""
     cfg = dict(n_layers=28, hidden=1024, n_q_heads=16, n_kv_heads=8, head_dim=128, inter=3072, vocab=151936,
                max_seq=128, max_batch=1)
-    ref, eng, _ = _pair(oracle, engine_mod, cfg, seed=0)
+    ref, eng, _ = _pair(oracle, engine_mod, cfg, seed=0, act_mode=act_mode)
     rng = np.random.default_rng(0)
     prompt = rng.integers(0, 151936, 64).astype(np.int32)
     _, nx_ref = ref.forward(prompt, np.arange(64, dtype=np.int32), logit_rows=1)
@@ -192,15 +199,16 @@ def test_qwen3_0p6b_shape_greedy_identity_32_tokens(oracle, engine_mod):
     ("qwen3-4b", dict(hidden=2560, n_q_heads=32, n_kv_heads=8, inter=9728)),
     ("qwen3-8b", dict(hidden=4096, n_q_heads=32, n_kv_heads=8, inter=12288)),
 ])
-def test_two_layer_cuts_of_the_4b_and_8b_shapes_match_oracle(oracle, engine_mod, name, shape):
+@pytest.mark.parametrize("act_mode", [2, 1])
+def test_two_layer_cuts_of_the_4b_and_8b_shapes_match_oracle(oracle, engine_mod, name, shape, act_mode):
     """Layer widths and the full vocabulary of the Qwen3-4B / 8B shapes, cut to two layers so that the CPU oracle
     finishes in seconds: prompt logits within tolerance and the 32 greedy tokens after it identical."""
     cfg = dict(n_layers=2, head_dim=128, vocab=151936, max_seq=96, max_batch=1, **shape)
     from helpers import make_model_weights_fast
-    ocfg = oracle.ModelConfig(**cfg, act_round=oracle.ROUND_FP16)
+    ocfg = oracle.ModelConfig(**cfg, act_round=_mirror(oracle, act_mode))
     weights = make_model_weights_fast(oracle, ocfg, seed=11)
     ref = oracle.OracleModel(ocfg, weights)
-    eng = engine_mod.Qwen3Engine(engine_mod.EngineConfig(**cfg, max_rows=8, act_mode=1))
+    eng = engine_mod.Qwen3Engine(engine_mod.EngineConfig(**cfg, max_rows=8, act_mode=act_mode))
     eng.load(weights)
     rng = np.random.default_rng(12)
     prompt = rng.integers(0, 151936, 16).astype(np.int32)

@@ -23,10 +23,11 @@ def main():
     # 8 kv heads and an intermediate width of 8 groups: shards evenly over 2, 4 and 8 ranks
     cfg = dict(n_layers=2, hidden=512, n_q_heads=16, n_kv_heads=8, head_dim=128, inter=1024, vocab=1000, max_seq=64,
                max_batch=1)
-    ocfg = orc.ModelConfig(**cfg, act_round=orc.ROUND_FP16)
+    act_mode = int(os.environ.get("KUIPER_TEST_ACT_MODE", "2"))
+    ocfg = orc.ModelConfig(**cfg, act_round=orc.ROUND_ENGINE if act_mode == 2 else orc.ROUND_FP16)
     weights = make_model_weights(orc, ocfg, seed=21)
     ref = orc.OracleModel(ocfg, weights)
-    eng = engine.Qwen3Engine(engine.EngineConfig(**cfg, tp_rank=rank, tp_size=world))
+    eng = engine.Qwen3Engine(engine.EngineConfig(**cfg, tp_rank=rank, tp_size=world, act_mode=act_mode))
     eng.load(weights)  # every rank gets the unsharded weights; the engine slices its part
     uid = [engine.Qwen3Engine.tp_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(uid, 0)
