@@ -260,6 +260,17 @@ KUIPER_API int kuiper_flash_decode(const float* q, const uint16_t* kcache, const
                         void* workspace, size_t workspace_bytes, kuiper_stream_t stream);
 
 /*
+ * Causal attention for a prompt chunk: the M rows are consecutive tokens of ONE sequence (row m at position pos0 + m of
+ * sequence `slot`, already appended to the caches) and row m attends to cache positions [0, pos0 + m].  Tiled: every K / V
+ * tile is loaded once per block of 64 / (Nq / Nkv) query rows (bf16 mma.sync, fp32 softmax; q and the probabilities as
+ * bf16 high + low parts like the decode kernel), no workspace.  Same placeholder (kuiper/include/op/mha.h:1-11).
+ * pos0 and slot are host values: a prompt is fed from the host, chunk by chunk.
+ */
+KUIPER_API int kuiper_flash_prefill(const float* q, const uint16_t* kcache, const uint16_t* vcache, float* out,
+                                    int M, int Nq, int Nkv, int D, int max_seq, int n_slots, int pos0, int slot,
+                                    kuiper_stream_t stream);
+
+/*
  * The two calls above in one kernel, for decode batches: every token row m must belong to a different
  * sequence slot and seq_len[m] == pos[m] + 1.  Each CTA forms q (per-head RMSNorm + rotary) for its kv
  * head from the raw projection row in qkv; the CTA whose slice ends the sequence appends the new K / V

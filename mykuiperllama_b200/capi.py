@@ -235,6 +235,18 @@ def flash_decode(q, kcache, vcache, seq_len, slot, workspace=None, out=None, fre
     return out
 
 
+def flash_prefill(q, kcache, vcache, pos0, slot, out=None):
+    """Causal attention of a prompt chunk: q [M, Nq, D], row m at position pos0 + m of sequence `slot` (rows already in
+    the caches); returns [M, Nq, D]."""
+    _dev(q, kcache, vcache, out)
+    M, Nq, D = q.shape
+    n_slots, Nkv, max_seq, _ = kcache.shape
+    out = torch.empty_like(q) if out is None else out
+    check(kernels().kuiper_flash_prefill(_ptr(q), _ptr(kcache), _ptr(vcache), _ptr(out), M, Nq, Nkv, D, max_seq, n_slots,
+                                         int(pos0), int(slot), _stream()))
+    return out
+
+
 def rope_flash_decode(qkv, q_norm_w, k_norm_w, cos_t, sin_t, pos, seq_len, slot, Nq, Nkv, D, eps, kcache, vcache,
                       workspace=None, out=None, fresh_rows=-1, clear_input=False, clear_extra=None):
     """q/k-norm + rotary + KV append + flash-decoding in one kernel (decode batches: one row per sequence slot,

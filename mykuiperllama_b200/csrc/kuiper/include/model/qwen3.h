@@ -103,6 +103,11 @@ private:
     // attention kernel may fetch all older cache rows before the rotary kernel has finished
     bool rows_compact_ = false;
     bool slots_distinct_ = false;  // every row of the current pass has its own sequence slot
+    // the rows of the current pass are consecutive tokens of one sequence (a prompt chunk): position of the first row,
+    // the sequence slot; chunks of at least kPrefillAttentionMinRows rows take the tiled prefill attention kernel
+    bool rows_are_chunk_ = false;
+    int32_t chunk_pos0_ = 0, chunk_slot_ = 0;
+    static constexpr int32_t kPrefillAttentionMinRows = 16;
 };
 
 }  // namespace model

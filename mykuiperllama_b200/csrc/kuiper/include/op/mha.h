@@ -27,6 +27,9 @@ public:
     // `rows` cache rows of a sequence, everything below seq_len - rows (and seq_len / slot) was final before it
     // started.  The attention kernel then fetches those rows while that kernel is still finishing.  -1 = no promise.
     void set_fresh_rows(int32_t rows) { fresh_rows_ = rows; }
+    // Prompt chunk: the rows of `query` are consecutive tokens of sequence `slot` starting at position pos0 (their K / V
+    // rows are in the cache already); causal attention with every K / V tile loaded once per block of query rows.
+    base::Status forward_prefill(const tensor::Tensor& query, int32_t pos0, int32_t slot, const tensor::Tensor& output);
 
 private:
     int32_t head_num_ = 0, kv_head_num_ = 0, head_size_ = 0;

@@ -363,6 +363,12 @@ base::Status Qwen3Model::upload_rows(const int32_t* tokens, const int32_t* pos, 
             lo[size_t(slot[m])] = std::min(lo[size_t(slot[m])], pos[m]);
             hi[size_t(slot[m])] = std::max(hi[size_t(slot[m])], pos[m]);
         }
+        // a prompt chunk: one sequence, consecutive positions
+        chunk_pos0_ = pos[0];
+        chunk_slot_ = slot[0];
+        rows_are_chunk_ = M >= kPrefillAttentionMinRows;
+        for (int32_t m = 1; m < M && rows_are_chunk_; m++)
+            if (slot[m] != slot[0] || pos[m] != pos[0] + m) rows_are_chunk_ = false;
         rows_compact_ = true;
         for (int32_t b = 0; b < config_.max_batch; b++)
             if (hi[size_t(b)] >= 0 && hi[size_t(b)] - lo[size_t(b)] >= M) rows_compact_ = false;
@@ -444,8 +450,13 @@ base::Status Qwen3Model::run_pass(int32_t M, bool inputs_settled) {
             // sequence lie within M consecutive positions, every cache row below seq_len - M is older than this pass.
             // The promise also covers seq_len / slot, so it is only made when those were settled before the pass
             // (kernels under programmatic dependent launch may start ahead of earlier copies of the same pass).
-            L.mha->set_fresh_rows(rows_compact_ && inputs_settled ? M : -1);
-            RETURN_IF_ERROR(L.mha->forward(q, seq_len, slot, att));
+            if (rows_are_chunk_ && !inputs_settled) {
+                // prompt chunk of one sequence: tiled causal attention, K / V tiles shared by a block of query rows
+                RETURN_IF_ERROR(L.mha->forward_prefill(q, chunk_pos0_, chunk_slot_, att));
+            } else {
+                L.mha->set_fresh_rows(rows_compact_ && inputs_settled ? M : -1);
+                RETURN_IF_ERROR(L.mha->forward(q, seq_len, slot, att));
+            }
         }
         RETURN_IF_ERROR(project_and_reduce(*L.o, att));
         if (accumulate_cols_) {

@@ -180,6 +180,22 @@ void mha_kernel_cu(const Tensor& query, const Tensor& key_cache, const Tensor& v
                                   out_ptr<void>(workspace), workspace.byte_size(), as_stream(stream)));
 }
 
+void mha_prefill_kernel_cu(const Tensor& query, const Tensor& key_cache, const Tensor& value_cache, const Tensor& output,
+                           int32_t head_num, int32_t kv_head_num, int32_t head_size, int32_t pos0, int32_t slot, void* stream) {
+    require_cuda(query, "mha query");
+    require_cuda(output, "mha output");
+    require_cuda(key_cache, "mha key cache");
+    require_cuda(value_cache, "mha value cache");
+    CHECK_EQ(key_cache.dims_size(), 4);
+    const int32_t row = head_num * head_size;
+    CHECK_EQ(query.size() % size_t(row), size_t(0));
+    const int32_t M = int32_t(query.size() / size_t(row));
+    CHECK_EQ(output.size(), query.size());
+    KERNEL_OK(kuiper_flash_prefill(query.ptr<float>(), key_cache.ptr<uint16_t>(), value_cache.ptr<uint16_t>(),
+                                   out_ptr<float>(output), M, head_num, kv_head_num, head_size, key_cache.get_dim(2),
+                                   key_cache.get_dim(0), pos0, slot, as_stream(stream)));
+}
+
 void rope_mha_kernel_cu(const Tensor& qkv, const Tensor& q_norm, const Tensor& k_norm, const Tensor& cos_cache,
                         const Tensor& sin_cache, const Tensor& pos, const Tensor& seq_len, const Tensor& slot,
                         const Tensor& output, const Tensor& key_cache, const Tensor& value_cache, int32_t head_num,
@@ -262,6 +278,7 @@ MatmulKernelQuantGemm get_matmul_kernel_quant_gemm(base::DeviceType d) {
 RMSNormKernel get_rmsnorm_kernel(base::DeviceType d) { return pick<RMSNormKernel>(d, rmsnorm_kernel_cu, "rmsnorm"); }
 RoPEKernel get_rope_kernel(base::DeviceType d) { return pick<RoPEKernel>(d, rope_kernel_cu, "rope"); }
 MHAKernel get_mha_kernel(base::DeviceType d) { return pick<MHAKernel>(d, mha_kernel_cu, "mha"); }
+MHAPrefillKernel get_mha_prefill_kernel(base::DeviceType d) { return pick<MHAPrefillKernel>(d, mha_prefill_kernel_cu, "prefill mha"); }
 RoPEMHAKernel get_rope_mha_kernel(base::DeviceType d) { return pick<RoPEMHAKernel>(d, rope_mha_kernel_cu, "rope+mha"); }
 SwigluKernel get_swiglu_kernel(base::DeviceType d) { return pick<SwigluKernel>(d, swiglu_kernel_cu, "swiglu"); }
 EmbeddingKernel get_emb_kernel(base::DeviceType d) { return pick<EmbeddingKernel>(d, emb_kernel_cu, "embedding"); }

@@ -69,6 +69,11 @@ using MHAKernel = void (*)(const tensor::Tensor& query, const tensor::Tensor& ke
                            int32_t head_num, int32_t kv_head_num, int32_t head_size, int32_t fresh_rows,
                            const tensor::Tensor& workspace, void* stream);
 
+// causal attention of a prompt chunk: the M rows are consecutive tokens of one sequence starting at position pos0
+using MHAPrefillKernel = void (*)(const tensor::Tensor& query, const tensor::Tensor& key_cache, const tensor::Tensor& value_cache,
+                                  const tensor::Tensor& output, int32_t head_num, int32_t kv_head_num, int32_t head_size,
+                                  int32_t pos0, int32_t slot, void* stream);
+
 using SwigluKernel = void (*)(const tensor::Tensor& gate_up, const tensor::Tensor& output, bool clear_input, void* stream);
 
 using EmbeddingKernel = void (*)(const tensor::Tensor& tokens, const tensor::Tensor& table, const tensor::Tensor& output,
@@ -84,6 +89,7 @@ MatmulKernelQuantGemm get_matmul_kernel_quant_gemm(base::DeviceType device_type)
 RMSNormKernel get_rmsnorm_kernel(base::DeviceType device_type);
 RoPEKernel get_rope_kernel(base::DeviceType device_type);
 MHAKernel get_mha_kernel(base::DeviceType device_type);
+MHAPrefillKernel get_mha_prefill_kernel(base::DeviceType device_type);
 RoPEMHAKernel get_rope_mha_kernel(base::DeviceType device_type);
 SwigluKernel get_swiglu_kernel(base::DeviceType device_type);
 EmbeddingKernel get_emb_kernel(base::DeviceType device_type);

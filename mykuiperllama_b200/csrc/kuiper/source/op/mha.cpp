@@ -57,4 +57,23 @@ base::Status MultiHeadAttention::forward() {
     return base::error::success();
 }
 
+base::Status MultiHeadAttention::forward_prefill(const tensor::Tensor& query, int32_t pos0, int32_t slot,
+                                                 const tensor::Tensor& output) {
+    base::Status status = check_tensor(query, device_type_, data_type_);
+    const int32_t row = head_num_ * head_size_;
+    if (status && (query.size() % size_t(row) != 0 || output.size() != query.size()))
+        status = base::error::invalid_argument("The query / output tensors of the prefill attention have a wrong size.");
+    if (!status) return status;
+    status = check_tensor(output, device_type_, data_type_);
+    if (!status) return status;
+    const int32_t M = int32_t(query.size() / size_t(row));
+    if (key_cache_.is_empty() || value_cache_.is_empty() || key_cache_.dims_size() != 4)
+        return base::error::invalid_argument("The KV cache is not set.");
+    if (slot < 0 || slot >= key_cache_.get_dim(0) || pos0 < 0 || pos0 + M > key_cache_.get_dim(2))
+        return base::error::invalid_argument("The prompt chunk does not fit the KV cache.");
+    kernel::get_mha_prefill_kernel(device_type_)(query, key_cache_, value_cache_, output, head_num_, kv_head_num_, head_size_,
+                                                 pos0, slot, stream());
+    return base::error::success();
+}
+
 }  // namespace op
