@@ -490,9 +490,7 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
 
     ctx_mid = prompt_len + args.warmup + args.steps // 2
     peak, peak_kind = measured_peak_gbs()
-    step_bytes = token_bytes(cfg, ctx_mid, B) / world  # per GPU under tensor parallelism (lm_head is replicated)
-    if world > 1:
-        step_bytes += (world - 1) / world * cfg["vocab"] * cfg["hidden"] * 2
+    step_bytes = token_bytes(cfg, ctx_mid, B) / world  # per GPU under tensor parallelism (the lm_head is split over the vocabulary)
     roof_tps = peak * 1e9 / step_bytes
     line = {
         "metric": "Qwen3 INT4 decode tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,

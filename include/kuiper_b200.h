@@ -193,21 +193,37 @@ KUIPER_API int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const
                                    kuiper_stream_t stream);
 KUIPER_API int kuiper_awq_gemm_status(void);
 
-/* ---- one-shot all-reduce (sum, fp32) over peer-mapped exchange buffers: tensor-parallel decode.  No counterpart in
- * the reference (it has no multi-GPU code).
+/* ---- tensor-parallel exchanges for decode rows over peer-mapped buffers.  No counterpart in the reference (it has no
+ * multi-GPU code).
  * Every rank owns an exchange buffer of kuiper_allreduce_buffer_bytes(world, max_count) bytes, zero-initialised once,
  * 128-byte aligned, and mapped into every other rank's process (CUDA IPC); rank_buffers is a HOST array of `world`
- * device pointers, entry r = rank r's buffer as this process sees it (entry `rank` = the own buffer).  state: two
- * zero-initialised uint32 on the device (sequence number, error word), private to the rank.  All ranks must issue
- * the same sequence of calls with the same count.  data (16-byte aligned, count % 4 == 0, count <= max_count,
- * max_count % 32 == 0) holds the partial row on entry and the sum on return; every rank adds in rank order, so all
- * ranks get identical bits.  Waits on peers are bounded (default five seconds, tuning key "allreduce_timeout_ms"):
- * when one runs out the call's result is void and kuiper_allreduce_status (synchronous) returns 5. ---- */
+ * device pointers, entry r = rank r's buffer as this process sees it (entry `rank` = the own buffer).  state:
+ * kuiper_allreduce_state_bytes() zero-initialised bytes on the device, private to the rank (sequence numbers and an
+ * error word).  All ranks must issue the same sequence of calls with the same sizes.
+ *
+ * kuiper_allreduce_sum_f32: out[i] = residual[i] + sum over ranks of partial[i] (residual may be NULL; it must hold the
+ * same values on every rank; out may alias residual).  Every value travels as one 8-byte word {value, sequence
+ * number} stored straight into the peers' buffers; the receiver polls the words themselves and adds them in rank
+ * order, so all ranks get identical bits and there is no flag, fence or barrier between sending and receiving.
+ * clear_partial != 0 zeroes `partial` after it has been read (ready for the next accumulating projection).
+ * count <= max_count <= 65536, max_count % 16 == 0.
+ *
+ * kuiper_argmax_allgather: the greedy token over a vocabulary split across ranks.  logits_local is this rank's slice
+ * [M, V_local] (rank r holds global indices [r V_local, (r+1) V_local)); next[m] = lowest global index of the maximum
+ * over all slices (the tie rule of kuiper_argmax_f32), identical on every rank.  M <= 16.
+ *
+ * Waits on peers are bounded (default five seconds, tuning key "allreduce_timeout_ms"): when one runs out the call's
+ * result is void, an error word is set, and kuiper_allreduce_status (synchronous; clear != 0 resets the word)
+ * returns 5. ---- */
 KUIPER_API size_t kuiper_allreduce_buffer_bytes(int world, int64_t max_count);
-KUIPER_API int kuiper_allreduce_oneshot_f32(float* data, int64_t count, int rank, int world,
-                                            void* const* rank_buffers, int64_t max_count, uint32_t* state,
-                                            kuiper_stream_t stream);
-KUIPER_API int kuiper_allreduce_status(const uint32_t* state);
+KUIPER_API size_t kuiper_allreduce_state_bytes(void);
+KUIPER_API int kuiper_allreduce_sum_f32(const float* partial, const float* residual, float* out, int clear_partial,
+                                        int64_t count, int rank, int world, void* const* rank_buffers,
+                                        int64_t max_count, uint32_t* state, kuiper_stream_t stream);
+KUIPER_API int kuiper_argmax_allgather(const float* logits_local, int32_t* next, int M, int V_local, int rank, int world,
+                                       void* const* rank_buffers, int64_t max_count, uint32_t* state,
+                                       kuiper_stream_t stream);
+KUIPER_API int kuiper_allreduce_status(uint32_t* state, int clear);
 
 /* ---- BF16 GEMV (lm_head): W bf16 [N, K], y[M,N] = x[M,K] . W^T ---- */
 KUIPER_API int kuiper_bf16_gemv_f32(const float* x, const uint16_t* W, float* y, int M, int K, int N,

@@ -53,8 +53,10 @@ KERNEL_API = {
     "kuiper_awq_gemm_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "kuiper_awq_gemm_status": (_i32, []),
     "kuiper_allreduce_buffer_bytes": (_sz, [_i32, _i64]),
-    "kuiper_allreduce_oneshot_f32": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _vp]),
-    "kuiper_allreduce_status": (_i32, [_vp]),
+    "kuiper_allreduce_state_bytes": (_sz, []),
+    "kuiper_allreduce_sum_f32": (_i32, [_vp, _vp, _vp, _i32, _i64, _i32, _i32, _vp, _i64, _vp, _vp]),
+    "kuiper_argmax_allgather": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp]),
+    "kuiper_allreduce_status": (_i32, [_vp, _i32]),
     "kuiper_bf16_gemv_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_rmsnorm_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _vp]),
     "kuiper_qknorm_rope_kvwrite": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _i32,

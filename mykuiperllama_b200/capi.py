@@ -271,17 +271,36 @@ def allreduce_buffer(world, max_count, device="cuda"):
     return torch.zeros(n, dtype=torch.uint8, device=device)
 
 
-def allreduce_oneshot(data, rank, world, rank_buffers, max_count, state):
-    """In-place sum of `data` over the ranks whose exchange buffers are listed in rank_buffers (tensors or raw pointers)."""
+def allreduce_state(device="cuda"):
+    return torch.zeros(kernels().kuiper_allreduce_state_bytes() // 4, dtype=torch.int32, device=device)
+
+
+def _buffer_ptrs(rank_buffers, world):
     import ctypes
-    _dev(data, state)
-    ptrs = (ctypes.c_void_p * world)(*[b if isinstance(b, int) else b.data_ptr() for b in rank_buffers])
-    check(kernels().kuiper_allreduce_oneshot_f32(_ptr(data), data.numel(), rank, world, ptrs, max_count, _ptr(state), _stream()))
-    return data
+    return (ctypes.c_void_p * world)(*[b if isinstance(b, int) else b.data_ptr() for b in rank_buffers])
 
 
-def allreduce_status(state) -> None:
-    check(kernels().kuiper_allreduce_status(_ptr(state)))
+def allreduce_sum(partial, rank, world, rank_buffers, max_count, state, residual=None, out=None, clear_partial=False):
+    """out = residual + sum over the ranks of `partial` (see kuiper_allreduce_sum_f32); rank_buffers: tensors or raw pointers."""
+    _dev(partial, state, residual, out)
+    out = torch.empty_like(partial) if out is None else out
+    check(kernels().kuiper_allreduce_sum_f32(_ptr(partial), _ptr(residual), _ptr(out), int(clear_partial), partial.numel(), rank, world,
+                                             _buffer_ptrs(rank_buffers, world), max_count, _ptr(state), _stream()))
+    return out
+
+
+def argmax_allgather(logits_local, rank, world, rank_buffers, max_count, state):
+    """Greedy ids over a vocabulary split across ranks; logits_local: this rank's [M, V_local] slice."""
+    _dev(logits_local, state)
+    M, V_local = logits_local.shape
+    out = torch.empty(M, dtype=torch.int32, device=logits_local.device)
+    check(kernels().kuiper_argmax_allgather(_ptr(logits_local), _ptr(out), M, V_local, rank, world, _buffer_ptrs(rank_buffers, world),
+                                            max_count, _ptr(state), _stream()))
+    return out
+
+
+def allreduce_status(state, clear=False) -> None:
+    check(kernels().kuiper_allreduce_status(_ptr(state), int(clear)))
 
 
 def swiglu(gate_up, out=None, clear_input=False):

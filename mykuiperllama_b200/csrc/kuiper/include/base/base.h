@@ -51,6 +51,8 @@ enum class ModelBufferType {
     MatmulWorkspace = 36,
     MHAWorkspace = 37,
     GemmWorkspace = 38,  // fp16 copy of the activation rows for the tensor-core matmul
+    LogitsShard = 39,    // tensor parallelism: this rank's slice of the logits [rows, vocab / tp]
+    LogitsGather = 40,   // tensor parallelism: the slices of all ranks [tp, rows, vocab / tp]
 };
 }  // namespace model
 

@@ -86,6 +86,7 @@ private:
     std::unique_ptr<sampler::ArgmaxSampler> sampler_;
     std::vector<bool> layer_loaded_;
     bool globals_loaded_ = false;
+    int32_t vocab_local_ = 0;       // rows of the lm_head on this rank (the vocabulary is split under tensor parallelism)
     bool accumulate_ = false;       // every projection runs in accumulate mode (single GPU, see init)
     bool accumulate_cols_ = false;  // the column-split projections (QKV, gate|up) do; true under tensor parallelism too
 

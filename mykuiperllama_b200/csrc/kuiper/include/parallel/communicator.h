@@ -33,9 +33,20 @@ public:
     // its peers' buffers.  If any rank cannot, all ranks keep using NCCL (the outcome is agreed with an all-reduce).
     base::Status enable_one_shot(size_t max_count);
     bool one_shot_enabled() const { return one_shot_; }
-    // in-place sum over all ranks of `count` fp32 values, enqueued on `stream`; rows that fit the one-shot
-    // exchange go through it, everything else through ncclAllReduce
+    // in-place sum over all ranks of `count` fp32 values through ncclAllReduce, enqueued on `stream`
     base::Status all_reduce_sum(float* data, size_t count, cudaStream_t stream) const;
+    // does a row of `count` floats fit the low-latency exchange over peer memory?
+    bool fits_one_shot(size_t count) const { return one_shot_ && count <= one_shot_max_count_; }
+    // out = residual + sum over ranks of partial through the low-latency exchange (identical bits on every rank);
+    // `partial` is zeroed afterwards (ready for the next accumulating projection).  Needs fits_one_shot(count).
+    base::Status exchange_sum(float* partial, const float* residual, float* out, size_t count, cudaStream_t stream) const;
+    // greedy ids over a vocabulary split across the ranks: logits_local [rows, v_local]; the same ids on every rank.
+    // Through the low-latency exchange when it is enabled (rows <= 16), else an NCCL all-gather of the per-rank pairs
+    // is not available and the caller gathers the logits instead (returns function_not_implement).
+    base::Status exchange_argmax(const float* logits_local, int32_t* next, int32_t rows, int32_t v_local,
+                                 cudaStream_t stream) const;
+    // concatenation over ranks of `count` floats each: out [world][count]
+    base::Status all_gather(const float* in, float* out, size_t count, cudaStream_t stream) const;
     // synchronous health check of the one-shot path: error if a bounded wait on a peer ever ran out (the result of
     // that exchange, and of everything computed from it, is void); clear = true resets the error word once reported
     base::Status one_shot_status(bool clear = false) const;

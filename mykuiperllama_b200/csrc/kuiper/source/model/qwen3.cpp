@@ -113,7 +113,7 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     total += 4 * round256(size_t(R) * H * 4);                               // h, h_alt, two norm outputs
     total += round256(size_t(R) * QKV * 4) + 2 * round256(size_t(R) * Hq * D * 4);
     total += round256(size_t(R) * 2 * I * 4) + round256(size_t(R) * I * 4);
-    total += round256(size_t(R) * c.vocab_size * 4);
+    total += round256(size_t(R) * c.vocab_size * 4) * (c.tp_size > 1 ? 3 : 1);  // + logits shard and gather under tensor parallelism
     total += 2 * round256(size_t(c.max_seq_len) * (D / 2) * 4);
     total += round256(ws_mm) + round256(ws_mha) + round256(ws_gemm) + (1u << 20);
     total += size_t(c.layer_num) * 4 * 256;  // balance counters of the four projections of a layer
@@ -138,6 +138,13 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::W1Output, dev(DataType::DataTypeFp32, {R, 2 * I})));
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::W2Output, dev(DataType::DataTypeFp32, {R, I})));
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::ForwardOutput, dev(DataType::DataTypeFp32, {R, c.vocab_size})));
+    // tensor parallelism: the lm_head is split over the vocabulary (rank r holds rows [r V/tp, (r+1) V/tp)); the local
+    // logits and, for passes that want the whole row, the gathered slices of all ranks
+    vocab_local_ = (c.tp_size > 1 && c.vocab_size % c.tp_size == 0) ? c.vocab_size / c.tp_size : c.vocab_size;
+    if (vocab_local_ != c.vocab_size) {
+        RETURN_IF_ERROR(insert_buffer(ModelBufferType::LogitsShard, dev(DataType::DataTypeFp32, {R, vocab_local_})));
+        RETURN_IF_ERROR(insert_buffer(ModelBufferType::LogitsGather, dev(DataType::DataTypeFp32, {c.tp_size, R, vocab_local_})));
+    }
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::CosCache, dev(DataType::DataTypeFp32, {c.max_seq_len, D / 2})));
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::SinCache, dev(DataType::DataTypeFp32, {c.max_seq_len, D / 2})));
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::MatmulWorkspace, dev(DataType::DataTypeInt8, {int32_t(ws_mm)})));
@@ -145,6 +152,8 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     RETURN_IF_ERROR(insert_buffer(ModelBufferType::GemmWorkspace, dev(DataType::DataTypeInt8, {int32_t(ws_gemm)})));
     CUDA_OK(cudaMemset(get_buffer(ModelBufferType::MatmulWorkspace).ptr<void>(), 0, ws_mm));
     CUDA_OK(cudaMemset(get_buffer(ModelBufferType::MHAWorkspace).ptr<void>(), 0, ws_mha));
+    // the partial-row buffer of the row-split projections starts (and is always left) zeroed
+    CUDA_OK(cudaMemset(get_buffer(ModelBufferType::AttnOutput).ptr<void>(), 0, get_buffer(ModelBufferType::AttnOutput).byte_size()));
     // accumulating projections need their output buffers zero before the first pass
     CUDA_OK(cudaMemset(get_buffer(ModelBufferType::QKVOutput).ptr<void>(), 0, get_buffer(ModelBufferType::QKVOutput).byte_size()));
     CUDA_OK(cudaMemset(get_buffer(ModelBufferType::W1Output).ptr<void>(), 0, get_buffer(ModelBufferType::W1Output).byte_size()));
@@ -195,24 +204,21 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         STATUS_CHECK(l->set_weight(0, dev(DataType::DataTypeBf16, {dim})));
         return l;
     };
-    // with tensor parallelism only rank 0 folds the residual into its partial sum
-    const bool fold_residual = c.tp_size == 1 || c.tp_rank == 0;
-    // Single GPU, fp16-operand mode: every projection accumulates into its output (the residual stream for O
-    // and down; a buffer that its consumer left zeroed for QKV and gate|up), which needs no ordered combine.
-    // Under tensor parallelism the row-split projections (O, down) keep the ordered combine - their output is a
-    // partial sum that goes through the all-reduce - while QKV and gate|up, whose outputs stay on the rank, still
-    // accumulate with their pre-norms fused in.
+    // Every projection accumulates into its output (the residual stream for O and down; a buffer that its consumer
+    // left zeroed for QKV and gate|up), which needs no ordered combine.  Under tensor parallelism the row-split
+    // projections (O, down) accumulate into a zeroed partial-row buffer instead; the exchange that follows adds the
+    // residual stream and the partial rows of all ranks and leaves the buffer zeroed again.
     accumulate_cols_ = c.act_mode != 0 && QKV % 32 == 0 && H % 32 == 0 && (2 * I) % 32 == 0;
-    accumulate_ = accumulate_cols_ && c.tp_size == 1;
+    accumulate_ = accumulate_cols_;
     layers_.resize(size_t(c.layer_num));
     layer_loaded_.assign(size_t(c.layer_num), false);
     for (Qwen3Layer& L : layers_) {
         L.input_norm = make_norm(H);
         L.post_norm = make_norm(H);
         L.qkv = make_quant(sh_qkv, false);
-        L.o = make_quant(sh_o, fold_residual && !accumulate_);
+        L.o = make_quant(sh_o, c.tp_size == 1 && !accumulate_);
         L.gate_up = make_quant(sh_gu, false);
-        L.down = make_quant(sh_down, fold_residual && !accumulate_);
+        L.down = make_quant(sh_down, c.tp_size == 1 && !accumulate_);
         for (op::MatmulLayer* m : {L.qkv.get(), L.gate_up.get()}) m->set_accumulate(accumulate_cols_);
         for (op::MatmulLayer* m : {L.o.get(), L.down.get()}) m->set_accumulate(accumulate_);
         if (accumulate_cols_) {
@@ -253,9 +259,9 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
     embedding_->set_cuda_config(cuda_config_);
     STATUS_CHECK(embedding_->set_weight(0, dev(DataType::DataTypeBf16, {c.vocab_size, H})));
     final_norm_ = make_norm(H);
-    lm_head_ = std::make_unique<op::MatmulLayer>(device_type_, c.vocab_size, H, false);
+    lm_head_ = std::make_unique<op::MatmulLayer>(device_type_, vocab_local_, H, false);
     lm_head_->set_cuda_config(cuda_config_);
-    STATUS_CHECK(lm_head_->set_weight(0, dev(DataType::DataTypeBf16, {c.vocab_size, H})));
+    STATUS_CHECK(lm_head_->set_weight(0, dev(DataType::DataTypeBf16, {vocab_local_, H})));
     sampler_ = std::make_unique<sampler::ArgmaxSampler>(device_type_);
 
     CUDA_OK(cudaMallocHost(reinterpret_cast<void**>(&host_stage_), size_t(R) * 4 * sizeof(int32_t)));
@@ -333,7 +339,10 @@ base::Status Qwen3Model::load_globals(const void* embed, const void* final_norm,
     const size_t table = size_t(config_.vocab_size) * config_.dim * 2;
     CUDA_OK(cudaMemcpy(embedding_->get_weight(0).ptr<void>(), embed, table, kind));
     CUDA_OK(cudaMemcpy(final_norm_->get_weight(0).ptr<void>(), final_norm, size_t(config_.dim) * 2, kind));
-    CUDA_OK(cudaMemcpy(lm_head_->get_weight(0).ptr<void>(), lm_head, table, kind));
+    // this rank's slice of the vocabulary (all of it on one GPU)
+    const size_t shard = size_t(vocab_local_) * config_.dim * 2;
+    const size_t shard_off = vocab_local_ != config_.vocab_size ? size_t(config_.tp_rank) * shard : 0;
+    CUDA_OK(cudaMemcpy(lm_head_->get_weight(0).ptr<void>(), static_cast<const char*>(lm_head) + shard_off, shard, kind));
     if (on_device) CUDA_OK(cudaDeviceSynchronize());
     globals_loaded_ = true;
     return base::error::success();
@@ -421,14 +430,20 @@ base::Status Qwen3Model::run_pass(int32_t M, bool inputs_settled) {
     const Tensor& cos_t = get_buffer(ModelBufferType::CosCache);
     const Tensor& sin_t = get_buffer(ModelBufferType::SinCache);
     const bool tp = c.tp_size > 1;
-    const bool fold_residual = !tp || c.tp_rank == 0;
 
-    // row-split projection: out = h + x.W summed over ranks
+    // row-split projection: h += x.W summed over ranks
     auto project_and_reduce = [&](op::MatmulLayer& layer, const Tensor& x) -> base::Status {
         if (!tp) return accumulate_ ? layer.forward(x, h) : layer.forward(x, h, h);
-        RETURN_IF_ERROR(fold_residual ? layer.forward(x, h, h_alt) : layer.forward(x, h_alt));
-        RETURN_IF_ERROR(communicator_->all_reduce_sum(const_cast<float*>(h_alt.ptr<float>()), size_t(M) * H, stream()));
-        std::swap(h, h_alt);
+        // this rank's partial row goes into the zeroed buffer (accumulated, or written by the ordered kernel)
+        RETURN_IF_ERROR(layer.forward(x, h_alt));
+        float* partial = const_cast<float*>(h_alt.ptr<float>());
+        float* hp = const_cast<float*>(h.ptr<float>());
+        const size_t count = size_t(M) * H;
+        if (communicator_->fits_one_shot(count))
+            return communicator_->exchange_sum(partial, hp, hp, count, stream());  // h = h + sum_r partial_r; clears partial
+        RETURN_IF_ERROR(communicator_->all_reduce_sum(partial, count, stream()));
+        kernel::get_add_kernel(device_type_)(h, h_alt, h, stream());
+        CUDA_OK(cudaMemsetAsync(partial, 0, count * sizeof(float), stream()));
         return base::error::success();
     };
 
@@ -480,8 +495,31 @@ base::Status Qwen3Model::run_pass(int32_t M, bool inputs_settled) {
         const Tensor lg_tail = view(logits, F, {logit_rows_, c.vocab_size}, size_t(r0) * c.vocab_size);
         const Tensor nx_tail = view(next, I32, {logit_rows_}, size_t(r0));
         RETURN_IF_ERROR(final_norm_->forward(h_tail, xn_tail));
-        RETURN_IF_ERROR(lm_head_->forward(xn_tail, lg_tail));
-        sampler_->sample(lg_tail, nx_tail, stream());
+        if (vocab_local_ == c.vocab_size) {
+            RETURN_IF_ERROR(lm_head_->forward(xn_tail, lg_tail));
+            sampler_->sample(lg_tail, nx_tail, stream());
+        } else {
+            // vocabulary-split lm_head: every rank scores its slice
+            const Tensor shard = view(get_buffer(ModelBufferType::LogitsShard), F, {logit_rows_, vocab_local_});
+            RETURN_IF_ERROR(lm_head_->forward(xn_tail, shard));
+            base::Status ex = base::error::function_not_implement("");
+            if (inputs_settled)  // decode graph: only the per-rank (maximum, index) pairs travel
+                ex = communicator_->exchange_argmax(shard.ptr<float>(), const_cast<int32_t*>(nx_tail.ptr<int32_t>()), logit_rows_,
+                                                    vocab_local_, stream());
+            if (!ex) {
+                if (ex.get_err_code() != base::StatusCode::FunctionUnImplement) return ex;
+                // eager passes (and ranks without the peer-memory path): gather the slices into whole rows, so that
+                // read_logits() sees them, and pick on the whole row
+                float* gathered = const_cast<float*>(get_buffer(ModelBufferType::LogitsGather).ptr<float>());
+                const size_t slice = size_t(logit_rows_) * vocab_local_;
+                RETURN_IF_ERROR(communicator_->all_gather(shard.ptr<float>(), gathered, slice, stream()));
+                for (int32_t r = 0; r < c.tp_size; r++)
+                    CUDA_OK(cudaMemcpy2DAsync(const_cast<float*>(lg_tail.ptr<float>()) + size_t(r) * vocab_local_,
+                                              size_t(c.vocab_size) * 4, gathered + size_t(r) * slice, size_t(vocab_local_) * 4,
+                                              size_t(vocab_local_) * 4, size_t(logit_rows_), cudaMemcpyDeviceToDevice, stream()));
+                sampler_->sample(lg_tail, nx_tail, stream());
+            }
+        }
     }
     return base::error::success();
 }

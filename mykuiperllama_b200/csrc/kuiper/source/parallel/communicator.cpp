@@ -93,6 +93,7 @@ base::Status Communicator::enable_one_shot(size_t max_count) {
     if (one_shot_) return base::error::success();
     if (world_size_ > 8 || !api().AllGather) return base::error::success();  // stays on NCCL
     max_count = (max_count + 31) / 32 * 32;
+    if (max_count > 65536) return base::error::success();  // rows this long stay on NCCL
     const size_t bytes = kuiper_allreduce_buffer_bytes(world_size_, int64_t(max_count));
     // every step below is attempted on every rank; `good` is agreed at the end so that all ranks take the same path
     float good = 1.f;
@@ -100,8 +101,8 @@ base::Status Communicator::enable_one_shot(size_t max_count) {
     std::memset(&mine, 0, sizeof(mine));
     char* d_handles = nullptr;
     if (bytes == 0 || cudaMalloc(&exchange_, bytes) != cudaSuccess || cudaMemset(exchange_, 0, bytes) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void**>(&state_), 2 * sizeof(uint32_t)) != cudaSuccess ||
-        cudaMemset(state_, 0, 2 * sizeof(uint32_t)) != cudaSuccess || cudaIpcGetMemHandle(&mine, exchange_) != cudaSuccess)
+        cudaMalloc(reinterpret_cast<void**>(&state_), kuiper_allreduce_state_bytes()) != cudaSuccess ||
+        cudaMemset(state_, 0, kuiper_allreduce_state_bytes()) != cudaSuccess || cudaIpcGetMemHandle(&mine, exchange_) != cudaSuccess)
         good = 0.f;
     const size_t hb = sizeof(cudaIpcMemHandle_t);
     std::vector<cudaIpcMemHandle_t> all(static_cast<size_t>(world_size_));
@@ -143,24 +144,37 @@ base::Status Communicator::enable_one_shot(size_t max_count) {
 
 base::Status Communicator::one_shot_status(bool clear) const {
     if (!one_shot_) return base::error::success();
-    if (kuiper_allreduce_status(state_) != 0) {
-        const std::string msg = kuiper_last_error();
-        // the error word is sticky on the device; once reported it is cleared so that the next call starts clean
-        if (clear) cudaMemset(reinterpret_cast<char*>(state_) + sizeof(uint32_t), 0, sizeof(uint32_t));
-        return base::error::internal_error(msg);
-    }
+    // the error word is sticky on the device; once reported it is cleared so that the next call starts clean
+    if (kuiper_allreduce_status(state_, clear ? 1 : 0) != 0) return base::error::internal_error(kuiper_last_error());
     return base::error::success();
 }
 
 base::Status Communicator::all_reduce_sum(float* data, size_t count, cudaStream_t stream) const {
     if (!comm_) return base::error::internal_error("communicator is not initialised");
-    if (one_shot_ && count <= one_shot_max_count_ && count % 4 == 0) {
-        if (kuiper_allreduce_oneshot_f32(data, int64_t(count), rank_, world_size_, rank_buffers_, int64_t(one_shot_max_count_),
-                                         state_, reinterpret_cast<kuiper_stream_t>(stream)) != 0)
-            return base::error::internal_error(kuiper_last_error());
-        return base::error::success();
-    }
     return nccl_status(api().AllReduce(data, data, count, kNcclFloat32, kNcclSum, comm_, stream), "ncclAllReduce");
+}
+
+base::Status Communicator::exchange_sum(float* partial, const float* residual, float* out, size_t count,
+                                        cudaStream_t stream) const {
+    if (!fits_one_shot(count)) return base::error::invalid_argument("row does not fit the low-latency exchange");
+    if (kuiper_allreduce_sum_f32(partial, residual, out, 1, int64_t(count), rank_, world_size_, rank_buffers_,
+                                 int64_t(one_shot_max_count_), state_, reinterpret_cast<kuiper_stream_t>(stream)) != 0)
+        return base::error::internal_error(kuiper_last_error());
+    return base::error::success();
+}
+
+base::Status Communicator::exchange_argmax(const float* logits_local, int32_t* next, int32_t rows, int32_t v_local,
+                                           cudaStream_t stream) const {
+    if (!one_shot_ || rows > 16) return base::error::function_not_implement("argmax exchange needs the peer-memory path and <= 16 rows");
+    if (kuiper_argmax_allgather(logits_local, next, rows, v_local, rank_, world_size_, rank_buffers_,
+                                int64_t(one_shot_max_count_), state_, reinterpret_cast<kuiper_stream_t>(stream)) != 0)
+        return base::error::internal_error(kuiper_last_error());
+    return base::error::success();
+}
+
+base::Status Communicator::all_gather(const float* in, float* out, size_t count, cudaStream_t stream) const {
+    if (!comm_ || !api().AllGather) return base::error::internal_error("communicator is not initialised");
+    return nccl_status(api().AllGather(in, out, count, kNcclFloat32, comm_, stream), "ncclAllGather");
 }
 
 }  // namespace parallel

@@ -408,49 +408,89 @@ def test_awq_gemm_rejects_bad_arguments(cuda):
     assert e.value.code == 7
 
 
-# ----------------------------------------------------------------------------- one-shot all-reduce (single-GPU checks)
-def test_allreduce_oneshot_two_ranks_emulated_on_one_gpu(cuda, oracle):
-    # Both "ranks" live on this GPU and their kernels are issued one after the other on one stream, so the first one
-    # cannot see the second one's flag: pre-load rank 1's slot and flag by hand instead, then run rank 0 only.
+# ----------------------------------------------------------------------------- tensor-parallel exchanges (single-GPU checks)
+def _words(values, seq):
+    """8-byte exchange words {value bits, sequence number} as an int32 tensor [n, 2]."""
+    v = np.ascontiguousarray(values)
+    w = np.empty((v.size, 2), np.uint32)
+    w[:, 0] = v.view(np.uint32).ravel()
+    w[:, 1] = seq
+    return torch.from_numpy(w.view(np.int32)).cuda()
+
+
+def test_allreduce_sum_two_ranks_emulated_on_one_gpu(cuda, oracle):
+    # Both "ranks" live on this GPU and their kernels would run one after the other on one stream, so rank 0 could never
+    # see rank 1's words: rank 1's slot in rank 0's buffer is filled by hand instead, then rank 0 runs alone.
     rng = np.random.default_rng(41)
     world, count, max_count = 2, 4096, 8192
     bufs = [cuda.allreduce_buffer(world, max_count) for _ in range(world)]
-    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    state = cuda.allreduce_state()
     a = rng.standard_normal(count).astype(np.float32)
     b = rng.standard_normal(count).astype(np.float32)
-    # sequence number 1 -> parity 1; slot (parity 1, src 1) of rank 0's buffer, flag (parity 1, src 1)
+    h = rng.standard_normal(count).astype(np.float32)
+    # sequence number 1 -> parity 1; sum slot (parity 1, src 1) of rank 0's buffer
+    words = bufs[0].view(torch.int32).view(-1, 2)
     slot = (1 * world + 1) * max_count
-    bufs[0].view(torch.float32)[slot:slot + count] = dev(b)
-    flags = bufs[0][2 * world * max_count * 4:].view(torch.int32)
-    flags[(1 * world + 1) * 32] = 1
-    data = dev(a)
-    cuda.allreduce_oneshot(data, 0, world, bufs, max_count, state)
+    words[slot:slot + count] = _words(b, 1)
+    partial, resid = dev(a), dev(h)
+    out = cuda.allreduce_sum(partial, 0, world, bufs, max_count, state, residual=resid, clear_partial=True)
     torch.cuda.synchronize()
-    assert np.array_equal(data.cpu().numpy(), a + b)  # rank order: a first, then b
-    assert state.cpu().tolist() == [1, 0]
-    # rank 0 also delivered its row and flag to "rank 1"
-    assert np.array_equal(bufs[1].view(torch.float32)[(1 * world + 0) * max_count:(1 * world + 0) * max_count + count].cpu().numpy(), a)
+    assert np.array_equal(out.cpu().numpy(), (h + a) + b)  # residual first, then the ranks in order
+    assert float(partial.abs().max()) == 0.0               # cleared for the next accumulating projection
+    st = state.cpu().numpy()
+    assert list(st[:4]) == [1, 1, 1, 1] and st[64 + 1] == 0  # four CTAs advanced their sequence numbers, no error
+    # rank 0 also delivered its words to "rank 1": slot (parity 1, src 0) of rank 1's buffer
+    got = bufs[1].view(torch.int32).view(-1, 2)[(1 * world + 0) * max_count:(1 * world + 0) * max_count + count].cpu().numpy()
+    assert np.array_equal(got[:, 0].view(np.float32), a) and (got[:, 1] == 1).all()
     cuda.allreduce_status(state)
 
 
-def test_allreduce_oneshot_wait_is_bounded(cuda):
-    # a peer that never raises its flag: the kernel gives up after the time limit, reports which rank, and the
-    # context stays usable
+def test_argmax_allgather_two_ranks_emulated_on_one_gpu(cuda, oracle):
+    rng = np.random.default_rng(43)
+    world, M, V_local, max_count = 2, 3, 18992, 8192
+    bufs = [cuda.allreduce_buffer(world, max_count) for _ in range(world)]
+    state = cuda.allreduce_state()
+    full = rng.standard_normal((M, world * V_local)).astype(np.float32)
+    full[1, 77] = full[1, V_local + 5] = 9.0   # tie across the two slices: the lower global index wins
+    full[2, V_local + 18991] = 50.0            # last element of the upper slice
+    want = oracle.argmax(full)
+    # rank 1's (maximum, index) words, by hand, into rank 0's buffer: argmax slot (parity 1, src 1)
+    hi = full[:, V_local:]
+    idx1 = hi.argmax(1)
+    base = 2 * world * max_count * 8 + (1 * world + 1) * 16 * 16
+    area = bufs[0][base:base + M * 16].view(torch.int32).view(M, 2, 2)
+    area[:, 0] = _words(hi[np.arange(M), idx1], 1)
+    area[:, 1] = _words((idx1 + V_local).astype(np.uint32).view(np.float32), 1)
+    got = cuda.argmax_allgather(dev(np.ascontiguousarray(full[:, :V_local])), 0, world, bufs, max_count, state)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), want)
+    assert got.cpu().tolist()[1] == 77
+    cuda.allreduce_status(state)
+
+
+def test_exchange_waits_are_bounded(cuda):
+    # a peer whose words never arrive: the kernels give up after the time limit, report which rank, and the context
+    # stays usable; the error word can be cleared
     from mykuiperllama_b200._lib import KuiperError
     world, count, max_count = 2, 1024, 1024
     bufs = [cuda.allreduce_buffer(world, max_count) for _ in range(world)]
-    state = torch.zeros(2, dtype=torch.int32, device="cuda")
-    data = torch.ones(count, device="cuda")
+    state = cuda.allreduce_state()
     cuda.set_tuning("allreduce_timeout_ms", 50)
     try:
-        cuda.allreduce_oneshot(data, 0, world, bufs, max_count, state)
+        cuda.allreduce_sum(torch.ones(count, device="cuda"), 0, world, bufs, max_count, state)
         torch.cuda.synchronize()
+        with pytest.raises(KuiperError) as e:
+            cuda.allreduce_status(state, clear=True)
+        assert e.value.code == 5 and "rank 1" in str(e.value)
+        cuda.allreduce_status(state)  # cleared
+        assert state.cpu().tolist()[0] == 1  # the sequence number still advanced
+        cuda.argmax_allgather(torch.zeros((2, 64), device="cuda"), 0, world, bufs, max_count, state)
+        torch.cuda.synchronize()
+        with pytest.raises(KuiperError) as e:
+            cuda.allreduce_status(state)
+        assert e.value.code == 5
     finally:
         cuda.set_tuning("allreduce_timeout_ms", 5000)
-    with pytest.raises(KuiperError) as e:
-        cuda.allreduce_status(state)
-    assert e.value.code == 5 and "rank 1" in str(e.value)
-    assert state.cpu().tolist()[0] == 1  # the sequence number still advanced
     assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
 
 
