@@ -50,6 +50,15 @@ KUIPER_LLAMA_API int kuiper_model_load_layer(kuiper_model* model, int layer, con
 KUIPER_LLAMA_API int kuiper_model_load_globals(kuiper_model* model, const void* embed, const void* final_norm,
                                                const void* lm_head, int on_device);
 
+/* Every weight from an AWQ checkpoint in the safetensors container, Hugging Face tensor names of a quantised Qwen3 model
+ * (model.layers.<i>.self_attn.{q,k,v,o}_proj.{qweight,qzeros,scales}, mlp.{gate,up,down}_proj..., the norms,
+ * model.embed_tokens.weight, model.norm.weight, lm_head.weight or tied).  This is the loader behind the hook the
+ * reference leaves empty for quantised layers (LayerParam::set_weight, kuiper/source/op/layer.cpp:256-276). */
+KUIPER_LLAMA_API int kuiper_model_load_checkpoint(kuiper_model* model, const char* path);
+/* Parses a safetensors file's header (no GPU needed) and writes one line per tensor, "name dtype [shape] bytes", and one
+ * per metadata entry into `report`; 0 if the file is well formed. */
+KUIPER_LLAMA_API int kuiper_checkpoint_inspect(const char* path, char* report, size_t report_bytes);
+
 /* tensor parallelism: rank 0 makes a 128-byte id, every rank passes it to init_tp */
 KUIPER_LLAMA_API int kuiper_tp_unique_id(void* out128);
 KUIPER_LLAMA_API int kuiper_model_init_tp(kuiper_model* model, const void* unique_id128);

@@ -121,6 +121,8 @@ HOST_API = {
     "kuiper_model_destroy": (None, [_vp]),
     "kuiper_model_load_layer": (_i32, [_vp, _i32, C.POINTER(LayerWeightsC), _i32]),
     "kuiper_model_load_globals": (_i32, [_vp, _vp, _vp, _vp, _i32]),
+    "kuiper_model_load_checkpoint": (_i32, [_vp, C.c_char_p]),
+    "kuiper_checkpoint_inspect": (_i32, [C.c_char_p, C.c_char_p, _sz]),
     "kuiper_tp_unique_id": (_i32, [_vp]),
     "kuiper_model_init_tp": (_i32, [_vp, _vp]),
     "kuiper_model_tp_one_shot": (_i32, [_vp]),

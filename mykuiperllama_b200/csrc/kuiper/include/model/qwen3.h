@@ -48,6 +48,12 @@ public:
     base::Status load_layer(int32_t layer, const RawLayerWeights& w, bool on_device);
     base::Status load_globals(const void* embed, const void* final_norm, const void* lm_head, bool on_device);
 
+    // Every weight from an AWQ checkpoint in the safetensors container (Hugging Face tensor names of a quantised Qwen3
+    // model: separate q / k / v and gate / up projections, which are fused here); the file's tensors enter through
+    // LayerParam::set_weight(idx, dims, ptr, DeviceCPU) as borrowed pointers into the mapping and are then copied, and
+    // under tensor parallelism sharded, into the model's own device memory.
+    base::Status load_checkpoint(const std::string& path);
+
     // whole prompt of one sequence, in chunks of max_rows; `next` = greedy id after the last token
     base::Status prefill(const int32_t* tokens, int32_t n, int32_t slot, int32_t* next);
 

@@ -4,6 +4,7 @@
 #include <cstring>
 #include <string>
 
+#include "model/checkpoint.h"
 #include "model/qwen3.h"
 
 namespace {
@@ -72,6 +73,31 @@ int kuiper_model_load_globals(kuiper_model* model, const void* embed, const void
                               int on_device) {
     if (!model) return fail(base::error::invalid_argument("null model"));
     return done(as_model(model)->load_globals(embed, final_norm, lm_head, on_device != 0));
+}
+
+int kuiper_model_load_checkpoint(kuiper_model* model, const char* path) {
+    if (!model || !path) return fail(base::error::invalid_argument("null pointer"));
+    return done(as_model(model)->load_checkpoint(path));
+}
+
+int kuiper_checkpoint_inspect(const char* path, char* report, size_t report_bytes) {
+    if (!path) return fail(base::error::invalid_argument("null path"));
+    std::unique_ptr<model::SafetensorsFile> f;
+    base::Status st = model::SafetensorsFile::open(path, &f);
+    if (!st) return fail(st);
+    std::string text;
+    for (const auto& kv : f->tensors()) {
+        text += kv.first + " " + kv.second.dtype + " [";
+        for (size_t i = 0; i < kv.second.shape.size(); i++) text += (i ? "," : "") + std::to_string(kv.second.shape[i]);
+        text += "] " + std::to_string(kv.second.bytes) + "\n";
+    }
+    for (const auto& kv : f->metadata()) text += "__metadata__ " + kv.first + "=" + kv.second + "\n";
+    if (report && report_bytes > 0) {
+        const size_t n = text.size() < report_bytes - 1 ? text.size() : report_bytes - 1;
+        std::memcpy(report, text.data(), n);
+        report[n] = 0;
+    }
+    return int(f->tensors().size()) > 0 ? 0 : fail(base::error::model_parse_error("the file holds no tensors"));
 }
 
 int kuiper_tp_unique_id(void* out128) {

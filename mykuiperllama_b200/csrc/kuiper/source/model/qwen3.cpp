@@ -8,6 +8,7 @@
 #include <cstring>
 
 #include "kuiper_b200.h"
+#include "model/checkpoint.h"
 #include "op/kernel/kernel_interface.h"
 
 namespace model {
@@ -346,6 +347,164 @@ base::Status Qwen3Model::load_globals(const void* embed, const void* final_norm,
     if (on_device) CUDA_OK(cudaDeviceSynchronize());
     globals_loaded_ = true;
     return base::error::success();
+}
+
+// ------------------------------------------------------------------ checkpoint file
+namespace {
+
+// bf16 bits of a checkpoint tensor stored as BF16, F16 or F32 (round to nearest even)
+base::Status to_bf16(const CheckpointTensor& t, int64_t expect, const std::string& name, std::vector<uint16_t>* out) {
+    if (t.element_count() != expect)
+        return base::error::model_parse_error(name + " has " + std::to_string(t.element_count()) + " elements, expected " + std::to_string(expect));
+    out->resize(size_t(expect));
+    auto f32_to_bf16 = [](float f) {
+        uint32_t u;
+        std::memcpy(&u, &f, 4);
+        if ((u & 0x7fffffffu) > 0x7f800000u) return uint16_t((u >> 16) | 0x40);
+        u += 0x7fffu + ((u >> 16) & 1u);
+        return uint16_t(u >> 16);
+    };
+    if (t.dtype == "BF16") {
+        std::memcpy(out->data(), t.data, size_t(expect) * 2);
+    } else if (t.dtype == "F32") {
+        const float* p = reinterpret_cast<const float*>(t.data);
+        for (int64_t i = 0; i < expect; i++) (*out)[size_t(i)] = f32_to_bf16(p[i]);
+    } else if (t.dtype == "F16") {
+        const uint16_t* p = reinterpret_cast<const uint16_t*>(t.data);
+        for (int64_t i = 0; i < expect; i++) {
+            const uint32_t h = p[i], sign = (h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+            uint32_t u;
+            if (exp == 0) {
+                if (man == 0) {
+                    u = sign;
+                } else {  // subnormal half: normalise
+                    int e = -1;
+                    uint32_t m = man;
+                    do { e++; m <<= 1; } while ((m & 0x400u) == 0);
+                    u = sign | uint32_t(127 - 15 - e) << 23 | (m & 0x3ffu) << 13;
+                }
+            } else if (exp == 31) {
+                u = sign | 0x7f800000u | man << 13;
+            } else {
+                u = sign | (exp + 127 - 15) << 23 | man << 13;
+            }
+            float f;
+            std::memcpy(&f, &u, 4);
+            (*out)[size_t(i)] = f32_to_bf16(f);
+        }
+    } else {
+        return base::error::model_parse_error(name + " has dtype " + t.dtype + " (BF16, F16 or F32 expected)");
+    }
+    return base::error::success();
+}
+
+// one INT4-AWQ projection of the file, entered through the layer hook the reference reserves for it:
+// LayerParam::set_weight(idx, dims, ptr, device) with borrowed host pointers (quantised branch), set_scales()
+struct StagedProjection {
+    std::unique_ptr<op::MatmulLayer> layer;  // host-side layer object that only holds the borrowed tensors
+    int32_t K = 0, N = 0;
+};
+
+base::Status stage_projection(const SafetensorsFile& f, const std::string& prefix, int32_t K, int32_t N, int32_t g,
+                              StagedProjection* out) {
+    const CheckpointTensor* qw = f.find(prefix + ".qweight");
+    const CheckpointTensor* qz = f.find(prefix + ".qzeros");
+    const CheckpointTensor* sc = f.find(prefix + ".scales");
+    if (!qw || !qz || !sc) return base::error::model_parse_error(prefix + ": qweight / qzeros / scales missing");
+    auto shape_is = [](const CheckpointTensor& t, int64_t a, int64_t b) { return t.shape.size() == 2 && t.shape[0] == a && t.shape[1] == b; };
+    if (qw->dtype != "I32" || !shape_is(*qw, K, N / 8)) return base::error::model_parse_error(prefix + ".qweight is not I32 [" + std::to_string(K) + ", " + std::to_string(N / 8) + "]");
+    if (qz->dtype != "I32" || !shape_is(*qz, K / g, N / 8)) return base::error::model_parse_error(prefix + ".qzeros is not I32 [in/group, out/8]");
+    if (sc->dtype != "F16" || !shape_is(*sc, K / g, N)) return base::error::model_parse_error(prefix + ".scales is not F16 [in/group, out]");
+    out->layer = std::make_unique<op::MatmulLayer>(base::DeviceType::DeviceCPU, N, K, true);
+    out->layer->set_group_size(g);
+    RETURN_IF_ERROR(out->layer->set_weight(0, {K, N / 8}, qw->data, base::DeviceType::DeviceCPU));
+    RETURN_IF_ERROR(out->layer->set_weight(1, {K / g, N / 8}, qz->data, base::DeviceType::DeviceCPU));
+    tensor::Tensor scales(DataType::DataTypeFp16, std::vector<int32_t>{K / g, N}, false, nullptr, const_cast<unsigned char*>(sc->data));
+    scales.set_device_type(base::DeviceType::DeviceCPU);
+    out->layer->set_scales(scales);
+    out->K = K;
+    out->N = N;
+    return base::error::success();
+}
+
+// N-concatenation of staged projections that share K: packed words and zeros by word columns, scales by columns
+void fuse_columns(const std::vector<const StagedProjection*>& parts, int32_t g, std::vector<int32_t>* qw, std::vector<int32_t>* qz,
+                  std::vector<uint16_t>* sc) {
+    const int32_t K = parts[0]->K;
+    int32_t N = 0;
+    for (const StagedProjection* p : parts) N += p->N;
+    qw->resize(size_t(K) * (N / 8));
+    qz->resize(size_t(K / g) * (N / 8));
+    sc->resize(size_t(K / g) * N);
+    int32_t col = 0;
+    for (const StagedProjection* p : parts) {
+        const int32_t* w = p->layer->get_weight(0).ptr<int32_t>();
+        const int32_t* z = p->layer->get_weight(1).ptr<int32_t>();
+        const uint16_t* s = p->layer->scales().ptr<uint16_t>();
+        for (int32_t k = 0; k < K; k++)
+            std::memcpy(qw->data() + size_t(k) * (N / 8) + col / 8, w + size_t(k) * (p->N / 8), size_t(p->N / 8) * 4);
+        for (int32_t r = 0; r < K / g; r++) {
+            std::memcpy(qz->data() + size_t(r) * (N / 8) + col / 8, z + size_t(r) * (p->N / 8), size_t(p->N / 8) * 4);
+            std::memcpy(sc->data() + size_t(r) * N + col, s + size_t(r) * p->N, size_t(p->N) * 2);
+        }
+        col += p->N;
+    }
+}
+
+}  // namespace
+
+base::Status Qwen3Model::load_checkpoint(const std::string& path) {
+    if (layers_.empty()) return base::error::internal_error("init() must run before load_checkpoint()");
+    std::unique_ptr<SafetensorsFile> file;
+    RETURN_IF_ERROR(SafetensorsFile::open(path, &file));
+    const ModelConfig& c = config_;
+    const int32_t D = c.head_size, H = c.dim, g = c.group_size, I = c.hidden_dim;
+    auto named = [&](const std::string& name, const CheckpointTensor** t) -> base::Status {
+        *t = file->find(name);
+        if (!*t) return base::error::model_parse_error("tensor " + name + " is missing from " + path);
+        return base::error::success();
+    };
+    std::vector<uint16_t> in_norm, post_norm, q_norm, k_norm, sc_qkv, sc_gu;
+    std::vector<int32_t> qw_qkv, qz_qkv, qw_gu, qz_gu;
+    for (int32_t l = 0; l < c.layer_num; l++) {
+        const std::string base_name = "model.layers." + std::to_string(l);
+        const CheckpointTensor* t = nullptr;
+        RETURN_IF_ERROR(named(base_name + ".input_layernorm.weight", &t));
+        RETURN_IF_ERROR(to_bf16(*t, H, base_name + ".input_layernorm.weight", &in_norm));
+        RETURN_IF_ERROR(named(base_name + ".post_attention_layernorm.weight", &t));
+        RETURN_IF_ERROR(to_bf16(*t, H, base_name + ".post_attention_layernorm.weight", &post_norm));
+        RETURN_IF_ERROR(named(base_name + ".self_attn.q_norm.weight", &t));
+        RETURN_IF_ERROR(to_bf16(*t, D, base_name + ".self_attn.q_norm.weight", &q_norm));
+        RETURN_IF_ERROR(named(base_name + ".self_attn.k_norm.weight", &t));
+        RETURN_IF_ERROR(to_bf16(*t, D, base_name + ".self_attn.k_norm.weight", &k_norm));
+        StagedProjection q, k, v, o, gate, up, down;
+        RETURN_IF_ERROR(stage_projection(*file, base_name + ".self_attn.q_proj", H, c.head_num * D, g, &q));
+        RETURN_IF_ERROR(stage_projection(*file, base_name + ".self_attn.k_proj", H, c.kv_head_num * D, g, &k));
+        RETURN_IF_ERROR(stage_projection(*file, base_name + ".self_attn.v_proj", H, c.kv_head_num * D, g, &v));
+        RETURN_IF_ERROR(stage_projection(*file, base_name + ".self_attn.o_proj", c.head_num * D, H, g, &o));
+        RETURN_IF_ERROR(stage_projection(*file, base_name + ".mlp.gate_proj", H, I, g, &gate));
+        RETURN_IF_ERROR(stage_projection(*file, base_name + ".mlp.up_proj", H, I, g, &up));
+        RETURN_IF_ERROR(stage_projection(*file, base_name + ".mlp.down_proj", I, H, g, &down));
+        fuse_columns({&q, &k, &v}, g, &qw_qkv, &qz_qkv, &sc_qkv);   // q heads | k heads | v heads
+        fuse_columns({&gate, &up}, g, &qw_gu, &qz_gu, &sc_gu);        // gate | up
+        RawLayerWeights w;
+        w.input_norm = in_norm.data(); w.post_norm = post_norm.data(); w.q_norm = q_norm.data(); w.k_norm = k_norm.data();
+        w.qkv_qw = qw_qkv.data(); w.qkv_qz = qz_qkv.data(); w.qkv_s = sc_qkv.data();
+        w.o_qw = o.layer->get_weight(0).ptr<void>(); w.o_qz = o.layer->get_weight(1).ptr<void>(); w.o_s = o.layer->scales().ptr<void>();
+        w.gu_qw = qw_gu.data(); w.gu_qz = qz_gu.data(); w.gu_s = sc_gu.data();
+        w.down_qw = down.layer->get_weight(0).ptr<void>(); w.down_qz = down.layer->get_weight(1).ptr<void>();
+        w.down_s = down.layer->scales().ptr<void>();
+        RETURN_IF_ERROR(load_layer(l, w, false));
+    }
+    const CheckpointTensor *embed = nullptr, *norm = nullptr;
+    RETURN_IF_ERROR(named("model.embed_tokens.weight", &embed));
+    RETURN_IF_ERROR(named("model.norm.weight", &norm));
+    const CheckpointTensor* head = file->find("lm_head.weight");  // absent: tied to the embedding
+    std::vector<uint16_t> embed_b, norm_b, head_b;
+    RETURN_IF_ERROR(to_bf16(*embed, int64_t(c.vocab_size) * H, "model.embed_tokens.weight", &embed_b));
+    RETURN_IF_ERROR(to_bf16(*norm, H, "model.norm.weight", &norm_b));
+    if (head) RETURN_IF_ERROR(to_bf16(*head, int64_t(c.vocab_size) * H, "lm_head.weight", &head_b));
+    return load_globals(embed_b.data(), norm_b.data(), head ? head_b.data() : embed_b.data(), false);
 }
 
 base::Status Qwen3Model::check_loaded() const {

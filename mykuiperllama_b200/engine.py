@@ -78,6 +78,10 @@ class Qwen3Engine:
         for i, lw in enumerate(weights["layers"]):
             self.load_layer(i, lw)
 
+    def load_checkpoint(self, path: str) -> None:
+        """Loads every weight from an AWQ checkpoint in the safetensors container (Hugging Face Qwen3 tensor names)."""
+        check_host(host().kuiper_model_load_checkpoint(self._h, str(path).encode()))
+
     # ---- tensor parallel
     @staticmethod
     def tp_unique_id() -> bytes:

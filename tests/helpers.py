@@ -94,3 +94,54 @@ def make_model_weights_fast(oracle, cfg, seed=0, norm_jitter=0.02):
         weights["layers"].append(lw)
     torch.cuda.empty_cache()
     return weights
+
+
+def write_safetensors(path, tensors, metadata=None):
+    """Minimal writer of the safetensors container: tensors = {name: (dtype string, numpy array)}; the array's bytes are
+    written as they are (BF16 / F16 travel as uint16 bit patterns)."""
+    import json
+    import struct
+    header, blobs, off = {}, [], 0
+    if metadata:
+        header["__metadata__"] = metadata
+    for name, (dtype, arr) in tensors.items():
+        raw = np.ascontiguousarray(arr).tobytes()
+        header[name] = {"dtype": dtype, "shape": list(arr.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    text = json.dumps(header, separators=(",", ":")).encode()
+    text += b" " * (-len(text) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(text)))
+        f.write(text)
+        for raw in blobs:
+            f.write(raw)
+
+
+def checkpoint_tensors(cfg, weights):
+    """The synthetic model under the tensor names of a Hugging Face AWQ Qwen3 checkpoint: the fused q|k|v and gate|up
+    projections are cut back into their separate tensors (packed words hold 8 columns, so cuts fall on word boundaries)."""
+    D = cfg.head_dim
+    nq, nkv, I = cfg.n_q_heads * D, cfg.n_kv_heads * D, cfg.inter
+    out = {"model.embed_tokens.weight": ("BF16", weights["embed"]), "model.norm.weight": ("BF16", weights["final_norm"]),
+           "lm_head.weight": ("BF16", weights["lm_head"])}
+
+    def cut(prefix, qw, qz, s, c0, c1):
+        out[prefix + ".qweight"] = ("I32", qw[:, c0 // 8:c1 // 8])
+        out[prefix + ".qzeros"] = ("I32", qz[:, c0 // 8:c1 // 8])
+        out[prefix + ".scales"] = ("F16", s[:, c0:c1])
+
+    for i, lw in enumerate(weights["layers"]):
+        p = f"model.layers.{i}"
+        out[p + ".input_layernorm.weight"] = ("BF16", lw["input_norm"])
+        out[p + ".post_attention_layernorm.weight"] = ("BF16", lw["post_norm"])
+        out[p + ".self_attn.q_norm.weight"] = ("BF16", lw["q_norm"])
+        out[p + ".self_attn.k_norm.weight"] = ("BF16", lw["k_norm"])
+        cut(p + ".self_attn.q_proj", lw["qkv_qw"], lw["qkv_qz"], lw["qkv_s"], 0, nq)
+        cut(p + ".self_attn.k_proj", lw["qkv_qw"], lw["qkv_qz"], lw["qkv_s"], nq, nq + nkv)
+        cut(p + ".self_attn.v_proj", lw["qkv_qw"], lw["qkv_qz"], lw["qkv_s"], nq + nkv, nq + 2 * nkv)
+        cut(p + ".self_attn.o_proj", lw["o_qw"], lw["o_qz"], lw["o_s"], 0, cfg.hidden)
+        cut(p + ".mlp.gate_proj", lw["gu_qw"], lw["gu_qz"], lw["gu_s"], 0, I)
+        cut(p + ".mlp.up_proj", lw["gu_qw"], lw["gu_qz"], lw["gu_s"], I, 2 * I)
+        cut(p + ".mlp.down_proj", lw["down_qw"], lw["down_qz"], lw["down_s"], 0, cfg.hidden)
+    return out

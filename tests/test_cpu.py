@@ -270,3 +270,40 @@ def test_python_front_ends_import_without_a_gpu():
     import importlib
     for name in ("mykuiperllama_b200.capi", "mykuiperllama_b200.engine"):
         importlib.import_module(name)
+
+
+# ----------------------------------------------------------------------------- checkpoint container (host only)
+def test_safetensors_header_is_parsed_and_checked(oracle, tmp_path):
+    import ctypes as C
+    import struct
+    from helpers import checkpoint_tensors, make_model_weights, write_safetensors
+    from mykuiperllama_b200 import _lib
+    lib = _lib.host()
+    cfg = oracle.ModelConfig(n_layers=1, hidden=256, n_q_heads=4, n_kv_heads=2, head_dim=128, inter=512, vocab=64, max_seq=8, max_batch=1)
+    tensors = checkpoint_tensors(cfg, make_model_weights(oracle, cfg, seed=2))
+    path = str(tmp_path / "tiny.safetensors")
+    write_safetensors(path, tensors, metadata={"format": "pt", "note": "a \"quoted\" value"})
+    buf = C.create_string_buffer(1 << 16)
+    assert lib.kuiper_checkpoint_inspect(path.encode(), buf, len(buf)) == 0
+    lines = buf.value.decode().splitlines()
+    assert "model.layers.0.self_attn.q_proj.qweight I32 [256,64] 65536" in lines
+    assert "model.layers.0.mlp.down_proj.scales F16 [4,256] 2048" in lines
+    assert "model.embed_tokens.weight BF16 [64,256] 32768" in lines
+    assert "__metadata__ format=pt" in lines
+    assert len([l for l in lines if not l.startswith("__metadata__")]) == len(tensors)
+    # malformed files are refused with a parse error (3) or a path error (2), never read out of bounds
+    raw = open(path, "rb").read()
+    cases = {
+        "missing": None,
+        "short": raw[:5],
+        "header_too_long": struct.pack("<Q", len(raw)) + raw[8:],
+        "truncated_data": raw[:-100],
+        "bad_json": raw[:8] + b"{" + b"x" * (struct.unpack("<Q", raw[:8])[0] - 1) + raw[8 + struct.unpack("<Q", raw[:8])[0]:],
+    }
+    for name, blob in cases.items():
+        bad = str(tmp_path / (name + ".safetensors"))
+        if blob is not None:
+            open(bad, "wb").write(blob)
+        rc = lib.kuiper_checkpoint_inspect(bad.encode(), buf, len(buf))
+        assert rc in (2, 3), (name, rc)
+        assert lib.kuiper_llama_last_error()

@@ -234,3 +234,47 @@ def test_two_layer_cuts_of_the_4b_and_8b_shapes_match_oracle(oracle, engine_mod,
         tok = int(nx[0])
     print("%s cut: oracle top-1/top-2 logit margins: min %.3e median %.3e" % (name, min(margins), float(np.median(margins))))
     eng.close()
+
+
+def test_checkpoint_file_round_trip_reproduces_the_greedy_stream(oracle, engine_mod, tmp_path):
+    """The synthetic model written as an AWQ checkpoint (safetensors container, Hugging Face tensor names, separate
+    q / k / v and gate / up projections), loaded through the file reader: the 32 greedy tokens of the in-memory
+    engine and of the oracle."""
+    from helpers import checkpoint_tensors, write_safetensors
+    cfg = {**TINY, "max_seq": 96}
+    ocfg = oracle.ModelConfig(**cfg, act_round=oracle.ROUND_ENGINE)
+    weights = make_model_weights(oracle, ocfg, seed=9)
+    path = str(tmp_path / "model.safetensors")
+    write_safetensors(path, checkpoint_tensors(ocfg, weights), metadata={"format": "pt"})
+    ref = oracle.OracleModel(ocfg, weights)
+    from_file = engine_mod.Qwen3Engine(engine_mod.EngineConfig(**cfg, max_rows=8, act_mode=2))
+    from_file.load_checkpoint(path)
+    in_memory = engine_mod.Qwen3Engine(engine_mod.EngineConfig(**cfg, max_rows=8, act_mode=2))
+    in_memory.load(weights)
+    prompt = np.random.default_rng(10).integers(0, 1000, 11).astype(np.int32)
+    _, nx_ref = ref.forward(prompt, np.arange(11, dtype=np.int32), logit_rows=1)
+    streams = []
+    for eng in (from_file, in_memory):
+        first = eng.prefill(prompt)
+        assert first == nx_ref[-1]
+        eng.decode_begin([first], [11], [0])
+        got = []
+        for _ in range(32):
+            eng.decode_step(1)
+            got.append(int(eng.decode_read(1)[0]))
+        streams.append(got)
+    assert streams[0] == streams[1]
+    tok, want = int(nx_ref[-1]), []
+    for i in range(32):
+        _, nx = ref.forward([tok], [11 + i])
+        want.append(int(nx[0]))
+        tok = int(nx[0])
+    assert streams[0] == want
+    # a file that lacks a tensor is refused with a parse error naming it
+    from mykuiperllama_b200._lib import KuiperError
+    tensors = checkpoint_tensors(ocfg, weights)
+    del tensors["model.layers.1.mlp.up_proj.qzeros"]
+    write_safetensors(str(tmp_path / "broken.safetensors"), tensors)
+    with pytest.raises(KuiperError) as e:
+        from_file.load_checkpoint(str(tmp_path / "broken.safetensors"))
+    assert e.value.code == 3 and "up_proj" in str(e.value)
