@@ -703,9 +703,26 @@ def run_attn_micro(args):
     slot = torch.arange(B, dtype=torch.int32, device="cuda")
     ws = capi.flash_decode_workspace(B, Nq, D, L)
 
-    def sweep():
-        for i in range(n):
-            capi.flash_decode(q, kc[i], vc[i], seq, slot, workspace=ws, out=out)
+    if args.fused:
+        # the engine's decode call: q/k-norm + rotary + KV append + attention in one kernel, from a raw projection row
+        # (the row is rewritten before every launch because the kernel clears it; that copy is part of the timed graph)
+        qkv0 = torch.randn((B, (Nq + 2 * Nkv) * D), device="cuda", generator=gen)
+        qkv = qkv0.clone()
+        ones = torch.ones(D, device="cuda").bfloat16()
+        half = torch.arange(D // 2, device="cuda", dtype=torch.float64)
+        ang = torch.arange(L, device="cuda", dtype=torch.float64)[:, None] * torch.pow(torch.tensor(1e6, dtype=torch.float64, device="cuda"), -2.0 * half / D)[None, :]
+        cos_t, sin_t = torch.cos(ang).float().contiguous(), torch.sin(ang).float().contiguous()
+        pos = torch.full((B,), L - 1, dtype=torch.int32, device="cuda")
+
+        def sweep():
+            for i in range(n):
+                qkv.copy_(qkv0)
+                capi.rope_flash_decode(qkv, ones, ones, cos_t, sin_t, pos, seq, slot, Nq, Nkv, D, 1e-6, kc[i], vc[i], workspace=ws,
+                                       out=out, fresh_rows=1, clear_input=True)
+    else:
+        def sweep():
+            for i in range(n):
+                capi.flash_decode(q, kc[i], vc[i], seq, slot, workspace=ws, out=out)
 
     for _ in range(args.warmup):
         sweep()
@@ -733,7 +750,7 @@ def run_attn_micro(args):
         "dtype": "bf16 KV cache, bf16 x bf16 -> fp32 mma (q and probabilities as bf16 high + low parts), fp32 softmax", "data": "synthetic",
         "config": {"workload": f"flash-decoding batch {B}, 32 q heads / 8 kv heads, head_dim 128, KV length {L}",
                    "distinct_caches": n, "l2_policy": f"{n} caches ({kv_bytes * n >> 20} MiB) visited in turn: larger than L2"},
-        "roofline": {"bound": "hbm", "kernel": "flash_decode_mma_kernel<4>", "achieved": gbs, "peak": peak, "peak_kind": kind,
+        "roofline": {"bound": "hbm", "kernel": "flash_decode_mma_kernel<4 heads per kv head%s>" % (", fused rotary" if args.fused else ""), "achieved": gbs, "peak": peak, "peak_kind": kind,
                      "unit": "GB/s", "frac": gbs / peak, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
                      # ncu: dram bytes / KV bytes = 1.01 on batch 16, 4096 rows (profiles/flash_decode_mma_b16_kv4096.md)
                      "traffic": int(kv_bytes * 1.01),
@@ -760,6 +777,7 @@ def main():
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for a profiler run with profile-from-start off)")
     ap.add_argument("--act-mode", type=int, default=2, help="INT4 matmul operand: 2 block-scaled 16-bit integers for one-row passes "
                     "(integer tensor-core kernel; fp16 for passes of several rows), 1 fp16 everywhere")
+    ap.add_argument("--fused", action="store_true", help="attn workload: the fused rotary + append + attention call of the decode step")
     ap.add_argument("--group-tickets", action="store_true", help="gemv-impl 5: hand the tail of the grouped launch out by ticket")
     ap.add_argument("--gemv-trace", default=None, metavar="FILE.npy",
                     help="gemv workload with the KUIPER_TRACE=1 build: save the per-CTA clock readings of the last GEMV launch")

@@ -489,8 +489,8 @@ awq_gemv_mma_kernel(const __grid_constant__ GemvItem item0, const GemvCall p) {
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);
                 // consumer lane (g, tig) of 8-row step st reads 8 bytes at ((st * 4 + tig) * 8 + g) * 8: the fragment
-                // words of rows 8 st + tig and 8 st + tig + 4; column g = (byte position g >> 1, digit g & 1)
-                const int st = lane >> 3, hi_row = (lane >> 2) & 1, tq = lane & 3;
+                // words of rows 8 st + 2 tig and 8 st + 2 tig + 1; column g = (byte position g >> 1, digit g & 1)
+                const int st = lane >> 3, hi_row = lane & 1, tq = (lane >> 1) & 3;
                 unsigned char* base = xs + ((st * 4 + tq) * 8) * 8 + 4 * hi_row;
 #pragma unroll
                 for (int gg = 0; gg < 8; gg++) {
@@ -568,15 +568,16 @@ awq_gemv_mma_kernel(const __grid_constant__ GemvItem item0, const GemvCall p) {
 
     if constexpr (INT8) {
         // This warp: word columns 16*warp .. 16*warp+15 of the tile = two blocks of 8 (cb = 2*warp, 2*warp+1) in TMA box
-        // warp>>1.  Lane (g, tig) reads word g of the block in rows tig and tig+4 of each 8-row step (the 128-byte
-        // swizzle XORs the 16-byte chunk index with row & 7, which spreads the 32 lanes over all banks).
+        // warp>>1.  Lane (g, tig) reads word g of the block in rows 2 tig and 2 tig + 1 of each 8-row step (the 128-byte
+        // swizzle XORs the 16-byte chunk index with row & 7, which spreads the 32 lanes over all banks).  The first
+        // half of the contraction index (k < 16) therefore stands for the even rows of the step, the second for the odd ones.
         uint32_t offA[2], offB[2];
 #pragma unroll
         for (int cbi = 0; cbi < 2; cbi++) {
             const int cbl = 2 * (warp & 1) + cbi;
             const int chunk = 2 * cbl + (g >> 2);
-            offA[cbi] = uint32_t((warp >> 1) * kBoxBytes + tig * 128 + ((chunk ^ tig) << 4) + (g & 3) * 4);
-            offB[cbi] = uint32_t((warp >> 1) * kBoxBytes + (tig + 4) * 128 + ((chunk ^ (tig + 4)) << 4) + (g & 3) * 4);
+            offA[cbi] = uint32_t((warp >> 1) * kBoxBytes + (2 * tig) * 128 + ((chunk ^ (2 * tig)) << 4) + (g & 3) * 4);
+            offB[cbi] = uint32_t((warp >> 1) * kBoxBytes + (2 * tig + 1) * 128 + ((chunk ^ (2 * tig + 1)) << 4) + (g & 3) * 4);
         }
         const uint32_t xoff8 = uint32_t(kOffX + tig * 64 + g * 8);
         const uint32_t inv_off = uint32_t(kOffX + kXBytesInt8);
@@ -619,7 +620,7 @@ awq_gemv_mma_kernel(const __grid_constant__ GemvItem item0, const GemvCall p) {
 #pragma unroll
                     for (int cbi = 0; cbi < 2; cbi++) {
                         const uint32_t a = wA[cbi][st], b = wB[cbi][st];
-                        // fragment rows g / g+8 = low / high nibbles of word g; contraction halves = weight rows tig / tig+4
+                        // fragment rows g / g+8 = low / high nibbles of word g; contraction halves = weight rows 2 tig / 2 tig + 1
                         mma_u8s8(acc[cbi], a & 0x0f0f0f0fu, a & 0xf0f0f0f0u, b & 0x0f0f0f0fu, b & 0xf0f0f0f0u, xb[st].x, xb[st].y);
                     }
                 }
@@ -1074,6 +1075,7 @@ bool get_map_mma(const int32_t* qweight, int K, int N, CUtensorMap* out) {
 // away without finishing sooner; it pays for a launch that nothing follows closely.
 int g_dyn_pct = 0;
 int g_dyn_chunk = 0;   // 128-row groups per ticket; 0: one (tuning key "gemv_dyn_chunk")
+int g_stages = 0;      // ring depth of the one-row integer-operand kernel, 3..6; 0: kStagesM (tuning key "gemv_stages")
 
 template <int MT, int STAGES, bool ACCUM, bool NORM, bool GROUPED, bool INT8 = false>
 int launch_mma(const GemvItem& item, const GemvCall& call, int ctas, cudaStream_t stream) {
@@ -1163,6 +1165,7 @@ int awq_gemv_trace_read(long long* out, int max_values) {
 void awq_gemv_mma_set_tuning(const char* key, int value) {
     if (!strcmp(key, "gemv_dyn_pct")) g_dyn_pct = value < 0 ? 0 : value;
     if (!strcmp(key, "gemv_dyn_chunk")) g_dyn_chunk = value < 0 ? 0 : value;
+    if (!strcmp(key, "gemv_stages")) g_stages = value < 0 ? 0 : value;
 }
 
 int awq_gemv_mma_status() {
@@ -1213,6 +1216,16 @@ int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* q
     }
     plan_tickets(call, int(ctas), accumulate ? tickets : nullptr);
     if (int_operand && rows == 1) {
+        if (accumulate && g_stages >= 4 && g_stages <= 6) {  // measurement aid: deeper rings
+            if (norm_w) {
+                if (g_stages == 4) return launch_mma<1, 4, true, true, false, true>(item, call, int(ctas), stream);
+                if (g_stages == 5) return launch_mma<1, 5, true, true, false, true>(item, call, int(ctas), stream);
+                return launch_mma<1, 6, true, true, false, true>(item, call, int(ctas), stream);
+            }
+            if (g_stages == 4) return launch_mma<1, 4, true, false, false, true>(item, call, int(ctas), stream);
+            if (g_stages == 5) return launch_mma<1, 5, true, false, false, true>(item, call, int(ctas), stream);
+            return launch_mma<1, 6, true, false, false, true>(item, call, int(ctas), stream);
+        }
         if (accumulate && norm_w) return launch_mma<1, kStagesM, true, true, false, true>(item, call, int(ctas), stream);
         if (accumulate) return launch_mma<1, kStagesM, true, false, false, true>(item, call, int(ctas), stream);
         return launch_mma<1, kStagesM, false, false, false, true>(item, call, int(ctas), stream);

@@ -894,45 +894,87 @@ flash_decode_mma_kernel(const FlashParams p) {
     __syncthreads();
     flash_trace(7);
     if (!s_last) return;
-    // ---- final combine by the last CTA, in slice order.  Every load is independent of every other (the slice weights
-    // come from the (max, sum) pairs, the sums from the partial outputs), so they are all issued before the first use:
-    // one trip to the L2 for up to kInFlight slices (20 for the eight-warp CTAs of a 4:1 head ratio).
-    constexpr int kInFlight = HP <= 2 ? 20 : (HP == 4 ? 12 : 6);
-    float acc[HP], den[HP], gmax[HP];
+    float acc[HP], den[HP];
 #pragma unroll
-    for (int j = 0; j < HP; j++) { acc[j] = 0.f; den[j] = 0.f; gmax[j] = -INFINITY; }
+    for (int j = 0; j < HP; j++) { acc[j] = 0.f; den[j] = 0.f; }
     const float* po = p.part_o + pbase * R * kD + d;
     const float* pml = p.part_ml + pbase * R * 2;
-    // global maximum per head first (cheap: one float2 per slice and head, the same address for all threads of a head)
-    for (int sp0 = 0; sp0 < n_active; sp0 += kInFlight) {
-        float2 ml[kInFlight][HP];
-        float a[kInFlight][HP];
+    if constexpr (WARPS == 8) {
+        // ---- final combine by the last CTA, in slice order.  Every load is independent of every other (the slice weights
+        // come from the (max, sum) pairs, the sums from the partial outputs), so they are all issued before the first
+        // use: one trip to the L2 for up to kInFlight slices (each thread serves two heads, so 20 slices fit registers).
+        constexpr int kInFlight = 20;
+        float gmax[HP];
 #pragma unroll
-        for (int q = 0; q < kInFlight; q++)
+        for (int j = 0; j < HP; j++) gmax[j] = -INFINITY;
+        for (int sp0 = 0; sp0 < n_active; sp0 += kInFlight) {
+            float2 ml[kInFlight][HP];
+            float a[kInFlight][HP];
+#pragma unroll
+            for (int q = 0; q < kInFlight; q++)
+#pragma unroll
+                for (int j = 0; j < HP; j++) {
+                    const int h = hh + j * HS;
+                    const bool ok = sp0 + q < n_active && h < R;
+                    ml[q][j] = ok ? __ldcg(reinterpret_cast<const float2*>(pml + (size_t(sp0 + q) * R + h) * 2)) : make_float2(-INFINITY, 0.f);
+                    a[q][j] = ok ? __ldcg(po + (size_t(sp0 + q) * R + h) * kD) : 0.f;
+                }
 #pragma unroll
             for (int j = 0; j < HP; j++) {
-                const int h = hh + j * HS;
-                const bool ok = sp0 + q < n_active && h < R;
-                ml[q][j] = ok ? __ldcg(reinterpret_cast<const float2*>(pml + (size_t(sp0 + q) * R + h) * 2)) : make_float2(-INFINITY, 0.f);
-                a[q][j] = ok ? __ldcg(po + (size_t(sp0 + q) * R + h) * kD) : 0.f;
-            }
+                float bm = gmax[j];
 #pragma unroll
-        for (int j = 0; j < HP; j++) {
-            float bm = gmax[j];
+                for (int q = 0; q < kInFlight; q++) bm = fmaxf(bm, ml[q][j].x);
+                // rescale what was accumulated under the previous maximum (slice order is kept: a fixed summation order)
+                const float c = (gmax[j] == -INFINITY) ? 0.f : __expf(gmax[j] - bm);
+                acc[j] *= c;
+                den[j] *= c;
+                gmax[j] = bm;
 #pragma unroll
-            for (int q = 0; q < kInFlight; q++) bm = fmaxf(bm, ml[q][j].x);
-            // rescale what was accumulated under the previous maximum (slice order is kept: a fixed summation order)
-            const float c = (gmax[j] == -INFINITY) ? 0.f : __expf(gmax[j] - bm);
-            acc[j] *= c;
-            den[j] *= c;
-            gmax[j] = bm;
-#pragma unroll
-            for (int q = 0; q < kInFlight; q++) {
-                const float w = (ml[q][j].x == -INFINITY) ? 0.f : __expf(ml[q][j].x - bm);
-                acc[j] = fmaf(a[q][j], w, acc[j]);
-                den[j] = fmaf(ml[q][j].y, w, den[j]);
+                for (int q = 0; q < kInFlight; q++) {
+                    const float w = (ml[q][j].x == -INFINITY) ? 0.f : __expf(ml[q][j].x - bm);
+                    acc[j] = fmaf(a[q][j], w, acc[j]);
+                    den[j] = fmaf(ml[q][j].y, w, den[j]);
+                }
             }
         }
+    } else {
+        // ---- final combine by the last CTA (four warps, one thread per dimension, every head).  Weights first: warp w
+        // takes heads w, w + 4, ...; lane l holds the (max, sum) of slices l and l + 32, so the maximum and the
+        // denominator are two warp reductions; then the partial outputs in slice order, eight slices of every head in
+        // flight per thread (few registers: this variant runs five CTAs per SM).
+        __shared__ float s_w[64 * R];   // weight of slice sp for head h at [sp * R + h]
+        __shared__ float s_den[R];
+        for (int h = warp; h < R; h += WARPS) {
+            float2 ml0 = make_float2(-INFINITY, 0.f), ml1 = ml0;
+            if (lane < n_active) ml0 = __ldcg(reinterpret_cast<const float2*>(pml + (size_t(lane) * R + h) * 2));
+            if (lane + 32 < n_active) ml1 = __ldcg(reinterpret_cast<const float2*>(pml + (size_t(lane + 32) * R + h) * 2));
+            const float nm = warp_max(fmaxf(ml0.x, ml1.x));
+            const float w0 = (ml0.x == -INFINITY) ? 0.f : __expf(ml0.x - nm);
+            const float w1 = (ml1.x == -INFINITY) ? 0.f : __expf(ml1.x - nm);
+            const float dsum = warp_sum(ml0.y * w0 + ml1.y * w1);
+            s_w[lane * R + h] = w0;
+            s_w[(lane + 32) * R + h] = w1;
+            if (lane == 0) s_den[h] = dsum;
+        }
+        __syncthreads();
+        int sp = 0;
+        for (; sp + 8 <= n_active; sp += 8) {
+            float a[8][HP];
+#pragma unroll
+            for (int q = 0; q < 8; q++)
+#pragma unroll
+                for (int j = 0; j < HP; j++) a[q][j] = __ldcg(po + (size_t(sp + q) * R + j) * kD);
+#pragma unroll
+            for (int q = 0; q < 8; q++)
+#pragma unroll
+                for (int j = 0; j < HP; j++) acc[j] = fmaf(a[q][j], s_w[(sp + q) * R + j], acc[j]);
+        }
+        for (; sp < n_active; sp++) {
+#pragma unroll
+            for (int j = 0; j < HP; j++) acc[j] = fmaf(__ldcg(po + (size_t(sp) * R + j) * kD), s_w[sp * R + j], acc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < HP; j++) den[j] = s_den[j];
     }
     flash_trace(8);
 #pragma unroll
