@@ -19,7 +19,7 @@
 //
 // Data movement: a weight [K, N/8] int32 is cut into units of 32 rows x 1024 columns (16 KB), numbered
 // column-tile major / K minor (over all matrices of a grouped call) and dealt out in contiguous runs to 2 CTAs
-// per SM; optionally a tail of 128-row groups is handed out through an atomic ticket counter instead (off by
+// per SM (3 for large one-row integer-operand launches, see g_int8_ctas); optionally a tail of 128-row groups is handed out through an atomic ticket counter instead (off by
 // default, see g_dyn_pct).  Warp 8 keeps a ring of stages full: per unit a descriptor (item, tile, row block,
 // first-of-group / last-of-run flags) that the other warps follow, four cp.async.bulk.tensor boxes (32 words x 32
 // rows, 128-byte swizzle so that the fragment loads are bank-conflict free) and, for the first unit of a 128-row
@@ -46,6 +46,7 @@ constexpr int kWarpsC = 8;                      // consumer warps
 constexpr int kConsumersC = kWarpsC * 32;       // 256
 constexpr int kThreadsMma = kConsumersC + 64;   // + weight producer warp + activation warp
 constexpr int kCtasPerSmMma = 2;
+constexpr int kCtasPerSmInt8 = 3;  // the integer-operand consumers fit in 64 registers: a third CTA per SM is possible
 constexpr int kUnitRowsM = 32;
 constexpr int kTileWordsM = 128;                // 1024 columns
 constexpr int kTileColsM = kTileWordsM * 8;
@@ -229,8 +230,8 @@ struct UnitRef {
 // low / high nibbles), contraction index = (weight row, byte position c), B column = (byte position c', digit):
 // B[(r, c)][(c', d)] = digit d of x'[r] when c == c', else 0, which separates the four bytes of a word into four
 // result columns.  All sums are exact integers inside a unit; 512 weights per mma, 2 integer instructions per word.
-template <int MT, int STAGES, bool ACCUM, bool NORM, bool GROUPED, bool INT8>
-__global__ void __launch_bounds__(kThreadsMma, kCtasPerSmMma)
+template <int MT, int STAGES, bool ACCUM, bool NORM, bool GROUPED, bool INT8, int OCC>
+__global__ void __launch_bounds__(kThreadsMma, OCC)
 awq_gemv_mma_kernel(const __grid_constant__ GemvItem item0, const GemvCall p) {
     static_assert(!INT8 || MT == 1, "the integer operand path takes one token row");
     constexpr int kXStage = x_stage_bytes(MT, INT8);
@@ -1075,11 +1076,16 @@ bool get_map_mma(const int32_t* qweight, int K, int N, CUtensorMap* out) {
 // away without finishing sooner; it pays for a launch that nothing follows closely.
 int g_dyn_pct = 0;
 int g_dyn_chunk = 0;   // 128-row groups per ticket; 0: one (tuning key "gemv_dyn_chunk")
-int g_stages = 0;      // ring depth of the one-row integer-operand kernel, 3..6; 0: kStagesM (tuning key "gemv_stages")
+// One-row integer-operand launches in accumulate mode: a matrix of at least g_int8_ctas3_units units runs three CTAs
+// per SM (consumers held to 64 registers: more loads in flight, 4096 x 24576 goes from 11.7 to 10.5 us), a smaller one
+// two CTAs per SM of the 96-register build (4096 x 4096: 3.6 us against 3.9).  Tuning keys "gemv_ctas" (2 switches the
+// three-CTA build off) and "gemv_ctas3_units".
+int g_int8_ctas = kCtasPerSmInt8;
+int g_int8_ctas3_units = 1024;
 
-template <int MT, int STAGES, bool ACCUM, bool NORM, bool GROUPED, bool INT8 = false>
+template <int MT, int STAGES, bool ACCUM, bool NORM, bool GROUPED, bool INT8 = false, int OCC = kCtasPerSmMma>
 int launch_mma(const GemvItem& item, const GemvCall& call, int ctas, cudaStream_t stream) {
-    auto kern = awq_gemv_mma_kernel<MT, STAGES, ACCUM, NORM, GROUPED, INT8>;
+    auto kern = awq_gemv_mma_kernel<MT, STAGES, ACCUM, NORM, GROUPED, INT8, OCC>;
     const size_t smem = 1024 + size_t(STAGES) * stage_bytes(MT, INT8) + (ACCUM ? 0 : size_t(MT) * kTileColsM * sizeof(float));
     static size_t configured[kMaxDevices] = {};  // per instantiation and device
     if (!ensure_dynamic_smem(kern, smem, configured)) {
@@ -1165,7 +1171,8 @@ int awq_gemv_trace_read(long long* out, int max_values) {
 void awq_gemv_mma_set_tuning(const char* key, int value) {
     if (!strcmp(key, "gemv_dyn_pct")) g_dyn_pct = value < 0 ? 0 : value;
     if (!strcmp(key, "gemv_dyn_chunk")) g_dyn_chunk = value < 0 ? 0 : value;
-    if (!strcmp(key, "gemv_stages")) g_stages = value < 0 ? 0 : value;
+    if (!strcmp(key, "gemv_ctas3_units")) g_int8_ctas3_units = value < 1 ? 1 : value;
+    if (!strcmp(key, "gemv_ctas")) g_int8_ctas = value >= kCtasPerSmInt8 ? kCtasPerSmInt8 : kCtasPerSmMma;
 }
 
 int awq_gemv_mma_status() {
@@ -1208,7 +1215,8 @@ int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* q
     }
     call.counters = reinterpret_cast<int*>(workspace);
     call.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + head);
-    long long ctas = (long long)device_sm_count() * kCtasPerSmMma;
+    const bool three = int_operand && rows == 1 && accumulate && g_int8_ctas == kCtasPerSmInt8 && call.U >= g_int8_ctas3_units;
+    long long ctas = (long long)device_sm_count() * (three ? kCtasPerSmInt8 : kCtasPerSmMma);
     if (ctas > call.U) ctas = call.U;
     if ((norm_w || swiglu) && !accumulate) {
         set_error("awq_gemv_mma: the fused input norm / SwiGLU exist in accumulate mode only");
@@ -1216,15 +1224,9 @@ int awq_gemv_mma_launch(const float* x, const int32_t* qweight, const int32_t* q
     }
     plan_tickets(call, int(ctas), accumulate ? tickets : nullptr);
     if (int_operand && rows == 1) {
-        if (accumulate && g_stages >= 4 && g_stages <= 6) {  // measurement aid: deeper rings
-            if (norm_w) {
-                if (g_stages == 4) return launch_mma<1, 4, true, true, false, true>(item, call, int(ctas), stream);
-                if (g_stages == 5) return launch_mma<1, 5, true, true, false, true>(item, call, int(ctas), stream);
-                return launch_mma<1, 6, true, true, false, true>(item, call, int(ctas), stream);
-            }
-            if (g_stages == 4) return launch_mma<1, 4, true, false, false, true>(item, call, int(ctas), stream);
-            if (g_stages == 5) return launch_mma<1, 5, true, false, false, true>(item, call, int(ctas), stream);
-            return launch_mma<1, 6, true, false, false, true>(item, call, int(ctas), stream);
+        if (accumulate && three) {
+            if (norm_w) return launch_mma<1, kStagesM, true, true, false, true, kCtasPerSmInt8>(item, call, int(ctas), stream);
+            return launch_mma<1, kStagesM, true, false, false, true, kCtasPerSmInt8>(item, call, int(ctas), stream);
         }
         if (accumulate && norm_w) return launch_mma<1, kStagesM, true, true, false, true>(item, call, int(ctas), stream);
         if (accumulate) return launch_mma<1, kStagesM, true, false, false, true>(item, call, int(ctas), stream);
@@ -1264,9 +1266,11 @@ int awq_gemv_group_launch(const void* device_table, int n_items, long long units
     call.items = reinterpret_cast<const GemvItem*>(device_table);
     call.n_items = n_items;
     call.U = int(units);
-    long long ctas = (long long)device_sm_count() * kCtasPerSmMma;
+    const bool three = int_operand && g_int8_ctas == kCtasPerSmInt8 && call.U >= g_int8_ctas3_units;
+    long long ctas = (long long)device_sm_count() * (three ? kCtasPerSmInt8 : kCtasPerSmMma);
     if (ctas > call.U) ctas = call.U;
     plan_tickets(call, int(ctas), tickets);
+    if (three) return launch_mma<1, kStagesM, true, false, true, true, kCtasPerSmInt8>(none, call, int(ctas), stream);
     if (int_operand) return launch_mma<1, kStagesM, true, false, true, true>(none, call, int(ctas), stream);
     return launch_mma<1, kStagesM, true, false, true>(none, call, int(ctas), stream);
 }
