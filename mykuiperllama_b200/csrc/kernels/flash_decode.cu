@@ -22,6 +22,10 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kWarps = 4;
+constexpr int kMaxSplits = 64;      // slices per (row, kv head)
+constexpr int kMaxSplitsMma = 128;  // same for calls of at most kFewRows rows on the four-warp tensor-core kernel
+constexpr int kFewRows = 2;
+constexpr int kCtasStandalone = 2, kCtasFusedNarrow = 2;  // resident CTAs per SM the four-warp tensor-core kernels are built for
 constexpr int kRowsPerStep = 8;  // row slots per half warp per step
 
 int g_force_splits = 0;
@@ -512,13 +516,14 @@ __device__ __forceinline__ void head_norm_rope_regs(float a0, float a1, float b0
     out[3] = __fadd_rn(__fmul_rn(y1, cs[1]), __fmul_rn(x1, cs[3]));
 }
 
-// Launch shapes.  Stand-alone: four warps, five CTAs per SM (96 registers) - long caches are bound by memory latency, so
-// resident warps matter more than a few spilled values.  Fused, four warps: the rows fetched ahead of the wait stay in
-// registers across the prologue, three CTAs per SM.  Fused, eight warps: one CTA per SM and one 128-row step per CTA -
+// Launch shapes.  Four warps (stand-alone and fused): two CTAs per SM, up to 255 registers - a warp holds two steps of
+// cache rows (the one it works on and the next one in flight, 128 registers), which hides the memory latency better
+// than the five CTAs per SM of one-step warps did (batch 1, 32 768 rows: 3.0 -> 4.6 TB/s; batch 16: 5.2 -> 5.7 TB/s).
+// Fused, eight warps: one CTA per SM and one 128-row step per CTA -
 // the shape for a single sequence at a context of a few thousand rows, where the kernel is a chain of latencies and the
 // number of slices the last CTA has to combine is what counts.
 template <int R, bool FUSED, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, FUSED ? (WARPS == 8 ? 1 : 3) : 5)
+__global__ void __launch_bounds__(WARPS * 32, FUSED ? (WARPS == 8 ? 1 : kCtasFusedNarrow) : kCtasStandalone)
 flash_decode_mma_kernel(const FlashParams p) {
     constexpr int kBlk = WARPS * 16;  // cache rows per CTA step
     constexpr int kThreads = WARPS * 32;
@@ -721,30 +726,35 @@ flash_decode_mma_kernel(const FlashParams p) {
 #pragma unroll
     for (int b = 0; b < 8; b++) { oacc[b][0] = oacc[b][1] = oacc[b][2] = oacc[b][3] = 0.f; }
 
-    // warp w takes rows begin + w*16 + step*kBlk .. +15: fragment rows g and g+8
-    for (int base = base0; base < end; base += kBlk) {
+    // One step of a warp = rows base + g and base + g + 8 (16 cache rows, 8 KB of K and V).  The four-warp CTAs run many
+    // steps and keep the next step's rows in flight in a second register set while they work on the current one (the
+    // per-step chain load -> scores -> softmax -> PV is ~3.5 us long; without the overlap only occupancy hides it);
+    // the eight-warp CTAs run a single step.
+    auto load_step = [&](int base, uint4 (&K0)[4], uint4 (&K1)[4], uint4 (&V0)[4], uint4 (&V1)[4]) {
         const int r0 = base + g, r1 = base + g + 8;
         const bool ok0 = r0 < end, ok1 = r1 < end;
-        if (!FUSED || base != base0) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                k0[i] = ok0 ? ld_row(kb + size_t(r0) * kD + 32 * i + 8 * t, FUSED && r0 >= newest) : make_uint4(0, 0, 0, 0);
-                k1[i] = ok1 ? ld_row(kb + size_t(r1) * kD + 32 * i + 8 * t, FUSED && r1 >= newest) : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                v0[i] = ok0 ? ld_row(vb + size_t(r0) * kD + 32 * i + 8 * t, FUSED && r0 >= newest) : make_uint4(0, 0, 0, 0);
-                v1[i] = ok1 ? ld_row(vb + size_t(r1) * kD + 32 * i + 8 * t, FUSED && r1 >= newest) : make_uint4(0, 0, 0, 0);
-            }
+        for (int i = 0; i < 4; i++) {
+            K0[i] = ok0 ? ld_row(kb + size_t(r0) * kD + 32 * i + 8 * t, FUSED && r0 >= newest) : make_uint4(0, 0, 0, 0);
+            K1[i] = ok1 ? ld_row(kb + size_t(r1) * kD + 32 * i + 8 * t, FUSED && r1 >= newest) : make_uint4(0, 0, 0, 0);
         }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            V0[i] = ok0 ? ld_row(vb + size_t(r0) * kD + 32 * i + 8 * t, FUSED && r0 >= newest) : make_uint4(0, 0, 0, 0);
+            V1[i] = ok1 ? ld_row(vb + size_t(r1) * kD + 32 * i + 8 * t, FUSED && r1 >= newest) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    auto compute_step = [&](int base, const uint4 (&K0)[4], const uint4 (&K1)[4], const uint4 (&V0)[4], const uint4 (&V1)[4]) {
+        const int r0 = base + g, r1 = base + g + 8;
+        const bool ok0 = r0 < end, ok1 = r1 < end;
         // scores S^T[rows g, g+8][heads 2t, 2t+1]
         float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            mma_bf16(s, k0[i].x, k1[i].x, k0[i].y, k1[i].y, qh[i][0][0], qh[i][0][1]);
-            mma_bf16(s, k0[i].x, k1[i].x, k0[i].y, k1[i].y, ql[i][0][0], ql[i][0][1]);
-            mma_bf16(s, k0[i].z, k1[i].z, k0[i].w, k1[i].w, qh[i][1][0], qh[i][1][1]);
-            mma_bf16(s, k0[i].z, k1[i].z, k0[i].w, k1[i].w, ql[i][1][0], ql[i][1][1]);
+            mma_bf16(s, K0[i].x, K1[i].x, K0[i].y, K1[i].y, qh[i][0][0], qh[i][0][1]);
+            mma_bf16(s, K0[i].x, K1[i].x, K0[i].y, K1[i].y, ql[i][0][0], ql[i][0][1]);
+            mma_bf16(s, K0[i].z, K1[i].z, K0[i].w, K1[i].w, qh[i][1][0], qh[i][1][1]);
+            mma_bf16(s, K0[i].z, K1[i].z, K0[i].w, K1[i].w, ql[i][1][0], ql[i][1][1]);
         }
         s[0] = ok0 ? s[0] * scale : -INFINITY;
         s[1] = ok0 ? s[1] * scale : -INFINITY;
@@ -781,20 +791,38 @@ flash_decode_mma_kernel(const FlashParams p) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             {
-                const uint32_t a0 = movmatrix_trans(v0[i].x), a1 = movmatrix_trans(v0[i].y);
-                const uint32_t a2 = movmatrix_trans(v1[i].x), a3 = movmatrix_trans(v1[i].y);
+                const uint32_t a0 = movmatrix_trans(V0[i].x), a1 = movmatrix_trans(V0[i].y);
+                const uint32_t a2 = movmatrix_trans(V1[i].x), a3 = movmatrix_trans(V1[i].y);
                 mma_bf16(oacc[2 * i], a0, a1, a2, a3, bh0, bh1);
                 mma_bf16(oacc[2 * i], a0, a1, a2, a3, bl0, bl1);
             }
             {
-                const uint32_t a0 = movmatrix_trans(v0[i].z), a1 = movmatrix_trans(v0[i].w);
-                const uint32_t a2 = movmatrix_trans(v1[i].z), a3 = movmatrix_trans(v1[i].w);
+                const uint32_t a0 = movmatrix_trans(V0[i].z), a1 = movmatrix_trans(V0[i].w);
+                const uint32_t a2 = movmatrix_trans(V1[i].z), a3 = movmatrix_trans(V1[i].w);
                 mma_bf16(oacc[2 * i + 1], a0, a1, a2, a3, bh0, bh1);
                 mma_bf16(oacc[2 * i + 1], a0, a1, a2, a3, bl0, bl1);
             }
         }
+    };
+    constexpr bool kPipelined = WARPS == 4;
+    if (!FUSED && base0 < end) load_step(base0, k0, k1, v0, v1);  // fused: the first step was fetched above
+    if constexpr (kPipelined) {
+        uint4 kn0[4], kn1[4], vn0[4], vn1[4];
+        for (int base = base0; base < end; base += 2 * kBlk) {
+            const bool more = base + kBlk < end;
+            if (more) load_step(base + kBlk, kn0, kn1, vn0, vn1);
+            compute_step(base, k0, k1, v0, v1);
+            if (more) {
+                if (base + 2 * kBlk < end) load_step(base + 2 * kBlk, k0, k1, v0, v1);
+                compute_step(base + kBlk, kn0, kn1, vn0, vn1);
+            }
+        }
+    } else {
+        for (int base = base0; base < end; base += kBlk) {
+            if (base != base0) load_step(base, k0, k1, v0, v1);
+            compute_step(base, k0, k1, v0, v1);
+        }
     }
-
     flash_trace(5);
     // sums over all rows of the warp: the 8 lanes with this t hold different rows
 #pragma unroll
@@ -941,19 +969,28 @@ flash_decode_mma_kernel(const FlashParams p) {
         // ---- final combine by the last CTA (four warps, one thread per dimension, every head).  Weights first: warp w
         // takes heads w, w + 4, ...; lane l holds the (max, sum) of slices l and l + 32, so the maximum and the
         // denominator are two warp reductions; then the partial outputs in slice order, eight slices of every head in
-        // flight per thread (few registers: this variant runs five CTAs per SM).
-        __shared__ float s_w[64 * R];   // weight of slice sp for head h at [sp * R + h]
+        // flight per thread.
+        __shared__ float s_w[kMaxSplitsMma * R];   // weight of slice sp for head h at [sp * R + h]
         __shared__ float s_den[R];
+        constexpr int kPerLane = kMaxSplitsMma / 32;
         for (int h = warp; h < R; h += WARPS) {
-            float2 ml0 = make_float2(-INFINITY, 0.f), ml1 = ml0;
-            if (lane < n_active) ml0 = __ldcg(reinterpret_cast<const float2*>(pml + (size_t(lane) * R + h) * 2));
-            if (lane + 32 < n_active) ml1 = __ldcg(reinterpret_cast<const float2*>(pml + (size_t(lane + 32) * R + h) * 2));
-            const float nm = warp_max(fmaxf(ml0.x, ml1.x));
-            const float w0 = (ml0.x == -INFINITY) ? 0.f : __expf(ml0.x - nm);
-            const float w1 = (ml1.x == -INFINITY) ? 0.f : __expf(ml1.x - nm);
-            const float dsum = warp_sum(ml0.y * w0 + ml1.y * w1);
-            s_w[lane * R + h] = w0;
-            s_w[(lane + 32) * R + h] = w1;
+            float2 ml[kPerLane];
+            float nm = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kPerLane; i++) {
+                ml[i] = make_float2(-INFINITY, 0.f);
+                if (lane + 32 * i < n_active) ml[i] = __ldcg(reinterpret_cast<const float2*>(pml + (size_t(lane + 32 * i) * R + h) * 2));
+                nm = fmaxf(nm, ml[i].x);
+            }
+            nm = warp_max(nm);
+            float part = 0.f;
+#pragma unroll
+            for (int i = 0; i < kPerLane; i++) {
+                const float w = (ml[i].x == -INFINITY) ? 0.f : __expf(ml[i].x - nm);
+                part = fmaf(ml[i].y, w, part);
+                s_w[(lane + 32 * i) * R + h] = w;
+            }
+            const float dsum = warp_sum(part);
             if (lane == 0) s_den[h] = dsum;
         }
         __syncthreads();
@@ -987,14 +1024,23 @@ flash_decode_mma_kernel(const FlashParams p) {
 }
 
 
+// Upper bound of the slices per (row, kv head): 64; 128 for a few rows on the four-warp tensor-core kernel, where a
+// long context of one sequence would otherwise leave the SMs short of resident warps (the kernel hides memory latency
+// by occupancy: batch 1 at 32 768 rows streams 3.0 TB/s with 64 slices).
+int max_splits(int M, int rows_per_step, bool tensor_cores) {
+    return (tensor_cores && rows_per_step == 64 && M <= kFewRows) ? kMaxSplitsMma : kMaxSplits;
+}
+
 // rows per CTA step: 64 (four warps) or 128 (eight warps)
-int pick_splits(int M, int Nkv, int max_seq, int rows_per_step) {
+int pick_splits(int M, int Nkv, int max_seq, int rows_per_step, int ctas_per_sm, bool tensor_cores) {
     if (g_force_splits > 0) return g_force_splits;
     const int by_len = (max_seq + rows_per_step - 1) / rows_per_step;  // a slice is at least one step of the CTA
     int want = (device_sm_count() * 4 + M * Nkv - 1) / (M * Nkv);
+    const int cap = max_splits(M, rows_per_step, tensor_cores);
+    if (cap > kMaxSplits) want = device_sm_count() * ctas_per_sm / (M * Nkv);  // one full wave of the four-warp CTAs
     int s = want < by_len ? want : by_len;
     if (s < 1) s = 1;
-    if (s > 64) s = 64;
+    if (s > cap) s = cap;
     return s;
 }
 
@@ -1028,9 +1074,11 @@ extern "C" KUIPER_API int kuiper_flash_trace_read(int64_t* out, int max_values) 
 
 extern "C" size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq) {
     if (M <= 0 || Nq <= 0 || D <= 0 || max_seq <= 0) return 0;
-    const size_t S = 64;  // upper bound of pick_splits
-    return align256(size_t(M) * Nq * sizeof(int)) + align256(size_t(M) * Nq * S * D * sizeof(float)) +
-           align256(size_t(M) * Nq * S * 2 * sizeof(float));
+    // M rows at up to kMaxSplits slices, or the few rows that may use kMaxSplitsMma slices: whichever is larger
+    const size_t few = M < kFewRows ? size_t(M) : size_t(kFewRows);
+    const size_t slots = size_t(M) * kMaxSplits > few * kMaxSplitsMma ? size_t(M) * kMaxSplits : few * kMaxSplitsMma;
+    return align256(size_t(M) * Nq * sizeof(int)) + align256(slots * Nq * D * sizeof(float)) +
+           align256(slots * Nq * 2 * sizeof(float));
 }
 
 // argument checks, workspace carving and launch shared by the two entry points; `p` arrives with the tensors set
@@ -1048,7 +1096,7 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
     // last CTA of a kv head combines half as many slices; anything larger keeps the four-warp CTAs (more of them per SM)
     const bool wide = fused && g_flash_mma_fused && g_flash_wide &&
                       (long long)M * Nkv * ((max_seq + 127) / 128) <= 2ll * device_sm_count();
-    p.S = pick_splits(M, Nkv, max_seq, wide ? 128 : 64);
+    p.S = pick_splits(M, Nkv, max_seq, wide ? 128 : 64, fused ? kCtasFusedNarrow : kCtasStandalone, fused ? g_flash_mma_fused != 0 : g_flash_mma != 0);
     if (p.S > 1) {
         KUIPER_REQUIRE(workspace != nullptr, "flash_decode: split KV needs a workspace");
         KUIPER_REQUIRE(workspace_bytes >= kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq),
@@ -1057,7 +1105,7 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
         p.counters = reinterpret_cast<int*>(w);
         w += align256(size_t(M) * Nq * sizeof(int));
         p.part_o = reinterpret_cast<float*>(w);
-        w += align256(size_t(M) * Nq * 64 * D * sizeof(float));
+        w += align256(size_t(M) * Nq * p.S * D * sizeof(float));
         p.part_ml = reinterpret_cast<float*>(w);
     } else {
         p.counters = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
