@@ -363,6 +363,37 @@ def tp1_stream_check(cfg, ecfg, prompt, ids, device):
     return {"tokens_compared": len(ids), "matching_leading": matching, "tp1_margin_at_first_mismatch": margin}
 
 
+
+def _trace_stat(x):
+    return "min %.2f  median %.2f  p90 %.2f  max %.2f" % (x.min(), np.median(x), np.percentile(x, 90), x.max())
+
+
+def print_trace_summary(kind, trace, sm_mhz):
+    """Per-CTA timestamps of the measurement build (slot 0: global timer in ns at entry, slot 1: SM clock at entry, other
+    slots: SM clock at a milestone, 0 if not reached), summarised on stderr as microseconds since the CTA's entry and on
+    a common time axis.  Entries left from earlier launches (more than 30 us before the latest entry) are dropped."""
+    names = {"flash": {2: "early fetch issued", 3: "dependency wait passed", 4: "q ready", 5: "rows done",
+                       6: "partials visible", 7: "arrival counter answered", 8: "combine done", 9: "exit"},
+             "gemv": {8: "first weight unit issued", 6: "activation warp saw first descriptor", 2: "consumers past the wait",
+                      7: "first fragments written", 3: "first unit ready", 9: "last weight unit issued",
+                      4: "last unit consumed", 5: "consumer exit"}}[kind]
+    act = trace[trace[:, 1] != 0]
+    if len(act) == 0:
+        print(f"[{kind} trace] empty", file=sys.stderr)
+        return
+    act = act[act[:, 0] >= act[:, 0].max() - 30000]
+    t0 = act[:, 0].min()
+    per_us = sm_mhz  # SM cycles per microsecond
+    print(f"[{kind} trace] {len(act)} CTAs, SM clock {sm_mhz:.0f} MHz; entry spread (us): {_trace_stat((act[:, 0] - t0) / 1e3)}",
+          file=sys.stderr)
+    for slot, label in names.items():
+        w = act[(act[:, slot] > act[:, 1]) & (act[:, slot] < act[:, 1] + 1000 * per_us)]  # older launches' values dropped
+        if len(w) == 0:
+            continue
+        rel = (w[:, slot] - w[:, 1]) / per_us
+        print(f"[{kind} trace]   {label:38s} since entry: {_trace_stat(rel)} | common axis: {_trace_stat((w[:, 0] - t0) / 1e3 + rel)}  (n={len(w)})",
+              file=sys.stderr)
+
 def run_engine(args, cfg, prompt_len, desc, rank, world):
     import torch
     import torch.distributed as dist
@@ -455,6 +486,7 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         trace = np.zeros((1024, 10), np.int64)
         got = kernels().kuiper_flash_trace_read(trace.ctypes.data, trace.size)
         np.save(args.flash_trace, trace[: max(got, 0) // 10])
+        print_trace_summary("flash", trace[: max(got, 0) // 10], clocks.summary().get("sm_mhz") or 1965.0)
     ms = e0.elapsed_time(e1)
     t = torch.tensor([ms], device=device)
     if world > 1:
@@ -607,6 +639,7 @@ def run_gemv_micro(args):
         trace = np.zeros((304, 10), np.int64)
         kernels().kuiper_gemv_trace_read(trace.ctypes.data, trace.size)
         np.save(args.gemv_trace, trace)
+        print_trace_summary("gemv", trace, clocks.summary().get("sm_mhz") or 1965.0)
     ms = float(np.median(times))
     gbs = per * n / (ms * 1e-3) / 1e9
     peak, kind = measured_peak_gbs()

@@ -1037,7 +1037,9 @@ int pick_splits(int M, int Nkv, int max_seq, int rows_per_step, int ctas_per_sm,
     const int by_len = (max_seq + rows_per_step - 1) / rows_per_step;  // a slice is at least one step of the CTA
     int want = (device_sm_count() * 4 + M * Nkv - 1) / (M * Nkv);
     const int cap = max_splits(M, rows_per_step, tensor_cores);
-    if (cap > kMaxSplits) want = device_sm_count() * ctas_per_sm / (M * Nkv);  // one full wave of the four-warp CTAs
+    // the four-warp tensor-core CTAs are long-lived and few per SM: one wave of them, never a partial second one
+    // (batch 16 at 32 768 rows: 6.8 TB/s with 256 CTAs on 296 places, 5.7 TB/s with 640)
+    if (tensor_cores && rows_per_step == 64) want = device_sm_count() * ctas_per_sm / (M * Nkv);
     int s = want < by_len ? want : by_len;
     if (s < 1) s = 1;
     if (s > cap) s = cap;
