@@ -503,10 +503,15 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         tok = eng.decode_predict(tok)
     barrier()
     t0 = time.perf_counter()
+    marks = [t0]
     for _ in range(args.steps):
         tok = eng.decode_predict(tok)
+        marks.append(time.perf_counter())
     barrier()
     e2e_s = time.perf_counter() - t0
+    per_step_ms = np.diff(np.array(marks)) * 1e3  # spread of the host-side step times (the value uses the whole loop)
+    if os.environ.get("KUIPER_BENCH_VERBOSE"):
+        print("[e2e] per-step ms:", " ".join("%.3f" % v for v in per_step_ms), file=sys.stderr)
     if world > 1:
         eng.tp_status()
     t = torch.tensor([e2e_s], device=device)
@@ -534,7 +539,8 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
         "config": {"workload": desc if B == 1 else desc.replace("batch 1", f"batch {B}"), "batch": B, "prompt_tokens": prompt_tokens, "context_during_timing": ctx_mid,
                    "parallelism": f"tp{world}", "l2_policy": "inputs larger than L2 (weights streamed once per token)",
                    "prefill_s": round(prefill_s, 3), "greedy_ids_first32": ids, "tp1_stream_check": tp_parity},
-        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
+                "ms_per_step_min_median_max": [float(per_step_ms.min()), float(np.median(per_step_ms)), float(per_step_ms.max())]},
         "gpu_launches": eng.kernels_per_step * args.steps,
         "clocks": clocks.summary(),
         "decode_roofline": {"bytes_per_token_per_gpu": int(step_bytes), "tokens_per_s_at_peak": roof_tps,

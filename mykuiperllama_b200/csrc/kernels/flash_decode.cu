@@ -1037,9 +1037,9 @@ int pick_splits(int M, int Nkv, int max_seq, int rows_per_step, int ctas_per_sm,
     const int by_len = (max_seq + rows_per_step - 1) / rows_per_step;  // a slice is at least one step of the CTA
     int want = (device_sm_count() * 4 + M * Nkv - 1) / (M * Nkv);
     const int cap = max_splits(M, rows_per_step, tensor_cores);
-    // the four-warp tensor-core CTAs are long-lived and few per SM: one wave of them, never a partial second one
+    // the tensor-core CTAs are long-lived and few per SM: one wave of them, never a partial second one
     // (batch 16 at 32 768 rows: 6.8 TB/s with 256 CTAs on 296 places, 5.7 TB/s with 640)
-    if (tensor_cores && rows_per_step == 64) want = device_sm_count() * ctas_per_sm / (M * Nkv);
+    if (tensor_cores) want = device_sm_count() * ctas_per_sm / (M * Nkv);
     int s = want < by_len ? want : by_len;
     if (s < 1) s = 1;
     if (s > cap) s = cap;
@@ -1094,11 +1094,13 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
     KUIPER_REQUIRE(R == 1 || R == 2 || R == 4 || R == 8, "flash_decode: group size %d is not supported", R);
     p.M = M; p.Nq = Nq; p.Nkv = Nkv; p.max_seq = max_seq; p.n_slots = n_slots;
     p.fresh_rows = g_flash_early ? fresh_rows : -1;
-    // one sequence (or a few) at a context of a few thousand rows: eight-warp CTAs, one 128-row step each, so that the
-    // last CTA of a kv head combines half as many slices; anything larger keeps the four-warp CTAs (more of them per SM)
-    const bool wide = fused && g_flash_mma_fused && g_flash_wide &&
-                      (long long)M * Nkv * ((max_seq + 127) / 128) <= 2ll * device_sm_count();
-    p.S = pick_splits(M, Nkv, max_seq, wide ? 128 : 64, fused ? kCtasFusedNarrow : kCtasStandalone, fused ? g_flash_mma_fused != 0 : g_flash_mma != 0);
+    // one sequence (or a few) at a context of a few thousand rows: eight-warp CTAs, one per SM, one or two 128-row steps
+    // each, so that the last CTA of a kv head combines half as many slices; anything larger keeps the four-warp CTAs
+    const long long wide_slices = device_sm_count() / ((long long)M * Nkv);  // one CTA per SM, a single wave
+    const bool wide = fused && g_flash_mma_fused && g_flash_wide && wide_slices >= 8 &&
+                      (max_seq + 127) / 128 <= 2 * wide_slices;
+    p.S = pick_splits(M, Nkv, max_seq, wide ? 128 : 64, !fused ? kCtasStandalone : wide ? 1 : kCtasFusedNarrow,
+                      fused ? g_flash_mma_fused != 0 : g_flash_mma != 0);
     if (p.S > 1) {
         KUIPER_REQUIRE(workspace != nullptr, "flash_decode: split KV needs a workspace");
         KUIPER_REQUIRE(workspace_bytes >= kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq),
