@@ -1033,10 +1033,10 @@ int max_splits(int M, int rows_per_step, bool tensor_cores) {
 
 // rows per CTA step: 64 (four warps) or 128 (eight warps)
 int pick_splits(int M, int Nkv, int max_seq, int rows_per_step, int ctas_per_sm, bool tensor_cores) {
-    if (g_force_splits > 0) return g_force_splits;
+    const int cap = max_splits(M, rows_per_step, tensor_cores);
+    if (g_force_splits > 0) return g_force_splits < cap ? g_force_splits : cap;
     const int by_len = (max_seq + rows_per_step - 1) / rows_per_step;  // a slice is at least one step of the CTA
     int want = (device_sm_count() * 4 + M * Nkv - 1) / (M * Nkv);
-    const int cap = max_splits(M, rows_per_step, tensor_cores);
     // the tensor-core CTAs are long-lived and few per SM: one wave of them, never a partial second one
     // (batch 16 at 32 768 rows: 6.8 TB/s with 256 CTAs on 296 places, 5.7 TB/s with 640)
     if (tensor_cores) want = device_sm_count() * ctas_per_sm / (M * Nkv);

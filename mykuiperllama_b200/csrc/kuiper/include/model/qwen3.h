@@ -68,6 +68,9 @@ public:
 
     // copy of the last pass's logits [M, vocab] to the host (synchronises)
     base::Status read_logits(float* out, int32_t M);
+    // waits for everything enqueued on the model's stream, then reports a tensor-parallel exchange or a kernel
+    // pipeline whose bounded wait ran out since the last check
+    base::Status synchronize();
     // number of kernels one decode step launches
     int32_t kernels_per_step() const { return kernels_per_step_; }
 
@@ -79,6 +82,7 @@ private:
     base::Status ensure_graph(int32_t B);
     base::Status check_loaded() const;
     base::Status check_exchange() const;
+    base::Status check_kernels() const;
 
     int32_t local_heads() const { return config_.head_num / config_.tp_size; }
     int32_t local_kv_heads() const { return config_.kv_head_num / config_.tp_size; }

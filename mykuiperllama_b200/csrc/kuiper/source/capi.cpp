@@ -162,9 +162,7 @@ void* kuiper_model_stream(kuiper_model* model) { return model ? as_model(model)-
 
 int kuiper_model_synchronize(kuiper_model* model) {
     if (!model) return fail(base::error::invalid_argument("null model"));
-    cudaError_t err = cudaStreamSynchronize(as_model(model)->stream());
-    if (err != cudaSuccess) return fail(base::error::internal_error(cudaGetErrorString(err)));
-    return 0;
+    return done(as_model(model)->synchronize());
 }
 
 }  // extern "C"

@@ -690,6 +690,20 @@ base::Status Qwen3Model::check_exchange() const {
     return base::error::success();
 }
 
+// The pipelined GEMV and the tcgen05 GEMM bound every mbarrier wait and record a word on the device when one runs out
+// (their results are void then).  Reading the words costs two small synchronous copies, so this runs where the caller
+// already pays for a synchronisation that is not on the per-token path: after a prefill, in decode_read and synchronize.
+base::Status Qwen3Model::check_kernels() const {
+    if (kuiper_awq_gemv_status() != 0 || kuiper_awq_gemm_status() != 0) return base::error::internal_error(kuiper_last_error());
+    return base::error::success();
+}
+
+base::Status Qwen3Model::synchronize() {
+    CUDA_OK(cudaStreamSynchronize(stream()));
+    RETURN_IF_ERROR(check_exchange());
+    return check_kernels();
+}
+
 base::Status Qwen3Model::forward(const int32_t* tokens, const int32_t* pos, const int32_t* slot, int32_t M) {
     RETURN_IF_ERROR(check_loaded());
     if (!tokens || !pos || !slot) return base::error::invalid_argument("null input pointer");
@@ -732,8 +746,7 @@ base::Status Qwen3Model::prefill(const int32_t* tokens, int32_t n, int32_t slot,
             *next = host_stage_[0];
         }
     }
-    CUDA_OK(cudaStreamSynchronize(stream()));
-    return check_exchange();
+    return synchronize();
 }
 
 // ------------------------------------------------------------------ graph decode loop
@@ -816,8 +829,7 @@ base::Status Qwen3Model::decode_read(int32_t* tokens, int32_t B) {
     if (!tokens || B <= 0 || B > config_.max_rows) return base::error::invalid_argument("bad read request");
     CUDA_OK(cudaMemcpyAsync(host_stage_, get_buffer(ModelBufferType::NextTokens).ptr<void>(), size_t(B) * 4,
                             cudaMemcpyDeviceToHost, stream()));
-    CUDA_OK(cudaStreamSynchronize(stream()));
-    RETURN_IF_ERROR(check_exchange());
+    RETURN_IF_ERROR(synchronize());
     std::memcpy(tokens, host_stage_, size_t(B) * 4);
     return base::error::success();
 }

@@ -684,6 +684,28 @@ def test_flash_decode_batch16_and_32k(cuda, oracle, name, tensor_cores):
     assert err <= SPEC_TOL and err <= (5e-5 if tensor_cores else 1e-5)
 
 
+@pytest.mark.parametrize("splits", [65, 100, 128])
+def test_flash_decode_more_than_64_slices(cuda, oracle, splits):
+    # calls of one or two rows may be cut into up to 128 slices per kv head (tensor-core kernel): the combining CTA then
+    # holds four (max, sum) pairs per lane
+    rng = np.random.default_rng(splits)
+    B, Nq, Nkv, D, L = 2, 32, 8, 128, 9000
+    q = rng.standard_normal((B, Nq, D)).astype(np.float32)
+    kc = oracle.f32_to_bf16(rng.standard_normal((B, Nkv, L, D)).astype(np.float32))
+    vc = oracle.f32_to_bf16(rng.standard_normal((B, Nkv, L, D)).astype(np.float32))
+    seq = np.array([L, 8321], np.int32)
+    slot = np.arange(B, dtype=np.int32)
+    ref = oracle.attention(q, kc, vc, seq, slot)
+    ws = cuda.flash_decode_workspace(B, Nq, D, L)
+    cuda.set_tuning("flash_splits", splits)
+    try:
+        out = cuda.flash_decode(dev(q), dev(kc, torch.bfloat16), dev(vc, torch.bfloat16), dev(seq), dev(slot), workspace=ws).cpu().numpy()
+    finally:
+        cuda.set_tuning("flash_splits", 0)
+    err = rel_err(out, ref)
+    assert err <= SPEC_TOL and err <= 5e-5
+
+
 def test_flash_decode_early_fetch_matches_conservative_path(cuda, oracle):
     # fresh_rows = F lets the kernel read cache rows below seq_len - F before the previous kernel has finished;
     # on a static cache both paths must give the same bits
@@ -707,13 +729,18 @@ def test_flash_decode_early_fetch_matches_conservative_path(cuda, oracle):
             cuda.set_tuning("flash_mma", FLASH_MMA_DEFAULT)
 
 
-@pytest.mark.parametrize("Nq,Nkv,lens", [(32, 8, [2084, 1, 700]), (16, 8, [65, 64]), (8, 8, [130]), (32, 8, [2084]), (32, 8, [2048, 129]),
-                                         (64, 8, [1000])])
-def test_rope_fused_into_flash_decode_is_bit_identical(cuda, oracle, Nq, Nkv, lens):
+@pytest.mark.parametrize("Nq,Nkv,lens,Lmax", [
+    (32, 8, [2084, 1, 700], 2100), (16, 8, [65, 64], 2100), (8, 8, [130], 2100), (32, 8, [2084], 2100),
+    (32, 8, [2048, 129], 2100), (64, 8, [1000], 2100),
+    (32, 8, [4400], 4500),               # one sequence, eight-warp CTAs with two steps each
+    (32, 8, [2305, 2304], 2400),         # two sequences, eight-warp CTAs, slices of uneven length
+    (32, 8, [8200, 300, 5000], 9000),    # four-warp CTAs, many steps per slice (two register sets in flight)
+    (32, 8, [20000], 20100)])            # one sequence past the eight-warp range: four-warp CTAs, one wave of slices
+def test_rope_fused_into_flash_decode_is_bit_identical(cuda, oracle, Nq, Nkv, lens, Lmax):
     # decode batch: one row per slot, seq_len = pos + 1; the fused kernel must reproduce the two-kernel path bit for bit,
     # caches included, and may clear the raw projection rows and a side buffer
     rng = np.random.default_rng(31 + Nq)
-    B, D, Lmax = len(lens), 128, 2100
+    B, D = len(lens), 128
     kc = torch.randn((B, Nkv, Lmax, D), device="cuda").bfloat16()
     vc = torch.randn((B, Nkv, Lmax, D), device="cuda").bfloat16()
     kc2, vc2 = kc.clone(), vc.clone()

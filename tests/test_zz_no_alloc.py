@@ -70,3 +70,30 @@ def test_noalloc_entry_rejects_sizes_beyond_its_scratch(cuda):
     assert b"exceeds" in lib.kuiper_last_error()
     assert lib.kuiper_awq_gemv_f32_noalloc(*args, None, 9, 128, 1024, 128, None) == 7         # more than 8 rows
     assert lib.kuiper_awq_gemv_f32_noalloc(*args, None, 1, 128, 1000, 128, None) == 7         # N % 32 != 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_noalloc_entry_on_a_second_device(cuda, oracle):
+    # the scratch address, the shared-memory attribute of the kernel and the SM count are kept per device: a call on
+    # device 1 after device 0 has been used must configure device 1 on its own
+    from mykuiperllama_b200._lib import check, kernels
+    lib = kernels()
+    rng = np.random.default_rng(77)
+    M, K, N = 2, 1024, 4096
+    q, z, s = awq_random(rng, K, N)
+    xh = rng.standard_normal((M, K)).astype(np.float32)
+    ref = oracle.awq_gemv(xh, oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16), acc_double=True,
+                          act_round=oracle.ROUND_FP16).astype(np.float64)
+    for device in (0, 1, 0):
+        with torch.cuda.device(device):
+            dev = f"cuda:{device}"
+            qw = torch.from_numpy(oracle.awq_pack(q)).to(dev)
+            qz = torch.from_numpy(oracle.awq_pack(z)).to(dev)
+            sc = torch.from_numpy(s.view(np.uint16).copy()).to(dev).view(torch.float16)
+            x = torch.from_numpy(xh).to(dev)
+            y = torch.full((M, N), float("nan"), device=dev)
+            stream = torch.cuda.current_stream().cuda_stream
+            check(lib.kuiper_awq_gemv_f32_noalloc(x.data_ptr(), qw.data_ptr(), qz.data_ptr(), sc.data_ptr(), y.data_ptr(),
+                                                  None, M, K, N, 128, stream))
+            torch.cuda.synchronize()
+            assert rel_err(y.cpu().numpy(), ref) <= 2e-6, device
