@@ -258,8 +258,8 @@ KUIPER_API int kuiper_qknorm_rope_kvwrite(float* qkv, const uint16_t* q_norm_w, 
  * out[m,h,:] = softmax(q[m,h,:].K^T / sqrt(D)) . V over cache positions [0, seq_len[m]) of
  * sequence slot[m]; q head h reads kv head h / (Nq/Nkv).  The KV range is split across
  * CTAs and the partial (max, sum, out) triples are merged with a log-sum-exp combine.
- * workspace: kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq) bytes, counters zeroed once
- * with kuiper_workspace_init.  D must be 128, Nq/Nkv in {1,2,4,8}.
+ * workspace: kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq) bytes, all of it zeroed once
+ * with kuiper_workspace_init (arrival counters, launch numbers and tagged words start from zero).  D must be 128, Nq/Nkv in {1,2,4,8}.
  * fresh_rows: -1 = the kernel touches nothing before the stream's previous kernel has completed.
  * fresh_rows = F >= 0 is a promise by the caller: seq_len, slot and every cache row below
  * seq_len[m] - F were final before the previous kernel on the stream started (that kernel appended
@@ -270,6 +270,9 @@ KUIPER_API int kuiper_qknorm_rope_kvwrite(float* qkv, const uint16_t* q_norm_w, 
  * ~1e-5; fresh_rows is accepted and ignored), kuiper_set_tuning("flash_mma", 0) selects the SIMT kernel.
  */
 KUIPER_API size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq);
+/* health check (synchronises): 5 if the bounded wait of a combining CTA (fused decode kernel) ran out on this device
+ * since the last call (the outputs of that launch are zeros) */
+KUIPER_API int kuiper_flash_decode_status(void);
 KUIPER_API int kuiper_flash_decode(const float* q, const uint16_t* kcache, const uint16_t* vcache,
                         const int32_t* seq_len, const int32_t* slot, float* out,
                         int M, int Nq, int Nkv, int D, int max_seq, int n_slots, int fresh_rows,

@@ -62,6 +62,7 @@ KERNEL_API = {
     "kuiper_qknorm_rope_kvwrite": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _i32,
                                           _vp, _vp, _vp, _i32, _vp, _i64, _vp]),
     "kuiper_flash_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32]),
+    "kuiper_flash_decode_status": (_i32, []),
     "kuiper_flash_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "kuiper_flash_prefill": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_rope_flash_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32,

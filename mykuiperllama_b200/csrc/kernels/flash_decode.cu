@@ -29,6 +29,18 @@ constexpr int kCtasStandalone = 2, kCtasFusedNarrow = 2;  // resident CTAs per S
 constexpr int kRowsPerStep = 8;  // row slots per half warp per step
 
 int g_force_splits = 0;
+int g_flash_drop_slice = -1;  // tuning key "flash_drop_slice" (tests only)
+long long g_flash_timeout_ns = 1000000000ll;  // bound of the combining CTA's wait for the other slices (tuning key "flash_timeout_ms")
+__device__ int g_flash_wait_error = 0;
+
+__device__ __forceinline__ void st_tagged(uint2* p, float v, unsigned int tag) {
+    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_tagged(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.relaxed.gpu.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
 int g_flash_early = 1;  // 0: ignore fresh_rows, touch nothing before the dependent-launch wait
 int g_flash_mma_fused = 1;  // the fused decode kernel (rotary + append + attention) also uses the tensor cores (0: SIMT)
 int g_flash_mma = 1;    // the stand-alone attention call runs its contractions on the tensor cores (0: SIMT kernel)
@@ -62,6 +74,12 @@ struct FlashParams {
     float* part_o;        // [M, Nkv, S, R, 128]
     float* part_ml;       // [M, Nkv, S, R, 2]
     int* counters;        // [M * Nkv]
+    // eight-warp CTAs: the partials travel as 8-byte words {value, launch number} that the combining CTA polls
+    uint2* ll_o;          // [M, Nkv, S, R, 128]
+    uint2* ll_ml;         // [M, Nkv, S, R, 2]
+    unsigned int* ll_seq; // [M * Nkv] launch number of the last combine
+    long long ll_timeout_ns;
+    int ll_drop;          // test hook: this slice never sends its words (-1: none), so that the bounded wait can be exercised
     int M, Nq, Nkv, max_seq, n_slots, S;
     int fresh_rows;       // cache rows >= seq_len - fresh_rows may still be in flight from the previous kernel; < 0: all
     // fused rotary prologue (FUSED kernels): q and the newest K / V row are produced here from the raw projection
@@ -532,6 +550,7 @@ flash_decode_mma_kernel(const FlashParams p) {
     __shared__ float s_ml[WARPS][R][2];
     __shared__ __align__(16) uint16_t s_new[FUSED ? 2 : 1][kD];  // fused: the K / V row appended by this CTA
     __shared__ int s_last;
+    __shared__ unsigned int s_tag;
 
     const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -540,6 +559,13 @@ flash_decode_mma_kernel(const FlashParams p) {
     flash_trace(0);
     flash_trace(1);
     pdl_launch_dependents();
+    if (WARPS == 8 && threadIdx.x == 0 && p.ll_seq != nullptr) {
+        // launch number of this (row, kv head): last written by the combining CTA of the previous attention launch, which
+        // completed long ago (a whole layer lies between two attention launches)
+        unsigned int seq;
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seq) : "l"(p.ll_seq + m * p.Nkv + kvh) : "memory");
+        s_tag = seq + 1u == 0u ? 1u : seq + 1u;
+    }
     // fused: rows older than this pass are fetched ahead of the dependency wait, exactly as in the SIMT kernel
     // (fresh_rows, re-check of seq_len / slot after the wait); the stand-alone call waits first
     bool waited = !FUSED || p.fresh_rows < 0;
@@ -900,6 +926,99 @@ flash_decode_mma_kernel(const FlashParams p) {
     }
 
     const size_t pbase = (size_t(m) * p.Nkv + kvh) * p.S;
+    if constexpr (WARPS == 8) {
+        // ---- eight-warp CTAs: no arrival counter.  Every partial value travels as one 8-byte word {value, launch
+        // number}; the CTA of the last slice (the one that also appends the new row, so the slowest) polls the words of
+        // the other slices: a word that carries this launch's number is complete, because an aligned 8-byte store is
+        // one transaction - no fence, no atomic, no second trip for the data.  Slice order and a common maximum per
+        // head keep the summation order fixed.  The wait is bounded by the wall clock.
+        const unsigned int tag = s_tag;  // written before the barrier after the prologue
+        uint2* llo = p.ll_o + pbase * R * kD + d;
+        uint2* llm = p.ll_ml + pbase * R * 2;
+        if (split != n_active - 1) {
+            if (split == p.ll_drop) return;
+#pragma unroll
+            for (int j = 0; j < HP; j++) {
+                const int h = hh + j * HS;
+                if (h < R) {
+                    st_tagged(llo + (size_t(split) * R + h) * kD, fo[j], tag);
+                    if (d == 0) {
+                        st_tagged(llm + (size_t(split) * R + h) * 2, fm[j], tag);
+                        st_tagged(llm + (size_t(split) * R + h) * 2 + 1, fs[j], tag);
+                    }
+                }
+            }
+            flash_trace(6);
+            return;
+        }
+        constexpr int kSlices = 20;  // upper bound of n_active here: one CTA per SM and at least 8 slices per kv head
+        float acc[HP], den[HP];
+        const long long t0 = (long long)globaltimer_ns();
+        bool complete = false, gave_up = false;
+        uint2 wo[kSlices][HP];
+        uint2 wm[HP], wl[HP];  // lane l: (max, sum) of slice l for this thread's heads
+        while (true) {
+            bool ok = true;
+#pragma unroll
+            for (int q = 0; q < kSlices; q++)
+#pragma unroll
+                for (int j = 0; j < HP; j++) {
+                    const int h = hh + j * HS;
+                    const bool remote = q < n_active - 1 && h < R;
+                    wo[q][j] = remote ? ld_tagged(llo + (size_t(q) * R + h) * kD) : make_uint2(0u, tag);
+                }
+#pragma unroll
+            for (int j = 0; j < HP; j++) {
+                const int h = hh + j * HS;
+                const bool remote = lane < n_active - 1 && h < R;
+                wm[j] = remote ? ld_tagged(llm + (size_t(lane) * R + h) * 2) : make_uint2(0u, tag);
+                wl[j] = remote ? ld_tagged(llm + (size_t(lane) * R + h) * 2 + 1) : make_uint2(0u, tag);
+                ok = ok && wm[j].y == tag && wl[j].y == tag;
+            }
+#pragma unroll
+            for (int q = 0; q < kSlices; q++)
+#pragma unroll
+                for (int j = 0; j < HP; j++) ok = ok && wo[q][j].y == tag;
+            complete = __syncthreads_and(ok ? 1 : 0) != 0;
+            if (complete) break;
+            if ((long long)globaltimer_ns() - t0 > p.ll_timeout_ns) gave_up = true;
+            if (__syncthreads_or(gave_up ? 1 : 0)) {
+                if (threadIdx.x == 0) atomicExch(&g_flash_wait_error, 1);
+                break;
+            }
+        }
+        flash_trace(7);
+#pragma unroll
+        for (int j = 0; j < HP; j++) {
+            const int h = hh + j * HS;
+            // lane l holds slice l (l < n_active - 1) or this CTA's own slice (l == n_active - 1)
+            float ml_m = -INFINITY, ml_l = 0.f;
+            if (lane < n_active - 1) { ml_m = __uint_as_float(wm[j].x); ml_l = __uint_as_float(wl[j].x); }
+            if (lane == n_active - 1) { ml_m = fm[j]; ml_l = fs[j]; }
+            if (!complete || h >= R) { ml_m = -INFINITY; ml_l = 0.f; }
+            const float gm = warp_max(ml_m);
+            const float w = (ml_m == -INFINITY) ? 0.f : __expf(ml_m - gm);
+            den[j] = warp_sum(ml_l * w);
+            float a = 0.f;
+#pragma unroll
+            for (int q = 0; q < kSlices; q++) {
+                const float wq = __shfl_sync(0xffffffffu, w, q);
+                const float v = q < n_active - 1 ? __uint_as_float(wo[q][j].x) : (q == n_active - 1 ? fo[j] : 0.f);
+                a = fmaf(v, wq, a);
+            }
+            acc[j] = a;
+        }
+        flash_trace(8);
+#pragma unroll
+        for (int j = 0; j < HP; j++) {
+            const int h = hh + j * HS;
+            if (h < R) p.out[(size_t(m) * p.Nq + kvh * R + h) * kD + d] = den[j] > 0.f ? acc[j] / den[j] : 0.f;
+        }
+        if (threadIdx.x == 0) p.ll_seq[m * p.Nkv + kvh] = tag;
+        clear_raw();
+        flash_trace(9);
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < HP; j++) {
         const int h = hh + j * HS;
@@ -927,45 +1046,7 @@ flash_decode_mma_kernel(const FlashParams p) {
     for (int j = 0; j < HP; j++) { acc[j] = 0.f; den[j] = 0.f; }
     const float* po = p.part_o + pbase * R * kD + d;
     const float* pml = p.part_ml + pbase * R * 2;
-    if constexpr (WARPS == 8) {
-        // ---- final combine by the last CTA, in slice order.  Every load is independent of every other (the slice weights
-        // come from the (max, sum) pairs, the sums from the partial outputs), so they are all issued before the first
-        // use: one trip to the L2 for up to kInFlight slices (each thread serves two heads, so 20 slices fit registers).
-        constexpr int kInFlight = 20;
-        float gmax[HP];
-#pragma unroll
-        for (int j = 0; j < HP; j++) gmax[j] = -INFINITY;
-        for (int sp0 = 0; sp0 < n_active; sp0 += kInFlight) {
-            float2 ml[kInFlight][HP];
-            float a[kInFlight][HP];
-#pragma unroll
-            for (int q = 0; q < kInFlight; q++)
-#pragma unroll
-                for (int j = 0; j < HP; j++) {
-                    const int h = hh + j * HS;
-                    const bool ok = sp0 + q < n_active && h < R;
-                    ml[q][j] = ok ? __ldcg(reinterpret_cast<const float2*>(pml + (size_t(sp0 + q) * R + h) * 2)) : make_float2(-INFINITY, 0.f);
-                    a[q][j] = ok ? __ldcg(po + (size_t(sp0 + q) * R + h) * kD) : 0.f;
-                }
-#pragma unroll
-            for (int j = 0; j < HP; j++) {
-                float bm = gmax[j];
-#pragma unroll
-                for (int q = 0; q < kInFlight; q++) bm = fmaxf(bm, ml[q][j].x);
-                // rescale what was accumulated under the previous maximum (slice order is kept: a fixed summation order)
-                const float c = (gmax[j] == -INFINITY) ? 0.f : __expf(gmax[j] - bm);
-                acc[j] *= c;
-                den[j] *= c;
-                gmax[j] = bm;
-#pragma unroll
-                for (int q = 0; q < kInFlight; q++) {
-                    const float w = (ml[q][j].x == -INFINITY) ? 0.f : __expf(ml[q][j].x - bm);
-                    acc[j] = fmaf(a[q][j], w, acc[j]);
-                    den[j] = fmaf(ml[q][j].y, w, den[j]);
-                }
-            }
-        }
-    } else {
+    {
         // ---- final combine by the last CTA (four warps, one thread per dimension, every head).  Weights first: warp w
         // takes heads w, w + 4, ...; lane l holds the (max, sum) of slices l and l + 32, so the maximum and the
         // denominator are two warp reductions; then the partial outputs in slice order, eight slices of every head in
@@ -1048,10 +1129,20 @@ int pick_splits(int M, int Nkv, int max_seq, int rows_per_step, int ctas_per_sm,
 
 size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
+// Tagged-word area of the eight-warp CTAs at the end of the workspace: at most one CTA per SM, so at most SMs slices of
+// up to 8 heads each are in flight; launch numbers: one per (row, kv head) <= SMs.
+constexpr int kWideMaxSlices = 20;  // slices per (row, kv head) the combining CTA of the eight-warp kernel can poll
+size_t ll_o_bytes() { return align256(size_t(device_sm_count()) * 8 * kD * sizeof(uint2)); }
+size_t ll_ml_bytes() { return align256(size_t(device_sm_count()) * 8 * 2 * sizeof(uint2)); }
+size_t ll_seq_bytes() { return align256(size_t(device_sm_count()) * sizeof(unsigned int)); }
+size_t ll_area_bytes() { return ll_o_bytes() + ll_ml_bytes() + ll_seq_bytes(); }
+
 }  // namespace
 
 void flash_decode_set_tuning(const char* key, int value) {
     if (!strcmp(key, "flash_splits")) g_force_splits = value;
+    if (!strcmp(key, "flash_drop_slice")) g_flash_drop_slice = value;
+    if (!strcmp(key, "flash_timeout_ms")) g_flash_timeout_ns = (long long)(value < 1 ? 1 : value) * 1000000ll;
     if (!strcmp(key, "flash_early")) g_flash_early = value;
     if (!strcmp(key, "flash_mma")) g_flash_mma = value;
     if (!strcmp(key, "flash_mma_fused")) g_flash_mma_fused = value;
@@ -1074,13 +1165,23 @@ extern "C" KUIPER_API int kuiper_flash_trace_read(int64_t* out, int max_values) 
 }
 #endif
 
+extern "C" int kuiper_flash_decode_status(void) {
+    int v = 0;
+    const int zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_flash_wait_error, sizeof(int)) != cudaSuccess) v = -1;
+    if (v == 0) return KUIPER_OK;
+    cudaMemcpyToSymbol(g_flash_wait_error, &zero, sizeof(int));  // reported once
+    set_error("flash_decode: the combining CTA's bounded wait for the other slices ran out (code %d)", v);
+    return KUIPER_INTERNAL_ERROR;
+}
+
 extern "C" size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq) {
     if (M <= 0 || Nq <= 0 || D <= 0 || max_seq <= 0) return 0;
     // M rows at up to kMaxSplits slices, or the few rows that may use kMaxSplitsMma slices: whichever is larger
     const size_t few = M < kFewRows ? size_t(M) : size_t(kFewRows);
     const size_t slots = size_t(M) * kMaxSplits > few * kMaxSplitsMma ? size_t(M) * kMaxSplits : few * kMaxSplitsMma;
     return align256(size_t(M) * Nq * sizeof(int)) + align256(slots * Nq * D * sizeof(float)) +
-           align256(slots * Nq * 2 * sizeof(float));
+           align256(slots * Nq * 2 * sizeof(float)) + ll_area_bytes();
 }
 
 // argument checks, workspace carving and launch shared by the two entry points; `p` arrives with the tensors set
@@ -1096,11 +1197,13 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
     p.fresh_rows = g_flash_early ? fresh_rows : -1;
     // one sequence (or a few) at a context of a few thousand rows: eight-warp CTAs, one per SM, one or two 128-row steps
     // each, so that the last CTA of a kv head combines half as many slices; anything larger keeps the four-warp CTAs
-    const long long wide_slices = device_sm_count() / ((long long)M * Nkv);  // one CTA per SM, a single wave
+    long long wide_slices = device_sm_count() / ((long long)M * Nkv);  // one CTA per SM, a single wave
+    if (wide_slices > kWideMaxSlices) wide_slices = kWideMaxSlices;
     const bool wide = fused && g_flash_mma_fused && g_flash_wide && wide_slices >= 8 &&
                       (max_seq + 127) / 128 <= 2 * wide_slices;
     p.S = pick_splits(M, Nkv, max_seq, wide ? 128 : 64, !fused ? kCtasStandalone : wide ? 1 : kCtasFusedNarrow,
                       fused ? g_flash_mma_fused != 0 : g_flash_mma != 0);
+    if (wide && p.S > kWideMaxSlices) p.S = kWideMaxSlices;
     if (p.S > 1) {
         KUIPER_REQUIRE(workspace != nullptr, "flash_decode: split KV needs a workspace");
         KUIPER_REQUIRE(workspace_bytes >= kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq),
@@ -1111,8 +1214,16 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
         p.part_o = reinterpret_cast<float*>(w);
         w += align256(size_t(M) * Nq * p.S * D * sizeof(float));
         p.part_ml = reinterpret_cast<float*>(w);
+        // the tagged-word area sits at the very end of the workspace, where the other layouts never write
+        char* ll = reinterpret_cast<char*>(workspace) + kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq) - ll_area_bytes();
+        p.ll_o = reinterpret_cast<uint2*>(ll);
+        p.ll_ml = reinterpret_cast<uint2*>(ll + ll_o_bytes());
+        p.ll_seq = reinterpret_cast<unsigned int*>(ll + ll_o_bytes() + ll_ml_bytes());
+        p.ll_timeout_ns = g_flash_timeout_ns;
+        p.ll_drop = g_flash_drop_slice;
     } else {
         p.counters = nullptr; p.part_o = nullptr; p.part_ml = nullptr;
+        p.ll_o = nullptr; p.ll_ml = nullptr; p.ll_seq = nullptr; p.ll_timeout_ns = 0; p.ll_drop = -1;
     }
 
     cudaLaunchConfig_t cfg = {};

@@ -690,11 +690,12 @@ base::Status Qwen3Model::check_exchange() const {
     return base::error::success();
 }
 
-// The pipelined GEMV and the tcgen05 GEMM bound every mbarrier wait and record a word on the device when one runs out
+// The pipelined GEMV, the tcgen05 GEMM and the fused attention kernel bound every wait and record a word on the device when one runs out
 // (their results are void then).  Reading the words costs two small synchronous copies, so this runs where the caller
 // already pays for a synchronisation that is not on the per-token path: after a prefill, in decode_read and synchronize.
 base::Status Qwen3Model::check_kernels() const {
-    if (kuiper_awq_gemv_status() != 0 || kuiper_awq_gemm_status() != 0) return base::error::internal_error(kuiper_last_error());
+    if (kuiper_awq_gemv_status() != 0 || kuiper_awq_gemm_status() != 0 || kuiper_flash_decode_status() != 0)
+        return base::error::internal_error(kuiper_last_error());
     return base::error::success();
 }
 

@@ -843,3 +843,42 @@ def test_flash_prefill_rejects_bad_arguments(cuda):
     with pytest.raises(KuiperError) as e:
         cuda.flash_prefill(q, kc, kc, 0, 1)    # slot out of range
     assert e.value.code == 7
+
+
+def test_rope_flash_decode_combine_wait_is_bounded(cuda, oracle):
+    # eight-warp CTAs: the CTA of the last slice polls the other slices' words.  A slice that never sends (test hook) makes
+    # the wait run out after the limit: the call returns, the status reports it once, and the next call is correct again
+    from mykuiperllama_b200._lib import kernels
+    lib = kernels()
+    rng = np.random.default_rng(5)
+    Nq, Nkv, D, Lmax, L = 32, 8, 128, 2100, 1500
+    kc = torch.randn((1, Nkv, Lmax, D), device="cuda").bfloat16()
+    vc = torch.randn((1, Nkv, Lmax, D), device="cuda").bfloat16()
+    qkv = dev(rng.standard_normal((1, (Nq + 2 * Nkv) * D)).astype(np.float32))
+    qn = dev(oracle.f32_to_bf16(np.ones(D, np.float32)))
+    kn = dev(oracle.f32_to_bf16(np.ones(D, np.float32)))
+    cos_t, sin_t = (dev(t) for t in oracle.rope_tables(Lmax, D, 1e6))
+    seq, pos, slot = dev(np.array([L], np.int32)), dev(np.array([L - 1], np.int32)), dev(np.zeros(1, np.int32))
+    ws = cuda.flash_decode_workspace(1, Nq, D, Lmax)
+
+    def run():
+        out = cuda.rope_flash_decode(qkv.clone(), qn, kn, cos_t, sin_t, pos, seq, slot, Nq, Nkv, D, 1e-6, kc.clone(), vc.clone(),
+                                     workspace=ws, fresh_rows=1)
+        torch.cuda.synchronize()
+        return out
+
+    assert lib.kuiper_flash_decode_status() == 0
+    good = run()
+    cuda.set_tuning("flash_timeout_ms", 50)
+    cuda.set_tuning("flash_drop_slice", 3)
+    try:
+        run()
+        assert lib.kuiper_flash_decode_status() == 5
+        assert b"bounded wait" in lib.kuiper_last_error()
+        assert lib.kuiper_flash_decode_status() == 0  # reported once
+    finally:
+        cuda.set_tuning("flash_drop_slice", -1)
+        cuda.set_tuning("flash_timeout_ms", 1000)
+    again = run()
+    assert torch.equal(again, good)
+    assert lib.kuiper_flash_decode_status() == 0
