@@ -579,6 +579,33 @@ flash_decode_mma_kernel(const FlashParams p) {
     // rotary row of position seq_len - 1, also fetched ahead of the wait (they do not depend on the previous kernel
     // beyond seq_len, which is re-checked)
     float nw[4] = {1.f, 1.f, 1.f, 1.f}, nwk[4] = {1.f, 1.f, 1.f, 1.f}, cs[4] = {1.f, 1.f, 0.f, 0.f};
+    // Eight-warp CTAs are chosen when every slice is a single step (seq_len <= S * 128), and decode batches usually keep
+    // sequence i in slot i.  Under those two assumptions the rows of this warp are known before seq_len and slot have
+    // been read, so they are requested first; the assumptions are checked when the two values arrive (a wrong guess
+    // costs a second request, never a wrong result: rows past the end of the slice are zeroed after the wait, the
+    // newest rows are fetched after the wait as always).
+    bool speculated = false, spec_kept = false;
+    int sl_guess = 0;
+    if constexpr (FUSED && WARPS == 8) {
+        if (!waited) {
+            sl_guess = m < p.n_slots ? m : 0;
+            const uint16_t* kg = p.kc + (size_t(sl_guess) * p.Nkv + kvh) * p.max_seq * kD;
+            const uint16_t* vg = p.vc + (size_t(sl_guess) * p.Nkv + kvh) * p.max_seq * kD;
+            const int ra = split * kBlk + warp * 16 + g, rb = ra + 8;
+            const bool oa = ra < p.max_seq, ob = rb < p.max_seq;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                k0[i] = oa ? ld_stream_u4(kg + size_t(ra) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+                k1[i] = ob ? ld_stream_u4(kg + size_t(rb) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                v0[i] = oa ? ld_stream_u4(vg + size_t(ra) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+                v1[i] = ob ? ld_stream_u4(vg + size_t(rb) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+            }
+            speculated = true;
+        }
+    }
     while (true) {
         L = __ldcg(p.seq_len + m);
         sl = __ldcg(p.slot + m);
@@ -598,15 +625,19 @@ flash_decode_mma_kernel(const FlashParams p) {
         const int safe_end = waited ? (FUSED ? min(end, L - 1) : end) : min(end, L - max(p.fresh_rows, 1));
         fetched_end = safe_end;
         const bool f0 = FUSED && has_rows && base0 + g < safe_end, f1 = FUSED && has_rows && base0 + g + 8 < safe_end;
+        spec_kept = speculated && per == 1 && sl == sl_guess && sl_seen == sl;  // the registers already hold (or await) these rows
+        speculated = false;
+        if (!spec_kept) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            k0[i] = f0 ? ld_stream_u4(kb + size_t(base0 + g) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
-            k1[i] = f1 ? ld_stream_u4(kb + size_t(base0 + g + 8) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
-        }
+            for (int i = 0; i < 4; i++) {
+                k0[i] = f0 ? ld_stream_u4(kb + size_t(base0 + g) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+                k1[i] = f1 ? ld_stream_u4(kb + size_t(base0 + g + 8) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            v0[i] = f0 ? ld_stream_u4(vb + size_t(base0 + g) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
-            v1[i] = f1 ? ld_stream_u4(vb + size_t(base0 + g + 8) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < 4; i++) {
+                v0[i] = f0 ? ld_stream_u4(vb + size_t(base0 + g) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+                v1[i] = f1 ? ld_stream_u4(vb + size_t(base0 + g + 8) * kD + 32 * i + 8 * t) : make_uint4(0, 0, 0, 0);
+            }
         }
         if (FUSED && has_rows) {
             // the position of a decode row is seq_len - 1 (the caller's contract for the fused call)
@@ -686,6 +717,16 @@ flash_decode_mma_kernel(const FlashParams p) {
     // rows of the first step that were not fetched ahead of the wait (the stand-alone call loads inside the loop)
     if (FUSED) {
         const int r0 = base0 + g, r1 = base0 + g + 8;
+        if (spec_kept) {  // requested before the length was known: what lies past the slice's end counts as zeros
+            if (r0 >= end) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) { k0[i] = make_uint4(0, 0, 0, 0); v0[i] = make_uint4(0, 0, 0, 0); }
+            }
+            if (r1 >= end) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) { k1[i] = make_uint4(0, 0, 0, 0); v1[i] = make_uint4(0, 0, 0, 0); }
+            }
+        }
         if (r0 >= fetched_end && r0 < end) {
             if (appends && r0 == newest) {
 #pragma unroll
