@@ -411,7 +411,7 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
     steps_total = args.warmup + args.steps
     n_ids = 32  # greedy ids printed with the line (the first tokens after the prompt, read back step by step)
     max_seq = prompt_len + n_ids + 2 * steps_total + 16
-    ecfg = eng_mod.EngineConfig(**cfg, max_seq=max_seq, max_batch=B, max_rows=max(512, B), tp_rank=rank, tp_size=world,
+    ecfg = eng_mod.EngineConfig(**cfg, max_seq=max_seq, max_batch=B, max_rows=max(int(os.environ.get('KUIPER_BENCH_MAX_ROWS', '2048')), B), tp_rank=rank, tp_size=world,
                                 act_mode=args.act_mode)
     eng = eng_mod.Qwen3Engine(ecfg)
 

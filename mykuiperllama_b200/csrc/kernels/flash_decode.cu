@@ -1178,6 +1178,17 @@ size_t ll_ml_bytes() { return align256(size_t(device_sm_count()) * 8 * 2 * sizeo
 size_t ll_seq_bytes() { return align256(size_t(device_sm_count()) * sizeof(unsigned int)); }
 size_t ll_area_bytes() { return ll_o_bytes() + ll_ml_bytes() + ll_seq_bytes(); }
 
+// Upper bound of rows x slices of any call with at most M rows: the slice count of a call is sized to the GPU (at most
+// four or five CTAs per SM over all rows and kv heads), and a call of one or two rows may use kMaxSplitsMma slices; a
+// forced slice count (tuning, tests) is checked against the workspace at launch.
+size_t flash_slots(int M) {
+    const size_t by_gpu = size_t(M) + 8 * size_t(device_sm_count());
+    const size_t by_cap = size_t(M) * kMaxSplits;
+    const size_t few = size_t(M < kFewRows ? M : kFewRows) * kMaxSplitsMma;
+    const size_t slots = by_gpu < by_cap ? by_gpu : by_cap;
+    return slots > few ? slots : few;
+}
+
 }  // namespace
 
 void flash_decode_set_tuning(const char* key, int value) {
@@ -1218,11 +1229,11 @@ extern "C" int kuiper_flash_decode_status(void) {
 
 extern "C" size_t kuiper_flash_decode_workspace_bytes(int M, int Nq, int D, int max_seq) {
     if (M <= 0 || Nq <= 0 || D <= 0 || max_seq <= 0) return 0;
-    // M rows at up to kMaxSplits slices, or the few rows that may use kMaxSplitsMma slices: whichever is larger
-    const size_t few = M < kFewRows ? size_t(M) : size_t(kFewRows);
-    const size_t slots = size_t(M) * kMaxSplits > few * kMaxSplitsMma ? size_t(M) * kMaxSplits : few * kMaxSplitsMma;
-    return align256(size_t(M) * Nq * sizeof(int)) + align256(slots * Nq * D * sizeof(float)) +
-           align256(slots * Nq * 2 * sizeof(float)) + ll_area_bytes();
+    // Layout: [tagged-word area of the eight-warp CTAs (fixed size and position, whatever M a call has)]
+    // [arrival counters] [partial outputs] [partial (max, sum)].  Slices in flight: a call never runs more than
+    // max_slots(M) (row, kv head, slice) triples per kv head count - see flash_slots().
+    return ll_area_bytes() + align256(size_t(M) * Nq * sizeof(int)) + align256(flash_slots(M) * Nq * D * sizeof(float)) +
+           align256(flash_slots(M) * Nq * 2 * sizeof(float));
 }
 
 // argument checks, workspace carving and launch shared by the two entry points; `p` arrives with the tensors set
@@ -1247,16 +1258,18 @@ static int flash_launch(FlashParams& p, bool fused, int M, int Nq, int Nkv, int 
     if (wide && p.S > kWideMaxSlices) p.S = kWideMaxSlices;
     if (p.S > 1) {
         KUIPER_REQUIRE(workspace != nullptr, "flash_decode: split KV needs a workspace");
-        KUIPER_REQUIRE(workspace_bytes >= kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq),
-                       "flash_decode: workspace of %zu bytes is too small", workspace_bytes);
-        char* w = reinterpret_cast<char*>(workspace);
+        const size_t need = ll_area_bytes() + align256(size_t(M) * Nq * sizeof(int)) +
+                            align256(size_t(M) * Nq * p.S * D * sizeof(float)) + align256(size_t(M) * Nq * p.S * 2 * sizeof(float));
+        KUIPER_REQUIRE(workspace_bytes >= need, "flash_decode: workspace of %zu bytes is too small (%zu needed for %d slices)",
+                       workspace_bytes, need, p.S);
+        // the tagged-word area comes first: a fixed place that the layouts of other row counts never touch
+        char* ll = reinterpret_cast<char*>(workspace);
+        char* w = ll + ll_area_bytes();
         p.counters = reinterpret_cast<int*>(w);
         w += align256(size_t(M) * Nq * sizeof(int));
         p.part_o = reinterpret_cast<float*>(w);
         w += align256(size_t(M) * Nq * p.S * D * sizeof(float));
         p.part_ml = reinterpret_cast<float*>(w);
-        // the tagged-word area sits at the very end of the workspace, where the other layouts never write
-        char* ll = reinterpret_cast<char*>(workspace) + kuiper_flash_decode_workspace_bytes(M, Nq, D, max_seq) - ll_area_bytes();
         p.ll_o = reinterpret_cast<uint2*>(ll);
         p.ll_ml = reinterpret_cast<uint2*>(ll + ll_o_bytes());
         p.ll_seq = reinterpret_cast<unsigned int*>(ll + ll_o_bytes() + ll_ml_bytes());

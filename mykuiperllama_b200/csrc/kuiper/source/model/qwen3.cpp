@@ -105,6 +105,9 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
         ws_gemm = std::max(ws_gemm, kernel::matmul_quant_gemm_workspace_bytes(R, s.K));
     }
     const size_t ws_mha = kernel::mha_workspace_bytes(R, Hq, D, c.max_seq_len);
+    // tensor dimensions are 32-bit (tensor::Tensor, as in the reference): a workspace has to stay below 2 GiB
+    if (ws_mm > size_t(INT32_MAX) || ws_mha > size_t(INT32_MAX) || ws_gemm > size_t(INT32_MAX))
+        return base::error::invalid_argument("max_rows is too large: a kernel workspace would exceed 2 GiB");
     size_t total = 0;
     total += size_t(c.layer_num) * (sh_qkv.total(g) + sh_o.total(g) + sh_gu.total(g) + sh_down.total(g) +
                                     2 * round256(size_t(H) * 2) + 2 * round256(size_t(D) * 2) +
