@@ -882,3 +882,31 @@ def test_rope_flash_decode_combine_wait_is_bounded(cuda, oracle):
     again = run()
     assert torch.equal(again, good)
     assert lib.kuiper_flash_decode_status() == 0
+
+
+@pytest.mark.parametrize("lens,slots", [([2084], [2]), ([1500, 900], [1, 0]), ([2305, 64], [0, 2])])
+def test_rope_flash_decode_with_rows_in_other_slots(cuda, oracle, lens, slots):
+    # the eight-warp CTAs request their cache rows before slot[] has been read, guessing that row i sits in slot i; when
+    # the guess is wrong they must fetch again - the result is that of the two-kernel path
+    rng = np.random.default_rng(97 + len(lens))
+    B, Nq, Nkv, D, Lmax, n_slots = len(lens), 32, 8, 128, 2400, 3
+    kc = torch.randn((n_slots, Nkv, Lmax, D), device="cuda").bfloat16()
+    vc = torch.randn((n_slots, Nkv, Lmax, D), device="cuda").bfloat16()
+    qkv = dev(rng.standard_normal((B, (Nq + 2 * Nkv) * D)).astype(np.float32))
+    qn = dev(oracle.f32_to_bf16((1 + 0.1 * rng.standard_normal(D)).astype(np.float32)))
+    kn = dev(oracle.f32_to_bf16((1 + 0.1 * rng.standard_normal(D)).astype(np.float32)))
+    cos_t, sin_t = (dev(t) for t in oracle.rope_tables(Lmax, D, 1e6))
+    seq = dev(np.array(lens, np.int32))
+    pos = dev(np.array(lens, np.int32) - 1)
+    slot = dev(np.array(slots, np.int32))
+    ws = cuda.flash_decode_workspace(B, Nq, D, Lmax)
+    k_ref, v_ref = kc.clone(), vc.clone()
+    q = cuda.qknorm_rope_kvwrite(qkv.clone(), qn, kn, cos_t, sin_t, pos, slot, Nq, Nkv, D, 1e-6, k_ref, v_ref)
+    ref = cuda.flash_decode(q, k_ref, v_ref, seq, slot, workspace=ws)
+    for fresh in (-1, 1):
+        k_f, v_f = kc.clone(), vc.clone()
+        got = cuda.rope_flash_decode(qkv.clone(), qn, kn, cos_t, sin_t, pos, seq, slot, Nq, Nkv, D, 1e-6, k_f, v_f, workspace=ws,
+                                     fresh_rows=fresh)
+        torch.cuda.synchronize()
+        assert rel_err(got.cpu().numpy(), ref.cpu().numpy()) <= 5e-5, fresh
+        assert torch.equal(k_f.view(torch.int16), k_ref.view(torch.int16)) and torch.equal(v_f.view(torch.int16), v_ref.view(torch.int16))
