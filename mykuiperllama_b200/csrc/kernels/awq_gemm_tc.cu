@@ -333,11 +333,255 @@ __global__ void __launch_bounds__(kGemmThreads, 2) awq_gemm_tc2_kernel(const Gem
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Third generation: the same tiles, stages and dequantisation, but nobody waits at a block-wide barrier per stage.
+//   * eight producer warps fill the stages (weights dequantised into stage s, activations of the next tile by cp.async);
+//     each thread arrives on the stage's "full" mbarrier once its own copies have landed and its stores are visible to
+//     the tensor-core proxy;
+//   * a ninth warp only waits for "full", issues the four tcgen05.mma of the stage and commits them onto the stage's
+//     "free" mbarrier, which the producers check before they overwrite the stage - so a producer warp that is ahead
+//     keeps working on the next tile instead of waiting for the slowest warp of the block;
+//   * zero words and scales are loaded and prepared once per 128-row group (two stages), addresses are carried as running
+//     pointers, and the swizzled store offsets are computed once.
+constexpr int kProducerThreads3 = 256;
+constexpr int kGemmThreads3 = kProducerThreads3 + 32;
+
+__global__ void __launch_bounds__(kGemmThreads3, 2) awq_gemm_tc3_kernel(const GemmParams2 pp) {
+    const GemmParams& p = pp.g;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
+    unsigned char* sA = smem;                          // kStages2 x 16 KB
+    unsigned char* sB = smem + kStages2 * kStageA2;    // kStages2 x 32 KB
+    __shared__ uint64_t full_bar[kStages2];            // producers -> MMA warp
+    __shared__ uint64_t free_bar[kStages2];            // tcgen05.commit -> producers
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_dead;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * kBN2, m0 = blockIdx.y * kBM;
+    const int NW = p.N >> 3;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < kStages2; i++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(&full_bar[i])), "r"(uint32_t(kProducerThreads3)));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&free_bar[i])));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_dead = 0;
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&s_tmem)), "r"(uint32_t(kBN2))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    const int nk = p.K / kBK;
+    bool dead = false;
+
+    if (warp == kProducerThreads3 / 32) {
+        // ------------------------------------------------------------ MMA warp: one lane issues
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (uint32_t(kBN2 >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+            for (int it = 0; it < nk && !dead; it++) {
+                const int s = it % kStages2;
+                if (!tc_mbar_wait(&full_bar[s], uint32_t(it / kStages2) & 1u)) {
+                    atomicExch(&g_gemm_wait_error, 5);
+                    s_dead = 1;
+                    dead = true;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_base = smem_addr(sA + s * kStageA2), b_base = smem_addr(sB + s * kStageB2);
+#pragma unroll
+                for (int kk = 0; kk < kBK / 16; kk++) {
+                    const uint64_t adesc = make_desc(a_base + kk * 32);
+                    const uint64_t bdesc = make_desc(b_base + kk * 32);
+                    const uint32_t accumulate = (it > 0 || kk > 0) ? 1u : 0u;
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "setp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                        ::"r"(tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                        : "memory");
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(&free_bar[s]))
+                             : "memory");
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ producers
+        // activations: four 16-byte chunks (row m, K octet koct), global fp16 -> swizzled shared memory, one tile ahead
+        const unsigned char* a_src[4];
+        uint32_t a_dst[4], a_bytes[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int item = q * kProducerThreads3 + tid;
+            const int koct = item & 7, m = item >> 3;
+            const bool ok = m0 + m < p.M;
+            a_src[q] = reinterpret_cast<const unsigned char*>(pp.x16 + size_t(ok ? m0 + m : 0) * p.K + koct * 8);
+            a_dst[q] = smem_addr(sA) + (m >> 3) * 1024 + (m & 7) * 128 + ((koct ^ (m & 7)) << 4);
+            a_bytes[q] = ok ? 16u : 0u;  // 0: the chunk is zero filled
+        }
+        auto issue_a = [&](int stage) {  // the next tile along K; the sources advance by one tile
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(a_dst[q] + stage * kStageA2), "l"(a_src[q]),
+                             "r"(a_bytes[q])
+                             : "memory");
+                a_src[q] += kBK * sizeof(__half);
+            }
+        };
+        // weights: packed word column j of the tile (8 output columns), K octet koct (8 rows)
+        const int koct_b = tid & 7, j_b = tid >> 3;
+        const int wcol = (n0 >> 3) + j_b;
+        const bool col_ok = wcol < NW;
+        const uint32_t* w_next = p.qw + (col_ok ? size_t(koct_b * 8) * NW + wcol : 0);  // rows of the next tile to load
+        const uint32_t* z_next = p.qz + (col_ok ? wcol : 0);                            // zero word of the next group to load
+        const uint4* s_next = reinterpret_cast<const uint4*>(p.scales + (col_ok ? n0 + j_b * 8 : 0));
+        const size_t tile_words = size_t(kBK) * NW;
+        const size_t row_words = size_t(NW);
+        const size_t scale_vecs = size_t(p.N >> 3);
+        auto load_w = [&](uint32_t (&w)[8]) {
+#pragma unroll
+            for (int r = 0; r < 8; r++) w[r] = col_ok ? __ldg(w_next + r * row_words) : 0u;
+            w_next += tile_words;
+        };
+        auto load_consts = [&](uint32_t& zw, uint4& sraw) {
+            zw = col_ok ? __ldg(z_next) : 0u;
+            sraw = col_ok ? __ldg(s_next) : make_uint4(0, 0, 0, 0);
+            z_next += row_words;
+            s_next += scale_vecs;
+        };
+        // swizzled 16-byte store slots of this thread inside its 1024-byte column block
+        uint32_t b_off[8];
+#pragma unroll
+        for (int c = 0; c < 8; c++) b_off[c] = uint32_t(c * 128 + ((koct_b ^ c) << 4));
+        const uint32_t b_dst = smem_addr(sB) + j_b * 1024;
+
+        TileConsts tc;
+        auto tile_step = [&](int it, uint32_t (&w)[8]) {
+            const int s = it % kStages2;
+            {
+                uint32_t d[8][4];  // [row][column pair]
+#pragma unroll
+                for (int r = 0; r < 8; r++) dequant_word_consts(w[r], tc, d[r]);
+                if (it + 2 < nk) load_w(w);
+                const uint32_t dst = b_dst + s * kStageB2;
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    const int pr = c >> 1;
+                    const uint32_t sel = (c & 1) ? 0x7632u : 0x5410u;
+                    const uint32_t o0 = __byte_perm(d[0][pr], d[1][pr], sel), o1 = __byte_perm(d[2][pr], d[3][pr], sel);
+                    const uint32_t o2 = __byte_perm(d[4][pr], d[5][pr], sel), o3 = __byte_perm(d[6][pr], d[7][pr], sel);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + b_off[c]), "r"(o0), "r"(o1), "r"(o2), "r"(o3)
+                                 : "memory");
+                }
+            }
+            // the next tile's activations go into the other stage once the MMAs that last read it have finished
+            if (it + 1 < nk) {
+                const int sn = (it + 1) % kStages2;
+                if (it + 1 >= kStages2 && !dead) {
+                    if (!tc_mbar_wait(&free_bar[sn], uint32_t((it + 1) / kStages2 - 1) & 1u)) {
+                        atomicExch(&g_gemm_wait_error, 3);
+                        s_dead = 1;
+                        dead = true;
+                    }
+                }
+                issue_a(sn);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");  // everything but the newest group: this tile's activations
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(&full_bar[s])) : "memory");
+        };
+
+        uint32_t w_even[8], w_odd[8], zw;
+        uint4 sraw;
+        issue_a(0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        load_w(w_even);
+        if (nk > 1) load_w(w_odd);
+        load_consts(zw, sraw);
+        for (int it = 0; it < nk; it += 2) {  // two 64-row tiles = one 128-row group: one set of constants
+            tc = make_tile_consts(zw, sraw);
+            if (it + 2 < nk) load_consts(zw, sraw);
+            tile_step(it, w_even);
+            if (it + 1 < nk) tile_step(it + 1, w_odd);
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+        // ---- all MMAs done?  (they complete in order: the last commit covers everything)
+        if (!dead) {
+            const int last = nk - 1;
+            if (!tc_mbar_wait(&free_bar[last % kStages2], uint32_t(last / kStages2) & 1u)) {
+                atomicExch(&g_gemm_wait_error, 4);
+                dead = true;
+            }
+        }
+        dead = dead || (s_dead != 0);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+        if (!dead) {
+            // ---- epilogue: warp w reads TMEM lanes 32*(w&3).., columns 128*(w>>2)..; one output row per thread
+            const int row = m0 + (warp & 3) * 32 + lane;
+            const int cbase = (warp >> 2) * 128;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem + (uint32_t((warp & 3) * 32) << 16) + uint32_t(cbase + ch * 32);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                      "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < p.M) {
+                    const int col0 = n0 + cbase + ch * 32;
+                    float* yp = p.y + size_t(row) * p.N + col0;
+                    const float* rp = p.mode == 1 ? p.residual + size_t(row) * p.N + col0 : (p.mode == 2 ? yp : nullptr);
+#pragma unroll
+                    for (int v = 0; v < 8; v++) {
+                        if (col0 + v * 4 < p.N) {
+                            float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                   __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                            if (rp) {
+                                const float4 a = __ldcg(reinterpret_cast<const float4*>(rp) + v);
+                                o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
+                            }
+                            reinterpret_cast<float4*>(yp)[v] = o;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(uint32_t(kBN2)) : "memory");
+    }
+}
+
+int g_gemm_impl = 3;  // 3: mbarrier hand-over to a dedicated MMA warp (default); 2: stages handed over at a block-wide barrier (tuning key "gemm_impl")
+
 }  // namespace
 
 void awq_gemm_set_tuning(const char* key, int value) {
-    (void)key;
-    (void)value;
+    if (!strcmp(key, "gemm_impl")) g_gemm_impl = value == 3 ? 3 : 2;
 }
 
 }  // namespace kuiper
@@ -399,5 +643,13 @@ extern "C" int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const
         return KUIPER_INTERNAL_ERROR;
     }
     const dim3 grid2((N + kBN2 - 1) / kBN2, (M + kBM - 1) / kBM, 1);
+    if (g_gemm_impl == 3) {
+        static size_t configured3[kMaxDevices] = {};
+        if (!ensure_dynamic_smem(awq_gemm_tc3_kernel, smem2, configured3)) {
+            set_error("awq_gemm: cannot reserve %zu bytes of shared memory", smem2);
+            return KUIPER_INTERNAL_ERROR;
+        }
+        return pdl_status(launch_pdl(awq_gemm_tc3_kernel, grid2, dim3(kGemmThreads3), smem2, as_stream(stream), p2), "awq_gemm");
+    }
     return pdl_status(launch_pdl(awq_gemm_tc2_kernel, grid2, dim3(kGemmThreads), smem2, as_stream(stream), p2), "awq_gemm");
 }

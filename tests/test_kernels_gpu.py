@@ -13,6 +13,7 @@ from helpers import awq_random, rel_err
 pytestmark = pytest.mark.gpu
 
 SPEC_TOL = 1e-2
+GEMM_IMPL_DEFAULT = 3
 
 
 def dev(a, dtype=None):
@@ -355,7 +356,16 @@ def test_awq_gemv_rejects_bad_arguments(cuda):
 # ----------------------------------------------------------------------------- INT4 GEMM (tcgen05), M >= 16
 @pytest.mark.parametrize("M,K,N", [(16, 128, 128), (16, 256, 136), (100, 1024, 384), (128, 4096, 1024), (129, 512, 256),
                                    (300, 1024, 4104), (16, 4096, 6144), (64, 3072, 1024)])
-def test_awq_gemm_tensor_core(cuda, oracle, M, K, N):
+@pytest.mark.parametrize("impl", [3, 2])  # 3: mbarrier hand-over to a dedicated MMA warp; 2: block-wide barrier per stage
+def test_awq_gemm_tensor_core(cuda, oracle, M, K, N, impl):
+    cuda.set_tuning("gemm_impl", impl)
+    try:
+        _gemm_case(cuda, oracle, M, K, N)
+    finally:
+        cuda.set_tuning("gemm_impl", GEMM_IMPL_DEFAULT)
+
+
+def _gemm_case(cuda, oracle, M, K, N):
     rng = np.random.default_rng(M + K + N)
     q, z, s = awq_random(rng, K, N)
     qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
