@@ -13,8 +13,10 @@
 // store.  Both operands are stored K-major with the 128-byte swizzle: a tile row is the 64 K values (128
 // bytes) of one token row / weight column, eight rows form a 1024-byte atom, and the 16-byte chunk c of row
 // r sits at chunk position c ^ (r % 8).  One thread issues four tcgen05.mma (K = 16 each) per stage and a
-// tcgen05.commit onto the stage's mbarrier; a stage is refilled only after that commit.  The epilogue reads
-// the accumulator with tcgen05.ld (one TMEM lane = one output row per thread).
+// tcgen05.commit onto the stage's mbarrier; a stage is refilled only after that commit.  In the default kernel
+// (awq_gemm_tc3_kernel) that thread belongs to a warp of its own and learns through a second mbarrier that the
+// producer warps have filled the stage; awq_gemm_tc2_kernel hands the stage over at a block-wide barrier.  The
+// epilogue reads the accumulator with tcgen05.ld (one TMEM lane = one output row per thread).
 //
 // Every mbarrier wait is bounded; on a timeout the CTA records an error word, stops issuing work,
 // still frees its tensor memory and returns.
