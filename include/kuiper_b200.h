@@ -300,6 +300,9 @@ KUIPER_API int kuiper_flash_prefill(const float* q, const uint16_t* kcache, cons
  * kuiper_set_tuning("flash_mma_fused", 0) it uses the SIMT arithmetic and is then bit-identical to
  * kuiper_qknorm_rope_kvwrite followed by kuiper_flash_decode with its SIMT kernel ("flash_mma" = 0).  The two
  * arithmetic paths agree to ~1e-5; the appended cache rows are identical.
+ * For one or two sequences at a context of a few thousand rows the call runs eight-warp CTAs whose partial results reach
+ * one combining CTA per (row, kv head) as tagged 8-byte words; that CTA's wait for them is bounded (1 s by default) and
+ * a run-out is reported by kuiper_flash_decode_status().  The workspace must have been zeroed once, all of it.
  */
 KUIPER_API int kuiper_rope_flash_decode(float* qkv, const uint16_t* q_norm_w, const uint16_t* k_norm_w,
                                         const float* cos_t, const float* sin_t, const int32_t* pos,
