@@ -117,18 +117,24 @@ constexpr int kStages2 = 2;   // 96 KB per CTA: two CTAs (16 warps, 2 x 256 TMEM
 constexpr int kStageA2 = kBM * kBK * 2;   // 16 KB
 constexpr int kStageB2 = kBN2 * kBK * 2;  // 32 KB
 
-__global__ void convert_f16_kernel(const float4* __restrict__ x, uint2* __restrict__ out, int64_t n4) {
+// x -> fp16 copy; optionally zeroes the output of a split-K call (zero4 float4s), so that the zeroing is a kernel of
+// the programmatic-dependent-launch chain like everything else (the GEMM's dependency wait covers it)
+__global__ void convert_f16_kernel(const float4* __restrict__ x, uint2* __restrict__ out, int64_t n4, float4* __restrict__ zero,
+                                   int64_t zero4) {
     pdl_launch_dependents();
     pdl_wait();
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
         const float4 v = __ldcg(x + i);
         out[i] = make_uint2(tc_h22u(__floats2half2_rn(v.x, v.y)), tc_h22u(__floats2half2_rn(v.z, v.w)));
     }
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < zero4; i += stride) zero[i] = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
 struct GemmParams2 {
     GemmParams g;
     const __half* x16;  // [M, K] fp16 copy of x
+    int tiles_per_split; // third generation: 64-row K tiles of one CTA (grid.z CTAs share an output tile); 0 = all of K
 };
 
 __global__ void __launch_bounds__(kGemmThreads, 2) awq_gemm_tc2_kernel(const GemmParams2 pp) {
@@ -386,7 +392,10 @@ __global__ void __launch_bounds__(kGemmThreads3, 2) awq_gemm_tc3_kernel(const Ge
     pdl_launch_dependents();
     pdl_wait();
 
-    const int nk = p.K / kBK;
+    // split K: grid.z CTAs work on consecutive runs of K tiles of the same output tile and add their sums with reductions
+    const int nk = pp.tiles_per_split > 0 ? pp.tiles_per_split : p.K / kBK;
+    const int tile0 = int(blockIdx.z) * nk;
+    const bool split_k = gridDim.z > 1;
     bool dead = false;
 
     if (warp == kProducerThreads3 / 32) {
@@ -429,7 +438,7 @@ __global__ void __launch_bounds__(kGemmThreads3, 2) awq_gemm_tc3_kernel(const Ge
             const int item = q * kProducerThreads3 + tid;
             const int koct = item & 7, m = item >> 3;
             const bool ok = m0 + m < p.M;
-            a_src[q] = reinterpret_cast<const unsigned char*>(pp.x16 + size_t(ok ? m0 + m : 0) * p.K + koct * 8);
+            a_src[q] = reinterpret_cast<const unsigned char*>(pp.x16 + size_t(ok ? m0 + m : 0) * p.K + koct * 8 + size_t(tile0) * kBK);
             a_dst[q] = smem_addr(sA) + (m >> 3) * 1024 + (m & 7) * 128 + ((koct ^ (m & 7)) << 4);
             a_bytes[q] = ok ? 16u : 0u;  // 0: the chunk is zero filled
         }
@@ -446,12 +455,13 @@ __global__ void __launch_bounds__(kGemmThreads3, 2) awq_gemm_tc3_kernel(const Ge
         const int koct_b = tid & 7, j_b = tid >> 3;
         const int wcol = (n0 >> 3) + j_b;
         const bool col_ok = wcol < NW;
-        const uint32_t* w_next = p.qw + (col_ok ? size_t(koct_b * 8) * NW + wcol : 0);  // rows of the next tile to load
-        const uint32_t* z_next = p.qz + (col_ok ? wcol : 0);                            // zero word of the next group to load
-        const uint4* s_next = reinterpret_cast<const uint4*>(p.scales + (col_ok ? n0 + j_b * 8 : 0));
         const size_t tile_words = size_t(kBK) * NW;
         const size_t row_words = size_t(NW);
         const size_t scale_vecs = size_t(p.N >> 3);
+        const size_t group0 = size_t(tile0 >> 1);  // a split starts at a 128-row group
+        const uint32_t* w_next = p.qw + (col_ok ? size_t(koct_b * 8) * NW + wcol + size_t(tile0) * tile_words : 0);  // next tile to load
+        const uint32_t* z_next = p.qz + (col_ok ? wcol + group0 * row_words : 0);       // zero word of the next group to load
+        const uint4* s_next = reinterpret_cast<const uint4*>(p.scales + (col_ok ? n0 + j_b * 8 : 0)) + (col_ok ? group0 * scale_vecs : 0);
         auto load_w = [&](uint32_t (&w)[8]) {
 #pragma unroll
             for (int r = 0; r < 8; r++) w[r] = col_ok ? __ldg(w_next + r * row_words) : 0u;
@@ -554,7 +564,10 @@ __global__ void __launch_bounds__(kGemmThreads3, 2) awq_gemm_tc3_kernel(const Ge
                 if (row < p.M) {
                     const int col0 = n0 + cbase + ch * 32;
                     float* yp = p.y + size_t(row) * p.N + col0;
-                    const float* rp = p.mode == 1 ? p.residual + size_t(row) * p.N + col0 : (p.mode == 2 ? yp : nullptr);
+                    // split K: every CTA adds into y (zeroed by the host unless the call accumulates); the residual rides
+                    // with the first split
+                    const float* rp = p.mode == 1 ? (split_k && blockIdx.z != 0 ? nullptr : p.residual + size_t(row) * p.N + col0)
+                                                  : (p.mode == 2 && !split_k ? yp : nullptr);
 #pragma unroll
                     for (int v = 0; v < 8; v++) {
                         if (col0 + v * 4 < p.N) {
@@ -564,7 +577,12 @@ __global__ void __launch_bounds__(kGemmThreads3, 2) awq_gemm_tc3_kernel(const Ge
                                 const float4 a = __ldcg(reinterpret_cast<const float4*>(rp) + v);
                                 o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w;
                             }
-                            reinterpret_cast<float4*>(yp)[v] = o;
+                            if (split_k)
+                                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(yp + 4 * v), "f"(o.x), "f"(o.y), "f"(o.z),
+                                             "f"(o.w)
+                                             : "memory");
+                            else
+                                reinterpret_cast<float4*>(yp)[v] = o;
                         }
                     }
                 }
@@ -578,12 +596,15 @@ __global__ void __launch_bounds__(kGemmThreads3, 2) awq_gemm_tc3_kernel(const Ge
     }
 }
 
+constexpr int kMaxSplitK = 8;
+int g_gemm_split_k = 1;  // tuning key "gemm_split_k": 0 switches the K split of the third generation off
 int g_gemm_impl = 3;  // 3: mbarrier hand-over to a dedicated MMA warp (default); 2: stages handed over at a block-wide barrier (tuning key "gemm_impl")
 
 }  // namespace
 
 void awq_gemm_set_tuning(const char* key, int value) {
     if (!strcmp(key, "gemm_impl")) g_gemm_impl = value == 3 ? 3 : 2;
+    if (!strcmp(key, "gemm_split_k")) g_gemm_split_k = value < 0 ? 0 : value;
 }
 
 }  // namespace kuiper
@@ -622,36 +643,57 @@ extern "C" int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const
     p.y = y;
     p.residual = residual;
     p.M = M; p.K = K; p.N = N;
-    p.mode = accumulate ? 2 : (residual ? 1 : 0);
+    p.mode = accumulate ? 2 : (residual ? (residual == y ? 2 : 1) : 0);  // y + residual with residual == y is y += 
     KUIPER_REQUIRE(workspace != nullptr && workspace_bytes >= kuiper_awq_gemm_workspace_bytes(M, K) &&
                        (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
                    "awq_gemm: needs a 16-byte aligned workspace of kuiper_awq_gemm_workspace_bytes(M, K) bytes (got %zu)",
                    workspace_bytes);
-    // activations converted to fp16 once, then 128 x 256 output tiles
+    // Few output tiles (a decode batch, a short chunk: one row of tiles is N / 256 CTAs) leave most SMs without work while
+    // every CTA streams a whole column panel of the weight: the third generation then splits K so that about two CTAs
+    // per SM are busy.  A split is a whole number of 128-row groups; the sums meet through reductions, so y starts from
+    // zero (or from its content when the call accumulates) and the summation order is no longer fixed.
+    const dim3 grid2((N + kBN2 - 1) / kBN2, (M + kBM - 1) / kBM, 1);
+    int splits = 1;
+    if (g_gemm_impl == 3 && g_gemm_split_k) {
+        // up to a third of a second wave is still a gain (measured: 96 tiles run 48 us with 4 splits, 55 us with 2)
+        const int tiles = int(grid2.x * grid2.y), groups = K / 128, want = (2 * device_sm_count() * 4 / 3 + tiles - 1) / tiles;
+        for (int sdiv = 2; sdiv <= groups && sdiv <= kMaxSplitK && sdiv <= want; sdiv++)
+            if (groups % sdiv == 0) splits = sdiv;
+        if (g_gemm_split_k > 1 && groups % g_gemm_split_k == 0) splits = g_gemm_split_k;  // forced (measurement aid)
+    }
+    const bool zero_y = splits > 1 && p.mode != 2;
+    // activations converted to fp16 once (the same launch zeroes y for a split call), then 128 x 256 output tiles
     const int64_t n4 = int64_t(M) * K / 4;
-    int blocks = int((n4 + 255) / 256);
+    const int64_t zero4 = zero_y ? int64_t(M) * N / 4 : 0;
+    int blocks = int(((n4 > zero4 ? n4 : zero4) + 255) / 256);
     if (blocks > 148 * 8) blocks = 148 * 8;
     int rc = pdl_status(launch_pdl(convert_f16_kernel, dim3(blocks), dim3(256), 0, as_stream(stream),
-                                   reinterpret_cast<const float4*>(x), reinterpret_cast<uint2*>(workspace), n4),
+                                   reinterpret_cast<const float4*>(x), reinterpret_cast<uint2*>(workspace), n4,
+                                   reinterpret_cast<float4*>(y), zero4),
                         "awq_gemm convert");
     if (rc != KUIPER_OK) return rc;
     GemmParams2 p2;
     p2.g = p;
     p2.x16 = reinterpret_cast<const __half*>(workspace);
+    p2.tiles_per_split = 0;
     const size_t smem2 = 1024 + size_t(kStages2) * (kStageA2 + kStageB2);
-    static size_t configured[kMaxDevices] = {};
-    if (!ensure_dynamic_smem(awq_gemm_tc2_kernel, smem2, configured)) {
-        set_error("awq_gemm: cannot reserve %zu bytes of shared memory", smem2);
-        return KUIPER_INTERNAL_ERROR;
-    }
-    const dim3 grid2((N + kBN2 - 1) / kBN2, (M + kBM - 1) / kBM, 1);
     if (g_gemm_impl == 3) {
         static size_t configured3[kMaxDevices] = {};
         if (!ensure_dynamic_smem(awq_gemm_tc3_kernel, smem2, configured3)) {
             set_error("awq_gemm: cannot reserve %zu bytes of shared memory", smem2);
             return KUIPER_INTERNAL_ERROR;
         }
-        return pdl_status(launch_pdl(awq_gemm_tc3_kernel, grid2, dim3(kGemmThreads3), smem2, as_stream(stream), p2), "awq_gemm");
+        dim3 grid3 = grid2;
+        if (splits > 1) {
+            grid3.z = splits;
+            p2.tiles_per_split = (K / kBK) / splits;
+        }
+        return pdl_status(launch_pdl(awq_gemm_tc3_kernel, grid3, dim3(kGemmThreads3), smem2, as_stream(stream), p2), "awq_gemm");
+    }
+    static size_t configured[kMaxDevices] = {};
+    if (!ensure_dynamic_smem(awq_gemm_tc2_kernel, smem2, configured)) {
+        set_error("awq_gemm: cannot reserve %zu bytes of shared memory", smem2);
+        return KUIPER_INTERNAL_ERROR;
     }
     return pdl_status(launch_pdl(awq_gemm_tc2_kernel, grid2, dim3(kGemmThreads), smem2, as_stream(stream), p2), "awq_gemm");
 }

@@ -229,7 +229,7 @@ base::Status Qwen3Model::init(base::DeviceType device_type) {
             // the two pre-norms run inside the projections that consume them
             L.qkv->set_input_norm(L.input_norm->get_weight(0), c.eps);
             L.gate_up->set_input_norm(L.post_norm->get_weight(0), c.eps);
-            // passes of 64 rows or more take the tensor-core path, which wants the normed rows materialised
+            // passes of 16 rows or more take the tensor-core path, which wants the normed rows materialised
             L.qkv->set_norm_scratch(get_buffer(ModelBufferType::OutputRMSNorm));
             L.gate_up->set_norm_scratch(get_buffer(ModelBufferType::FFNRMSNorm));
         }

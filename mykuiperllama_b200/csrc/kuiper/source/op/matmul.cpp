@@ -1,3 +1,4 @@
+#include <cstdlib>
 // MatmulLayer: y = x . W for INT4-AWQ (dequant-fused GEMV) and bf16 weights.
 #include "op/matmul.h"
 
@@ -11,6 +12,7 @@ MatmulLayer::MatmulLayer(base::DeviceType device_type, int32_t dim0, int32_t dim
     reset_output_size(1);
     reset_weights_size(is_quant_layer ? 2 : 1);
     if (is_quant_layer) group_size_ = 128;
+    if (const char* env = std::getenv("KUIPER_GEMM_MIN_ROWS")) gemm_min_rows_ = std::atoi(env);  // measurement aid
 }
 
 base::DataType MatmulLayer::weight_data_type(int32_t) const {

@@ -356,16 +356,18 @@ def test_awq_gemv_rejects_bad_arguments(cuda):
 # ----------------------------------------------------------------------------- INT4 GEMM (tcgen05), M >= 16
 @pytest.mark.parametrize("M,K,N", [(16, 128, 128), (16, 256, 136), (100, 1024, 384), (128, 4096, 1024), (129, 512, 256),
                                    (300, 1024, 4104), (16, 4096, 6144), (64, 3072, 1024)])
-@pytest.mark.parametrize("impl", [3, 2])  # 3: mbarrier hand-over to a dedicated MMA warp; 2: block-wide barrier per stage
-def test_awq_gemm_tensor_core(cuda, oracle, M, K, N, impl):
+@pytest.mark.parametrize("impl,split_k", [(3, 1), (3, 0), (2, 0)])  # 3: mbarrier hand-over to a dedicated MMA warp, with
+def test_awq_gemm_tensor_core(cuda, oracle, M, K, N, impl, split_k):     # and without the K split; 2: block-wide barrier
     cuda.set_tuning("gemm_impl", impl)
+    cuda.set_tuning("gemm_split_k", split_k)
     try:
-        _gemm_case(cuda, oracle, M, K, N)
+        _gemm_case(cuda, oracle, M, K, N, exact=not split_k)
     finally:
         cuda.set_tuning("gemm_impl", GEMM_IMPL_DEFAULT)
+        cuda.set_tuning("gemm_split_k", 1)
 
 
-def _gemm_case(cuda, oracle, M, K, N):
+def _gemm_case(cuda, oracle, M, K, N, exact):
     rng = np.random.default_rng(M + K + N)
     q, z, s = awq_random(rng, K, N)
     qw, qz, su = oracle.awq_pack(q), oracle.awq_pack(z), s.view(np.uint16)
@@ -383,10 +385,14 @@ def _gemm_case(cuda, oracle, M, K, N):
     err = rel_err(y.cpu().numpy(), ref)
     assert err <= SPEC_TOL and err <= 1e-3
     assert rel_err(y_res.cpu().numpy(), ref + res) <= 1e-3
-    assert torch.equal(y_acc, y_res)  # same tile, same order: bit-identical
     again = cuda.awq_gemm(tx, tqw, tqz, ts, workspace=ws)
     torch.cuda.synchronize()
-    assert torch.equal(again, y)  # fixed summation order: deterministic
+    if exact:
+        assert torch.equal(y_acc, y_res)  # same tile, same order: bit-identical
+        assert torch.equal(again, y)      # fixed summation order: deterministic
+    else:  # the K split adds its partial sums with reductions: only the fp32 summation order may differ
+        assert rel_err(y_acc.cpu().numpy(), y_res.cpu().numpy()) <= 2e-6
+        assert rel_err(again.cpu().numpy(), y.cpu().numpy()) <= 2e-6
     cuda.awq_gemm_status()
 
 
