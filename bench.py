@@ -501,10 +501,10 @@ def run_engine(args, cfg, prompt_len, desc, rank, world):
     value = args.steps * B / (ms * 1e-3)
     tok_after = eng.decode_read(B)
 
-    # ---- end to end: host token in, host token out, every step
-    pos_now = prompt_len + steps_total
-    eng.decode_begin(tok_after, [pos_now] * B, list(range(B)))
-    tok = np.array(tok_after, np.int32)
+    # ---- end to end: host token in, host token out, every step, over the same positions as the device-resident loop
+    #      (so that the two numbers differ by the host round trip only, not by the context length)
+    eng.decode_begin(firsts, [prompt_len] * B, list(range(B)))
+    tok = np.array(firsts, np.int32)
     for _ in range(args.warmup):
         tok = eng.decode_predict(tok)
     barrier()
