@@ -181,7 +181,9 @@ KUIPER_API int kuiper_awq_gemv_f32_noalloc(const float* x, const int32_t* qweigh
  * (q - z) * s is rounded to fp16, accumulation is fp32 in tensor memory.
  *   accumulate == 0, residual == NULL : y  = x . W
  *   accumulate == 0, residual != NULL : y  = x . W + residual   (residual may alias y)
- *   accumulate != 0                   : y += x . W              (summation order fixed: deterministic)
+ *   accumulate != 0                   : y += x . W
+ * A launch with few output tiles (M <= 128 or so) splits K over several CTAs per tile, which add their sums with
+ * reductions: the summation order is then not fixed (differences ~1e-6); larger launches are deterministic.
  * Any M > 0 is accepted (rows are padded to 128 inside the kernel); K % 128 == 0, N % 8 == 0.
  * workspace: kuiper_awq_gemm_workspace_bytes(M, K) bytes (16-byte aligned) for the fp16 copy of x that the
  * pipelined kernel reads (128 x 256 tiles); required.
@@ -191,6 +193,11 @@ KUIPER_API int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const
                                    const uint16_t* scales, float* y, const float* residual, int accumulate,
                                    int M, int K, int N, int group, void* workspace, size_t workspace_bytes,
                                    kuiper_stream_t stream);
+/* The same call for activations that already are fp16 [M, K] (as kuiper_rmsnorm_f16 / kuiper_swiglu_f16 leave them): no
+ * conversion pass, no workspace. */
+KUIPER_API int kuiper_awq_gemm_f16in_f32(const uint16_t* x16, const int32_t* qweight, const int32_t* qzeros,
+                                         const uint16_t* scales, float* y, const float* residual, int accumulate,
+                                         int M, int K, int N, int group, kuiper_stream_t stream);
 KUIPER_API int kuiper_awq_gemm_status(void);
 
 /* ---- tensor-parallel exchanges for decode rows over peer-mapped buffers.  No counterpart in the reference (it has no
@@ -233,6 +240,9 @@ KUIPER_API int kuiper_bf16_gemv_f32(const float* x, const uint16_t* W, float* y,
 /* y = (x * rstd) * w, rstd = 1/sqrt(mean(x^2) + eps); w bf16 [H]; y may alias x */
 KUIPER_API int kuiper_rmsnorm_f32(const float* x, const uint16_t* w, float* y, int M, int H, float eps,
                        kuiper_stream_t stream);
+/* the same row norm with the result rounded to fp16 (the tensor-core GEMM's activation type) */
+KUIPER_API int kuiper_rmsnorm_f16(const float* x, const uint16_t* w, uint16_t* y16, int M, int H, float eps,
+                                  kuiper_stream_t stream);
 
 /* ---- per-head q/k RMSNorm + rotary + KV-cache write: placeholder kuiper/include/op/rope.h:1-10 ---- */
 /*
@@ -327,6 +337,8 @@ KUIPER_API int kuiper_gemv_trace_read(int64_t* out, int max_values);
 /* ---- SwiGLU: placeholder kuiper/include/op/swiglu.h:1-10 ---- */
 /* out[m,i] = silu(gate_up[m,i]) * gate_up[m,I+i]; gate_up is [M, 2I]; clear_input != 0 zeroes gate_up afterwards */
 KUIPER_API int kuiper_swiglu_f32(float* gate_up, float* out, int M, int I, int clear_input, kuiper_stream_t stream);
+/* the same with the result rounded to fp16 */
+KUIPER_API int kuiper_swiglu_f16(float* gate_up, uint16_t* out16, int M, int I, int clear_input, kuiper_stream_t stream);
 
 /* ---- embedding gather: placeholder kuiper/include/op/embedding.h:1-10 ---- */
 KUIPER_API int kuiper_embedding_bf16(const int32_t* tokens, const uint16_t* table, float* out, int M, int H,

@@ -51,6 +51,7 @@ KERNEL_API = {
     "kuiper_awq_gemv_f32_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_awq_gemm_workspace_bytes": (_sz, [_i32, _i32]),
     "kuiper_awq_gemm_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
+    "kuiper_awq_gemm_f16in_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
     "kuiper_awq_gemm_status": (_i32, []),
     "kuiper_allreduce_buffer_bytes": (_sz, [_i32, _i64]),
     "kuiper_allreduce_state_bytes": (_sz, []),
@@ -59,6 +60,7 @@ KERNEL_API = {
     "kuiper_allreduce_status": (_i32, [_vp, _i32]),
     "kuiper_bf16_gemv_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_rmsnorm_f32": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _vp]),
+    "kuiper_rmsnorm_f16": (_i32, [_vp, _vp, _vp, _i32, _i32, _f32, _vp]),
     "kuiper_qknorm_rope_kvwrite": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _i32, _i32,
                                           _vp, _vp, _vp, _i32, _vp, _i64, _vp]),
     "kuiper_flash_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32]),
@@ -68,6 +70,7 @@ KERNEL_API = {
     "kuiper_rope_flash_decode": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32,
                                         _i32, _i32, _i32, _i32, _vp, _i64, _vp, _sz, _vp]),
     "kuiper_swiglu_f32": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),
+    "kuiper_swiglu_f16": (_i32, [_vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_embedding_bf16": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "kuiper_argmax_f32": (_i32, [_vp, _vp, _i32, _i32, _vp]),
     "kuiper_decode_advance": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp]),

@@ -176,6 +176,19 @@ def awq_gemm(x, qweight, qzeros, scales, y=None, residual=None, accumulate=False
     return y
 
 
+def awq_gemm_f16in(x16, qweight, qzeros, scales, y=None, residual=None, accumulate=False, group=128):
+    """The tensor-core GEMM for activations that already are fp16 [M, K] (no conversion pass, no workspace)."""
+    _dev(x16, qweight, qzeros, scales)
+    M, K = x16.shape
+    N = qweight.shape[1] * 8
+    if y is None:
+        y = torch.empty((M, N), dtype=torch.float32, device=x16.device)
+    check(kernels().kuiper_awq_gemm_f16in_f32(_ptr(x16), _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(y),
+                                              _ptr(residual) if residual is not None else None, int(bool(accumulate)),
+                                              M, K, N, group, _stream()))
+    return y
+
+
 def awq_gemm_status() -> None:
     check(kernels().kuiper_awq_gemm_status())
 
@@ -198,6 +211,24 @@ def rmsnorm(x, w, eps=1e-6, out=None):
     M, H = x.shape
     out = torch.empty_like(x) if out is None else out
     check(kernels().kuiper_rmsnorm_f32(_ptr(x), _ptr(w), _ptr(out), M, H, eps, _stream()))
+    return out
+
+
+def rmsnorm_f16(x, w, eps=1e-6):
+    """RMSNorm with the result rounded to fp16 (the tensor-core GEMM's activation type)."""
+    _dev(x, w)
+    M, H = x.shape
+    out = torch.empty((M, H), dtype=torch.float16, device=x.device)
+    check(kernels().kuiper_rmsnorm_f16(_ptr(x), _ptr(w), _ptr(out), M, H, eps, _stream()))
+    return out
+
+
+def swiglu_f16(gate_up, clear_input=False):
+    """silu(gate) * up of gate_up = [M, 2 I], rounded to fp16 [M, I]."""
+    _dev(gate_up)
+    M, I2 = gate_up.shape
+    out = torch.empty((M, I2 // 2), dtype=torch.float16, device=gate_up.device)
+    check(kernels().kuiper_swiglu_f16(_ptr(gate_up), _ptr(out), M, I2 // 2, int(bool(clear_input)), _stream()))
     return out
 
 

@@ -624,16 +624,17 @@ extern "C" size_t kuiper_awq_gemm_workspace_bytes(int M, int K) {
     return (size_t(M) * size_t(K) * sizeof(__half) + 255) / 256 * 256;  // fp16 copy of the activations
 }
 
-extern "C" int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
-                                   float* y, const float* residual, int accumulate, int M, int K, int N, int group,
-                                   void* workspace, size_t workspace_bytes, kuiper_stream_t stream) {
-    KUIPER_REQUIRE(x && qweight && qzeros && scales && y, "awq_gemm: null tensor pointer");
+// Shared by the two entry points: x is fp32 (converted into the workspace first) or already fp16 (x16, no workspace).
+static int gemm_common(const float* x, const __half* x16_in, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
+                       float* y, const float* residual, int accumulate, int M, int K, int N, int group, void* workspace,
+                       size_t workspace_bytes, kuiper_stream_t stream) {
+    KUIPER_REQUIRE((x || x16_in) && qweight && qzeros && scales && y, "awq_gemm: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && K > 0 && N > 0, "awq_gemm: empty shape M=%d K=%d N=%d", M, K, N);
     KUIPER_REQUIRE(group == 128, "awq_gemm: group size %d is not supported (128 only)", group);
     KUIPER_REQUIRE(K % 128 == 0 && N % 8 == 0, "awq_gemm: needs K %% 128 == 0 and N %% 8 == 0 (K=%d N=%d)", K, N);
     KUIPER_REQUIRE(!(accumulate && residual), "awq_gemm: accumulate and residual are exclusive");
-    KUIPER_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(scales) |
-                     reinterpret_cast<uintptr_t>(residual)) & 15) == 0 && (N % 4 == 0),
+    KUIPER_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(x16_in) | reinterpret_cast<uintptr_t>(y) |
+                     reinterpret_cast<uintptr_t>(scales) | reinterpret_cast<uintptr_t>(residual)) & 15) == 0 && (N % 4 == 0),
                    "awq_gemm: x, y, scales and residual must be 16-byte aligned");
     GemmParams p;
     p.x = x;
@@ -644,8 +645,8 @@ extern "C" int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const
     p.residual = residual;
     p.M = M; p.K = K; p.N = N;
     p.mode = accumulate ? 2 : (residual ? (residual == y ? 2 : 1) : 0);  // y + residual with residual == y is y += 
-    KUIPER_REQUIRE(workspace != nullptr && workspace_bytes >= kuiper_awq_gemm_workspace_bytes(M, K) &&
-                       (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+    KUIPER_REQUIRE(x16_in != nullptr || (workspace != nullptr && workspace_bytes >= kuiper_awq_gemm_workspace_bytes(M, K) &&
+                                         (reinterpret_cast<uintptr_t>(workspace) & 15) == 0),
                    "awq_gemm: needs a 16-byte aligned workspace of kuiper_awq_gemm_workspace_bytes(M, K) bytes (got %zu)",
                    workspace_bytes);
     // Few output tiles (a decode batch, a short chunk: one row of tiles is N / 256 CTAs) leave most SMs without work while
@@ -663,18 +664,20 @@ extern "C" int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const
     }
     const bool zero_y = splits > 1 && p.mode != 2;
     // activations converted to fp16 once (the same launch zeroes y for a split call), then 128 x 256 output tiles
-    const int64_t n4 = int64_t(M) * K / 4;
+    const int64_t n4 = x16_in ? 0 : int64_t(M) * K / 4;  // activations that arrive as fp16 need no conversion
     const int64_t zero4 = zero_y ? int64_t(M) * N / 4 : 0;
-    int blocks = int(((n4 > zero4 ? n4 : zero4) + 255) / 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    int rc = pdl_status(launch_pdl(convert_f16_kernel, dim3(blocks), dim3(256), 0, as_stream(stream),
-                                   reinterpret_cast<const float4*>(x), reinterpret_cast<uint2*>(workspace), n4,
-                                   reinterpret_cast<float4*>(y), zero4),
-                        "awq_gemm convert");
-    if (rc != KUIPER_OK) return rc;
+    if (n4 > 0 || zero4 > 0) {
+        int blocks = int(((n4 > zero4 ? n4 : zero4) + 255) / 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        int rc = pdl_status(launch_pdl(convert_f16_kernel, dim3(blocks), dim3(256), 0, as_stream(stream),
+                                       reinterpret_cast<const float4*>(x), reinterpret_cast<uint2*>(workspace), n4,
+                                       reinterpret_cast<float4*>(y), zero4),
+                            "awq_gemm convert");
+        if (rc != KUIPER_OK) return rc;
+    }
     GemmParams2 p2;
     p2.g = p;
-    p2.x16 = reinterpret_cast<const __half*>(workspace);
+    p2.x16 = x16_in ? x16_in : reinterpret_cast<const __half*>(workspace);
     p2.tiles_per_split = 0;
     const size_t smem2 = 1024 + size_t(kStages2) * (kStageA2 + kStageB2);
     if (g_gemm_impl == 3) {
@@ -696,4 +699,19 @@ extern "C" int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const
         return KUIPER_INTERNAL_ERROR;
     }
     return pdl_status(launch_pdl(awq_gemm_tc2_kernel, grid2, dim3(kGemmThreads), smem2, as_stream(stream), p2), "awq_gemm");
+}
+
+extern "C" int kuiper_awq_gemm_f32(const float* x, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
+                                   float* y, const float* residual, int accumulate, int M, int K, int N, int group,
+                                   void* workspace, size_t workspace_bytes, kuiper_stream_t stream) {
+    KUIPER_REQUIRE(x != nullptr, "awq_gemm: null tensor pointer");
+    return gemm_common(x, nullptr, qweight, qzeros, scales, y, residual, accumulate, M, K, N, group, workspace, workspace_bytes, stream);
+}
+
+extern "C" int kuiper_awq_gemm_f16in_f32(const uint16_t* x16, const int32_t* qweight, const int32_t* qzeros, const uint16_t* scales,
+                                         float* y, const float* residual, int accumulate, int M, int K, int N, int group,
+                                         kuiper_stream_t stream) {
+    KUIPER_REQUIRE(x16 != nullptr, "awq_gemm_f16in: null tensor pointer");
+    return gemm_common(nullptr, reinterpret_cast<const __half*>(x16), qweight, qzeros, scales, y, residual, accumulate, M, K, N, group,
+                       nullptr, 0, stream);
 }

@@ -60,13 +60,24 @@ __device__ __forceinline__ float block_sum_1024(float v, float* s_part) {
     return warp_sum(tot);  // every warp reduces the 32 partials itself: same order, same value everywhere
 }
 
-__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const float* x, const uint16_t* __restrict__ w, float* y, int H,
+// OUT16: the normalised row is written as fp16 (round to nearest: exactly what a conversion of the fp32 result gives),
+// for the tensor-core GEMM that takes its activations in that type
+__device__ __forceinline__ void norm_store(float* y, int i, float v) { y[i] = v; }
+__device__ __forceinline__ void norm_store(__half* y, int i, float v) { y[i] = __float2half_rn(v); }
+__device__ __forceinline__ void norm_store4(float* y, int i4, float4 o) { reinterpret_cast<float4*>(y)[i4] = o; }
+__device__ __forceinline__ void norm_store4(__half* y, int i4, float4 o) {
+    const __half2 a = __floats2half2_rn(o.x, o.y), b = __floats2half2_rn(o.z, o.w);
+    reinterpret_cast<uint2*>(y)[i4] = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
+template <typename OUT>
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const float* x, const uint16_t* __restrict__ w, OUT* y, int H,
                                                                float eps) {
     __shared__ float s_part[kNormThreads / 32];
     pdl_launch_dependents();
     pdl_wait();
     const float* xr = x + size_t(blockIdx.x) * H;
-    float* yr = y + size_t(blockIdx.x) * H;
+    OUT* yr = y + size_t(blockIdx.x) * H;
     const int t = threadIdx.x;
     if ((H & 3) == 0 && H <= kNormThreads * kNormVec * 4 && (reinterpret_cast<uintptr_t>(xr) & 15) == 0 &&
         (reinterpret_cast<uintptr_t>(yr) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 7) == 0) {
@@ -93,7 +104,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const float* x, c
                 float4 o;
                 o.x = (v[j].x * rstd) * bf16_lo(wv[j].x); o.y = (v[j].y * rstd) * bf16_hi(wv[j].x);
                 o.z = (v[j].z * rstd) * bf16_lo(wv[j].y); o.w = (v[j].w * rstd) * bf16_hi(wv[j].y);
-                reinterpret_cast<float4*>(yr)[i] = o;
+                norm_store4(yr, i, o);
             }
         }
         return;
@@ -105,18 +116,19 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(const float* x, c
         ss = fmaf(a, a, ss);
     }
     const float rstd = 1.0f / sqrtf(block_sum_1024(ss, s_part) / float(H) + eps);
-    for (int i = t; i < H; i += kNormThreads) yr[i] = (xr[i] * rstd) * bf16_bits_to_float(w[i]);
+    for (int i = t; i < H; i += kNormThreads) norm_store(yr, i, (xr[i] * rstd) * bf16_bits_to_float(w[i]));
 }
 
 // ---------------------------------------------------------------- swiglu
-__global__ void swiglu_kernel(float* gate_up, float* out, int M, int I, int clear_input) {
+template <typename OUT>
+__global__ void swiglu_kernel(float* gate_up, OUT* out, int M, int I, int clear_input) {
     pdl_launch_dependents();
     pdl_wait();
     const int64_t total = int64_t(M) * I;
     for (int64_t idx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += int64_t(gridDim.x) * blockDim.x) {
         const int64_t m = idx / I, i = idx - m * I;
         const float g = gate_up[m * 2 * I + i], u = gate_up[m * 2 * I + I + i];
-        out[idx] = (g / (1.0f + expf(-g))) * u;
+        norm_store(out + idx, 0, (g / (1.0f + expf(-g))) * u);
         if (clear_input) {  // leave the projection buffer zeroed for the next accumulating matmul
             gate_up[m * 2 * I + i] = 0.f;
             gate_up[m * 2 * I + I + i] = 0.f;
@@ -308,14 +320,29 @@ extern "C" int kuiper_rmsnorm_f32(const float* x, const uint16_t* w, float* y, i
                                   kuiper_stream_t stream) {
     KUIPER_REQUIRE(x && w && y, "rmsnorm: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && H > 0, "rmsnorm: empty shape M=%d H=%d", M, H);
-    return pdl_status(launch_pdl(rmsnorm_kernel, dim3(M), dim3(kNormThreads), 0, as_stream(stream), x, w, y, H, eps), "rmsnorm");
+    return pdl_status(launch_pdl(rmsnorm_kernel<float>, dim3(M), dim3(kNormThreads), 0, as_stream(stream), x, w, y, H, eps), "rmsnorm");
+}
+
+extern "C" int kuiper_rmsnorm_f16(const float* x, const uint16_t* w, uint16_t* y16, int M, int H, float eps,
+                                  kuiper_stream_t stream) {
+    KUIPER_REQUIRE(x && w && y16, "rmsnorm_f16: null tensor pointer");
+    KUIPER_REQUIRE(M > 0 && H > 0, "rmsnorm_f16: empty shape M=%d H=%d", M, H);
+    return pdl_status(launch_pdl(rmsnorm_kernel<__half>, dim3(M), dim3(kNormThreads), 0, as_stream(stream), x, w,
+                                 reinterpret_cast<__half*>(y16), H, eps), "rmsnorm_f16");
 }
 
 extern "C" int kuiper_swiglu_f32(float* gate_up, float* out, int M, int I, int clear_input, kuiper_stream_t stream) {
     KUIPER_REQUIRE(gate_up && out, "swiglu: null tensor pointer");
     KUIPER_REQUIRE(M > 0 && I > 0, "swiglu: empty shape M=%d I=%d", M, I);
-    return pdl_status(launch_pdl(swiglu_kernel, dim3(grid_for(int64_t(M) * I, 256)), dim3(256), 0, as_stream(stream), gate_up, out, M, I,
+    return pdl_status(launch_pdl(swiglu_kernel<float>, dim3(grid_for(int64_t(M) * I, 256)), dim3(256), 0, as_stream(stream), gate_up, out, M, I,
                                  clear_input), "swiglu");
+}
+
+extern "C" int kuiper_swiglu_f16(float* gate_up, uint16_t* out16, int M, int I, int clear_input, kuiper_stream_t stream) {
+    KUIPER_REQUIRE(gate_up && out16, "swiglu_f16: null tensor pointer");
+    KUIPER_REQUIRE(M > 0 && I > 0, "swiglu_f16: empty shape M=%d I=%d", M, I);
+    return pdl_status(launch_pdl(swiglu_kernel<__half>, dim3(grid_for(int64_t(M) * I, 256)), dim3(256), 0, as_stream(stream), gate_up,
+                                 reinterpret_cast<__half*>(out16), M, I, clear_input), "swiglu_f16");
 }
 
 extern "C" int kuiper_embedding_bf16(const int32_t* tokens, const uint16_t* table, float* out, int M, int H,

@@ -121,6 +121,13 @@ void matmul_kernel_quant_gemm_cu(const Tensor& input, const Tensor& qweight, con
     CHECK_EQ(input.size() % size_t(K), size_t(0));
     const int32_t M = int32_t(input.size() / size_t(K));
     CHECK_EQ(output.size(), size_t(M) * size_t(N));
+    if (input.data_type() == base::DataType::DataTypeFp16) {  // normalised / activated rows that already are fp16
+        KERNEL_OK(kuiper_awq_gemm_f16in_f32(input.ptr<uint16_t>(), qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(),
+                                            scales.ptr<uint16_t>(), out_ptr<float>(output),
+                                            residual ? residual->ptr<float>() : nullptr, accumulate ? 1 : 0, M, K, N, group_size,
+                                            as_stream(stream)));
+        return;
+    }
     KERNEL_OK(kuiper_awq_gemm_f32(input.ptr<float>(), qweight.ptr<int32_t>(), qzeros.ptr<int32_t>(), scales.ptr<uint16_t>(),
                                   out_ptr<float>(output), residual ? residual->ptr<float>() : nullptr, accumulate ? 1 : 0, M,
                                   K, N, group_size, workspace.is_empty() ? nullptr : out_ptr<void>(workspace),
@@ -134,6 +141,11 @@ void rmsnorm_kernel_cu(const Tensor& input, const Tensor& weight, const Tensor& 
     const int32_t H = int32_t(weight.size());
     CHECK_EQ(input.size() % size_t(H), size_t(0));
     CHECK_EQ(input.size(), output.size());
+    if (output.data_type() == base::DataType::DataTypeFp16) {
+        KERNEL_OK(kuiper_rmsnorm_f16(input.ptr<float>(), weight.ptr<uint16_t>(), out_ptr<uint16_t>(output),
+                                     int32_t(input.size() / size_t(H)), H, eps, as_stream(stream)));
+        return;
+    }
     KERNEL_OK(kuiper_rmsnorm_f32(input.ptr<float>(), weight.ptr<uint16_t>(), out_ptr<float>(output),
                                  int32_t(input.size() / size_t(H)), H, eps, as_stream(stream)));
 }
@@ -229,6 +241,11 @@ void swiglu_kernel_cu(const Tensor& gate_up, const Tensor& output, bool clear_in
     require_cuda(output, "swiglu output");
     CHECK_EQ(gate_up.size(), output.size() * 2);
     const int32_t I = output.get_dim(output.dims_size() - 1);
+    if (output.data_type() == base::DataType::DataTypeFp16) {
+        KERNEL_OK(kuiper_swiglu_f16(out_ptr<float>(gate_up), out_ptr<uint16_t>(output), int32_t(output.size() / size_t(I)), I,
+                                    clear_input ? 1 : 0, as_stream(stream)));
+        return;
+    }
     KERNEL_OK(kuiper_swiglu_f32(out_ptr<float>(gate_up), out_ptr<float>(output), int32_t(output.size() / size_t(I)), I,
                                 clear_input ? 1 : 0, as_stream(stream)));
 }

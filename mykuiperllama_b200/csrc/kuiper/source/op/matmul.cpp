@@ -79,10 +79,12 @@ base::Status MatmulLayer::forward() {
         const tensor::Tensor* x = &get_input(0);
         tensor::Tensor normed;
         if (accumulate_ && (!input_norm_.is_empty() || input_swiglu_)) {
-            if (norm_scratch_.is_empty() || norm_scratch_.size() < size_t(M) * size_t(dim1_))
-                return base::error::invalid_argument("the tensor-core path needs a scratch of the operand's size");
-            normed = tensor::Tensor(base::DataType::DataTypeFp32, std::vector<int32_t>{M, dim1_}, false, nullptr,
-                                    const_cast<float*>(norm_scratch_.ptr<float>()));
+            // the normalised / activated rows are written as fp16 straight into the GEMM's activation buffer (the
+            // rounding is that of the separate conversion pass, which is then not needed)
+            if (gemm_workspace_.is_empty() || gemm_workspace_.byte_size() < size_t(M) * size_t(dim1_) * sizeof(uint16_t))
+                return base::error::invalid_argument("the tensor-core path needs its fp16 activation workspace");
+            normed = tensor::Tensor(base::DataType::DataTypeFp16, std::vector<int32_t>{M, dim1_}, false, nullptr,
+                                    const_cast<void*>(gemm_workspace_.ptr<void>()));
             normed.set_device_type(device_type_);
             if (input_swiglu_)
                 kernel::get_swiglu_kernel(device_type_)(get_input(0), normed, false, stream());

@@ -926,3 +926,34 @@ def test_rope_flash_decode_with_rows_in_other_slots(cuda, oracle, lens, slots):
         torch.cuda.synchronize()
         assert rel_err(got.cpu().numpy(), ref.cpu().numpy()) <= 5e-5, fresh
         assert torch.equal(k_f.view(torch.int16), k_ref.view(torch.int16)) and torch.equal(v_f.view(torch.int16), v_ref.view(torch.int16))
+
+
+@pytest.mark.parametrize("M,K,N", [(16, 1024, 512), (48, 4096, 1024), (300, 2560, 4104)])
+def test_fp16_activation_path_of_the_gemm(cuda, oracle, M, K, N):
+    # the layer writes normalised / activated rows as fp16 straight into the GEMM's activation buffer: the results are
+    # those of the fp32 kernels followed by the GEMM's own conversion pass, bit for bit (both round to nearest once)
+    rng = np.random.default_rng(M + K)
+    q, z, s = awq_random(rng, K, N)
+    tqw, tqz, ts = dev(oracle.awq_pack(q)), dev(oracle.awq_pack(z)), dev(s.view(np.uint16), torch.float16)
+    h = dev(rng.standard_normal((M, K)).astype(np.float32))
+    nw = dev(oracle.f32_to_bf16((1 + 0.1 * rng.standard_normal(K)).astype(np.float32)))
+    gu = dev(rng.standard_normal((M, 2 * K)).astype(np.float32))
+    cuda.set_tuning("gemm_split_k", 0)  # fixed summation order, so that equality can be asserted
+    try:
+        x32 = cuda.rmsnorm(h, nw, 1e-6)
+        x16 = cuda.rmsnorm_f16(h, nw, 1e-6)
+        assert torch.equal(x16, x32.half())
+        assert torch.equal(cuda.awq_gemm_f16in(x16, tqw, tqz, ts), cuda.awq_gemm(x32, tqw, tqz, ts))
+        a32 = cuda.swiglu(gu.clone())
+        a16 = cuda.swiglu_f16(gu.clone())
+        assert torch.equal(a16, a32.half())
+        res = dev(rng.standard_normal((M, N)).astype(np.float32))
+        y1 = cuda.awq_gemm_f16in(a16, tqw, tqz, ts, y=res.clone(), accumulate=True)
+        y2 = cuda.awq_gemm(a32, tqw, tqz, ts, y=res.clone(), accumulate=True)
+        assert torch.equal(y1, y2)
+    finally:
+        cuda.set_tuning("gemm_split_k", 1)
+    # with the K split the same call agrees to the summation order
+    y3 = cuda.awq_gemm_f16in(x16, tqw, tqz, ts)
+    torch.cuda.synchronize()
+    assert rel_err(y3.cpu().numpy(), cuda.awq_gemm(x32, tqw, tqz, ts).cpu().numpy()) <= 2e-6
