@@ -232,7 +232,8 @@ KUIPER_API int kuiper_argmax_allgather(const float* logits_local, int32_t* next,
                                        kuiper_stream_t stream);
 KUIPER_API int kuiper_allreduce_status(uint32_t* state, int clear);
 
-/* ---- BF16 GEMV (lm_head): W bf16 [N, K], y[M,N] = x[M,K] . W^T ---- */
+/* ---- BF16 GEMV (lm_head): W bf16 [N, K], y[M,N] = x[M,K] . W^T; x stays fp32 in effect (one or two rows: fp32 FMAs;
+ * three rows and more: tensor cores with x as three bf16 parts), accumulation fp32 ---- */
 KUIPER_API int kuiper_bf16_gemv_f32(const float* x, const uint16_t* W, float* y, int M, int K, int N,
                          kuiper_stream_t stream);
 

@@ -24,6 +24,7 @@ void set_error(const char* fmt, ...) {
 void awq_gemv_set_tuning(const char* key, int value);
 void flash_decode_set_tuning(const char* key, int value);
 void awq_gemm_set_tuning(const char* key, int value);
+void bf16_gemv_set_tuning(const char* key, int value);
 void allreduce_set_tuning(const char* key, int value);
 
 namespace {
@@ -294,6 +295,7 @@ extern "C" int kuiper_set_tuning(const char* key, int value) {
     awq_gemv_set_tuning(key, value);
     flash_decode_set_tuning(key, value);
     awq_gemm_set_tuning(key, value);
+    bf16_gemv_set_tuning(key, value);
     allreduce_set_tuning(key, value);
     return KUIPER_OK;
 }

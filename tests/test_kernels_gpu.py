@@ -511,7 +511,8 @@ def test_exchange_waits_are_bounded(cuda):
 
 
 # ----------------------------------------------------------------------------- BF16 GEMV
-@pytest.mark.parametrize("M,K,N", [(1, 1024, 5000), (1, 2560, 1001), (3, 4096, 2048), (4, 1024, 777), (7, 520, 64)])
+@pytest.mark.parametrize("M,K,N", [(1, 1024, 5000), (1, 2560, 1001), (3, 4096, 2048), (4, 1024, 777), (7, 520, 64),
+                                   (8, 2560, 3001), (16, 4096, 1000), (5, 1024, 9), (20, 1024, 100)])  # 3+ rows: tensor cores
 def test_bf16_gemv(cuda, oracle, M, K, N):
     rng = np.random.default_rng(K + N)
     W = oracle.f32_to_bf16((rng.standard_normal((N, K)) * 0.02).astype(np.float32))
